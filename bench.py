@@ -1,0 +1,352 @@
+"""Benchmark of the quantized decode hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): configuration 1 of the baseline -- the Q4_K matvec, W 4096x4096 in raw
+GGUF Q4_K blocks, x fp32[4096], batch 1 -- repeated over a stack of LAYERS distinct weight
+tensors (default 128, 1.2 GB, far larger than the 126 MB L2, so every launch streams its
+weights from HBM).  One step = one pass over the stack: LAYERS matvec launches back to back.
+
+  value     GB/s of algorithmic bytes (blocks + x + y per matvec), inputs resident in HBM,
+            timed with CUDA events on the launching stream;
+  e2e       the same metric through the host-pointer C ABI call (skn_matmul): x copied from
+            pinned host memory and y copied back inside the timed region, weights resident;
+  roofline  the streaming matvec kernel against the measured HBM copy bandwidth;
+  cpu_baseline  the CPU oracle (a C restatement; the reference's Kotlin cannot run here)
+            timed on this host's cores on a bounded sample of the same workload.
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank streams its own row
+shard of an N-times taller stack (column-parallel: rank r owns rows [r*4096, (r+1)*4096) of
+each [N*4096, 4096] layer) and the y slices are all-gathered over NCCL once per layer;
+per-GPU work is fixed, so scaling is weak.
+
+--impl reference times the CPU oracle alone (all host threads) and prints the same line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_ROWS, N_COLS = 4096, 4096
+Q4_K = 12
+W_BYTES = N_ROWS * (N_COLS // 256) * 144
+ALG_BYTES = W_BYTES + 4 * N_COLS + 4 * N_ROWS      # 9 469 952 per matvec
+METRIC = "q4k_matvec_gbs"
+UNIT = "GB/s"
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [c.strip() for c in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(seconds: float = 10.0, threads: int = 0):
+    """The CPU restatement on a bounded sample: repeated cfg1 matvecs (fused dequant-dot,
+    fp64 accumulate, rows over OpenMP threads) for about `seconds`."""
+    from oracle import oracle
+    from skainet_b200 import synth
+    w, x = synth.cfg1(0)
+    cores = threads or (os.cpu_count() or 1)
+    oracle.matmul(Q4_K, w, N_ROWS, N_COLS, x, threads=cores)   # warm-up
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        oracle.matmul(Q4_K, w, N_ROWS, N_COLS, x, threads=cores)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or reps >= 2000:
+            break
+    gbs = reps * ALG_BYTES / dt / 1e9
+    return {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{reps} cfg1 matvecs (Q4_K 4096x4096, M=1) in {dt:.1f} s, fused dequant-dot in fp64, "
+                      f"OpenMP over rows; the reference's Kotlin has no JVM to run on"}, dt / reps
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    per_step_s = min(3.0, 60.0 / (steps + args.warmup))
+    from oracle import oracle
+    from skainet_b200 import synth
+    w, x = synth.cfg1(0)
+    cores = os.cpu_count() or 1
+    times = []
+    reps_per_step = None
+    for it in range(args.warmup + steps):
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            oracle.matmul(Q4_K, w, N_ROWS, N_COLS, x, threads=cores)
+            reps += 1
+            if (reps_per_step is not None and reps >= reps_per_step) or \
+               (reps_per_step is None and time.perf_counter() - t0 >= per_step_s):
+                break
+        dt = time.perf_counter() - t0
+        if reps_per_step is None:
+            reps_per_step = reps
+        if it >= args.warmup:
+            times.append(dt)
+    tot = sum(times)
+    gbs = steps * reps_per_step * ALG_BYTES / tot / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * tot / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "cfg1: Q4_K matvec 4096x4096, M=1", "sample_matvecs_per_step": reps_per_step},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{reps_per_step} cfg1 matvecs per step on the CPU oracle (C restatement; the "
+                                   "reference is Kotlin and has no quantized kernels or JVM here)"},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import skainet_b200 as skn
+    from skainet_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    layers = args.layers
+    ctx = skn.Context(local)
+    stream = torch.cuda.current_stream()
+    ctx.set_stream(stream.cuda_stream)
+
+    # Synthetic stack: one seeded cfg1-distribution weight, then `layers` variants of it
+    # (bytes rotated per layer) so that each layer is a distinct buffer with the same value
+    # distributions, without spending minutes in the host generator.
+    g = synth.rng(1000 + rank)
+    base = synth.make_weight(g, Q4_K, N_ROWS, N_COLS)
+    x_host = torch.from_numpy(synth.make_activations(g, 1, N_COLS)[0].copy()).pin_memory()
+    tensors = []
+    for i in range(layers):
+        wi = np.roll(base, i, axis=0) if i else base
+        tensors.append(skn.QuantTensor(ctx, (N_ROWS, N_COLS), Q4_K, wi))
+    x_dev = x_host.to(dev)
+    y_dev = torch.empty((layers, N_ROWS), dtype=torch.float32, device=dev)
+    y_all = torch.empty((layers, world * N_ROWS), dtype=torch.float32, device=dev) if world > 1 else None
+    y_host = torch.empty(N_ROWS, dtype=torch.float32).pin_memory()
+
+    def step_device():
+        for i, t in enumerate(tensors):
+            t.matmul_t_dev(x_dev, 1, y_dev[i])
+            if world > 1:
+                dist.all_gather_into_tensor(y_all[i], y_dev[i])
+
+    from skainet_b200 import _ffi
+    L = _ffi.lib()
+    xh_ptr, yh_ptr = x_host.data_ptr(), y_host.data_ptr()
+
+    def step_e2e():
+        for t in tensors:
+            rc = L.skn_matmul(ctx.handle, t.handle, xh_ptr, 1, N_COLS, None, yh_ptr)
+            if rc != 0:
+                raise RuntimeError(L.skn_last_error(ctx.handle).decode())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing --------------------------------------------------------
+    # The launch loop of one step is captured once into a CUDA graph (a matvec lasts a few
+    # microseconds, less than a host-side launch); the timed region replays the graph.
+    step_device()          # first call plans each tensor's launch geometry (not capturable)
+    barrier()
+    graph = None
+    run_step = step_device
+    if not args.no_graph:
+        cap_stream = torch.cuda.Stream()
+        cap_stream.wait_stream(stream)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap_stream):
+                ctx.set_stream(cap_stream.cuda_stream)
+                with torch.cuda.graph(graph, stream=cap_stream):
+                    step_device()
+            run_step = graph.replay
+        except Exception as exc:   # capture unsupported for this configuration: launch eagerly
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); launching eagerly\n")
+            graph = None
+            run_step = step_device
+        finally:
+            ctx.set_stream(stream.cuda_stream)
+        torch.cuda.synchronize()
+    for _ in range(max(3, args.warmup)):
+        run_step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        run_step()
+    ev1.record(stream)
+    barrier()
+    ctx.sync()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+
+    # ---- end to end through the host-pointer ABI ----------------------------------------
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        te = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # sanity: results are finite and the same from both paths
+    y_chk = y_dev[-1].cpu()
+    assert torch.isfinite(y_chk).all()
+    assert torch.equal(y_chk, y_host), "device-pointer and host-pointer paths disagree"
+
+    if rank == 0:
+        launches_per_step = layers
+        total_bytes = world * layers * ALG_BYTES
+        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        e2e_value = total_bytes * e2e_steps / e2e_s / 1e9
+        peak, peak_kind = measured_peak()
+        per_launch_us = ms * 1e3 / (args.steps * layers)
+        achieved = ALG_BYTES / (per_launch_us * 1e-6) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg1: Q4_K matvec 4096x4096, M=1, fp32 x", "layers_per_step": layers,
+                       "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
+                       "l2_policy": f"inputs larger than L2: {layers} distinct weights = "
+                                    f"{layers * W_BYTES / 1e6:.0f} MB streamed per step",
+                       "sharding": "none" if world == 1 else
+                       f"column-parallel rows over {world} ranks, NCCL all-gather of y slices per layer",
+                       "pct_of_8TBs": 100.0 * value / world / 8000.0},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": layers * 4 * N_COLS,
+                    "d2h_bytes_per_step": layers * 4 * N_ROWS, "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "skn_matvec_stream<Q4KStream>", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": UNIT, "frac": achieved / peak,
+                         "us_per_launch": per_launch_us, "traffic": None},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            cb, _ = cpu_baseline(args.cpu_seconds)
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+
+    for t in tensors:
+        t.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=128)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,137 @@
+/*
+ * libskainet_cuda.so -- C ABI of the B200 (sm_100a) quantized-inference backend for
+ * sk-ai-net/skainet.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int32 status
+ * (0 = SKN_OK) and never lets a C++ exception cross the boundary.  Handles are opaque
+ * pointers created and destroyed explicitly.  Host buffers are borrowed for the
+ * duration of one call.  Entry points whose name ends in `_dev` take DEVICE pointers
+ * and only enqueue work on the context's stream (call skn_sync to wait); all others
+ * take HOST pointers and return when the result is in the caller's buffer.
+ *
+ * The reference (Kotlin multiplatform, v0.0.7) has no FFI of its own; each function
+ * cites the reference interface it stands behind.  Paths are relative to the
+ * reference's repository root.
+ *
+ * A context is bound to one CUDA device and must be used by one host thread at a
+ * time.  There is no CPU fallback: without a usable CUDA device every compute entry
+ * point fails with SKN_ERR_CUDA.
+ */
+#ifndef SKAINET_CUDA_H
+#define SKAINET_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SKN_VERSION 100 /* 0.1.0 */
+
+/* status codes */
+#define SKN_OK 0
+#define SKN_ERR_SHAPE 1      /* maps to IllegalArgumentException("Shapes do not align.") */
+#define SKN_ERR_TYPE 2       /* unknown / unsupported GGML type id */
+#define SKN_ERR_ALIGN 3      /* pointer or pitch alignment */
+#define SKN_ERR_OOM 4
+#define SKN_ERR_CUDA 5
+#define SKN_ERR_TIMEOUT 6    /* a bounded device-side wait ran out */
+#define SKN_ERR_BAD_HANDLE 7
+#define SKN_ERR_ARG 8        /* null pointer, negative size, ... */
+#define SKN_ERR_COMM 9
+
+/* GGML type ids: gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:14-52 */
+#define SKN_TYPE_Q4_0 2
+#define SKN_TYPE_Q8_0 8
+#define SKN_TYPE_Q4_K 12
+#define SKN_TYPE_Q6_K 14
+
+typedef struct skn_ctx skn_ctx;
+typedef struct skn_tensor skn_tensor;
+typedef struct skn_kvcache skn_kvcache;
+
+/* ---- library / context ------------------------------------------------------------- */
+
+/* Library version (SKN_VERSION of the build). */
+int32_t skn_version(void);
+
+/* Message of the last failure on `ctx` (or, with ctx == NULL, of the last failing call
+ * on this thread that had no context).  Never NULL.  Plays the role of the exception
+ * message in the reference (core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:256). */
+const char *skn_last_error(const skn_ctx *ctx);
+
+/* Create a context on CUDA device `device` with its own non-blocking stream.
+ * Stands where the reference constructs its one backend,
+ * core/src/commonMain/kotlin/sk/ai/net/impl/DefaultTensorFactory.kt:9-17. */
+int32_t skn_ctx_create(int32_t device, skn_ctx **out);
+int32_t skn_ctx_destroy(skn_ctx *ctx);
+
+/* Make `_dev` entry points enqueue on `cuda_stream` (a cudaStream_t) instead of the
+ * context's own stream; NULL restores the context's stream. */
+int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
+
+/* Wait for everything enqueued on the context's stream; reports a pending
+ * device-side status (e.g. SKN_ERR_TIMEOUT) if a kernel recorded one. */
+int32_t skn_sync(skn_ctx *ctx);
+
+/* ---- block geometry ---------------------------------------------------------------- */
+
+/* (elements per block, bytes per block) of a GGML type:
+ * GGML_QUANT_SIZES, gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:58-90. */
+int32_t skn_quant_geometry(int32_t ggml_type, int32_t *block_elems, int32_t *block_bytes);
+
+/* Bytes of one row of `n_cols` weights; SKN_ERR_SHAPE when n_cols is not a multiple of
+ * the block size: quantShapeToByteShape, gguf/src/commonMain/kotlin/sk/ai/net/gguf/Quants.kt:10-20. */
+int32_t skn_quant_row_bytes(int32_t ggml_type, int64_t n_cols, int64_t *row_bytes);
+
+/* ---- quantized weight tensors ------------------------------------------------------ */
+
+/* Upload the raw blocks of a [n_rows, n_cols] weight (GGUF order: n_cols contiguous,
+ * i.e. Linear's [out, in], core/src/commonMain/kotlin/sk/ai/net/nn/Linear.kt:43-49) to
+ * HBM, unchanged.  `host_blocks` is what GGUFReader hands out for a quantized tensor
+ * (gguf/src/commonMain/kotlin/sk/ai/net/gguf/GGUFReader.kt:370-398); n_bytes must equal
+ * n_rows * row_bytes.  Replaces the branch that skips quantized tensors,
+ * samples/mnist-mlp-cli/src/jvmMain/kotlin/sk/ai/net/samples/mnist/mlp/Main.kt:229-232. */
+int32_t skn_tensor_upload_quant(skn_ctx *ctx, int32_t ggml_type, int64_t n_rows, int64_t n_cols,
+                                const void *host_blocks, int64_t n_bytes, skn_tensor **out);
+
+/* Upload the sub-matrix rows [row_begin, row_begin+row_count) x columns
+ * [col_begin, col_begin+col_count) of a [n_rows_total, n_cols_total] weight whose full
+ * raw blocks are at host_blocks: the shard one GPU owns under column (row range) or row
+ * (column range) parallelism.  col_begin / col_count must be multiples of the block
+ * size.  Blocks are copied unchanged; the device row pitch is padded to 16 bytes.
+ * No counterpart in the reference (it has no multi-device notion, Tensor.kt:6-33). */
+int32_t skn_tensor_upload_quant_shard(skn_ctx *ctx, int32_t ggml_type, int64_t n_rows_total,
+                                      int64_t n_cols_total, const void *host_blocks, int64_t n_bytes,
+                                      int64_t row_begin, int64_t row_count, int64_t col_begin,
+                                      int64_t col_count, skn_tensor **out);
+
+int32_t skn_tensor_destroy(skn_tensor *t);
+
+/* shape / type / device layout of a tensor (any out pointer may be NULL):
+ * Tensor.shape / dataDescriptor, core/src/commonMain/kotlin/sk/ai/net/Tensor.kt:12-33. */
+int32_t skn_tensor_info(const skn_tensor *t, int32_t *ggml_type, int64_t *n_rows, int64_t *n_cols,
+                        int64_t *row_bytes, int64_t *row_pitch_bytes, void **device_blocks);
+
+/* Dequantise the whole tensor to fp32 [n_rows, n_cols] (bit-exact with gguf-py 0.19.0's
+ * dequantize, the code the reference's gguf module transliterates, Quants.kt:3-8). */
+int32_t skn_dequantize(skn_ctx *ctx, const skn_tensor *t, float *out_host);
+int32_t skn_dequantize_dev(skn_ctx *ctx, const skn_tensor *t, float *out_dev);
+
+/* Y[M, n_rows] = X[M, K] . W^T with W the quantized [n_rows, K] tensor, fp32
+ * accumulation; M = 1 is the decode matvec.  This is Linear.forward's
+ * input.matmul(weight.t()) (core/src/commonMain/kotlin/sk/ai/net/nn/Linear.kt:48) i.e.
+ * DoublesTensor.matmul's vector x matrix and matrix x matrix cases
+ * (core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:255-279) without the
+ * per-call transposed copy (DoublesTensor.kt:362-387).  K != n_cols fails with
+ * SKN_ERR_SHAPE ("Shapes do not align.", DoublesTensor.kt:256).  `bias` ([n_rows]
+ * fp32, may be NULL) is added as Linear does. */
+int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32_t M, int64_t K,
+                   const float *bias_host, float *y_host);
+int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
+                       const float *bias_dev, float *y_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKAINET_CUDA_H */

@@ -1,0 +1,311 @@
+// C ABI of libskainet_cuda.so: contexts, error reporting, weight upload, and the
+// host-pointer / device-pointer front ends of the kernels.  No exception leaves this file.
+#include "skn_internal.cuh"
+
+#include <new>
+#include <stdarg.h>
+#include <stdlib.h>
+
+static thread_local char g_tls_err[512] = "";
+
+int32_t skn_fail(skn_ctx *ctx, int32_t code, const char *fmt, ...) {
+    char *dst = (ctx && ctx->magic == SKN_MAGIC_CTX) ? ctx->err : g_tls_err;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(dst, 512, fmt, ap);
+    va_end(ap);
+    if (getenv("SKN_LOG")) fprintf(stderr, "[skainet_cuda] error %d: %s\n", code, dst);
+    return code;
+}
+
+int32_t skn_check_cuda(skn_ctx *ctx, cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return SKN_OK;
+    const int32_t code = (e == cudaErrorMemoryAllocation) ? SKN_ERR_OOM : SKN_ERR_CUDA;
+    return skn_fail(ctx, code, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+bool skn_ctx_ok(const skn_ctx *ctx) { return ctx && ctx->magic == SKN_MAGIC_CTX; }
+bool skn_tensor_ok(const skn_tensor *t) { return t && t->magic == SKN_MAGIC_TENSOR && skn_ctx_ok(t->ctx); }
+
+int32_t skn_stage_reserve(skn_ctx *ctx, void **buf, size_t *cap, size_t need) {
+    if (need <= *cap) return SKN_OK;
+    if (*buf) {
+        SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        SKN_CUDA(ctx, cudaFree(*buf));
+        *buf = nullptr;
+        *cap = 0;
+    }
+    size_t want = need < (1u << 20) ? (1u << 20) : need;
+    SKN_CUDA(ctx, cudaMalloc(buf, want));
+    *cap = want;
+    return SKN_OK;
+}
+
+extern "C" {
+
+int32_t skn_version(void) { return SKN_VERSION; }
+
+const char *skn_last_error(const skn_ctx *ctx) { return skn_ctx_ok(ctx) ? ctx->err : g_tls_err; }
+
+int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
+    if (!out) return skn_fail(nullptr, SKN_ERR_ARG, "skn_ctx_create: out is NULL");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return skn_fail(nullptr, SKN_ERR_CUDA, "no usable CUDA device (%s); this library has no CPU fallback",
+                        e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= n) return skn_fail(nullptr, SKN_ERR_ARG, "device %d out of range [0,%d)", device, n);
+    skn_ctx *ctx = new (std::nothrow) skn_ctx();
+    if (!ctx) return skn_fail(nullptr, SKN_ERR_OOM, "host allocation failed");
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->magic = SKN_MAGIC_CTX;
+    ctx->device = device;
+#define CTX_TRY(call)                                                \
+    do {                                                             \
+        cudaError_t e__ = (call);                                    \
+        if (e__ != cudaSuccess) {                                    \
+            int32_t rc__ = skn_check_cuda(nullptr, e__, #call);      \
+            if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream); \
+            if (ctx->d_status) cudaFree(ctx->d_status);              \
+            if (ctx->h_status) cudaFreeHost(ctx->h_status);          \
+            ctx->magic = 0;                                          \
+            delete ctx;                                              \
+            return rc__;                                             \
+        }                                                            \
+    } while (0)
+    CTX_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CTX_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        fprintf(stderr, "[skainet_cuda] warning: device %d is sm_%d%d; kernels are built for sm_100a only\n", device,
+                prop.major, prop.minor);
+    ctx->sm_count = prop.multiProcessorCount;
+    CTX_TRY(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
+    ctx->stream = ctx->own_stream;
+    CTX_TRY(cudaMalloc((void **)&ctx->d_status, 256));
+    CTX_TRY(cudaMemset(ctx->d_status, 0, 256));
+    CTX_TRY(cudaMallocHost((void **)&ctx->h_status, 256));
+#undef CTX_TRY
+    *ctx->h_status = 0;
+    *out = ctx;
+    return SKN_OK;
+}
+
+int32_t skn_ctx_destroy(skn_ctx *ctx) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "skn_ctx_destroy: bad context handle");
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->d_stage_in) cudaFree(ctx->d_stage_in);
+    if (ctx->d_stage_out) cudaFree(ctx->d_stage_out);
+    if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    ctx->magic = 0;
+    delete ctx;
+    return SKN_OK;
+}
+
+int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    return SKN_OK;
+}
+
+int32_t skn_sync(skn_ctx *ctx) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SKN_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const int32_t st = *ctx->h_status;
+    if (st != 0) {
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(int32_t), ctx->stream);
+        cudaStreamSynchronize(ctx->stream);
+        return skn_fail(ctx, st, "a kernel reported device-side status %d (%s)", st,
+                        st == SKN_ERR_TIMEOUT ? "a bounded wait ran out" : "see status codes");
+    }
+    return SKN_OK;
+}
+
+int32_t skn_quant_geometry(int32_t ggml_type, int32_t *block_elems, int32_t *block_bytes) {
+    int32_t e, b;
+    if (!skn_geometry(ggml_type, &e, &b)) return skn_fail(nullptr, SKN_ERR_TYPE, "unsupported GGML type id %d", ggml_type);
+    if (block_elems) *block_elems = e;
+    if (block_bytes) *block_bytes = b;
+    return SKN_OK;
+}
+
+int32_t skn_quant_row_bytes(int32_t ggml_type, int64_t n_cols, int64_t *row_bytes) {
+    int32_t e, b;
+    if (!skn_geometry(ggml_type, &e, &b)) return skn_fail(nullptr, SKN_ERR_TYPE, "unsupported GGML type id %d", ggml_type);
+    if (n_cols < 0 || n_cols % e)
+        return skn_fail(nullptr, SKN_ERR_SHAPE, "Quantized tensor row size (%lld) is not a multiple of block size (%d)",
+                        (long long)n_cols, e);
+    if (row_bytes) *row_bytes = n_cols / e * b;
+    return SKN_OK;
+}
+
+int32_t skn_tensor_upload_quant_shard(skn_ctx *ctx, int32_t ggml_type, int64_t n_rows_total, int64_t n_cols_total,
+                                      const void *host_blocks, int64_t n_bytes, int64_t row_begin, int64_t row_count,
+                                      int64_t col_begin, int64_t col_count, skn_tensor **out) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    int32_t e, b;
+    if (!skn_geometry(ggml_type, &e, &b)) return skn_fail(ctx, SKN_ERR_TYPE, "unsupported GGML type id %d", ggml_type);
+    if (n_rows_total < 0 || n_cols_total < 0) return skn_fail(ctx, SKN_ERR_ARG, "negative shape");
+    if (n_cols_total % e)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "Quantized tensor row size (%lld) is not a multiple of block size (%d)",
+                        (long long)n_cols_total, e);
+    const int64_t row_bytes_total = n_cols_total / e * b;
+    if (n_bytes != n_rows_total * row_bytes_total)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "byte length %lld does not match %lld rows x %lld bytes", (long long)n_bytes,
+                        (long long)n_rows_total, (long long)row_bytes_total);
+    if (row_begin < 0 || row_count < 0 || row_begin + row_count > n_rows_total || col_begin < 0 || col_count < 0 ||
+        col_begin + col_count > n_cols_total)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "shard range outside the tensor");
+    if (col_begin % e || col_count % e) return skn_fail(ctx, SKN_ERR_SHAPE, "shard columns must be whole blocks");
+    if (!host_blocks && n_bytes > 0) return skn_fail(ctx, SKN_ERR_ARG, "host_blocks is NULL");
+
+    skn_tensor *t = new (std::nothrow) skn_tensor();
+    if (!t) return skn_fail(ctx, SKN_ERR_OOM, "host allocation failed");
+    memset(t, 0, sizeof(*t));
+    t->magic = SKN_MAGIC_TENSOR;
+    t->ctx = ctx;
+    t->type = ggml_type;
+    t->n_rows = row_count;
+    t->n_cols = col_count;
+    t->row_bytes = col_count / e * b;
+    t->pitch = (t->row_bytes + 15) / 16 * 16;
+    const size_t dev_bytes = (size_t)(t->pitch * t->n_rows);
+    cudaError_t err = cudaSetDevice(ctx->device);
+    // a few spare bytes so that vector loads of the last row may over-read safely
+    if (err == cudaSuccess) err = cudaMalloc((void **)&t->d_blocks, dev_bytes + 256);
+    if (err == cudaSuccess && dev_bytes > 0) {
+        if (t->pitch != t->row_bytes) err = cudaMemsetAsync(t->d_blocks, 0, dev_bytes + 256, ctx->stream);
+        const uint8_t *src = (const uint8_t *)host_blocks + row_begin * row_bytes_total + col_begin / e * b;
+        if (err == cudaSuccess)
+            err = cudaMemcpy2DAsync(t->d_blocks, (size_t)t->pitch, src, (size_t)row_bytes_total, (size_t)t->row_bytes,
+                                    (size_t)t->n_rows, cudaMemcpyHostToDevice, ctx->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+    }
+    if (err != cudaSuccess) {
+        if (t->d_blocks) cudaFree(t->d_blocks);
+        t->magic = 0;
+        delete t;
+        return skn_check_cuda(ctx, err, "weight upload");
+    }
+    *out = t;
+    return SKN_OK;
+}
+
+int32_t skn_tensor_upload_quant(skn_ctx *ctx, int32_t ggml_type, int64_t n_rows, int64_t n_cols, const void *host_blocks,
+                                int64_t n_bytes, skn_tensor **out) {
+    return skn_tensor_upload_quant_shard(ctx, ggml_type, n_rows, n_cols, host_blocks, n_bytes, 0, n_rows, 0, n_cols, out);
+}
+
+int32_t skn_tensor_destroy(skn_tensor *t) {
+    if (!t || t->magic != SKN_MAGIC_TENSOR) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (skn_ctx_ok(t->ctx)) {
+        cudaSetDevice(t->ctx->device);
+        cudaStreamSynchronize(t->ctx->stream);
+    }
+    if (t->d_blocks) cudaFree(t->d_blocks);
+    t->magic = 0;
+    delete t;
+    return SKN_OK;
+}
+
+int32_t skn_tensor_info(const skn_tensor *t, int32_t *ggml_type, int64_t *n_rows, int64_t *n_cols, int64_t *row_bytes,
+                        int64_t *row_pitch_bytes, void **device_blocks) {
+    if (!skn_tensor_ok(t)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (ggml_type) *ggml_type = t->type;
+    if (n_rows) *n_rows = t->n_rows;
+    if (n_cols) *n_cols = t->n_cols;
+    if (row_bytes) *row_bytes = t->row_bytes;
+    if (row_pitch_bytes) *row_pitch_bytes = t->pitch;
+    if (device_blocks) *device_blocks = t->d_blocks;
+    return SKN_OK;
+}
+
+int32_t skn_dequantize_dev(skn_ctx *ctx, const skn_tensor *t, float *out_dev) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!skn_tensor_ok(t) || t->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (!out_dev) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    if (((uintptr_t)out_dev) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "output must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SKN_CUDA(ctx, skn_launch_dequant(t->type, t->d_blocks, t->pitch, t->n_rows, t->n_cols, out_dev, ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_dequantize(skn_ctx *ctx, const skn_tensor *t, float *out_host) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!skn_tensor_ok(t) || t->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (!out_host) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    const size_t bytes = (size_t)t->n_rows * (size_t)t->n_cols * sizeof(float);
+    if (bytes == 0) return SKN_OK;
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, bytes);
+    if (rc) return rc;
+    rc = skn_dequantize_dev(ctx, t, (float *)ctx->d_stage_out);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(out_host, ctx->d_stage_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
+}
+
+static int32_t check_matmul_args(skn_ctx *ctx, const skn_tensor *w, const void *x, int32_t M, int64_t K, const void *y) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!skn_tensor_ok(w) || w->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (M < 0) return skn_fail(ctx, SKN_ERR_ARG, "M is negative");
+    if (K != w->n_cols) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    if (M > 0 && (!x || !y)) return skn_fail(ctx, SKN_ERR_ARG, "x or y is NULL");
+    return SKN_OK;
+}
+
+int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
+                       const float *bias_dev, float *y_dev) {
+    int32_t rc = check_matmul_args(ctx, w, x_dev, M, K, y_dev);
+    if (rc) return rc;
+    if (M == 0 || w->n_rows == 0) return SKN_OK;
+    if ((((uintptr_t)x_dev) & 15) || (((uintptr_t)y_dev) & 15))
+        return skn_fail(ctx, SKN_ERR_ALIGN, "x and y must be 16-byte aligned device pointers");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (K == 0) {
+        // empty reduction: y = bias (or 0)
+        SKN_CUDA(ctx, cudaMemsetAsync(y_dev, 0, (size_t)M * w->n_rows * sizeof(float), ctx->stream));
+        if (bias_dev)
+            for (int32_t m = 0; m < M; ++m)
+                SKN_CUDA(ctx, cudaMemcpyAsync(y_dev + (size_t)m * w->n_rows, bias_dev, w->n_rows * sizeof(float),
+                                              cudaMemcpyDeviceToDevice, ctx->stream));
+        return SKN_OK;
+    }
+    SKN_CUDA(ctx, skn_launch_matvec(ctx, w, x_dev, M, bias_dev, y_dev, ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32_t M, int64_t K, const float *bias_host,
+                   float *y_host) {
+    int32_t rc = check_matmul_args(ctx, w, x_host, M, K, y_host);
+    if (rc) return rc;
+    if (M == 0 || w->n_rows == 0) return SKN_OK;
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)M * (size_t)K * sizeof(float);
+    const size_t bb = bias_host ? (size_t)w->n_rows * sizeof(float) : 0;
+    const size_t xb_al = (xb + 255) / 256 * 256;
+    const size_t yb = (size_t)M * (size_t)w->n_rows * sizeof(float);
+    rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, xb_al + bb + 256);
+    if (rc) return rc;
+    rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, yb);
+    if (rc) return rc;
+    float *dx = (float *)ctx->d_stage_in;
+    float *db = bias_host ? (float *)((uint8_t *)ctx->d_stage_in + xb_al) : nullptr;
+    if (xb) SKN_CUDA(ctx, cudaMemcpyAsync(dx, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    if (db) SKN_CUDA(ctx, cudaMemcpyAsync(db, bias_host, bb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = skn_matmul_dev(ctx, w, dx, M, K, db, (float *)ctx->d_stage_out);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->d_stage_out, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,39 @@
+// K1: raw GGUF blocks -> fp32 weights, bit-exact with gguf-py.  A verification /
+// export kernel, not on the decode path (the matvec kernels never materialise fp32
+// weights).  One thread decodes one 32-weight group and stores it as eight float4.
+#include "skn_blocks.cuh"
+
+template <int TYPE>
+__global__ void __launch_bounds__(128)
+skn_dequant_kernel(const uint8_t *__restrict__ blocks, int64_t pitch, int64_t n_rows,
+                   int64_t groups_per_row, float *__restrict__ out) {
+    const int64_t total = n_rows * groups_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / groups_per_row;
+        const int64_t g = i - r * groups_per_row;
+        float w[32];
+        decode_group<TYPE>(blocks + r * pitch, g, w);
+        float4 *o = reinterpret_cast<float4 *>(out + (r * groups_per_row + g) * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[q] = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+}
+
+cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitch, int64_t n_rows,
+                               int64_t n_cols, float *out, cudaStream_t stream) {
+    const int64_t gpr = n_cols / 32;
+    const int64_t total = n_rows * gpr;
+    if (total == 0) return cudaSuccess;
+    int64_t nblk = (total + 127) / 128;
+    if (nblk > 148 * 64) nblk = 148 * 64;
+    const dim3 grid((unsigned)nblk), block(128);
+    switch (type) {
+    case SKN_TYPE_Q4_0: skn_dequant_kernel<SKN_TYPE_Q4_0><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_Q8_0: skn_dequant_kernel<SKN_TYPE_Q8_0><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_Q4_K: skn_dequant_kernel<SKN_TYPE_Q4_K><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_Q6_K: skn_dequant_kernel<SKN_TYPE_Q6_K><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}

@@ -1,0 +1,77 @@
+// Internal declarations shared by the translation units of libskainet_cuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "skainet_cuda.h"
+
+#define SKN_MAGIC_CTX 0x736b6e63u     // 'sknc'
+#define SKN_MAGIC_TENSOR 0x736b6e74u  // 'sknt'
+#define SKN_MAGIC_KV 0x736b6e6bu      // 'sknk'
+
+struct skn_ctx {
+    uint32_t magic;
+    int device;
+    cudaStream_t own_stream;
+    cudaStream_t stream;        // stream `_dev` calls enqueue on
+    int sm_count;
+    int32_t *d_status;          // device status word written by bounded waits
+    int32_t *h_status;          // pinned mirror
+    // staging for the host-pointer entry points (grown on demand)
+    void *d_stage_in;  size_t d_stage_in_bytes;
+    void *d_stage_out; size_t d_stage_out_bytes;
+    void *d_scratch;   size_t d_scratch_bytes;   // kernel scratch (split partials etc.)
+    char err[512];
+};
+
+// cached launch geometry of the streaming matvec (state: 0 = not planned yet,
+// 1 = valid, -1 = shape not covered by the streaming kernel)
+struct skn_mv_plan {
+    int state;
+    int nch, wg, grid, threads;
+    size_t smem;
+};
+
+struct skn_tensor {
+    uint32_t magic;
+    skn_ctx *ctx;
+    int32_t type;
+    int64_t n_rows, n_cols;
+    int64_t row_bytes;   // n_cols / block_elems * block_bytes
+    int64_t pitch;       // device row pitch in bytes (multiple of 16)
+    uint8_t *d_blocks;
+    skn_mv_plan mv_plan;
+};
+
+// error plumbing (skn_api.cu)
+int32_t skn_fail(skn_ctx *ctx, int32_t code, const char *fmt, ...);
+int32_t skn_check_cuda(skn_ctx *ctx, cudaError_t e, const char *what);
+bool skn_ctx_ok(const skn_ctx *ctx);
+bool skn_tensor_ok(const skn_tensor *t);
+int32_t skn_stage_reserve(skn_ctx *ctx, void **buf, size_t *cap, size_t need);
+
+#define SKN_CUDA(ctx, call)                                            \
+    do {                                                               \
+        cudaError_t e__ = (call);                                      \
+        if (e__ != cudaSuccess) return skn_check_cuda(ctx, e__, #call); \
+    } while (0)
+
+static inline bool skn_geometry(int32_t type, int32_t *elems, int32_t *bytes) {
+    switch (type) {
+    case SKN_TYPE_Q4_0: *elems = 32;  *bytes = 18;  return true;
+    case SKN_TYPE_Q8_0: *elems = 32;  *bytes = 34;  return true;
+    case SKN_TYPE_Q4_K: *elems = 256; *bytes = 144; return true;
+    case SKN_TYPE_Q6_K: *elems = 256; *bytes = 210; return true;
+    default: return false;
+    }
+}
+
+// kernel launchers (one per translation unit); all enqueue on `stream` and return the
+// launch status
+cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitch, int64_t n_rows,
+                               int64_t n_cols, float *out, cudaStream_t stream);
+cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M,
+                              const float *bias, float *y, cudaStream_t stream);

@@ -1,0 +1,259 @@
+"""Host-side mirror of the reference's op / backend interface for the quantized path,
+written over the C ABI (ctypes).  Names, argument meaning and error behaviour follow the
+Kotlin originals so that tests read like the reference's own:
+
+  Shape            core/src/commonMain/kotlin/sk/ai/net/Shape.kt
+  QuantTensor      a Tensor (core/src/commonMain/kotlin/sk/ai/net/Tensor.kt:6-92) whose
+                   elements are raw GGUF blocks resident in HBM
+  QuantLinear      core/src/commonMain/kotlin/sk/ai/net/nn/Linear.kt:43-49  (x . W^T + b)
+  GGMLQuantizationType / GGML_QUANT_SIZES / quant_shape_to_byte_shape
+                   gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:14-90, Quants.kt:10-20
+
+Where the reference throws IllegalArgumentException this raises ValueError with the same
+message ("Shapes do not align.").  Other failures raise SknError carrying the status code.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _ffi
+
+SKN_OK, SKN_ERR_SHAPE, SKN_ERR_TYPE, SKN_ERR_ALIGN, SKN_ERR_OOM = 0, 1, 2, 3, 4
+SKN_ERR_CUDA, SKN_ERR_TIMEOUT, SKN_ERR_BAD_HANDLE, SKN_ERR_ARG, SKN_ERR_COMM = 5, 6, 7, 8, 9
+
+
+class GGMLQuantizationType(enum.IntEnum):
+    """Constants.kt:14-52 (the four block types this backend runs)."""
+    Q4_0 = 2
+    Q8_0 = 8
+    Q4_K = 12
+    Q6_K = 14
+
+
+QK_K = 256  # Constants.kt:55
+GGML_QUANT_SIZES = {  # Constants.kt:58-90
+    GGMLQuantizationType.Q4_0: (32, 2 + 16),
+    GGMLQuantizationType.Q8_0: (32, 2 + 32),
+    GGMLQuantizationType.Q4_K: (256, 2 + 2 + QK_K // 2 + 12),
+    GGMLQuantizationType.Q6_K: (256, 2 + QK_K // 2 + QK_K // 4 + QK_K // 16),
+}
+
+
+def quant_shape_to_byte_shape(shape: Sequence[int], quant_type: GGMLQuantizationType) -> tuple:
+    """Quants.kt:10-20."""
+    block_size, type_size = GGML_QUANT_SIZES[GGMLQuantizationType(quant_type)]
+    if shape[-1] % block_size != 0:
+        raise ValueError(
+            f"Quantized tensor row size ({shape[-1]}) is not a multiple of "
+            f"{GGMLQuantizationType(quant_type).name} block size ({block_size})")
+    return tuple(shape[:-1]) + (shape[-1] // block_size * type_size,)
+
+
+class SknError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class Shape:
+    """Shape.kt: dimensions, volume, rank."""
+
+    def __init__(self, *dimensions: int):
+        self.dimensions = tuple(int(d) for d in dimensions)
+
+    @property
+    def volume(self) -> int:
+        v = 1
+        for d in self.dimensions:
+            v *= d
+        return v
+
+    @property
+    def rank(self) -> int:
+        return len(self.dimensions)
+
+    def __eq__(self, other):
+        return isinstance(other, Shape) and other.dimensions == self.dimensions
+
+    def __hash__(self):
+        return hash(self.dimensions)
+
+    def __repr__(self):
+        return "Shape: Dimensions = [" + " x ".join(str(d) for d in self.dimensions) + f"], Size (Volume) = {self.volume}"
+
+
+def _raise(ctx_handle, code: int):
+    msg = _ffi.lib().skn_last_error(ctx_handle).decode("utf-8", "replace")
+    if code == SKN_ERR_SHAPE:
+        raise ValueError(msg)
+    raise SknError(code, msg)
+
+
+def _check(ctx_handle, code: int):
+    if code != SKN_OK:
+        _raise(ctx_handle, code)
+
+
+def _ptr(a) -> Optional[int]:
+    """Raw address of a numpy array (host) or a torch tensor (host or device)."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):
+        return a.data_ptr()
+    if isinstance(a, int):
+        return a
+    raise TypeError(f"cannot take the address of {type(a)}")
+
+
+class Context:
+    """One CUDA device + stream (skn_ctx).  Use as a context manager or call close()."""
+
+    def __init__(self, device: int = 0):
+        self._h = ctypes.c_void_p()
+        L = _ffi.lib()
+        rc = L.skn_ctx_create(int(device), ctypes.byref(self._h))
+        if rc != SKN_OK:
+            self._h = ctypes.c_void_p()
+            _raise(None, rc)
+        self.device = int(device)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def set_stream(self, cuda_stream: Optional[int]):
+        _check(self._h, _ffi.lib().skn_ctx_set_stream(self._h, cuda_stream))
+
+    def sync(self):
+        _check(self._h, _ffi.lib().skn_sync(self._h))
+
+    def close(self):
+        if self._h:
+            _ffi.lib().skn_ctx_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # TensorFactory-style entry (TensorFactory.kt:7-9 takes a DoubleArray and cannot carry
+    # raw blocks; this is the added factory function for quantized data)
+    def create_quantized(self, shape: Shape, quant_type, blocks) -> "QuantTensor":
+        return QuantTensor(self, shape, quant_type, blocks)
+
+
+class QuantTensor:
+    """A [out, in] weight stored as raw GGUF blocks in HBM."""
+
+    def __init__(self, ctx: Context, shape: Shape, quant_type, blocks, *, shard=None):
+        if isinstance(shape, (tuple, list)):
+            shape = Shape(*shape)
+        if shape.rank != 2:
+            raise ValueError("a quantized weight is a rank-2 tensor [out, in]")
+        self.ctx = ctx
+        self.quant_type = int(quant_type)
+        raw = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        self._h = ctypes.c_void_p()
+        n_rows, n_cols = shape.dimensions
+        L = _ffi.lib()
+        if shard is None:
+            rc = L.skn_tensor_upload_quant(ctx.handle, self.quant_type, n_rows, n_cols, raw.ctypes.data, raw.size,
+                                           ctypes.byref(self._h))
+            self.shape = shape
+        else:
+            r0, rc_, c0, cc = shard
+            rc = L.skn_tensor_upload_quant_shard(ctx.handle, self.quant_type, n_rows, n_cols, raw.ctypes.data, raw.size,
+                                                 r0, rc_, c0, cc, ctypes.byref(self._h))
+            self.shape = Shape(rc_, cc)
+        if rc != SKN_OK:
+            self._h = ctypes.c_void_p()
+            _raise(ctx.handle, rc)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def rank(self) -> int:
+        return self.shape.rank
+
+    @property
+    def size(self) -> int:
+        return self.shape.volume
+
+    def info(self) -> dict:
+        t, r, c = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64()
+        rb, pitch, dev = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_void_p()
+        _check(self.ctx.handle, _ffi.lib().skn_tensor_info(self._h, ctypes.byref(t), ctypes.byref(r), ctypes.byref(c),
+                                                          ctypes.byref(rb), ctypes.byref(pitch), ctypes.byref(dev)))
+        return {"type": t.value, "n_rows": r.value, "n_cols": c.value, "row_bytes": rb.value,
+                "row_pitch_bytes": pitch.value, "device_blocks": dev.value}
+
+    def dequantize(self) -> np.ndarray:
+        out = np.empty(self.shape.dimensions, dtype=np.float32)
+        _check(self.ctx.handle, _ffi.lib().skn_dequantize(self.ctx.handle, self._h, out.ctypes.data))
+        return out
+
+    def matmul_t(self, x: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
+        """x . W^T (+ bias): x is [K] or [M, K] fp32 on the host; result [N] or [M, N]."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.ndim == 1:
+            m, k, vec = 1, x.shape[0], True
+        elif x.ndim == 2:
+            m, k, vec = x.shape[0], x.shape[1], False
+        else:
+            raise ValueError("Shapes do not align.")
+        n = self.shape.dimensions[0]
+        y = np.empty((m, n), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        if b is not None and b.shape != (n,):
+            raise ValueError("Shapes do not align.")
+        _check(self.ctx.handle, _ffi.lib().skn_matmul(self.ctx.handle, self._h, x.ctypes.data, m, k, _ptr(b),
+                                                     y.ctypes.data))
+        return y[0] if vec else y
+
+    def matmul_t_dev(self, x_dev, m: int, y_dev, bias_dev=None, k: Optional[int] = None):
+        """Device-pointer form: enqueue only (x_dev, y_dev: torch CUDA tensors or addresses)."""
+        kk = self.shape.dimensions[1] if k is None else k
+        _check(self.ctx.handle, _ffi.lib().skn_matmul_dev(self.ctx.handle, self._h, _ptr(x_dev), m, kk, _ptr(bias_dev),
+                                                         _ptr(y_dev)))
+
+    def close(self):
+        if self._h:
+            _ffi.lib().skn_tensor_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class QuantLinear:
+    """Linear.kt:43-49 with a quantized weight: forward(x) = x . W^T + b."""
+
+    def __init__(self, weight: QuantTensor, bias: Optional[np.ndarray] = None, name: str = "linear"):
+        self.name = name
+        self.weight = weight
+        self.bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        return self.weight.matmul_t(x, self.bias)
+
+    __call__ = forward

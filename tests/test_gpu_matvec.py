@@ -1,0 +1,143 @@
+"""K2 parity: fused dequant-dot through the C ABI against the fp64 oracle.
+
+Tolerance (fp32 accumulation): |y - y_ref| <= 1e-5 * sum_k |w_k x_k| per output and
+relative L2 error <= 1e-5 (conftest.assert_close_dot)."""
+import numpy as np
+import pytest
+
+import skainet_b200 as skn
+from conftest import FP32_TOL, assert_close_dot
+from oracle import oracle
+from skainet_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TYPES = list(synth.TYPE_NAMES.items())
+
+
+def run_case(ctx, qt, N, K, M, seed, bias=False):
+    g = synth.rng(seed)
+    w = synth.make_weight(g, qt, N, K)
+    x = synth.make_activations(g, M, K)
+    b = g.standard_normal(N).astype(np.float32) if bias else None
+    t = skn.QuantTensor(ctx, (N, K), qt, w)
+    y = t.matmul_t(x if M > 1 else x[0], b)
+    t.close()
+    y_ref, absdot = oracle.matmul(qt, w, N, K, x)
+    if bias:
+        y_ref = y_ref + b.astype(np.float64)[None, :]
+        absdot = absdot + np.abs(b.astype(np.float64))[None, :]
+    assert_close_dot(np.asarray(y).reshape(M, N), y_ref, absdot, FP32_TOL, f"type {qt} {N}x{K} M={M}")
+    return y
+
+
+def test_cfg1_q4k_matvec(ctx):
+    """Config 1: Q4_K 4096x4096, x fp32[4096], seed 0."""
+    w, x = synth.cfg1(0)
+    t = skn.QuantTensor(ctx, (4096, 4096), synth.Q4_K, w)
+    y = t.matmul_t(x[0])
+    y2 = t.matmul_t(x[0])
+    t.close()
+    assert y.shape == (4096,)
+    assert np.array_equal(y, y2), "matvec must be deterministic run to run"
+    y_ref, absdot = oracle.matmul(synth.Q4_K, w, 4096, 4096, x)
+    assert_close_dot(y[None, :], y_ref, absdot, FP32_TOL, "cfg1")
+
+
+@pytest.mark.parametrize("qt,name", TYPES)
+@pytest.mark.parametrize("N,K", [(1, 256), (5, 512), (33, 2048), (148, 4096), (300, 2304), (64, 14336), (4096, 4096)])
+def test_matvec_m1_shapes(ctx, qt, name, N, K):
+    run_case(ctx, qt, N, K, 1, seed=1000 + N + K)
+
+
+@pytest.mark.parametrize("qt,name", TYPES)
+@pytest.mark.parametrize("M", [2, 3, 4, 5, 16, 17])
+def test_small_batch(ctx, qt, name, M):
+    run_case(ctx, qt, 96, 1024, M, seed=2000 + M, bias=(M % 2 == 0))
+
+
+@pytest.mark.parametrize("qt,name", TYPES)
+def test_bias_m1(ctx, qt, name):
+    run_case(ctx, qt, 200, 4096, 1, seed=77, bias=True)
+
+
+@pytest.mark.parametrize("qt", [synth.Q4_0, synth.Q8_0])
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [1, 4])
+def test_cfg2_shapes(ctx, qt, N, K, M):
+    """Config 2's large shapes at M = 1 and 4 (M = 16, 64 are covered at reduced N)."""
+    run_case(ctx, qt, N, K, M, seed=1)
+
+
+def test_linearity_at_full_size(ctx):
+    """Size-independent property at cfg1's size: W(a x1 + b x2) = a W x1 + b W x2."""
+    w, _ = synth.cfg1(0)
+    g = synth.rng(9)
+    x1, x2 = synth.make_activations(g, 1, 4096)[0], synth.make_activations(g, 1, 4096)[0]
+    t = skn.QuantTensor(ctx, (4096, 4096), synth.Q4_K, w)
+    y1, y2, y3 = t.matmul_t(x1), t.matmul_t(x2), t.matmul_t((2.0 * x1 - 0.5 * x2).astype(np.float32))
+    t.close()
+    lin = 2.0 * y1.astype(np.float64) - 0.5 * y2.astype(np.float64)
+    scale = np.abs(y1).max() + np.abs(y2).max()
+    assert np.max(np.abs(y3 - lin)) <= 2e-5 * scale * 10
+
+
+def test_sharded_matvec_equals_slices(ctx):
+    """Column-parallel shards (row ranges) give slices of y; row-parallel shards (column
+    ranges, Q6_K pitch not a multiple of 16) sum to y."""
+    g = synth.rng(3)
+    N, K = 64, 14336
+    for qt in (synth.Q4_K, synth.Q6_K):
+        w = synth.make_weight(g, qt, N, K)
+        x = synth.make_activations(g, 1, K)
+        y_ref, absdot = oracle.matmul(qt, w, N, K, x)
+        # row ranges
+        parts = []
+        for r in range(4):
+            t = skn.QuantTensor(ctx, (N, K), qt, w, shard=(r * 16, 16, 0, K))
+            parts.append(t.matmul_t(x[0]))
+            t.close()
+        assert_close_dot(np.concatenate(parts)[None, :], y_ref, absdot, FP32_TOL, "row shards")
+        # column ranges: 8 shards of 1792 columns (Q6_K: 1470 bytes per row -> padded pitch)
+        acc = np.zeros(N, dtype=np.float64)
+        for c in range(8):
+            t = skn.QuantTensor(ctx, (N, K), qt, w, shard=(0, N, c * 1792, 1792))
+            acc += t.matmul_t(x[0, c * 1792:(c + 1) * 1792])
+            t.close()
+        assert_close_dot(acc[None, :], y_ref, absdot, FP32_TOL, "column shards")
+
+
+def test_shapes_do_not_align(ctx):
+    # TensorTest.kt:65-70: IllegalArgumentException("Shapes do not align.")
+    w = synth.make_weight(synth.rng(1), synth.Q4_K, 4, 512)
+    t = skn.QuantTensor(ctx, (4, 512), synth.Q4_K, w)
+    with pytest.raises(ValueError, match="Shapes do not align."):
+        t.matmul_t(np.zeros(256, dtype=np.float32))
+    with pytest.raises(ValueError, match="Shapes do not align."):
+        t.matmul_t(np.zeros((2, 3, 512), dtype=np.float32))
+    t.close()
+
+
+def test_empty_inputs(ctx):
+    w = synth.make_weight(synth.rng(1), synth.Q8_0, 4, 64)
+    t = skn.QuantTensor(ctx, (4, 64), synth.Q8_0, w)
+    y = t.matmul_t(np.zeros((0, 64), dtype=np.float32))
+    assert y.shape == (0, 4)
+    t.close()
+    t0 = skn.QuantTensor(ctx, (0, 64), synth.Q8_0, np.zeros(0, dtype=np.uint8))
+    assert t0.matmul_t(np.zeros(64, dtype=np.float32)).shape == (0,)
+    t0.close()
+
+
+def test_extreme_activations(ctx):
+    """Zero, tiny and large activations stay within tolerance (the streaming kernel
+    pre-scales x by a power of two, which is exact over this range)."""
+    g = synth.rng(21)
+    N, K = 64, 4096
+    w = synth.make_weight(g, synth.Q4_K, N, K)
+    t = skn.QuantTensor(ctx, (N, K), synth.Q4_K, w)
+    for scale in (0.0, 1e-20, 1e-6, 1e6, 1e12):
+        x = (synth.make_activations(g, 1, K) * np.float32(scale)).astype(np.float32)
+        y = t.matmul_t(x[0])
+        y_ref, absdot = oracle.matmul(synth.Q4_K, w, N, K, x)
+        assert_close_dot(y[None, :], y_ref, absdot, FP32_TOL, f"x scale {scale}")
+    t.close()
