@@ -190,6 +190,7 @@ def run_ours(args):
     ctx = skn.Context(local)
     stream = torch.cuda.current_stream()
     ctx.set_stream(stream.cuda_stream)
+    ctx.set_relaxed_order(args.order == "relaxed")
 
     # Synthetic stack: one seeded cfg1-distribution weight, then `layers` variants of it
     # (bytes rotated per layer) so that each layer is a distinct buffer with the same value
@@ -305,6 +306,9 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "cfg1: Q4_K matvec 4096x4096, M=1, fp32 x", "layers_per_step": layers,
+                       "launch_order": ("relaxed: the layers of a step are independent and declared so "
+                                        "(SKN_OPT_RELAXED_ORDER)") if args.order == "relaxed" else
+                       "stream order: every launch waits for the previous one",
                        "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                        "l2_policy": f"inputs larger than L2: {layers} distinct weights = "
                                     f"{layers * W_BYTES / 1e6:.0f} MB streamed per step",
@@ -341,6 +345,9 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--order", default="relaxed", choices=["relaxed", "stream"],
+                    help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
+                         "may overlap; stream: each launch waits for the one before it")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

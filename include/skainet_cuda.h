@@ -70,6 +70,17 @@ int32_t skn_ctx_destroy(skn_ctx *ctx);
  * context's own stream; NULL restores the context's stream. */
 int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
 
+/* Context options.
+ * SKN_OPT_RELAXED_ORDER (default 0): with value 1 the caller promises that consecutive
+ * `_dev` launches on this context are independent of one another -- no launch reads a
+ * buffer that the launch before it writes, nor writes one that it reads or writes (as for
+ * the Q/K/V or gate/up projections of one activation, or a stack of unrelated layers).
+ * Launches may then overlap on the GPU instead of running in stream order; everything is
+ * still complete when skn_sync (or a later operation on the stream) returns.  The reference
+ * is single-threaded and has no notion of ordering (Tensor.kt:6-33): no counterpart. */
+#define SKN_OPT_RELAXED_ORDER 1
+int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value);
+
 /* Wait for everything enqueued on the context's stream; reports a pending
  * device-side status (e.g. SKN_ERR_TIMEOUT) if a kernel recorded one. */
 int32_t skn_sync(skn_ctx *ctx);

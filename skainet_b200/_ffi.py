@@ -10,7 +10,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libskainet_cuda.so")
+# SKAINET_CUDA_LIB points at an alternative build of the same library (e.g. a debug build)
+LIB_PATH = os.environ.get("SKAINET_CUDA_LIB") or os.path.join(_HERE, "libskainet_cuda.so")
 
 c_i32, c_i64, c_vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 P = ctypes.POINTER
@@ -22,6 +23,7 @@ SIGNATURES = {
     "skn_ctx_create": (c_i32, [c_i32, P(c_vp)]),
     "skn_ctx_destroy": (c_i32, [c_vp]),
     "skn_ctx_set_stream": (c_i32, [c_vp, c_vp]),
+    "skn_ctx_set_option": (c_i32, [c_vp, c_i32, c_i64]),
     "skn_sync": (c_i32, [c_vp]),
     "skn_quant_geometry": (c_i32, [c_i32, P(c_i32), P(c_i32)]),
     "skn_quant_row_bytes": (c_i32, [c_i32, c_i64, P(c_i64)]),

@@ -83,8 +83,8 @@ int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     CTX_TRY(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
     ctx->stream = ctx->own_stream;
-    CTX_TRY(cudaMalloc((void **)&ctx->d_status, 256));
-    CTX_TRY(cudaMemset(ctx->d_status, 0, 256));
+    CTX_TRY(cudaMalloc((void **)&ctx->d_status, 32768));
+    CTX_TRY(cudaMemset(ctx->d_status, 0, 32768));
     CTX_TRY(cudaMallocHost((void **)&ctx->h_status, 256));
 #undef CTX_TRY
     *ctx->h_status = 0;
@@ -111,6 +111,14 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
     ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
     return SKN_OK;
+}
+
+int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    switch (option) {
+    case SKN_OPT_RELAXED_ORDER: ctx->relaxed_order = value ? 1 : 0; return SKN_OK;
+    default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
+    }
 }
 
 int32_t skn_sync(skn_ctx *ctx) {
@@ -309,3 +317,13 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
 }
 
 }  // extern "C"
+
+#ifdef SKN_MV_TRACE
+// Profiling builds only (never in the shipped library): copies the raw status/trace area.
+extern "C" int32_t skn_debug_read_status(skn_ctx *ctx, void *out_host, int64_t bytes) {
+    if (!skn_ctx_ok(ctx) || bytes > 32768) return SKN_ERR_ARG;
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    SKN_CUDA(ctx, cudaMemcpy(out_host, ctx->d_status, (size_t)bytes, cudaMemcpyDeviceToHost));
+    return SKN_OK;
+}
+#endif

@@ -18,6 +18,7 @@ struct skn_ctx {
     cudaStream_t own_stream;
     cudaStream_t stream;        // stream `_dev` calls enqueue on
     int sm_count;
+    int relaxed_order;          // SKN_OPT_RELAXED_ORDER
     int32_t *d_status;          // device status word written by bounded waits
     int32_t *h_status;          // pinned mirror
     // staging for the host-pointer entry points (grown on demand)

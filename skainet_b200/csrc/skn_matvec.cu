@@ -22,6 +22,22 @@
 
 #include <stdlib.h>
 
+// SKN_MV_TRACE builds record per-CTA phase timestamps (SM clock and global timer) after the
+// status word; used only for profiling experiments, never in the shipped library.
+#ifdef SKN_MV_TRACE
+#define MV_STAMP(k)                                                                        \
+    do {                                                                                   \
+        if (threadIdx.x == 0) {                                                            \
+            long long *tr = reinterpret_cast<long long *>(status) + 16 + blockIdx.x * 16;  \
+            tr[2 * (k)] = clock64();                                                       \
+            tr[2 * (k) + 1] = (long long)skn_globaltimer_ns();                             \
+        }                                                                                  \
+    } while (0)
+#else
+#define MV_STAMP(k) do {} while (0)
+#endif
+
+
 // ----------------------------------------------------------------------------------------
 // generic kernel
 // ----------------------------------------------------------------------------------------
@@ -124,113 +140,189 @@ __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane)
 // ---- Q4_K ------------------------------------------------------------------------------
 // chunk = 8 super-blocks (2048 weights, 1152 bytes); lane = (block cb = lane/4, pair p =
 // lane%4): the 32 quant bytes whose low nibbles are sub-block 2p and high nibbles
-// sub-block 2p+1, i.e. 64 consecutive weights starting at 256*cb + 64*p.
+// sub-block 2p+1, i.e. the 64 consecutive weights ("group") starting at 256*cb + 64*p.
+//
+// The 32 quant bytes are read as four 64-bit values (two 32-bit words each).  The two
+// halves of a packed f32x2 operand are the SAME nibble position of the two words, so
+// `pair & mask64` is already the packed operand (no register shuffling).  Nibble position
+// n = 2k+h of byte k (h = 0 low nibble, 1 high nibble) sits at bit 4n; byte 3 is taken
+// from (pair >> 8), i.e. at bits 16 / 20, to stay inside the 24 bits that read as k*2^-149.
+//
+// Shared x layout produced by prep_x, per group G of 64 activations:
+//   xp[G]  : 32 packed pairs; pair j*8+n = {x[32h + 8j + k], x[32h + 8j + 4 + k]} * 2^(S-pos(n));
+//            the sixteen 16-byte slots of a group are rotated by G so that the lanes of a warp
+//            (consecutive groups) read conflict-free
+//   gsum[2G], gsum[2G+1] : plain sums of the low / high 32 activations (for the -dmin*m term)
+//   gun[G] : 2^(149-S), which undoes the 2^(S-149) carried by the dot
+// S (23..120) is chosen per group so that its largest |x| lands near 2^90 (for |x| up to
+// 2^67; larger activations simply keep S = 23): the pre-scaled activations do not overflow
+// and their products with k * 2^-149 stay normal numbers.
 struct Q4KStream {
     static constexpr int CHUNK_BLOCKS = 8;
     static constexpr int BLOCK_BYTES = 144;
+    static constexpr int BLOCK_WEIGHTS = 256;
     static constexpr int CHUNK_BYTES = CHUNK_BLOCKS * BLOCK_BYTES;
-    static constexpr int CHUNK_WEIGHTS = CHUNK_BLOCKS * 256;
+    static constexpr int CHUNK_WEIGHTS = CHUNK_BLOCKS * BLOCK_WEIGHTS;
+    // bytes of prepared x per weight column: 4 (pairs) + 2/32*4 (sums) + 1/64*4 (unscale)
+    static __host__ __device__ size_t xprep_bytes(int64_t kpad) { return (size_t)kpad * 4 + (size_t)kpad / 8 + (size_t)kpad / 16; }
 
-    uint64_t x2[32];   // {x_lo[i] * 2^(S - pos_lo), x_hi[i] * 2^(S - pos_hi)}
-    float sum_lo, sum_hi;
-    float unscale;     // 2^(85 - S); together with the constant 2^64 it undoes 2^(S - 149)
-    int cb, p;
+    struct Raw { ulonglong2 q0, q1; uint4 hdr; };   // one lane's share of a staged row-chunk
+
+    uint64_t x2[32];
+    float sum_lo, sum_hi, unscale;
+    int off;          // byte offset of this lane's block inside a staged chunk
+    int p;
+    uint32_t sel, m_low, m_top, m_nib;   // per-lane constants of the scale decode
     bool active;
 
-    __device__ __forceinline__ void load_x(const float *__restrict__ x, int chunk, int lane, int nblocks_in_chunk) {
-        cb = lane >> 2;
-        p = lane & 3;
-        active = cb < nblocks_in_chunk;
-        const float4 *xp = reinterpret_cast<const float4 *>(x + (int64_t)chunk * CHUNK_WEIGHTS + cb * 256 + p * 64);
-        float xl[32], xh[32];
+    // CTA-cooperative: K activations from global -> prepared form in shared memory.
+    // kpad (a multiple of 2048) is the padded length; columns >= K are written as zeros.
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+        float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
+        float *gun = gsum + kpad / 32;
+        const int nf = kpad / 4;
+        const int lane = threadIdx.x & 31;
+        constexpr int B = 4;   // float4 loads in flight per thread
+        for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
+            float4 v[B];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const float4 a = active ? __ldg(xp + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 b = active ? __ldg(xp + 8 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            xl[4 * q] = a.x; xl[4 * q + 1] = a.y; xl[4 * q + 2] = a.z; xl[4 * q + 3] = a.w;
-            xh[4 * q] = b.x; xh[4 * q + 1] = b.y; xh[4 * q + 2] = b.z; xh[4 * q + 3] = b.w;
-        }
-        float sl = 0.f, sh = 0.f;
-        uint32_t mx = 0;
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;
+                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            sl += xl[i];
-            sh += xh[i];
-            mx = max(mx, max(__float_as_uint(xl[i]), __float_as_uint(xh[i])) & 0x7fffffffu);
-        }
-        sum_lo = sl;
-        sum_hi = sh;
-        // Per-lane power-of-two pre-scale S: the largest |x| of this lane lands near 2^90, so
-        // x * 2^S never overflows and the products with k * 2^-149 stay normal numbers whatever
-        // the magnitude of the activations.
-        int S = 217 - (int)(mx >> 23);
-        S = S > 120 ? 120 : (S < -37 ? -37 : S);
-        unscale = skn_pow2f(85 - S);
-        // byte k of a 32-bit quant word: low nibble sits at bit 8k, high nibble at 8k+4;
-        // byte 3 is read from (word >> 8), i.e. at bits 16 / 20
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;   // 16 consecutive f = one group
+                float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+                float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int k = i & 3;
-            const int pos_lo = (k == 3) ? 16 : 8 * k;
-            const int pos_hi = pos_lo + 4;
-            x2[i] = skn_pack2(xl[i] * skn_pow2f(S - pos_lo), xh[i] * skn_pow2f(S - pos_hi));
+                for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                int S = 217 - (int)(__float_as_uint(mx) >> 23);
+                S = S > 120 ? 120 : (S < 23 ? 23 : S);
+                if (f < nf) {
+                    const int G = f >> 4;
+                    const int h = (f >> 3) & 1;             // 0: low-nibble half, 1: high-nibble half
+                    const int wi = f & 7;                   // quant word; v.x..v.w are its bytes 0..3
+                    const int j = wi >> 1, comp = wi & 1;
+                    const int ph = 4 * h;
+                    float *g32 = reinterpret_cast<float *>(xs + (size_t)G * 256);
+                    // byte k -> pair j*8 + 2k + h -> 16-byte slot j*4 + k, float 2h + comp
+                    g32[((j * 4 + 0 + G) & 15) * 4 + 2 * h + comp] = v[b].x * skn_pow2f(S - ph);
+                    g32[((j * 4 + 1 + G) & 15) * 4 + 2 * h + comp] = v[b].y * skn_pow2f(S - 8 - ph);
+                    g32[((j * 4 + 2 + G) & 15) * 4 + 2 * h + comp] = v[b].z * skn_pow2f(S - 16 - ph);
+                    g32[((j * 4 + 3 + G) & 15) * 4 + 2 * h + comp] = v[b].w * skn_pow2f(S - 16 - ph);
+                    if ((lane & 7) == 0) gsum[2 * G + h] = sm;
+                    if ((lane & 15) == 0) gun[G] = skn_pow2f(149 - S);
+                }
+            }
         }
     }
 
-    // partial dot of this lane's 64 weights of the row-chunk staged at `sb`
-    __device__ __forceinline__ float dot(const uint8_t *sb) const {
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(sb + cb * BLOCK_BYTES);
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + cb * BLOCK_BYTES + 16 + 32 * p);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + cb * BLOCK_BYTES + 32 + 32 * p);
-        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+    __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
+        const int cb = lane >> 2;
+        p = lane & 3;
+        off = cb * BLOCK_BYTES;
+        active = cb < nblocks_in_chunk;
+        sel = (p & 1) ? 0x4432u : 0x4410u;            // bytes (2,3) or (0,1), upper half zero
+        m_low = (p < 2) ? 0x3F3Fu : 0u;
+        m_top = (p < 2) ? 0u : 0x3030u;
+        m_nib = (p < 2) ? 0u : 0x0F0Fu;
+        const int G = (chunk * CHUNK_BLOCKS + cb) * 4 + p;
+        const ulonglong2 *g = reinterpret_cast<const ulonglong2 *>(xs + (size_t)G * 256);
+        const float *gsum = reinterpret_cast<const float *>(xs + (size_t)kpad * 4);
+        const float *gun = gsum + kpad / 32;
 #pragma unroll
-        for (int wi = 0; wi < 8; ++wi) {
-            const uint32_t w = qw[wi];
-            const uint32_t w8 = w >> 8;
-            acc[0] = skn_fma2(skn_pack2u(w & 0x0000000Fu, w & 0x000000F0u), x2[4 * wi + 0], acc[0]);
-            acc[1] = skn_fma2(skn_pack2u(w & 0x00000F00u, w & 0x0000F000u), x2[4 * wi + 1], acc[1]);
-            acc[2] = skn_fma2(skn_pack2u(w & 0x000F0000u, w & 0x00F00000u), x2[4 * wi + 2], acc[2]);
-            acc[3] = skn_fma2(skn_pack2u(w8 & 0x000F0000u, w8 & 0x00F00000u), x2[4 * wi + 3], acc[3]);
+        for (int s = 0; s < 16; ++s) {
+            const ulonglong2 v = g[(s + G) & 15];
+            x2[2 * s] = v.x;
+            x2[2 * s + 1] = v.y;
         }
-        float dlo, dhi;
-        skn_unpack2(skn_add2(skn_add2(acc[0], acc[1]), skn_add2(acc[2], acc[3])), dlo, dhi);
+        sum_lo = gsum[2 * G];
+        sum_hi = gsum[2 * G + 1];
+        unscale = gun[G];
+    }
 
-        // 6-bit scales / mins of sub-blocks 2p and 2p+1 (two adjacent bytes of each group)
-        const int sh = (p & 1) * 16;
-        const uint32_t a2 = (hdr.y >> sh) & 0xFFFFu, b2 = (hdr.z >> sh) & 0xFFFFu, c2 = (hdr.w >> sh) & 0xFFFFu;
-        const uint32_t sc2 = (p < 2) ? (a2 & 0x3F3Fu) : ((c2 & 0x0F0Fu) | ((a2 >> 2) & 0x3030u));
-        const uint32_t mn2 = (p < 2) ? (b2 & 0x3F3Fu) : (((c2 >> 4) & 0x0F0Fu) | ((b2 >> 2) & 0x3030u));
-        const float d = skn_half_bits_to_float(hdr.x & 0xFFFFu);
-        const float dmin = skn_half_bits_to_float(hdr.x >> 16);
-        const float t1 = fmaf((float)(sc2 >> 8), dhi, (float)(sc2 & 0xFFu) * dlo) * skn_pow2f(64) * unscale;
-        const float t2 = fmaf((float)(mn2 >> 8), sum_hi, (float)(mn2 & 0xFFu) * sum_lo);
-        const float r = fmaf(d, t1, -dmin * t2);
-        return active ? r : 0.f;
+    __device__ __forceinline__ Raw fetch(const uint8_t *sb) const {
+        Raw r;
+        r.hdr = *reinterpret_cast<const uint4 *>(sb + off);
+        r.q0 = *reinterpret_cast<const ulonglong2 *>(sb + off + 16 + 32 * p);
+        r.q1 = *reinterpret_cast<const ulonglong2 *>(sb + off + 32 + 32 * p);
+        return r;
+    }
+
+    // scale / min decode and final combination shared by dot() and dot2()
+    __device__ __forceinline__ float finish(const uint4 hdr, float dlo, float dhi) const {
+        // 6-bit scales / mins of sub-blocks 2p and 2p+1: two adjacent bytes of each of the three
+        // 4-byte groups; sel picks them with one byte-permute each, the three masks make the
+        // two packing rules (sub-blocks 0-3 / 4-7) one branch-free expression
+        const uint32_t a2 = __byte_perm(hdr.y, 0u, sel), b2 = __byte_perm(hdr.z, 0u, sel), c2 = __byte_perm(hdr.w, 0u, sel);
+        const uint32_t sc2 = (a2 & m_low) | ((a2 >> 2) & m_top) | (c2 & m_nib);
+        const uint32_t mn2 = (b2 & m_low) | ((b2 >> 2) & m_top) | ((c2 >> 4) & m_nib);
+        // small ints -> float without the conversion pipe: (2^23 + k) - 2^23
+        const float sc_lo = __uint_as_float(__byte_perm(sc2, 0x4B000000u, 0x7440)) - 8388608.f;
+        const float sc_hi = __uint_as_float(__byte_perm(sc2, 0x4B000000u, 0x7441)) - 8388608.f;
+        const float mn_lo = __uint_as_float(__byte_perm(mn2, 0x4B000000u, 0x7440)) - 8388608.f;
+        const float mn_hi = __uint_as_float(__byte_perm(mn2, 0x4B000000u, 0x7441)) - 8388608.f;
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));   // {d, dmin}
+        const float t1 = fmaf(sc_hi, dhi, sc_lo * dlo) * unscale;
+        const float t2 = fmaf(mn_hi, sum_hi, mn_lo * sum_lo);
+        const float res = fmaf(dd.x, t1, -dd.y * t2);
+        return active ? res : 0.f;
+    }
+
+    // partial dot of this lane's 64 weights
+    __device__ __forceinline__ float dot(const Raw &r) const {
+        const uint64_t qp[4] = {r.q0.x, r.q0.y, r.q1.x, r.q1.y};
+        uint64_t lo0 = 0ull, lo1 = 0ull, hi0 = 0ull, hi1 = 0ull;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint64_t P = qp[j];
+            const uint64_t P8 = P >> 8;
+            lo0 = skn_fma2(P & 0x0000000F0000000Full, x2[8 * j + 0], lo0);
+            hi0 = skn_fma2(P & 0x000000F0000000F0ull, x2[8 * j + 1], hi0);
+            lo1 = skn_fma2(P & 0x00000F0000000F00ull, x2[8 * j + 2], lo1);
+            hi1 = skn_fma2(P & 0x0000F0000000F000ull, x2[8 * j + 3], hi1);
+            lo0 = skn_fma2(P & 0x000F0000000F0000ull, x2[8 * j + 4], lo0);
+            hi0 = skn_fma2(P & 0x00F0000000F00000ull, x2[8 * j + 5], hi0);
+            lo1 = skn_fma2(P8 & 0x000F0000000F0000ull, x2[8 * j + 6], lo1);
+            hi1 = skn_fma2(P8 & 0x00F0000000F00000ull, x2[8 * j + 7], hi1);
+        }
+        float la, lb, ha, hb;
+        skn_unpack2(skn_add2(lo0, lo1), la, lb);
+        skn_unpack2(skn_add2(hi0, hi1), ha, hb);
+        const float dlo = la + lb, dhi = ha + hb;
+
+        return finish(r.hdr, dlo, dhi);
     }
 };
 
-// One kernel for every streaming decoder S (a struct with CHUNK_BLOCKS / BLOCK_BYTES /
-// CHUNK_BYTES / CHUNK_WEIGHTS, load_x() and dot()).
+// One kernel for every streaming decoder S.
 //   grid  : CTA b owns rows [b*N/grid, (b+1)*N/grid)
 //   block : nch * wg warps; warp w -> chunk c = w % nch, row slot g = w / nch
-//   smem  : [warps][MV_NST][CHUNK_BYTES] ring | [warps][MV_NST] mbarriers | [rows][nch] partials
+//   smem  : [warps][MV_NST][CHUNK_BYTES] ring | prepared x | [warps][MV_NST] mbarriers | [rows][nch] partials
+// Each warp walks its rows two at a time; stage s of its ring holds row i with i % MV_NST == s.
 template <class S>
 __global__ void __launch_bounds__(512, 1)
-skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int nb, int nch, int wg,
+skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K, int nch, int wg,
                   const float *__restrict__ x, const float *__restrict__ bias, float *__restrict__ y,
-                  int32_t *__restrict__ status) {
+                  int32_t *__restrict__ status, int relaxed) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
     const int c = warp % nch;
     const int g = warp / nch;
+    const int kpad = nch * S::CHUNK_WEIGHTS;
+    const int nb = K / S::BLOCK_WEIGHTS;
 
+    const size_t ring_bytes = (size_t)nwarps * MV_NST * S::CHUNK_BYTES;
     uint8_t *ring = smem + (size_t)warp * MV_NST * S::CHUNK_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)nwarps * MV_NST * S::CHUNK_BYTES) + warp * MV_NST;
-    float *part = reinterpret_cast<float *>(smem + (size_t)nwarps * MV_NST * S::CHUNK_BYTES +
-                                            (size_t)nwarps * MV_NST * sizeof(uint64_t));
+    uint8_t *xs = smem + ring_bytes;
+    const size_t xs_bytes = (S::xprep_bytes(kpad) + 127) / 128 * 128;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ring_bytes + xs_bytes) + warp * MV_NST;
+    float *part = reinterpret_cast<float *>(smem + ring_bytes + xs_bytes + (size_t)nwarps * MV_NST * sizeof(uint64_t));
 
     const int64_t row_begin = (int64_t)blockIdx.x * N / gridDim.x;
     const int64_t row_end = (int64_t)(blockIdx.x + 1) * N / gridDim.x;
@@ -243,62 +335,90 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int n
     const uint8_t *src0 = W + (row_begin + g) * pitch + (size_t)c * S::CHUNK_BYTES;
     const int64_t src_step = (int64_t)wg * pitch;
 
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < MV_NST; ++s) skn_mbar_init(&bars[s], 1);
+    MV_STAMP(0);
+    // weights never depend on the previous kernel: start streaming them right away, one
+    // stage per lane
+    if (lane < MV_NST) {
+        skn_mbar_init(&bars[lane], 1);
         skn_fence_mbar_init();
         skn_fence_proxy_async();
-        // weights never depend on the previous kernel: start streaming them right away
-#pragma unroll
-        for (int s = 0; s < MV_NST; ++s) {
-            if (s < cnt) {
-                skn_mbar_expect_tx(&bars[s], bytes);
-                skn_bulk_g2s(ring + s * S::CHUNK_BYTES, src0 + s * src_step, bytes, &bars[s]);
-            }
+        if (lane < cnt) {
+            skn_mbar_expect_tx(&bars[lane], bytes);
+            skn_bulk_g2s(ring + lane * S::CHUNK_BYTES, src0 + lane * src_step, bytes, &bars[lane]);
         }
     }
     __syncwarp();
+    MV_STAMP(1);
     skn_pdl_launch_dependents();
-    skn_pdl_wait();   // x (and y) may belong to the previous kernel in the stream
+    // x (and y) may belong to the previous kernel in the stream, unless the caller has
+    // declared its launches independent
+    if (!relaxed) skn_pdl_wait();
+    MV_STAMP(2);
 
-    S dec;
-    dec.load_x(x, c, lane, nbc);
-
-    bool failed = false;
-    for (int i0 = 0; i0 < cnt; i0 += MV_NST) {
-        const uint32_t parity = (uint32_t)(i0 / MV_NST) & 1u;
-        float acc[MV_NST];
-#pragma unroll
-        for (int ii = 0; ii < MV_NST; ++ii) {
-            acc[ii] = 0.f;
-            const int i = i0 + ii;
-            if (i < cnt && !failed) {
-                if (!__all_sync(0xffffffffu, skn_mbar_wait(&bars[ii], parity))) {
-                    failed = true;
-                    if (lane == 0) atomicExch(status, SKN_ERR_TIMEOUT);
-                } else {
-                    acc[ii] = dec.dot(ring + ii * S::CHUNK_BYTES);
-                    __syncwarp();   // every lane has consumed the stage
-                    if (lane == 0 && i + MV_NST < cnt) {
-                        skn_fence_proxy_async();
-                        skn_mbar_expect_tx(&bars[ii], bytes);
-                        skn_bulk_g2s(ring + ii * S::CHUNK_BYTES, src0 + (int64_t)(i + MV_NST) * src_step, bytes,
-                                     &bars[ii]);
-                    }
-                }
-            }
-        }
-        const float tot = skn_warp_reduce8(acc, lane);
-        const int ii = lane >> 2;
-        if ((lane & 3) == 0 && i0 + ii < cnt) part[(size_t)(g + (i0 + ii) * wg) * nch + c] = tot;
-    }
+    S::prep_x(x, K, kpad, xs);
     __syncthreads();
+    MV_STAMP(3);
+    S dec;
+    dec.load_x(xs, kpad, c, lane, nbc);
+    MV_STAMP(4);
+
+    // Two rows per iteration.  The warp-level sum of an iteration's two partial dots is a
+    // five-step butterfly; its steps are spread over the NEXT iteration so that the shuffle
+    // latency overlaps barrier polling, shared-memory reads and arithmetic.
+    // A wait that runs out records SKN_ERR_TIMEOUT and lets the thread go on (the result is
+    // then garbage, the status word says so); no thread ever leaves the warp's sync points.
+    bool failed = false;
+    float pend = 0.f;          // previous iteration: lanes 0-15 row i-2, lanes 16-31 row i-1
+    int pend_i = -1;
+    for (int i = 0; i < cnt; i += 2) {
+        const int s0 = i & (MV_NST - 1), s1 = (i + 1) & (MV_NST - 1);
+        const uint32_t parity = (uint32_t)(i / MV_NST) & 1u;    // i even: i and i+1 share the ring pass
+        const bool two = i + 1 < cnt;
+        pend += __shfl_xor_sync(0xffffffffu, pend, 8);
+        if (!failed && !(skn_mbar_wait(&bars[s0], parity) && (!two || skn_mbar_wait(&bars[s1], parity)))) {
+            failed = true;
+            atomicExch(status, SKN_ERR_TIMEOUT);
+        }
+        pend += __shfl_xor_sync(0xffffffffu, pend, 4);
+        const typename S::Raw r0 = dec.fetch(ring + s0 * S::CHUNK_BYTES);
+        const typename S::Raw r1 = dec.fetch(ring + (two ? s1 : s0) * S::CHUNK_BYTES);
+        __syncwarp();   // every lane holds its share in registers: the stages may be refilled
+        if (lane < 2 && i + lane + MV_NST < cnt) {
+            const int st = lane ? s1 : s0;
+            skn_fence_proxy_async();
+            skn_mbar_expect_tx(&bars[st], bytes);
+            skn_bulk_g2s(ring + st * S::CHUNK_BYTES, src0 + (int64_t)(i + lane + MV_NST) * src_step, bytes, &bars[st]);
+        }
+        pend += __shfl_xor_sync(0xffffffffu, pend, 2);
+        const float v0 = dec.dot(r0);
+        const float v1 = two ? dec.dot(r1) : 0.f;
+        pend += __shfl_xor_sync(0xffffffffu, pend, 1);
+        if ((lane & 15) == 0 && pend_i >= 0) {
+            const int ir = pend_i + (lane >> 4);
+            if (ir < cnt) part[(size_t)(g + ir * wg) * nch + c] = pend;
+        }
+        // first butterfly step: the upper half-warp takes over row i+1, the lower row i
+        pend = ((lane & 16) ? v1 : v0) + __shfl_xor_sync(0xffffffffu, (lane & 16) ? v0 : v1, 16);
+        pend_i = i;
+    }
+    if (pend_i >= 0) {
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) pend += __shfl_xor_sync(0xffffffffu, pend, o);
+        if ((lane & 15) == 0) {
+            const int ir = pend_i + (lane >> 4);
+            if (ir < cnt) part[(size_t)(g + ir * wg) * nch + c] = pend;
+        }
+    }
+    MV_STAMP(5);
+    __syncthreads();
+    MV_STAMP(6);
     for (int lr = threadIdx.x; lr < rows; lr += blockDim.x) {
         float s = 0.f;
         for (int cc = 0; cc < nch; ++cc) s += part[(size_t)lr * nch + cc];
         if (bias) s += bias[row_begin + lr];
         y[row_begin + lr] = s;
     }
+    MV_STAMP(7);
 }
 
 static int env_int(const char *name, int dflt) {
@@ -308,43 +428,41 @@ static int env_int(const char *name, int dflt) {
 
 // Launch geometry of the streaming kernel for one weight tensor; computed on first use and
 // cached in the tensor (it depends only on the tensor's shape and the device).
+//   - one CTA per SM (a second CTA slot is left free so that, under programmatic dependent
+//     launch, the next matvec's CTA can become resident and prefetch its weights while this
+//     one computes);
+//   - warps = nch * wg with wg chosen for about 8 warps.
 template <class S>
 static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &pl) {
     auto kern = skn_matvec_stream<S>;
     pl.state = -1;  // "no streaming plan" unless everything below works out
-    const int64_t nb = w->n_cols / (S::CHUNK_WEIGHTS / S::CHUNK_BLOCKS);  // blocks per row
+    if (w->n_cols % S::BLOCK_WEIGHTS || w->n_cols > (1 << 20)) return cudaSuccess;
+    const int64_t nb = w->n_cols / S::BLOCK_WEIGHTS;
     const int nch = (int)((nb + S::CHUNK_BLOCKS - 1) / S::CHUNK_BLOCKS);
     if (nch < 1 || nch > 16 || w->n_rows < 1) return cudaSuccess;
     static const int wg_env = env_int("SKN_MV_WG", 0);
-    static const int occ_env = env_int("SKN_MV_OCC", 0);
-    int wg = wg_env > 0 ? wg_env : (nch <= 8 ? 8 / nch : 1);
+    static const int warps_env = env_int("SKN_MV_WARPS", 8);
+    int wg = wg_env > 0 ? wg_env : (nch <= warps_env ? warps_env / nch : 1);
     if (wg < 1) wg = 1;
     while (nch * wg > 16) --wg;
+    if (wg < 1) return cudaSuccess;
     const int warps = nch * wg;
     const int threads = warps * 32;
-    const size_t ring = (size_t)warps * MV_NST * S::CHUNK_BYTES + (size_t)warps * MV_NST * sizeof(uint64_t);
+    const int kpad = nch * S::CHUNK_WEIGHTS;
+    const size_t fixed = (size_t)warps * MV_NST * S::CHUNK_BYTES + (S::xprep_bytes(kpad) + 127) / 128 * 128 +
+                         (size_t)warps * MV_NST * sizeof(uint64_t);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
-    int occ = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, ring + 1024);
-    if (e != cudaSuccess) return e;
-    if (occ_env > 0 && occ_env < occ) occ = occ_env;
-    if (occ < 1) return cudaSuccess;
-    int64_t grid = (int64_t)ctx->sm_count * occ;
+    int64_t grid = ctx->sm_count;
     if (grid > w->n_rows) grid = w->n_rows;
     const int64_t rows_max = (w->n_rows + grid - 1) / grid;
-    const size_t smem = ring + (size_t)rows_max * nch * sizeof(float);
-    if (smem > ring + 1024 || smem > 220 * 1024) {
-        // partial-sum area larger than what the occupancy query assumed: use one CTA per SM
-        grid = ctx->sm_count < w->n_rows ? ctx->sm_count : w->n_rows;
-        const int64_t rm = (w->n_rows + grid - 1) / grid;
-        const size_t sm2 = ring + (size_t)rm * nch * sizeof(float);
-        if (sm2 > 220 * 1024) return cudaSuccess;
-        pl.smem = sm2;
-    } else {
-        pl.smem = smem;
-    }
-    pl.nch = nch; pl.wg = wg; pl.grid = (int)grid; pl.threads = threads;
+    const size_t smem = fixed + (size_t)rows_max * nch * sizeof(float);
+    if (smem > 220 * 1024) return cudaSuccess;
+    int occ = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem);
+    if (e != cudaSuccess) return e;
+    if (occ < 1) return cudaSuccess;
+    pl.nch = nch; pl.wg = wg; pl.grid = (int)grid; pl.threads = threads; pl.smem = smem;
     pl.state = 1;
     return cudaSuccess;
 }
@@ -364,9 +482,8 @@ static cudaError_t launch_stream(skn_ctx *ctx, const skn_tensor *w, const float 
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    const int nb = (int)(w->n_cols / (S::CHUNK_WEIGHTS / S::CHUNK_BLOCKS));
-    return cudaLaunchKernelEx(&cfg, kern, (const uint8_t *)w->d_blocks, w->pitch, w->n_rows, nb, pl.nch, pl.wg, x,
-                              bias, y, ctx->d_status);
+    return cudaLaunchKernelEx(&cfg, kern, (const uint8_t *)w->d_blocks, w->pitch, w->n_rows, (int)w->n_cols, pl.nch,
+                              pl.wg, x, bias, y, ctx->d_status, ctx->relaxed_order);
 }
 
 template <class S>

@@ -131,6 +131,10 @@ class Context:
     def set_stream(self, cuda_stream: Optional[int]):
         _check(self._h, _ffi.lib().skn_ctx_set_stream(self._h, cuda_stream))
 
+    def set_relaxed_order(self, on: bool):
+        """Declare consecutive device-pointer launches independent (they may overlap)."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 1, 1 if on else 0))
+
     def sync(self):
         _check(self._h, _ffi.lib().skn_sync(self._h))
 
