@@ -142,6 +142,49 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
 int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
                        const float *bias_dev, float *y_dev);
 
+/* ---- KV cache and decode attention ------------------------------------------------------
+ * The reference has no KV cache, no attention and no usable softmax (its softmax(dim),
+ * core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:491-519, indexes the wrong axis);
+ * the nearest ancestor of a gather is the range slice DoublesTensor.get(vararg IntRange),
+ * DoublesTensor.kt:52-68.  These entry points are new surface in the style of the rest. */
+
+/* fp32 cache for `batch` sequences: K, V [batch][n_kv_heads][capacity][head_dim] (head-major
+ * ring buffer, device resident).  head_dim is 64 or 128. */
+int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
+                      skn_kvcache **out);
+int32_t skn_kv_destroy(skn_kvcache *kv);
+/* forget every cached token */
+int32_t skn_kv_reset(skn_kvcache *kv);
+/* Pre-fill: k_host, v_host are [batch][n_kv_heads][tokens][head_dim]; sequence b keeps its
+ * first lens_host[b] tokens (lens_host[b] <= tokens <= capacity). */
+int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, int32_t tokens,
+                    const int32_t *lens_host);
+/* Current length and ring start of every sequence (either pointer may be NULL). */
+int32_t skn_kv_lengths(skn_kvcache *kv, int32_t *lens_host, int32_t *start_host);
+/* Append one token per sequence: k_new, v_new are [batch][n_kv_heads][head_dim] (no rotary
+ * embedding is applied here).  A full ring overwrites its oldest token. */
+int32_t skn_kv_append(skn_kvcache *kv, const float *k_new_host, const float *v_new_host);
+int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *v_new_dev);
+/* Copy tokens [pos_begin, pos_begin+count) of sequence b, oldest first, to dense host arrays
+ * [n_kv_heads][count][head_dim]. */
+int32_t skn_kv_gather(skn_kvcache *kv, int32_t b, int32_t pos_begin, int32_t count, float *k_out_host,
+                      float *v_out_host);
+/* geometry and device pointers of the cache (any out pointer may be NULL) */
+int32_t skn_kv_info(const skn_kvcache *kv, int32_t *batch, int32_t *n_kv_heads, int32_t *head_dim,
+                    int32_t *capacity, void **k_dev, void **v_dev, void **len_dev, void **start_dev);
+
+/* out[b][h][:] = softmax(q[b][h] . K^T * scale) . V over the cached tokens of sequence b, with
+ * query head h reading kv head h / (n_q_heads / n_kv_heads); q and out are
+ * [batch][n_q_heads][head_dim] fp32.  A sequence without tokens gives zeros.  n_q_heads must
+ * be 1, 2, 4 or 8 times n_kv_heads ("Shapes do not align." otherwise).
+ * The device form needs skn_attn_scratch_bytes() bytes of device scratch for the partial
+ * results of its sequence splits: pass a buffer, or NULL to let the context allocate one. */
+int32_t skn_attn_decode(skn_kvcache *kv, const float *q_host, int32_t n_q_heads, float scale, float *out_host);
+int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, float scale, float *out_dev,
+                            void *scratch_dev);
+/* bytes of scratch skn_attn_decode_dev needs for this cache and head count (-1 on bad arguments) */
+int64_t skn_attn_scratch_bytes(const skn_kvcache *kv, int32_t n_q_heads);
+
 #ifdef __cplusplus
 }
 #endif

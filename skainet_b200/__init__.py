@@ -3,8 +3,8 @@
 The product is ``libskainet_cuda.so`` (C ABI in ``include/skainet_cuda.h``); this package
 is the Python host-side mirror of the reference's tensor / module interface over that ABI.
 """
-from .tensor import (Context, GGML_QUANT_SIZES, GGMLQuantizationType, QK_K, QuantLinear, QuantTensor, Shape,
+from .tensor import (Context, KVCache, GGML_QUANT_SIZES, GGMLQuantizationType, QK_K, QuantLinear, QuantTensor, Shape,
                      SknError, quant_shape_to_byte_shape)
 
-__all__ = ["Context", "GGML_QUANT_SIZES", "GGMLQuantizationType", "QK_K", "QuantLinear", "QuantTensor", "Shape",
+__all__ = ["Context", "KVCache", "GGML_QUANT_SIZES", "GGMLQuantizationType", "QK_K", "QuantLinear", "QuantTensor", "Shape",
            "SknError", "quant_shape_to_byte_shape"]

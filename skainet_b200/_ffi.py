@@ -36,6 +36,18 @@ SIGNATURES = {
     "skn_dequantize_dev": (c_i32, [c_vp, c_vp, c_vp]),
     "skn_matmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
     "skn_matmul_dev": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
+    "skn_kv_create": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, P(c_vp)]),
+    "skn_kv_destroy": (c_i32, [c_vp]),
+    "skn_kv_reset": (c_i32, [c_vp]),
+    "skn_kv_load": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp]),
+    "skn_kv_lengths": (c_i32, [c_vp, c_vp, c_vp]),
+    "skn_kv_append": (c_i32, [c_vp, c_vp, c_vp]),
+    "skn_kv_append_dev": (c_i32, [c_vp, c_vp, c_vp]),
+    "skn_kv_gather": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
+    "skn_kv_info": (c_i32, [c_vp, P(c_i32), P(c_i32), P(c_i32), P(c_i32), P(c_vp), P(c_vp), P(c_vp), P(c_vp)]),
+    "skn_attn_decode": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
+    "skn_attn_decode_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp, c_vp]),
+    "skn_attn_scratch_bytes": (c_i64, [c_vp, c_i32]),
 }
 
 _lib = None

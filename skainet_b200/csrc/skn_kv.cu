@@ -1,0 +1,581 @@
+// K5-K7: device-resident KV cache and decode attention.
+//
+// Layout (fp32, head-major ring):  K, V : [batch][n_kv_heads][capacity][head_dim].
+// Sequence b holds len[b] tokens; logical position p (0 = oldest) lives at ring slot
+// (start[b] + p) % capacity.  All tokens of one (sequence, kv head) are contiguous, so the
+// attention kernel streams them with fully coalesced 512-byte rows.
+//
+//  skn_kv_append_kernel   one CTA per sequence writes the new token of every kv head and then
+//                         advances len (or start, once the ring is full)
+//  skn_kv_gather_kernel   ring -> dense, oldest first (export / verification)
+//  skn_attn_split_kernel  grid (splits, kv heads, batch): one CTA attends G = Hq/Hkv query
+//                         heads to a chunk of 256 cached tokens.  Pass 1 reads K once and
+//                         leaves the chunk's scores in shared memory (lane = 4 head dims;
+//                         32 (token, head) partial dots are summed with one transposed
+//                         butterfly of 31 shuffles); pass 2 reads V once and accumulates
+//                         exp(s - max) * v with the probabilities broadcast from shared
+//                         memory.  Writes (max, sum, unnormalised output) per (head, split)
+//                         to scratch.
+//  skn_attn_merge_kernel  log-sum-exp merge of the splits -> out[b][h][:]
+//
+// HBM-bound: 2 * head_dim * 4 bytes per cached token per kv head, read exactly once.
+#include "skn_internal.cuh"
+
+#include <math.h>
+#include <new>
+
+struct skn_kvcache {
+    uint32_t magic;
+    skn_ctx *ctx;
+    int32_t batch, n_kv_heads, head_dim, capacity;
+    float *d_k, *d_v;
+    int32_t *d_len, *d_start;
+};
+
+constexpr int ATT_CHUNK = 256;   // cached tokens per CTA
+constexpr int ATT_WARPS = 4;
+
+static bool kv_ok(const skn_kvcache *kv) { return kv && kv->magic == SKN_MAGIC_KV && skn_ctx_ok(kv->ctx); }
+
+// ----------------------------------------------------------------------------------------
+__global__ void skn_kv_append_kernel(float *__restrict__ kc, float *__restrict__ vc, int32_t *__restrict__ len,
+                                     int32_t *__restrict__ start, const float *__restrict__ k_new,
+                                     const float *__restrict__ v_new, int Hkv, int D, int cap) {
+    const int b = blockIdx.x;
+    const int L = len[b], s0 = start[b];
+    const int slot = (L < cap) ? (s0 + L) % cap : s0;   // full ring: overwrite the oldest token
+    const int n4 = Hkv * D / 4;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const int h = (i * 4) / D, d = (i * 4) % D;
+        const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t src = ((size_t)b * Hkv + h) * D + d;
+        *reinterpret_cast<float4 *>(kc + dst) = *reinterpret_cast<const float4 *>(k_new + src);
+        *reinterpret_cast<float4 *>(vc + dst) = *reinterpret_cast<const float4 *>(v_new + src);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (L < cap) len[b] = L + 1;
+        else start[b] = (s0 + 1) % cap;
+    }
+}
+
+__global__ void skn_kv_gather_kernel(const float *__restrict__ kc, const float *__restrict__ vc,
+                                     const int32_t *__restrict__ start, int b, int Hkv, int D, int cap, int pos0,
+                                     int count, float *__restrict__ k_out, float *__restrict__ v_out) {
+    // out: [Hkv][count][D]
+    const int s0 = start[b];
+    const int d4 = D / 4;
+    const int64_t total = (int64_t)Hkv * count * d4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int d = (int)(i % d4) * 4;
+        const int p = (int)((i / d4) % count);
+        const int h = (int)(i / ((int64_t)d4 * count));
+        const int slot = (s0 + pos0 + p) % cap;
+        const size_t src = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t dst = ((size_t)h * count + p) * D + d;
+        *reinterpret_cast<float4 *>(k_out + dst) = *reinterpret_cast<const float4 *>(kc + src);
+        *reinterpret_cast<float4 *>(v_out + dst) = *reinterpret_cast<const float4 *>(vc + src);
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// Sum NV per-lane values across the warp.  NV is a power of two <= 32.  On return every lane
+// holds the total of value index (lane >> log2(32 / NV)).
+template <int NV>
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[NV], int lane) {
+    if constexpr (NV >= 32) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float send = (lane & 16) ? v[k] : v[k + 16];
+            const float keep = (lane & 16) ? v[k + 16] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+    }
+    constexpr int N16 = NV >= 32 ? 16 : NV;
+    constexpr int O16 = NV >= 32 ? 8 : 16;   // xor offset that splits N16 values
+    if constexpr (N16 >= 16) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float send = (lane & O16) ? v[k] : v[k + 8];
+            const float keep = (lane & O16) ? v[k + 8] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, O16);
+        }
+    }
+    constexpr int N8 = N16 >= 16 ? 8 : N16;
+    constexpr int O8 = N16 >= 16 ? O16 / 2 : 16;
+    if constexpr (N8 >= 8) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float send = (lane & O8) ? v[k] : v[k + 4];
+            const float keep = (lane & O8) ? v[k + 4] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, O8);
+        }
+    }
+    constexpr int N4 = N8 >= 8 ? 4 : N8;
+    constexpr int O4 = N8 >= 8 ? O8 / 2 : 16;
+    if constexpr (N4 >= 4) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float send = (lane & O4) ? v[k] : v[k + 2];
+            const float keep = (lane & O4) ? v[k + 2] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, O4);
+        }
+    }
+    constexpr int N2 = N4 >= 4 ? 2 : N4;
+    constexpr int O2 = N4 >= 4 ? O4 / 2 : 16;
+    if constexpr (N2 >= 2) {
+        const float send = (lane & O2) ? v[0] : v[1];
+        const float keep = (lane & O2) ? v[1] : v[0];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, O2);
+    }
+    constexpr int OR = N2 >= 2 ? O2 / 2 : 16;   // remaining plain butterfly steps
+    float r = v[0];
+#pragma unroll
+    for (int o = OR; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+template <int VEC> struct VecLoad;
+template <> struct VecLoad<4> {
+    static __device__ __forceinline__ void ld(const float *p, float (&r)[4]) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    }
+};
+template <> struct VecLoad<2> {
+    static __device__ __forceinline__ void ld(const float *p, float (&r)[2]) {
+        const float2 v = __ldg(reinterpret_cast<const float2 *>(p));
+        r[0] = v.x; r[1] = v.y;
+    }
+};
+
+// D: head dim (64 or 128); G: query heads per kv head; TT: tokens per warp tile (TT*G <= 32)
+template <int D, int G, int TT>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
+                      const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
+                      float scale, float *__restrict__ part, int S) {
+    constexpr int VEC = D / 32;
+    constexpr int NV = TT * G;
+    constexpr int REP = 32 / NV;                 // lanes holding the same (token, head) score
+    constexpr int TILES = ATT_CHUNK / (ATT_WARPS * TT);
+    __shared__ float s_sc[ATT_CHUNK][G];         // scores, then probabilities
+    __shared__ float s_red[ATT_WARPS][G];
+    __shared__ float s_m[G], s_l[G];
+    __shared__ float s_o[ATT_WARPS][G][D];
+
+    const int sp = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int L = len[b];
+    const int t0 = sp * ATT_CHUNK;
+    if (t0 >= L) return;
+    const int nt = min(ATT_CHUNK, L - t0);
+    const int s0 = start[b];
+    const int Hq = Hkv * G;
+    const float *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
+    const float *vbase = vc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
+
+    float qv[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        VecLoad<VEC>::ld(q + ((size_t)b * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qv[g][e] *= scale;
+    }
+
+    // ---- pass 1: scores ------------------------------------------------------------------
+    float mrun = -INFINITY;   // this lane's head only (head = value index % G)
+    const int vidx = lane / REP;          // value index held after the transposed reduce
+    const int my_j = vidx / G, my_g = vidx % G;
+#pragma unroll 2
+    for (int ti = 0; ti < TILES; ++ti) {
+        const int tl = (ti * ATT_WARPS + warp) * TT;      // first token of the tile within the chunk
+        if (tl >= nt) break;
+        float kr[TT][VEC];
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+            const int t = min(tl + j, nt - 1);            // clamp: the extra scores are discarded
+            const int slot = (s0 + t0 + t) % cap;
+            VecLoad<VEC>::ld(kbase + (size_t)slot * D, kr[j]);
+        }
+        float pv[NV];
+#pragma unroll
+        for (int j = 0; j < TT; ++j)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a = 0.f;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) a = fmaf(qv[g][e], kr[j][e], a);
+                pv[j * G + g] = a;
+            }
+        const float sc = warp_transpose_reduce<NV>(pv, lane);
+        const bool valid = tl + my_j < nt;
+        if (valid) {
+            if ((lane % REP) == 0) s_sc[tl + my_j][my_g] = sc;
+            mrun = fmaxf(mrun, sc);
+        }
+    }
+    // max over the lanes that hold the same head: lane bits above log2(REP * G)
+#pragma unroll
+    for (int o = 16; o >= REP * G; o >>= 1) mrun = fmaxf(mrun, __shfl_xor_sync(0xffffffffu, mrun, o));
+    if (lane < REP * G && (lane % REP) == 0) s_red[warp][lane / REP] = mrun;
+    __syncthreads();
+    if (threadIdx.x < G) {
+        float m = s_red[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; ++w) m = fmaxf(m, s_red[w][threadIdx.x]);
+        s_m[threadIdx.x] = m;
+    }
+    __syncthreads();
+    // probabilities in place + their sums
+    float lsum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) lsum[g] = 0.f;
+    for (int t = threadIdx.x; t < nt; t += ATT_WARPS * 32) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float p = expf(s_sc[t][g] - s_m[g]);
+            s_sc[t][g] = p;
+            lsum[g] += p;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum[g] += __shfl_xor_sync(0xffffffffu, lsum[g], o);
+    }
+    __syncthreads();            // s_red is reused
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) s_red[warp][g] = lsum[g];
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) l += s_red[w][threadIdx.x];
+        s_l[threadIdx.x] = l;
+    }
+
+    // ---- pass 2: probabilities x V ---------------------------------------------------------
+    float o[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[g][e] = 0.f;
+#pragma unroll 2
+    for (int ti = 0; ti < TILES; ++ti) {
+        const int tl = (ti * ATT_WARPS + warp) * TT;
+        if (tl >= nt) break;
+        float vr[TT][VEC];
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+            const int t = min(tl + j, nt - 1);
+            const int slot = (s0 + t0 + t) % cap;
+            VecLoad<VEC>::ld(vbase + (size_t)slot * D, vr[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+            if (tl + j < nt) {
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float p = s_sc[tl + j][g];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) o[g][e] = fmaf(p, vr[j][e], o[g][e]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s_o[warp][g][lane * VEC + e] = o[g][e];
+    __syncthreads();
+    // partial record per (head, split): [0] = max, [1] = sum, [2 .. 2+D) = unnormalised output
+    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) {
+        const int g = i / D, d = i % D;
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) a += s_o[w][g][d];
+        float *rec = part + (((size_t)b * Hq + kvh * G + g) * S + sp) * (D + 2);
+        rec[2 + d] = a;
+        if (d == 0) { rec[0] = s_m[g]; rec[1] = s_l[g]; }
+    }
+}
+
+template <int D>
+__global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
+                                      float *__restrict__ out) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int L = len[b];
+    const int ns = (L + ATT_CHUNK - 1) / ATT_CHUNK;
+    const float *rec = part + ((size_t)b * Hq + h) * S * (D + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < ns; ++s) m = fmaxf(m, rec[(size_t)s * (D + 2)]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float l = 0.f, a = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float w = expf(rec[(size_t)s * (D + 2)] - m);
+            l = fmaf(rec[(size_t)s * (D + 2) + 1], w, l);
+            a = fmaf(rec[(size_t)s * (D + 2) + 2 + d], w, a);
+        }
+        out[((size_t)b * Hq + h) * D + d] = ns > 0 ? a / l : 0.f;
+    }
+}
+
+template <int D, int G>
+static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scale, float *part, int S, float *out,
+                               cudaStream_t stream) {
+    constexpr int TT = (G >= 8) ? 4 : 8;
+    const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)kv->batch);
+    skn_attn_split_kernel<D, G, TT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+                                                                        kv->n_kv_heads, kv->capacity, scale, part, S);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)kv->batch);
+    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out);
+    return cudaGetLastError();
+}
+
+static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int S,
+                                 float *out, cudaStream_t st) {
+    if (kv->head_dim == 128) {
+        switch (G) {
+        case 1: return launch_attn<128, 1>(kv, q, scale, part, S, out, st);
+        case 2: return launch_attn<128, 2>(kv, q, scale, part, S, out, st);
+        case 4: return launch_attn<128, 4>(kv, q, scale, part, S, out, st);
+        case 8: return launch_attn<128, 8>(kv, q, scale, part, S, out, st);
+        }
+    } else if (kv->head_dim == 64) {
+        switch (G) {
+        case 1: return launch_attn<64, 1>(kv, q, scale, part, S, out, st);
+        case 2: return launch_attn<64, 2>(kv, q, scale, part, S, out, st);
+        case 4: return launch_attn<64, 4>(kv, q, scale, part, S, out, st);
+        case 8: return launch_attn<64, 8>(kv, q, scale, part, S, out, st);
+        }
+    }
+    return cudaErrorInvalidValue;
+}
+
+// ----------------------------------------------------------------------------------------
+extern "C" {
+
+int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
+                      skn_kvcache **out) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    if (batch < 1 || n_kv_heads < 1 || capacity < 1) return skn_fail(ctx, SKN_ERR_ARG, "batch, heads and capacity must be positive");
+    if (head_dim != 64 && head_dim != 128) return skn_fail(ctx, SKN_ERR_SHAPE, "head_dim must be 64 or 128 (got %d)", head_dim);
+    skn_kvcache *kv = new (std::nothrow) skn_kvcache();
+    if (!kv) return skn_fail(ctx, SKN_ERR_OOM, "host allocation failed");
+    memset(kv, 0, sizeof(*kv));
+    kv->magic = SKN_MAGIC_KV;
+    kv->ctx = ctx;
+    kv->batch = batch; kv->n_kv_heads = n_kv_heads; kv->head_dim = head_dim; kv->capacity = capacity;
+    const size_t n = (size_t)batch * n_kv_heads * capacity * head_dim * sizeof(float);
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_k, n);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_v, n);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_len, 2 * sizeof(int32_t) * batch);
+    if (e == cudaSuccess) {
+        kv->d_start = kv->d_len + batch;
+        e = cudaMemsetAsync(kv->d_len, 0, 2 * sizeof(int32_t) * batch, ctx->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        if (kv->d_k) cudaFree(kv->d_k);
+        if (kv->d_v) cudaFree(kv->d_v);
+        if (kv->d_len) cudaFree(kv->d_len);
+        kv->magic = 0;
+        delete kv;
+        return skn_check_cuda(ctx, e, "kv cache allocation");
+    }
+    *out = kv;
+    return SKN_OK;
+}
+
+int32_t skn_kv_destroy(skn_kvcache *kv) {
+    if (!kv || kv->magic != SKN_MAGIC_KV) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    if (skn_ctx_ok(kv->ctx)) {
+        cudaSetDevice(kv->ctx->device);
+        cudaStreamSynchronize(kv->ctx->stream);
+    }
+    cudaFree(kv->d_k);
+    cudaFree(kv->d_v);
+    cudaFree(kv->d_len);
+    kv->magic = 0;
+    delete kv;
+    return SKN_OK;
+}
+
+int32_t skn_kv_reset(skn_kvcache *kv) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SKN_CUDA(ctx, cudaMemsetAsync(kv->d_len, 0, 2 * sizeof(int32_t) * kv->batch, ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, int32_t tokens,
+                    const int32_t *lens_host) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (tokens < 0 || tokens > kv->capacity) return skn_fail(ctx, SKN_ERR_SHAPE, "tokens (%d) exceeds the capacity (%d)", tokens, kv->capacity);
+    if (!lens_host || (tokens > 0 && (!k_host || !v_host))) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    for (int b = 0; b < kv->batch; ++b)
+        if (lens_host[b] < 0 || lens_host[b] > tokens)
+            return skn_fail(ctx, SKN_ERR_SHAPE, "lens[%d] = %d outside [0, %d]", b, lens_host[b], tokens);
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t row = (size_t)tokens * kv->head_dim * sizeof(float);
+    const size_t pitch = (size_t)kv->capacity * kv->head_dim * sizeof(float);
+    const size_t nrows = (size_t)kv->batch * kv->n_kv_heads;
+    if (tokens > 0) {
+        SKN_CUDA(ctx, cudaMemcpy2DAsync(kv->d_k, pitch, k_host, row, row, nrows, cudaMemcpyHostToDevice, ctx->stream));
+        SKN_CUDA(ctx, cudaMemcpy2DAsync(kv->d_v, pitch, v_host, row, row, nrows, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    SKN_CUDA(ctx, cudaMemcpyAsync(kv->d_len, lens_host, sizeof(int32_t) * kv->batch, cudaMemcpyHostToDevice, ctx->stream));
+    SKN_CUDA(ctx, cudaMemsetAsync(kv->d_start, 0, sizeof(int32_t) * kv->batch, ctx->stream));
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_kv_lengths(skn_kvcache *kv, int32_t *lens_host, int32_t *start_host) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (lens_host) SKN_CUDA(ctx, cudaMemcpy(lens_host, kv->d_len, sizeof(int32_t) * kv->batch, cudaMemcpyDeviceToHost));
+    if (start_host) SKN_CUDA(ctx, cudaMemcpy(start_host, kv->d_start, sizeof(int32_t) * kv->batch, cudaMemcpyDeviceToHost));
+    return SKN_OK;
+}
+
+int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *v_new_dev) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    if ((((uintptr_t)k_new_dev) | ((uintptr_t)v_new_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "k/v must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    skn_kv_append_kernel<<<kv->batch, 256, 0, ctx->stream>>>(kv->d_k, kv->d_v, kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+                                                             kv->n_kv_heads, kv->head_dim, kv->capacity);
+    SKN_CUDA(ctx, cudaGetLastError());
+    return SKN_OK;
+}
+
+int32_t skn_kv_append(skn_kvcache *kv, const float *k_new_host, const float *v_new_host) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (!k_new_host || !v_new_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    const size_t n = (size_t)kv->batch * kv->n_kv_heads * kv->head_dim * sizeof(float);
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, 2 * n);
+    if (rc) return rc;
+    float *dk = (float *)ctx->d_stage_in, *dv = (float *)((uint8_t *)ctx->d_stage_in + n);
+    SKN_CUDA(ctx, cudaMemcpyAsync(dk, k_new_host, n, cudaMemcpyHostToDevice, ctx->stream));
+    SKN_CUDA(ctx, cudaMemcpyAsync(dv, v_new_host, n, cudaMemcpyHostToDevice, ctx->stream));
+    rc = skn_kv_append_dev(kv, dk, dv);
+    if (rc) return rc;
+    return skn_sync(ctx);
+}
+
+int32_t skn_kv_gather(skn_kvcache *kv, int32_t b, int32_t pos_begin, int32_t count, float *k_out_host,
+                      float *v_out_host) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (b < 0 || b >= kv->batch) return skn_fail(ctx, SKN_ERR_ARG, "sequence index out of range");
+    if (pos_begin < 0 || count < 0) return skn_fail(ctx, SKN_ERR_ARG, "negative range");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t L = 0;
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    SKN_CUDA(ctx, cudaMemcpy(&L, kv->d_len + b, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (pos_begin + count > L) return skn_fail(ctx, SKN_ERR_SHAPE, "range [%d, %d) outside the %d cached tokens", pos_begin, pos_begin + count, L);
+    if (count == 0) return SKN_OK;
+    if (!k_out_host || !v_out_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL output");
+    const size_t n = (size_t)kv->n_kv_heads * count * kv->head_dim * sizeof(float);
+    int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, 2 * n);
+    if (rc) return rc;
+    float *dk = (float *)ctx->d_stage_out, *dv = (float *)((uint8_t *)ctx->d_stage_out + n);
+    const int64_t total = (int64_t)kv->n_kv_heads * count * kv->head_dim / 4;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+    skn_kv_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(kv->d_k, kv->d_v, kv->d_start, b, kv->n_kv_heads, kv->head_dim,
+                                                          kv->capacity, pos_begin, count, dk, dv);
+    SKN_CUDA(ctx, cudaGetLastError());
+    SKN_CUDA(ctx, cudaMemcpyAsync(k_out_host, dk, n, cudaMemcpyDeviceToHost, ctx->stream));
+    SKN_CUDA(ctx, cudaMemcpyAsync(v_out_host, dv, n, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
+}
+
+int64_t skn_attn_scratch_bytes(const skn_kvcache *kv, int32_t n_q_heads) {
+    if (!kv_ok(kv) || n_q_heads < 1) return -1;
+    const int64_t S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    return (int64_t)kv->batch * n_q_heads * S * (kv->head_dim + 2) * (int64_t)sizeof(float);
+}
+
+static int32_t attn_check(skn_kvcache *kv, int32_t n_q_heads, const void *q, const void *out, int *G) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (!q || !out) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    if (n_q_heads < 1 || n_q_heads % kv->n_kv_heads) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    *G = n_q_heads / kv->n_kv_heads;
+    if (*G != 1 && *G != 2 && *G != 4 && *G != 8)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "query heads per kv head must be 1, 2, 4 or 8 (got %d)", *G);
+    return SKN_OK;
+}
+
+// scratch_dev: at least skn_attn_scratch_bytes() bytes of device memory, or NULL to use the
+// context's own scratch allocation (grown on demand)
+int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, float scale, float *out_dev,
+                            void *scratch_dev) {
+    int G = 0;
+    int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
+    if (rc) return rc;
+    skn_ctx *ctx = kv->ctx;
+    if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
+        return skn_fail(ctx, SKN_ERR_ALIGN, "q, out and scratch must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    float *part = (float *)scratch_dev;
+    if (!part) {
+        rc = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads));
+        if (rc) return rc;
+        part = (float *)ctx->d_scratch;
+    }
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_attn_decode(skn_kvcache *kv, const float *q_host, int32_t n_q_heads, float scale, float *out_host) {
+    int G = 0;
+    int32_t rc = attn_check(kv, n_q_heads, q_host, out_host, &G);
+    if (rc) return rc;
+    skn_ctx *ctx = kv->ctx;
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t n = (size_t)kv->batch * n_q_heads * kv->head_dim * sizeof(float);
+    rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, n);
+    if (rc) return rc;
+    rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, n);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, q_host, n, cudaMemcpyHostToDevice, ctx->stream));
+    rc = skn_attn_decode_dev(kv, (const float *)ctx->d_stage_in, n_q_heads, scale, (float *)ctx->d_stage_out, nullptr);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(out_host, ctx->d_stage_out, n, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
+}
+
+// device pointers of the cache (for callers that fill it with their own kernels)
+int32_t skn_kv_info(const skn_kvcache *kv, int32_t *batch, int32_t *n_kv_heads, int32_t *head_dim, int32_t *capacity,
+                    void **k_dev, void **v_dev, void **len_dev, void **start_dev) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    if (batch) *batch = kv->batch;
+    if (n_kv_heads) *n_kv_heads = kv->n_kv_heads;
+    if (head_dim) *head_dim = kv->head_dim;
+    if (capacity) *capacity = kv->capacity;
+    if (k_dev) *k_dev = kv->d_k;
+    if (v_dev) *v_dev = kv->d_v;
+    if (len_dev) *len_dev = kv->d_len;
+    if (start_dev) *start_dev = kv->d_start;
+    return SKN_OK;
+}
+
+}  // extern "C"

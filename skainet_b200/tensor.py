@@ -261,3 +261,86 @@ class QuantLinear:
         return self.weight.matmul_t(x, self.bias)
 
     __call__ = forward
+
+
+class KVCache:
+    """Device-resident fp32 KV cache (head-major ring) with decode attention."""
+
+    def __init__(self, ctx: Context, batch: int, n_kv_heads: int, head_dim: int, capacity: int):
+        self.ctx = ctx
+        self.batch, self.n_kv_heads, self.head_dim, self.capacity = batch, n_kv_heads, head_dim, capacity
+        self._h = ctypes.c_void_p()
+        rc = _ffi.lib().skn_kv_create(ctx.handle, batch, n_kv_heads, head_dim, capacity, ctypes.byref(self._h))
+        if rc != SKN_OK:
+            self._h = ctypes.c_void_p()
+            _raise(ctx.handle, rc)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def reset(self):
+        _check(self.ctx.handle, _ffi.lib().skn_kv_reset(self._h))
+
+    def load(self, k: np.ndarray, v: np.ndarray, lens):
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        lens = np.ascontiguousarray(lens, dtype=np.int32)
+        if k.shape != v.shape or k.ndim != 4 or k.shape[0] != self.batch or k.shape[1] != self.n_kv_heads \
+                or k.shape[3] != self.head_dim or lens.shape != (self.batch,):
+            raise ValueError("Shapes do not align.")
+        _check(self.ctx.handle, _ffi.lib().skn_kv_load(self._h, k.ctypes.data, v.ctypes.data, k.shape[2],
+                                                      lens.ctypes.data))
+
+    def lengths(self):
+        lens = np.empty(self.batch, dtype=np.int32)
+        start = np.empty(self.batch, dtype=np.int32)
+        _check(self.ctx.handle, _ffi.lib().skn_kv_lengths(self._h, lens.ctypes.data, start.ctypes.data))
+        return lens, start
+
+    def append(self, k_new: np.ndarray, v_new: np.ndarray):
+        k_new = np.ascontiguousarray(k_new, dtype=np.float32)
+        v_new = np.ascontiguousarray(v_new, dtype=np.float32)
+        if k_new.shape != (self.batch, self.n_kv_heads, self.head_dim) or v_new.shape != k_new.shape:
+            raise ValueError("Shapes do not align.")
+        _check(self.ctx.handle, _ffi.lib().skn_kv_append(self._h, k_new.ctypes.data, v_new.ctypes.data))
+
+    def append_dev(self, k_new_dev, v_new_dev):
+        _check(self.ctx.handle, _ffi.lib().skn_kv_append_dev(self._h, _ptr(k_new_dev), _ptr(v_new_dev)))
+
+    def gather(self, b: int, pos_begin: int, count: int):
+        k = np.empty((self.n_kv_heads, count, self.head_dim), dtype=np.float32)
+        v = np.empty_like(k)
+        _check(self.ctx.handle, _ffi.lib().skn_kv_gather(self._h, b, pos_begin, count, k.ctypes.data, v.ctypes.data))
+        return k, v
+
+    def attend(self, q: np.ndarray, scale: Optional[float] = None) -> np.ndarray:
+        """q [batch, n_q_heads, head_dim] on the host -> attention output of the same shape."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        if q.ndim != 3 or q.shape[0] != self.batch or q.shape[2] != self.head_dim:
+            raise ValueError("Shapes do not align.")
+        if scale is None:
+            scale = 1.0 / float(np.sqrt(self.head_dim))
+        out = np.empty_like(q)
+        _check(self.ctx.handle, _ffi.lib().skn_attn_decode(self._h, q.ctypes.data, q.shape[1], scale, out.ctypes.data))
+        return out
+
+    def attend_dev(self, q_dev, n_q_heads: int, out_dev, scale: Optional[float] = None, scratch_dev=None):
+        if scale is None:
+            scale = 1.0 / float(np.sqrt(self.head_dim))
+        _check(self.ctx.handle, _ffi.lib().skn_attn_decode_dev(self._h, _ptr(q_dev), n_q_heads, scale, _ptr(out_dev),
+                                                              _ptr(scratch_dev)))
+
+    def scratch_bytes(self, n_q_heads: int) -> int:
+        return int(_ffi.lib().skn_attn_scratch_bytes(self._h, n_q_heads))
+
+    def close(self):
+        if self._h:
+            _ffi.lib().skn_kv_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
