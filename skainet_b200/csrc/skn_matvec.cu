@@ -137,6 +137,82 @@ __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane)
     return c;
 }
 
+// CTA-cooperative preparation of x for the 4-bit decoders: K activations from global memory ->
+// per group of 64: 32 packed pairs (pre-scaled by 2^(S - nibble position)), the two 32-element
+// sums and the factor 2^(149 - S).  kpad (a multiple of 2048) is the padded length; columns
+// >= K are written as zeros.  A float4 of x is always the four bytes k = 0..3 of one quant
+// word, low-nibble (h = 0) or high-nibble (h = 1) half:
+//   Q4_K  (Q40 = false): group = sub-block pair; float4 f -> h = (f>>3)&1, word = f&7
+//   Q4_0  (Q40 = true) : group = two blocks;     float4 f -> block = (f>>3)&1, h = (f>>2)&1, word = f&3
+// The pair of word-pair j, nibble position n = 2k+h is {x[word 2j], x[word 2j+1]} and sits in
+// 16-byte slot j*4 + k (rotated by the group index, see load_x), float 2h + (word & 1).
+template <bool Q40>
+static __device__ __forceinline__ void skn_prep_nibble_groups(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+    float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
+    float *gun = gsum + kpad / 32;
+    const int nf = kpad / 4;
+    const int lane = threadIdx.x & 31;
+    constexpr int B = 4;   // float4 loads in flight per thread
+    for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
+        float4 v[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const int f = f0 + b * blockDim.x + threadIdx.x;
+            v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const int f = f0 + b * blockDim.x + threadIdx.x;   // 16 consecutive f = one group
+            float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+            float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+            int S = 217 - (int)(__float_as_uint(mx) >> 23);
+            S = S > 120 ? 120 : (S < 23 ? 23 : S);
+            if (f < nf) {
+                const int G = f >> 4;
+                const int half8 = (f >> 3) & 1;         // which 32-element sum this float4 belongs to
+                int h, j, comp;
+                if (Q40) {
+                    const int q = f & 3;
+                    h = (f >> 2) & 1;
+                    j = 2 * half8 + (q >> 1);
+                    comp = q & 1;
+                } else {
+                    const int wi = f & 7;
+                    h = half8;
+                    j = wi >> 1;
+                    comp = wi & 1;
+                }
+                const int ph = 4 * h;
+                float *g32 = reinterpret_cast<float *>(xs + (size_t)G * 256);
+                g32[((j * 4 + 0 + G) & 15) * 4 + 2 * h + comp] = v[b].x * skn_pow2f(S - ph);
+                g32[((j * 4 + 1 + G) & 15) * 4 + 2 * h + comp] = v[b].y * skn_pow2f(S - 8 - ph);
+                g32[((j * 4 + 2 + G) & 15) * 4 + 2 * h + comp] = v[b].z * skn_pow2f(S - 16 - ph);
+                g32[((j * 4 + 3 + G) & 15) * 4 + 2 * h + comp] = v[b].w * skn_pow2f(S - 16 - ph);
+                if ((lane & 7) == 0) gsum[2 * G + half8] = sm;
+                if ((lane & 15) == 0) gun[G] = skn_pow2f(149 - S);
+            }
+        }
+    }
+}
+
+// eight packed FMAs of one 64-bit pair of quant words against the eight nibble positions
+#define SKN_NIBBLE_PAIR_FMA(P, X, A0, A1, A2, A3)                                         \
+    do {                                                                                  \
+        const uint64_t P8__ = (P) >> 8;                                                    \
+        A0 = skn_fma2((P) & 0x0000000F0000000Full, (X)[0], A0);                            \
+        A1 = skn_fma2((P) & 0x000000F0000000F0ull, (X)[1], A1);                            \
+        A2 = skn_fma2((P) & 0x00000F0000000F00ull, (X)[2], A2);                            \
+        A3 = skn_fma2((P) & 0x0000F0000000F000ull, (X)[3], A3);                            \
+        A0 = skn_fma2((P) & 0x000F0000000F0000ull, (X)[4], A0);                            \
+        A1 = skn_fma2((P) & 0x00F0000000F00000ull, (X)[5], A1);                            \
+        A2 = skn_fma2(P8__ & 0x000F0000000F0000ull, (X)[6], A2);                           \
+        A3 = skn_fma2(P8__ & 0x00F0000000F00000ull, (X)[7], A3);                           \
+    } while (0)
+
 // ---- Q4_K ------------------------------------------------------------------------------
 // chunk = 8 super-blocks (2048 weights, 1152 bytes); lane = (block cb = lane/4, pair p =
 // lane%4): the 32 quant bytes whose low nibbles are sub-block 2p and high nibbles
@@ -175,49 +251,8 @@ struct Q4KStream {
     uint32_t sel, m_low, m_top, m_nib;   // per-lane constants of the scale decode
     bool active;
 
-    // CTA-cooperative: K activations from global -> prepared form in shared memory.
-    // kpad (a multiple of 2048) is the padded length; columns >= K are written as zeros.
     static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
-        float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
-        float *gun = gsum + kpad / 32;
-        const int nf = kpad / 4;
-        const int lane = threadIdx.x & 31;
-        constexpr int B = 4;   // float4 loads in flight per thread
-        for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
-            float4 v[B];
-#pragma unroll
-            for (int b = 0; b < B; ++b) {
-                const int f = f0 + b * blockDim.x + threadIdx.x;
-                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int b = 0; b < B; ++b) {
-                const int f = f0 + b * blockDim.x + threadIdx.x;   // 16 consecutive f = one group
-                float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
-                float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-#pragma unroll
-                for (int o = 4; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
-                int S = 217 - (int)(__float_as_uint(mx) >> 23);
-                S = S > 120 ? 120 : (S < 23 ? 23 : S);
-                if (f < nf) {
-                    const int G = f >> 4;
-                    const int h = (f >> 3) & 1;             // 0: low-nibble half, 1: high-nibble half
-                    const int wi = f & 7;                   // quant word; v.x..v.w are its bytes 0..3
-                    const int j = wi >> 1, comp = wi & 1;
-                    const int ph = 4 * h;
-                    float *g32 = reinterpret_cast<float *>(xs + (size_t)G * 256);
-                    // byte k -> pair j*8 + 2k + h -> 16-byte slot j*4 + k, float 2h + comp
-                    g32[((j * 4 + 0 + G) & 15) * 4 + 2 * h + comp] = v[b].x * skn_pow2f(S - ph);
-                    g32[((j * 4 + 1 + G) & 15) * 4 + 2 * h + comp] = v[b].y * skn_pow2f(S - 8 - ph);
-                    g32[((j * 4 + 2 + G) & 15) * 4 + 2 * h + comp] = v[b].z * skn_pow2f(S - 16 - ph);
-                    g32[((j * 4 + 3 + G) & 15) * 4 + 2 * h + comp] = v[b].w * skn_pow2f(S - 16 - ph);
-                    if ((lane & 7) == 0) gsum[2 * G + h] = sm;
-                    if ((lane & 15) == 0) gun[G] = skn_pow2f(149 - S);
-                }
-            }
-        }
+        skn_prep_nibble_groups<false>(x, K, kpad, xs);
     }
 
     __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
@@ -298,6 +333,197 @@ struct Q4KStream {
     }
 };
 
+// ---- Q4_0 ------------------------------------------------------------------------------
+// chunk = 64 blocks (2048 weights, 1152 bytes); lane = two adjacent 18-byte blocks = nine
+// aligned words [dA|q0 q1][q2..5][q6..9][q10..13][q14 q15|dB][B: q0..3] ... [B: q12..15].
+// Byte e of a block: low nibble = weight e, high nibble = weight e+16; value (n - 8) * d, so
+// a block contributes d * (sum n*x - 8 * sum x).
+struct Q40Stream {
+    static constexpr int CHUNK_BLOCKS = 64;
+    static constexpr int BLOCK_BYTES = 18;
+    static constexpr int BLOCK_WEIGHTS = 32;
+    static constexpr int CHUNK_BYTES = CHUNK_BLOCKS * BLOCK_BYTES;
+    static constexpr int CHUNK_WEIGHTS = CHUNK_BLOCKS * BLOCK_WEIGHTS;
+    static __host__ __device__ size_t xprep_bytes(int64_t kpad) { return (size_t)kpad * 4 + (size_t)kpad / 8 + (size_t)kpad / 16; }
+
+    struct Raw { uint32_t w[9]; };
+
+    uint64_t x2[32];
+    float sum_a, sum_b, unscale;
+    int off;
+    bool act_a, act_b;
+
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+        skn_prep_nibble_groups<true>(x, K, kpad, xs);
+    }
+
+    __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
+        off = lane * 2 * BLOCK_BYTES;
+        act_a = 2 * lane < nblocks_in_chunk;
+        act_b = 2 * lane + 1 < nblocks_in_chunk;
+        const int G = chunk * (CHUNK_BLOCKS / 2) + lane;
+        const ulonglong2 *g = reinterpret_cast<const ulonglong2 *>(xs + (size_t)G * 256);
+        const float *gsum = reinterpret_cast<const float *>(xs + (size_t)kpad * 4);
+        const float *gun = gsum + kpad / 32;
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            const ulonglong2 v = g[(s + G) & 15];
+            x2[2 * s] = v.x;
+            x2[2 * s + 1] = v.y;
+        }
+        sum_a = gsum[2 * G];
+        sum_b = gsum[2 * G + 1];
+        unscale = gun[G];
+    }
+
+    __device__ __forceinline__ Raw fetch(const uint8_t *sb) const {
+        Raw r;
+        const uint32_t *p = reinterpret_cast<const uint32_t *>(sb + off);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) r.w[i] = p[i];
+        return r;
+    }
+
+    __device__ __forceinline__ float dot(const Raw &r) const {
+        // block A's quant words straddle the aligned words by two bytes
+        const uint32_t a0 = __funnelshift_r(r.w[0], r.w[1], 16), a1 = __funnelshift_r(r.w[1], r.w[2], 16);
+        const uint32_t a2 = __funnelshift_r(r.w[2], r.w[3], 16), a3 = __funnelshift_r(r.w[3], r.w[4], 16);
+        const uint64_t pa0 = ((uint64_t)a1 << 32) | a0, pa1 = ((uint64_t)a3 << 32) | a2;
+        const uint64_t pb0 = ((uint64_t)r.w[6] << 32) | r.w[5], pb1 = ((uint64_t)r.w[8] << 32) | r.w[7];
+        uint64_t a_0 = 0ull, a_1 = 0ull, a_2 = 0ull, a_3 = 0ull, b_0 = 0ull, b_1 = 0ull, b_2 = 0ull, b_3 = 0ull;
+        SKN_NIBBLE_PAIR_FMA(pa0, x2 + 0, a_0, a_1, a_2, a_3);
+        SKN_NIBBLE_PAIR_FMA(pb0, x2 + 16, b_0, b_1, b_2, b_3);
+        SKN_NIBBLE_PAIR_FMA(pa1, x2 + 8, a_0, a_1, a_2, a_3);
+        SKN_NIBBLE_PAIR_FMA(pb1, x2 + 24, b_0, b_1, b_2, b_3);
+        float a_lo, a_hi, b_lo, b_hi;
+        skn_unpack2(skn_add2(skn_add2(a_0, a_1), skn_add2(a_2, a_3)), a_lo, a_hi);
+        skn_unpack2(skn_add2(skn_add2(b_0, b_1), skn_add2(b_2, b_3)), b_lo, b_hi);
+        const float da = skn_half_bits_to_float(r.w[0] & 0xFFFFu);
+        const float db = skn_half_bits_to_float(r.w[4] >> 16);
+        const float ra = da * fmaf(a_lo + a_hi, unscale, -8.f * sum_a);
+        const float rb = db * fmaf(b_lo + b_hi, unscale, -8.f * sum_b);
+        return (act_a ? ra : 0.f) + (act_b ? rb : 0.f);
+    }
+};
+
+// ---- Q8_0 ------------------------------------------------------------------------------
+// chunk = 32 blocks (1024 weights, 1088 bytes); lane = one 34-byte block, read as nine aligned
+// words and re-aligned with funnel shifts (blocks start on 2-byte boundaries).  A signed
+// byte b is used as the unsigned u = b ^ 0x80 = b + 128, so a block contributes
+// d * (sum u*x - 128 * sum x).  The two halves of a packed operand are the same byte position
+// of two adjacent quant words; byte 3 is taken from (pair >> 8).
+//
+// Shared x layout per group of 32 activations (one block): 16 packed pairs, pair j*4+k =
+// {x[8j + k], x[8j + 4 + k]} * 2^(S - pos(k)), pos = 0, 8, 16, 16; eight 16-byte slots rotated
+// by the group index; gsum[G] = plain sum, gun[G] = 2^(149 - S).
+struct Q80Stream {
+    static constexpr int CHUNK_BLOCKS = 32;
+    static constexpr int BLOCK_BYTES = 34;
+    static constexpr int BLOCK_WEIGHTS = 32;
+    static constexpr int CHUNK_BYTES = CHUNK_BLOCKS * BLOCK_BYTES;
+    static constexpr int CHUNK_WEIGHTS = CHUNK_BLOCKS * BLOCK_WEIGHTS;
+    static __host__ __device__ size_t xprep_bytes(int64_t kpad) { return (size_t)kpad * 4 + (size_t)kpad / 8 + (size_t)kpad / 8; }
+
+    struct Raw { uint32_t w[9]; };
+
+    uint64_t x2[16];
+    float sum, unscale;
+    int woff;       // byte offset of the aligned 36-byte window inside a staged chunk
+    int sh;         // 0 or 16: bit offset of the block inside the window
+    bool active;
+
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+        float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
+        float *gun = gsum + kpad / 32;
+        const int nf = kpad / 4;
+        const int lane = threadIdx.x & 31;
+        constexpr int B = 4;
+        for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
+            float4 v[B];
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;
+                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;   // 8 consecutive f = one group
+                float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+                float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) {
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                }
+                int S = 217 - (int)(__float_as_uint(mx) >> 23);
+                S = S > 120 ? 120 : (S < 23 ? 23 : S);
+                if (f < nf) {
+                    const int G = f >> 3;
+                    const int q = f & 7, j = q >> 1, comp = q & 1;
+                    float *g32 = reinterpret_cast<float *>(xs + (size_t)G * 128);
+                    // byte k -> pair j*4 + k -> 16-byte slot 2j + (k>>1), float 2*(k&1) + comp
+                    g32[((2 * j + 0 + G) & 7) * 4 + 0 + comp] = v[b].x * skn_pow2f(S);
+                    g32[((2 * j + 0 + G) & 7) * 4 + 2 + comp] = v[b].y * skn_pow2f(S - 8);
+                    g32[((2 * j + 1 + G) & 7) * 4 + 0 + comp] = v[b].z * skn_pow2f(S - 16);
+                    g32[((2 * j + 1 + G) & 7) * 4 + 2 + comp] = v[b].w * skn_pow2f(S - 16);
+                    if ((lane & 7) == 0) {
+                        gsum[G] = sm;
+                        gun[G] = skn_pow2f(149 - S);
+                    }
+                }
+            }
+        }
+    }
+
+    __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
+        const int boff = lane * BLOCK_BYTES;
+        woff = boff & ~3;
+        sh = (boff & 2) * 8;
+        active = lane < nblocks_in_chunk;
+        const int G = chunk * CHUNK_BLOCKS + lane;
+        const ulonglong2 *g = reinterpret_cast<const ulonglong2 *>(xs + (size_t)G * 128);
+        const float *gsum = reinterpret_cast<const float *>(xs + (size_t)kpad * 4);
+        const float *gun = gsum + kpad / 32;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const ulonglong2 v = g[(s + G) & 7];
+            x2[2 * s] = v.x;
+            x2[2 * s + 1] = v.y;
+        }
+        sum = gsum[G];
+        unscale = gun[G];
+    }
+
+    __device__ __forceinline__ Raw fetch(const uint8_t *sb) const {
+        Raw r;
+        const uint32_t *p = reinterpret_cast<const uint32_t *>(sb + woff);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) r.w[i] = p[i];
+        return r;
+    }
+
+    __device__ __forceinline__ float dot(const Raw &r) const {
+        uint32_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = __funnelshift_rc(r.w[i], r.w[i + 1], sh + 16);
+        uint64_t a0 = 0ull, a1 = 0ull, a2 = 0ull, a3 = 0ull;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint64_t P = (((uint64_t)q[2 * j + 1] << 32) | q[2 * j]) ^ 0x8080808080808080ull;
+            const uint64_t P8 = P >> 8;
+            a0 = skn_fma2(P & 0x000000FF000000FFull, x2[4 * j + 0], a0);
+            a1 = skn_fma2(P & 0x0000FF000000FF00ull, x2[4 * j + 1], a1);
+            a2 = skn_fma2(P & 0x00FF000000FF0000ull, x2[4 * j + 2], a2);
+            a3 = skn_fma2(P8 & 0x00FF000000FF0000ull, x2[4 * j + 3], a3);
+        }
+        float lo, hi;
+        skn_unpack2(skn_add2(skn_add2(a0, a1), skn_add2(a2, a3)), lo, hi);
+        const float d = skn_half_bits_to_float((r.w[0] >> sh) & 0xFFFFu);
+        const float res = d * fmaf(lo + hi, unscale, -128.f * sum);
+        return active ? res : 0.f;
+    }
+};
+
 // One kernel for every streaming decoder S.
 //   grid  : CTA b owns rows [b*N/grid, (b+1)*N/grid)
 //   block : nch * wg warps; warp w -> chunk c = w % nch, row slot g = w / nch
@@ -331,7 +557,9 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K
 
     int nbc = nb - c * S::CHUNK_BLOCKS;
     if (nbc > S::CHUNK_BLOCKS) nbc = S::CHUNK_BLOCKS;
-    const uint32_t bytes = (uint32_t)nbc * S::BLOCK_BYTES;
+    // a short last chunk may end off a 16-byte boundary: the copy runs a few bytes into the
+    // next row (or the slack after the last one); those bytes are never decoded
+    const uint32_t bytes = ((uint32_t)nbc * S::BLOCK_BYTES + 15u) & ~15u;
     const uint8_t *src0 = W + (row_begin + g) * pitch + (size_t)c * S::CHUNK_BYTES;
     const int64_t src_step = (int64_t)wg * pitch;
 
@@ -505,6 +733,8 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
     if (M == 1 && !force_generic && (w->pitch % 16) == 0) {
         cudaError_t err = cudaSuccess;
         if (w->type == SKN_TYPE_Q4_K && try_stream<Q4KStream>(ctx, w, x, bias, y, stream, err)) return err;
+        if (w->type == SKN_TYPE_Q4_0 && try_stream<Q40Stream>(ctx, w, x, bias, y, stream, err)) return err;
+        if (w->type == SKN_TYPE_Q8_0 && try_stream<Q80Stream>(ctx, w, x, bias, y, stream, err)) return err;
     }
     switch (w->type) {
     case SKN_TYPE_Q4_0: return launch_generic<SKN_TYPE_Q4_0>(w, x, M, bias, y, ctx->sm_count, stream);
