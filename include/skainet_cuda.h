@@ -185,6 +185,26 @@ int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
 /* bytes of scratch skn_attn_decode_dev needs for this cache and head count (-1 on bad arguments) */
 int64_t skn_attn_scratch_bytes(const skn_kvcache *kv, int32_t n_q_heads);
 
+/* skn_attn_decode_dev for callers that cannot allocate device memory when they call it (a
+ * server whose memory plan is frozen after start-up, code running where the CUDA allocator's
+ * implicit device synchronisation is not acceptable, an embedding runtime that passes a device
+ * but no allocator).  It has no counterpart in the reference.  Same inputs, outputs and
+ * results as skn_attn_decode_dev, but the split partials go to a 4 MiB array built into the
+ * library (held by every GPU that loads it, until the process exits) and the call performs
+ * no cudaMalloc / cudaFree of any kind.
+ *  - Limit: skn_attn_scratch_bytes(kv, n_q_heads) <= 4 MiB (4 194 304), i.e.
+ *    batch * n_q_heads * ceil(capacity / 256) * (head_dim + 2) * 4 bytes; larger problems are
+ *    refused with SKN_ERR_SHAPE and a message naming both sizes.
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress with that device current); make that first call before any stream
+ *    capture begins.
+ *  - All calls, from every context on the device, share the one array and it keeps whatever
+ *    the last call left in it.  Nothing in it needs clearing: each call writes every record
+ *    it later reads.  Two calls that overlap on the GPU (different streams, or relaxed order)
+ *    race on it; keep them in one stream's order. */
+int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, float scale,
+                                    float *out_dev);
+
 #ifdef __cplusplus
 }
 #endif

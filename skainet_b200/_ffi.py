@@ -48,6 +48,7 @@ SIGNATURES = {
     "skn_attn_decode": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
     "skn_attn_decode_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp, c_vp]),
     "skn_attn_scratch_bytes": (c_i64, [c_vp, c_i32]),
+    "skn_attn_decode_noalloc_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
 }
 
 _lib = None

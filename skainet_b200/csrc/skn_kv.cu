@@ -563,6 +563,47 @@ int32_t skn_attn_decode(skn_kvcache *kv, const float *q_host, int32_t n_q_heads,
     return skn_sync(ctx);
 }
 
+// ---- decode attention without any allocation -----------------------------------------------
+// Some hosts may not allocate device memory at the moment they need attention: a serving loop
+// whose memory budget was fixed at start-up, a caller inside a region where the CUDA allocator
+// must not run (it synchronises the device), or a runtime that hands this library a device
+// but no allocator at all.  For them the split partials live in the fixed array below, which
+// every GPU that loads the library carries until the process exits.
+constexpr int64_t SKN_ATTN_STATIC_SCRATCH_BYTES = 4ll << 20;   // 4 MiB
+static __device__ __align__(256) float g_attn_static_scratch[SKN_ATTN_STATIC_SCRATCH_BYTES / sizeof(float)];
+// Device address of the array per device.  The symbol's name is only a host-side stand-in;
+// kernels must be given the address cudaGetSymbolAddress returns for the current device.
+static float *g_attn_static_ptr[64] = {nullptr};
+
+int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, float scale,
+                                    float *out_dev) {
+    int G = 0;
+    int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
+    if (rc) return rc;
+    skn_ctx *ctx = kv->ctx;
+    if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "q and out must be 16-byte aligned");
+    const int64_t need = skn_attn_scratch_bytes(kv, n_q_heads);
+    if (need > SKN_ATTN_STATIC_SCRATCH_BYTES)
+        return skn_fail(ctx, SKN_ERR_SHAPE,
+                        "attention scratch of %lld bytes exceeds the built-in %lld bytes of the allocation-free "
+                        "entry point (batch * query heads * ceil(capacity / 256) * (head_dim + 2) * 4); use "
+                        "skn_attn_decode_dev with a caller-provided buffer",
+                        (long long)need, (long long)SKN_ATTN_STATIC_SCRATCH_BYTES);
+    if (ctx->device < 0 || ctx->device >= 64) return skn_fail(ctx, SKN_ERR_ARG, "device index %d not supported here", ctx->device);
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    float *part = g_attn_static_ptr[ctx->device];
+    if (!part) {
+        // one-time set-up for this device (it is current): resolve the array's device address
+        void *p = nullptr;
+        SKN_CUDA(ctx, cudaGetSymbolAddress(&p, g_attn_static_scratch));
+        if (!p) return skn_fail(ctx, SKN_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        part = g_attn_static_ptr[ctx->device] = (float *)p;
+    }
+    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream));
+    return SKN_OK;
+}
+
 // device pointers of the cache (for callers that fill it with their own kernels)
 int32_t skn_kv_info(const skn_kvcache *kv, int32_t *batch, int32_t *n_kv_heads, int32_t *head_dim, int32_t *capacity,
                     void **k_dev, void **v_dev, void **len_dev, void **start_dev) {
