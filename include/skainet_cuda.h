@@ -79,6 +79,11 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
  * still complete when skn_sync (or a later operation on the stream) returns.  The reference
  * is single-threaded and has no notion of ordering (Tensor.kt:6-33): no counterpart. */
 #define SKN_OPT_RELAXED_ORDER 1
+/* SKN_OPT_PREFILL_MIN_M (default 64): batch size M from which skn_matmul / skn_ffn_swiglu run on
+ * the tensor cores with bf16 operands and fp32 accumulation (relative error up to 1e-2 against
+ * the fp64 oracle); below it, and always with value 0, products are fp32 fused dequant-dot
+ * (1e-5). */
+#define SKN_OPT_PREFILL_MIN_M 2
 int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value);
 
 /* Wait for everything enqueued on the context's stream; reports a pending
@@ -141,6 +146,17 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
                    const float *bias_host, float *y_host);
 int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
                        const float *bias_dev, float *y_dev);
+
+/* Y[M, N] = (silu(X . Wg^T) * (X . Wu^T)) . Wd^T -- the SwiGLU feed-forward block; Wg, Wu are
+ * [F, K] (same block type), Wd is [N, F].  The reference has neither SiLU nor SwiGLU (its
+ * sigmoid(), core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:448-449, computes
+ * 1/exp(-x)); this is Linear.forward (nn/Linear.kt:43-49) applied three times around the
+ * textbook activation.  M >= SKN_OPT_PREFILL_MIN_M runs on the tensor cores (the intermediate
+ * is kept in bf16, never fp16). */
+int32_t skn_ffn_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
+                       const float *x_host, int32_t M, float *y_host);
+int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
+                           const float *x_dev, int32_t M, float *y_dev);
 
 /* ---- KV cache and decode attention ------------------------------------------------------
  * The reference has no KV cache, no attention and no usable softmax (its softmax(dim),

@@ -4,7 +4,7 @@ The product is ``libskainet_cuda.so`` (C ABI in ``include/skainet_cuda.h``); thi
 is the Python host-side mirror of the reference's tensor / module interface over that ABI.
 """
 from .tensor import (Context, KVCache, GGML_QUANT_SIZES, GGMLQuantizationType, QK_K, QuantLinear, QuantTensor, Shape,
-                     SknError, quant_shape_to_byte_shape)
+                     SknError, ffn_swiglu, quant_shape_to_byte_shape)
 
 __all__ = ["Context", "KVCache", "GGML_QUANT_SIZES", "GGMLQuantizationType", "QK_K", "QuantLinear", "QuantTensor", "Shape",
-           "SknError", "quant_shape_to_byte_shape"]
+           "SknError", "ffn_swiglu", "quant_shape_to_byte_shape"]

@@ -83,6 +83,7 @@ int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     CTX_TRY(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
     ctx->stream = ctx->own_stream;
+    ctx->prefill_min_m = 64;
     CTX_TRY(cudaMalloc((void **)&ctx->d_status, 32768));
     CTX_TRY(cudaMemset(ctx->d_status, 0, 32768));
     CTX_TRY(cudaMallocHost((void **)&ctx->h_status, 256));
@@ -117,6 +118,10 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
     switch (option) {
     case SKN_OPT_RELAXED_ORDER: ctx->relaxed_order = value ? 1 : 0; return SKN_OK;
+    case SKN_OPT_PREFILL_MIN_M:
+        if (value < 0 || value > (1 << 30)) return skn_fail(ctx, SKN_ERR_ARG, "prefill threshold out of range");
+        ctx->prefill_min_m = (int)value;
+        return SKN_OK;
     default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
     }
 }
@@ -288,8 +293,73 @@ int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, in
                                               cudaMemcpyDeviceToDevice, ctx->stream));
         return SKN_OK;
     }
+    if (ctx->prefill_min_m > 0 && M >= ctx->prefill_min_m && skn_tc_supported(w, M)) {
+        // prefill: bf16 copy of the activations, tensor-core matmul with fp32 accumulation
+        const size_t ab = (size_t)M * (size_t)K * 2;
+        int32_t rc2 = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, ab);
+        if (rc2) return rc2;
+        SKN_CUDA(ctx, skn_launch_f32_to_bf16(x_dev, ctx->d_scratch, (int64_t)M * K, ctx->sm_count, ctx->stream));
+        SKN_CUDA(ctx, skn_launch_matmul_tc(ctx, w, ctx->d_scratch, M, bias_dev, y_dev, ctx->stream));
+        return SKN_OK;
+    }
     SKN_CUDA(ctx, skn_launch_matvec(ctx, w, x_dev, M, bias_dev, y_dev, ctx->stream));
     return SKN_OK;
+}
+
+int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
+                           const float *x_dev, int32_t M, float *y_dev) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!skn_tensor_ok(wg) || !skn_tensor_ok(wu) || !skn_tensor_ok(wd) || wg->ctx != ctx || wu->ctx != ctx || wd->ctx != ctx)
+        return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (M < 0) return skn_fail(ctx, SKN_ERR_ARG, "M is negative");
+    if (wg->n_rows != wu->n_rows || wg->n_cols != wu->n_cols || wd->n_cols != wg->n_rows || wg->type != wu->type)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    if (M == 0 || wd->n_rows == 0) return SKN_OK;
+    if (!x_dev || !y_dev) return skn_fail(ctx, SKN_ERR_ARG, "x or y is NULL");
+    if ((((uintptr_t)x_dev) | ((uintptr_t)y_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "x and y must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int64_t F = wg->n_rows, K = wg->n_cols;
+    if (ctx->prefill_min_m > 0 && M >= ctx->prefill_min_m && skn_tc_supported(wg, M) && skn_tc_supported(wd, M)) {
+        // [A bf16 | H bf16] in the context scratch
+        const size_t ab = ((size_t)M * K * 2 + 255) / 256 * 256, hb = (size_t)M * F * 2;
+        int32_t rc = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, ab + hb);
+        if (rc) return rc;
+        void *a16 = ctx->d_scratch, *h16 = (uint8_t *)ctx->d_scratch + ab;
+        SKN_CUDA(ctx, skn_launch_f32_to_bf16(x_dev, a16, (int64_t)M * K, ctx->sm_count, ctx->stream));
+        SKN_CUDA(ctx, skn_launch_gate_up_tc(ctx, wg, wu, a16, M, h16, ctx->stream));
+        SKN_CUDA(ctx, skn_launch_matmul_tc(ctx, wd, h16, M, nullptr, y_dev, ctx->stream));
+        return SKN_OK;
+    }
+    // decode-size path: three fp32 fused dequant-dot products and an element-wise SwiGLU
+    const size_t gb = ((size_t)M * F * sizeof(float) + 255) / 256 * 256;
+    int32_t rc = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, 2 * gb);
+    if (rc) return rc;
+    float *g = (float *)ctx->d_scratch, *u = (float *)((uint8_t *)ctx->d_scratch + gb);
+    SKN_CUDA(ctx, skn_launch_matvec(ctx, wg, x_dev, M, nullptr, g, ctx->stream));
+    SKN_CUDA(ctx, skn_launch_matvec(ctx, wu, x_dev, M, nullptr, u, ctx->stream));
+    SKN_CUDA(ctx, skn_launch_silu_mul(g, u, g, (int64_t)M * F, ctx->sm_count, ctx->stream));
+    SKN_CUDA(ctx, skn_launch_matvec(ctx, wd, g, M, nullptr, y_dev, ctx->stream));
+    return SKN_OK;
+}
+
+int32_t skn_ffn_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
+                       const float *x_host, int32_t M, float *y_host) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!skn_tensor_ok(wg) || !skn_tensor_ok(wd)) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+    if (M < 0) return skn_fail(ctx, SKN_ERR_ARG, "M is negative");
+    if (M == 0) return SKN_OK;
+    if (!x_host || !y_host) return skn_fail(ctx, SKN_ERR_ARG, "x or y is NULL");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)M * wg->n_cols * sizeof(float), yb = (size_t)M * wd->n_rows * sizeof(float);
+    int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, xb);
+    if (rc) return rc;
+    rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, yb);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = skn_ffn_swiglu_dev(ctx, wg, wu, wd, (const float *)ctx->d_stage_in, M, (float *)ctx->d_stage_out);
+    if (rc) return rc;
+    SKN_CUDA(ctx, cudaMemcpyAsync(y_host, ctx->d_stage_out, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
 }
 
 int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32_t M, int64_t K, const float *bias_host,

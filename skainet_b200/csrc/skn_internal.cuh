@@ -19,6 +19,7 @@ struct skn_ctx {
     cudaStream_t stream;        // stream `_dev` calls enqueue on
     int sm_count;
     int relaxed_order;          // SKN_OPT_RELAXED_ORDER
+    int prefill_min_m;          // SKN_OPT_PREFILL_MIN_M: batch size from which the tensor-core path runs
     int32_t *d_status;          // device status word written by bounded waits
     int32_t *h_status;          // pinned mirror
     // staging for the host-pointer entry points (grown on demand)
@@ -76,3 +77,12 @@ cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitc
                                int64_t n_cols, float *out, cudaStream_t stream);
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M,
                               const float *bias, float *y, cudaStream_t stream);
+
+// tensor-core prefill path (skn_matmul_tc.cu)
+bool skn_tc_supported(const skn_tensor *w, int32_t M);
+cudaError_t skn_launch_f32_to_bf16(const float *in, void *out_bf16, int64_t n, int sm_count, cudaStream_t stream);
+cudaError_t skn_launch_matmul_tc(skn_ctx *ctx, const skn_tensor *w, const void *a_bf16, int32_t M, const float *bias,
+                                 float *y, cudaStream_t stream);
+cudaError_t skn_launch_gate_up_tc(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const void *a_bf16,
+                                  int32_t M, void *h_bf16, cudaStream_t stream);
+cudaError_t skn_launch_silu_mul(const float *g, const float *u, float *h, int64_t n, int sm_count, cudaStream_t stream);

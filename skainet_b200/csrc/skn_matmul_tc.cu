@@ -1,0 +1,348 @@
+// K3 / K4: prefill matmul on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   Y[M,N] = A[M,K] . W_q[N,K]^T      A = bf16 copy of the activations, W_q = raw GGUF blocks
+//
+// One CTA computes a 128 (tokens) x 128 (features) tile over the whole K in steps of 64:
+//   warps 0-3  dequantise the weight tile: thread t owns weight row t and turns 64 weights of
+//              raw blocks into one 128-byte bf16 row of the K-major, 128B-swizzled operand
+//              tile in shared memory (DUAL: a second tile from a second weight, same rows)
+//   warps 4-7  copy the activation tile (128 rows x 64 bf16) into the same layout
+//   warp  8    allocates tensor memory; its lane 0 issues tcgen05.mma (M=128, N=128, K=16,
+//              kind::f16, bf16 operands, fp32 accumulation in TMEM) four times per stage and
+//              commits each stage to the mbarrier that frees it
+//   warps 0-3  epilogue: tcgen05.ld the accumulator (lane = token row) and store fp32 rows,
+//              or, DUAL, silu(gate) * up as bf16 for the next matmul
+// A 4-stage ring of (A tile, B tile[, B2 tile]) with full/empty mbarriers decouples the three
+// roles.  Operand tiles are written by ordinary stores, so every producer thread issues
+// fence.proxy.async before its warp arrives on the full barrier.  All waits are bounded.
+#include "skn_blocks.cuh"
+#include "skn_ptx.cuh"
+
+#include <cuda_bf16.h>
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
+constexpr int TC_STAGES = 4;
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;   // 16 KB, one operand tile
+constexpr int TC_THREADS = 9 * 32;
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ void tc_alloc(uint32_t *slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(skn_smem_u32(slot_smem)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(skn_smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 128 x N x 16, bf16 in, fp32 out
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators -> 32 registers per thread
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, rows of 64 bf16 (128 bytes) in 8-row
+// groups of 1024 bytes, 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // swizzle mode: 128 bytes
+    return d;
+}
+// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, M x N tile
+__device__ __forceinline__ uint32_t tc_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// store 8 consecutive bf16 (one 16-byte chunk `c` of row `r`) into a swizzled tile
+__device__ __forceinline__ void tc_store_chunk(uint8_t *tile, int r, int c, uint4 v) {
+    *reinterpret_cast<uint4 *>(tile + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)) = v;
+}
+
+__device__ __forceinline__ uint32_t tc_pack_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// 64 weights of row `rp` starting at column k0 (a multiple of 64) -> bf16 row of the tile
+template <int TYPE>
+__device__ __forceinline__ void tc_dequant_row(const uint8_t *rp, int k0, uint8_t *tile, int r, bool valid) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float w[32];
+        if (valid) {
+            decode_group<TYPE>(rp, (int64_t)(k0 >> 5) + half, w);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = tc_pack_bf16(w[8 * c + 0], w[8 * c + 1]);
+            v.y = tc_pack_bf16(w[8 * c + 2], w[8 * c + 3]);
+            v.z = tc_pack_bf16(w[8 * c + 4], w[8 * c + 5]);
+            v.w = tc_pack_bf16(w[8 * c + 6], w[8 * c + 7]);
+            tc_store_chunk(tile, r, half * 4 + c, v);
+        }
+    }
+}
+
+__global__ void skn_f32_to_bf16_kernel(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(in) + i);
+        uint2 o;
+        o.x = tc_pack_bf16(v.x, v.y);
+        o.y = tc_pack_bf16(v.z, v.w);
+        reinterpret_cast<uint2 *>(out)[i] = o;
+    }
+}
+
+// TYPE: block type of W (and W2).  DUAL: out_bf16[m][n] = silu(A.W^T) * (A.W2^T), else
+// out_f32[m][n] = A.W^T (+ bias[n]).
+template <int TYPE, bool DUAL>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const uint8_t *__restrict__ W,
+                     const uint8_t *__restrict__ W2, int64_t pitch, int N, const float *__restrict__ bias,
+                     float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_bf16, int64_t ld_out,
+                     int32_t *__restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int NB = DUAL ? 2 : 1;
+    constexpr int STAGE_BYTES = (1 + NB) * TC_TILE_BYTES;
+    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], accum_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int fail_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int ksteps = K / TC_BK;
+    constexpr uint32_t TMEM_COLS = DUAL ? 256 : 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            skn_mbar_init(&full_bar[s], 8);      // one arrival per producer warp
+            skn_mbar_init(&empty_bar[s], 1);     // one tcgen05.commit
+        }
+        skn_mbar_init(&accum_bar, 1);
+        fail_flag = 0;
+        skn_fence_mbar_init();
+    }
+    if (warp == 8) tc_alloc(&tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp < 8) {
+        // ---------------- producers ----------------
+        const bool is_b = warp < 4;
+        const int r = threadIdx.x & 127;                    // row of the tile this thread fills
+        const int grow = is_b ? n0 + r : m0 + r;            // weight row / activation row
+        const bool valid = is_b ? (grow < N) : (grow < M);
+        const uint8_t *wrow = W + (int64_t)(valid ? grow : 0) * pitch;
+        const uint8_t *wrow2 = DUAL ? W2 + (int64_t)(valid ? grow : 0) * pitch : nullptr;
+        const __nv_bfloat16 *arow = A + (int64_t)(valid ? grow : 0) * K;
+        bool failed = false;
+        for (int it = 0; it < ksteps; ++it) {
+            const int s = it % TC_STAGES;
+            const uint32_t ph = (uint32_t)(it / TC_STAGES) & 1u;
+            if (!failed && !skn_mbar_wait(&empty_bar[s], ph ^ 1u)) {
+                failed = true;
+                atomicExch(status, SKN_ERR_TIMEOUT);
+                atomicExch(&fail_flag, 1);
+            }
+            uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
+            const int k0 = it * TC_BK;
+            if (is_b) {
+                tc_dequant_row<TYPE>(wrow, k0, stage + TC_TILE_BYTES, r, valid);
+                if (DUAL) tc_dequant_row<TYPE>(wrow2, k0, stage + 2 * TC_TILE_BYTES, r, valid);
+            } else {
+                const uint4 *src = reinterpret_cast<const uint4 *>(arow + k0);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+                    tc_store_chunk(stage, r, c, v);
+                }
+            }
+            skn_fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) skn_mbar_arrive(&full_bar[s]);
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
+        bool failed = false;
+        for (int it = 0; it < ksteps; ++it) {
+            const int s = it % TC_STAGES;
+            const uint32_t ph = (uint32_t)(it / TC_STAGES) & 1u;
+            if (!failed && !skn_mbar_wait(&full_bar[s], ph)) {
+                failed = true;
+                atomicExch(status, SKN_ERR_TIMEOUT);
+                atomicExch(&fail_flag, 1);
+            }
+            tc_fence_after();
+            const uint32_t a_addr = skn_smem_u32(smem + (size_t)s * STAGE_BYTES);
+            const uint64_t adesc = tc_smem_desc(a_addr);
+            const uint64_t bdesc = tc_smem_desc(a_addr + TC_TILE_BYTES);
+            const uint64_t bdesc2 = tc_smem_desc(a_addr + 2 * TC_TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k) {
+                const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                // advancing 16 bf16 (32 bytes) along K inside the swizzle atom = +2 in the address field
+                tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+                if (DUAL) tc_mma_bf16(tmem_base + 128, adesc + 2 * k, bdesc2 + 2 * k, idesc, acc);
+            }
+            tc_commit(&empty_bar[s]);    // frees the stage once these MMAs have read it
+        }
+        tc_commit(&accum_bar);           // all MMAs done: the accumulator is complete
+    }
+
+    // ---------------- epilogue: warps 0-3, TMEM lane = token row ----------------
+    if (warp < 4) {
+        bool ok = skn_mbar_wait(&accum_bar, 0u);
+        if (!ok) {
+            atomicExch(status, SKN_ERR_TIMEOUT);
+            atomicExch(&fail_flag, 1);
+        }
+        tc_fence_after();
+        const int m = m0 + warp * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+                uint32_t acc[32];
+                tc_ld32(lane_addr + c0, acc);
+                if (DUAL) {
+                    uint32_t up[32];
+                    tc_ld32(lane_addr + 128 + c0, up);
+                    if (m < M) {
+                        __nv_bfloat16 *dst = out_bf16 + (int64_t)m * ld_out + n0 + c0;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            if (n0 + c0 + i < N) {      // N is even
+                                const float g0 = __uint_as_float(acc[i]), g1 = __uint_as_float(acc[i + 1]);
+                                const float h0 = g0 / (1.f + expf(-g0)) * __uint_as_float(up[i]);
+                                const float h1 = g1 / (1.f + expf(-g1)) * __uint_as_float(up[i + 1]);
+                                *reinterpret_cast<uint32_t *>(dst + i) = tc_pack_bf16(h0, h1);
+                            }
+                        }
+                    }
+                } else if (m < M) {
+                    float *dst = out_f32 + (int64_t)m * ld_out + n0 + c0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (n0 + c0 + i < N) {          // N is a multiple of 4
+                            float4 v = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                                   __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+                            if (bias) {
+                                const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + n0 + c0 + i));
+                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                            }
+                            *reinterpret_cast<float4 *>(dst + i) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        __syncwarp();
+        tc_fence_after();
+        tc_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int TYPE, bool DUAL>
+static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_tensor *w, const skn_tensor *w2,
+                             const float *bias, float *out_f32, __nv_bfloat16 *out_bf16, int64_t ld_out,
+                             int32_t *status, cudaStream_t stream) {
+    auto kern = skn_matmul_tc_kernel<TYPE, DUAL>;
+    const size_t smem = (size_t)TC_STAGES * (DUAL ? 3 : 2) * TC_TILE_BYTES + 1024;
+    static bool attr_done[64] = {false};   // per device
+    int dev = 0;
+    cudaError_t e0 = cudaGetDevice(&dev);
+    if (e0 != cudaSuccess) return e0;
+    if (!attr_done[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_done[dev & 63] = true;
+    }
+    const dim3 grid((unsigned)((M + TC_BM - 1) / TC_BM), (unsigned)((w->n_rows + TC_BN - 1) / TC_BN));
+    kern<<<grid, TC_THREADS, smem, stream>>>(A, M, K, w->d_blocks, w2 ? w2->d_blocks : nullptr, w->pitch, (int)w->n_rows,
+                                             bias, out_f32, out_bf16, ld_out, status);
+    return cudaGetLastError();
+}
+
+template <bool DUAL>
+static cudaError_t dispatch_tc(const __nv_bfloat16 *A, int M, int K, const skn_tensor *w, const skn_tensor *w2,
+                               const float *bias, float *out_f32, __nv_bfloat16 *out_bf16, int64_t ld_out,
+                               int32_t *status, cudaStream_t stream) {
+    switch (w->type) {
+    case SKN_TYPE_Q4_0: return launch_tc<SKN_TYPE_Q4_0, DUAL>(A, M, K, w, w2, bias, out_f32, out_bf16, ld_out, status, stream);
+    case SKN_TYPE_Q8_0: return launch_tc<SKN_TYPE_Q8_0, DUAL>(A, M, K, w, w2, bias, out_f32, out_bf16, ld_out, status, stream);
+    case SKN_TYPE_Q4_K: return launch_tc<SKN_TYPE_Q4_K, DUAL>(A, M, K, w, w2, bias, out_f32, out_bf16, ld_out, status, stream);
+    case SKN_TYPE_Q6_K: return launch_tc<SKN_TYPE_Q6_K, DUAL>(A, M, K, w, w2, bias, out_f32, out_bf16, ld_out, status, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+bool skn_tc_supported(const skn_tensor *w, int32_t M) {
+    return M >= 1 && (w->n_cols % TC_BK) == 0 && w->n_cols >= TC_BK && (w->n_rows % 4) == 0 &&
+           (reinterpret_cast<uintptr_t>(w->d_blocks) & 1) == 0;
+}
+
+cudaError_t skn_launch_f32_to_bf16(const float *in, void *out_bf16, int64_t n, int sm_count, cudaStream_t stream) {
+    const int64_t n4 = n / 4;
+    if (n4 == 0) return cudaSuccess;
+    int64_t blocks = (n4 + 255) / 256;
+    if (blocks > (int64_t)sm_count * 8) blocks = (int64_t)sm_count * 8;
+    skn_f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(in, (__nv_bfloat16 *)out_bf16, n4);
+    return cudaGetLastError();
+}
+
+// Y = A_bf16 . W^T (+bias), fp32 out
+cudaError_t skn_launch_matmul_tc(skn_ctx *ctx, const skn_tensor *w, const void *a_bf16, int32_t M, const float *bias,
+                                 float *y, cudaStream_t stream) {
+    return dispatch_tc<false>((const __nv_bfloat16 *)a_bf16, M, (int)w->n_cols, w, nullptr, bias, y, nullptr, w->n_rows,
+                              ctx->d_status, stream);
+}
+
+// H_bf16 = silu(A . Wg^T) * (A . Wu^T)
+cudaError_t skn_launch_gate_up_tc(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const void *a_bf16,
+                                  int32_t M, void *h_bf16, cudaStream_t stream) {
+    return dispatch_tc<true>((const __nv_bfloat16 *)a_bf16, M, (int)wg->n_cols, wg, wu, nullptr, nullptr,
+                             (__nv_bfloat16 *)h_bf16, wg->n_rows, ctx->d_status, stream);
+}

@@ -135,6 +135,10 @@ class Context:
         """Declare consecutive device-pointer launches independent (they may overlap)."""
         _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 1, 1 if on else 0))
 
+    def set_prefill_min_m(self, m: int):
+        """Batch size from which matmuls use the tensor cores (bf16 operands); 0 = never."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 2, int(m)))
+
     def sync(self):
         _check(self._h, _ffi.lib().skn_sync(self._h))
 
@@ -261,6 +265,19 @@ class QuantLinear:
         return self.weight.matmul_t(x, self.bias)
 
     __call__ = forward
+
+
+def ffn_swiglu(ctx: Context, wg: QuantTensor, wu: QuantTensor, wd: QuantTensor, x: np.ndarray) -> np.ndarray:
+    """(silu(x Wg^T) * (x Wu^T)) Wd^T for x [M, K] (or [K]) on the host."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    vec = x.ndim == 1
+    x2 = x.reshape(1, -1) if vec else x
+    if x2.ndim != 2 or x2.shape[1] != wg.shape.dimensions[1]:
+        raise ValueError("Shapes do not align.")
+    y = np.empty((x2.shape[0], wd.shape.dimensions[0]), dtype=np.float32)
+    _check(ctx.handle, _ffi.lib().skn_ffn_swiglu(ctx.handle, wg.handle, wu.handle, wd.handle, x2.ctypes.data,
+                                                 x2.shape[0], y.ctypes.data))
+    return y[0] if vec else y
 
 
 class KVCache:
