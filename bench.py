@@ -188,7 +188,10 @@ def run_ours(args):
 
     layers = args.layers
     ctx = skn.Context(local)
-    stream = torch.cuda.current_stream()
+    # a stream of our own: handle 0 (the legacy default stream) would mean "the context's own
+    # stream" to skn_ctx_set_stream, and the timing events must sit on the launching stream
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
     ctx.set_relaxed_order(args.order == "relaxed")
 
@@ -335,6 +338,173 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# Secondary workloads (not the headline line): --workload ffn | attn | sweep.  Single GPU.
+# --------------------------------------------------------------------------------------------
+def _events_ms(torch, stream, fn, steps, warmup):
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_ffn(args):
+    """Config 3: SwiGLU FFN prefill, X fp32 [512,4096], W_gate/W_up 14336x4096 Q4_K, W_down
+    4096x14336 Q6_K, on the tensor cores.  Inputs (229 MB of weights + activations) exceed L2."""
+    import torch
+    import skainet_b200 as skn
+    from skainet_b200 import _ffi, synth
+    M, K, F = 512, 4096, 14336
+    dev = torch.device("cuda", 0)
+    ctx = skn.Context(0)
+    # a stream of our own: handle 0 (the legacy default stream) would mean "the context's own
+    # stream" to skn_ctx_set_stream, and the timing events must sit on the launching stream
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    g = synth.rng(2)
+    x = torch.from_numpy(synth.make_activations(g, M, K)).to(dev)
+    base = synth.make_weight(g, 12, F, K)
+    wg = skn.QuantTensor(ctx, (F, K), 12, base)
+    wu = skn.QuantTensor(ctx, (F, K), 12, np.roll(base, 1, axis=0))
+    wd = skn.QuantTensor(ctx, (K, F), 14, synth.make_weight(g, 14, K, F))
+    y = torch.empty((M, K), dtype=torch.float32, device=dev)
+    L = _ffi.lib()
+
+    def step():
+        rc = L.skn_ffn_swiglu_dev(ctx.handle, wg.handle, wu.handle, wd.handle, x.data_ptr(), M, y.data_ptr())
+        assert rc == 0, L.skn_last_error(ctx.handle)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = _events_ms(torch, stream, step, args.steps, args.warmup)
+    clocks = sampler.stop()
+    ctx.sync()
+    flops = 3 * 2 * M * K * F
+    tfl = flops / (ms * 1e-3) / 1e12
+    peak = 1672.7
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    print(json.dumps({
+        "metric": "ffn_prefill_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg3: SwiGLU FFN prefill M=512, 4096 -> 14336 (Q4_K gate/up) -> 4096 (Q6_K down)",
+                   "tokens_per_s": M / (ms * 1e-3)},
+        "gpu_launches": 3 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "skn_matmul_tc_kernel", "achieved": tfl, "peak": peak,
+                     "peak_kind": "measured burst", "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None},
+        "clocks": clocks}), flush=True)
+
+
+def run_attn(args):
+    """Config 4: decode attention, 32 query / 8 kv heads, head_dim 128, batch 8, fp32 cache
+    pre-filled (lengths uniform 1024..4096); a step appends one token and attends.  The
+    cache (1.1 GB) exceeds L2."""
+    import torch
+    import skainet_b200 as skn
+    from skainet_b200 import _ffi, synth
+    B, Hq, Hkv, D, T = 8, 32, 8, 128, 4096
+    steps = min(args.steps, 128)
+    cap = T + 128 + 8
+    dev = torch.device("cuda", 0)
+    ctx = skn.Context(0)
+    # a stream of our own: handle 0 (the legacy default stream) would mean "the context's own
+    # stream" to skn_ctx_set_stream, and the timing events must sit on the launching stream
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    g = synth.rng(3)
+    kv = skn.KVCache(ctx, B, Hkv, D, cap)
+    lens = g.integers(1024, 4097, size=B).astype(np.int32)
+    kc = g.standard_normal((B, Hkv, T, D), dtype=np.float32)
+    kv.load(kc, kc[:, ::-1].copy(), lens)
+    q = torch.randn((B, Hq, D), device=dev)
+    kn = torch.randn((B, Hkv, D), device=dev)
+    out = torch.empty_like(q)
+    L = _ffi.lib()
+    scale = 1.0 / float(np.sqrt(D))
+
+    def step():
+        assert L.skn_kv_append_dev(kv.handle, kn.data_ptr(), kn.data_ptr()) == 0
+        assert L.skn_attn_decode_dev(kv.handle, q.data_ptr(), Hq, scale, out.data_ptr(), None) == 0
+
+    warm = 3
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    # bytes: K and V of every cached token of every kv head, mean length over the timed steps
+    mean_len = float(lens.mean()) + warm + (steps + 1) / 2.0
+    alg = B * mean_len * Hkv * D * 4 * 2 + B * Hkv * D * 4 * 2 + 2 * B * Hq * D * 4
+    gbs = alg / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak()
+    print(json.dumps({
+        "metric": "attn_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg4: GQA decode attention B=8, 32q/8kv heads, D=128, ctx 1024..4096 (+1 per step)",
+                   "mean_len": mean_len, "steps_per_s": 1e3 / ms},
+        "gpu_launches": 3 * steps,
+        "roofline": {"bound": "hbm", "kernel": "skn_attn_split_kernel", "achieved": gbs, "peak": peak, "peak_kind": kind,
+                     "unit": "GB/s", "frac": gbs / peak, "traffic": None}}), flush=True)
+
+
+def run_sweep(args):
+    """Config 2 (and the Q4_K / Q6_K analogues): matvec / small-batch matmul GB/s per type,
+    shape and M.  Each case cycles over enough distinct weights to exceed L2."""
+    import torch
+    import skainet_b200 as skn
+    from skainet_b200 import synth
+    dev = torch.device("cuda", 0)
+    ctx = skn.Context(0)
+    # a stream of our own: handle 0 (the legacy default stream) would mean "the context's own
+    # stream" to skn_ctx_set_stream, and the timing events must sit on the launching stream
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    ctx.set_relaxed_order(args.order == "relaxed")
+    g = synth.rng(1)
+    rows = []
+    for qt in (2, 8, 12, 14):
+        e, bb = synth.GEOMETRY[qt]
+        for (N, K) in ((4096, 4096), (14336, 4096), (4096, 14336)):
+            wbytes = N * K // e * bb
+            nl = max(2, int(400e6 // wbytes) + 1)
+            base = synth.make_weight(g, qt, N, K)
+            ts = [skn.QuantTensor(ctx, (N, K), qt, np.roll(base, i, axis=0)) for i in range(nl)]
+            for M in (1, 4, 16, 64):
+                x = torch.randn((M, K), device=dev)
+                y = torch.empty((nl, M, N), device=dev)
+
+                def step():
+                    for i, t in enumerate(ts):
+                        t.matmul_t_dev(x, M, y[i])
+                reps = 3 if M >= 16 else 5
+                ms = _events_ms(torch, stream, step, reps, 3) / nl
+                alg = wbytes + 4 * M * (K + N)
+                rows.append({"type": synth.TYPE_NAMES[qt], "N": N, "K": K, "M": M, "us": ms * 1e3,
+                             "gbs": alg / (ms * 1e-3) / 1e9, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12})
+            for t in ts:
+                t.close()
+    peak, kind = measured_peak()
+    print(json.dumps({"metric": "matvec_sweep_gbs", "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+                      "config": {"workload": "cfg2 sweep over types, shapes, M", "order": args.order},
+                      "peak": peak, "peak_kind": kind, "cases": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -348,7 +518,11 @@ def main():
     ap.add_argument("--order", default="relaxed", choices=["relaxed", "stream"],
                     help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
                          "may overlap; stream: each launch waits for the one before it")
+    ap.add_argument("--workload", default="matvec", choices=["matvec", "ffn", "attn", "sweep"],
+                    help="matvec is the headline line; the others print one secondary JSON line (1 GPU)")
     args = ap.parse_args()
+    if args.impl == "ours" and args.workload != "matvec":
+        return {"ffn": run_ffn, "attn": run_attn, "sweep": run_sweep}[args.workload](args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -670,7 +670,9 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
     if (nch < 1 || nch > 16 || w->n_rows < 1) return cudaSuccess;
     static const int wg_env = env_int("SKN_MV_WG", 0);
     static const int warps_env = env_int("SKN_MV_WARPS", 8);
+    // about `warps_env` warps per CTA; long rows (nch > 4) get two row slots when they fit
     int wg = wg_env > 0 ? wg_env : (nch <= warps_env ? warps_env / nch : 1);
+    if (wg_env <= 0 && nch > 4 && nch <= 8) wg = 2;
     if (wg < 1) wg = 1;
     while (nch * wg > 16) --wg;
     if (wg < 1) return cudaSuccess;
@@ -730,11 +732,23 @@ static bool try_stream(skn_ctx *ctx, const skn_tensor *w, const float *x, const 
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M, const float *bias,
                               float *y, cudaStream_t stream) {
     static const int force_generic = env_int("SKN_MV_GENERIC", 0);
-    if (M == 1 && !force_generic && (w->pitch % 16) == 0) {
+    if (M >= 1 && !force_generic && (w->pitch % 16) == 0) {
+        // small batches run the streaming matvec once per activation row (the weights of the
+        // later rows come from L2); each launch is a complete fp32 fused dequant-dot
         cudaError_t err = cudaSuccess;
-        if (w->type == SKN_TYPE_Q4_K && try_stream<Q4KStream>(ctx, w, x, bias, y, stream, err)) return err;
-        if (w->type == SKN_TYPE_Q4_0 && try_stream<Q40Stream>(ctx, w, x, bias, y, stream, err)) return err;
-        if (w->type == SKN_TYPE_Q8_0 && try_stream<Q80Stream>(ctx, w, x, bias, y, stream, err)) return err;
+        bool done = false;
+        for (int32_t m = 0; m < M; ++m) {
+            const float *xm = x + (int64_t)m * w->n_cols;
+            float *ym = y + (int64_t)m * w->n_rows;
+            bool took = false;
+            if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
+            else if (w->type == SKN_TYPE_Q4_0) took = try_stream<Q40Stream>(ctx, w, xm, bias, ym, stream, err);
+            else if (w->type == SKN_TYPE_Q8_0) took = try_stream<Q80Stream>(ctx, w, xm, bias, ym, stream, err);
+            if (!took) break;               // shape not covered: the generic kernel below does all rows
+            if (err != cudaSuccess) return err;
+            done = (m == M - 1);
+        }
+        if (done) return cudaSuccess;
     }
     switch (w->type) {
     case SKN_TYPE_Q4_0: return launch_generic<SKN_TYPE_Q4_0>(w, x, M, bias, y, ctx->sm_count, stream);
