@@ -21,7 +21,6 @@
 #include <cuda_bf16.h>
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
-constexpr int TC_STAGES = 4;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;   // 16 KB, one operand tile
 constexpr int TC_THREADS = 9 * 32;
 
@@ -92,7 +91,8 @@ __device__ __forceinline__ uint32_t tc_pack_bf16(float a, float b) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// 64 weights of row `rp` starting at column k0 (a multiple of 64) -> bf16 row of the tile
+// ---- 64 weights of one row -> one 128-byte bf16 row of the operand tile ------------------------
+// Generic form (any type): two 32-weight groups through the byte-granular decoder.
 template <int TYPE>
 __device__ __forceinline__ void tc_dequant_row(const uint8_t *rp, int k0, uint8_t *tile, int r, bool valid) {
 #pragma unroll
@@ -116,6 +116,144 @@ __device__ __forceinline__ void tc_dequant_row(const uint8_t *rp, int k0, uint8_
     }
 }
 
+// (2^23 + k * 2^pos) read as a float, minus 2^23, times scale * 2^-pos, minus off: the value
+// scale * k - off of a quant field left in place at bit `pos` (no shift, no int->float unit).
+// Products and the subtraction round exactly as (scale * k) - off does in fp32.
+__device__ __forceinline__ float tc_field(uint32_t masked_or_magic, float scale_shifted, float off) {
+    return fmaf(__uint_as_float(masked_or_magic) - 8388608.f, scale_shifted, -off);
+}
+
+// Q4_K: 64 weights at k0 = one 32-byte run of quants (low nibbles: sub-block 2p, high nibbles:
+// sub-block 2p+1) plus the block header; three 16-byte loads.
+template <int TYPE> struct TcRaw { };                       // generic types: nothing is prefetched
+template <> struct TcRaw<SKN_TYPE_Q4_K> { uint4 hdr, qa, qb; };
+template <> struct TcRaw<SKN_TYPE_Q6_K> { uint32_t rq[17], rh[9], s_lo, s_hi, dword; };
+
+// raw bytes of the 64 weights at k0 into registers (issued one stage ahead of their decode)
+template <int TYPE>
+__device__ __forceinline__ void tc_load_row(const uint8_t *, int, bool, TcRaw<TYPE> &) {}
+template <>
+__device__ __forceinline__ void tc_load_row<SKN_TYPE_Q4_K>(const uint8_t *rp, int k0, bool valid, TcRaw<SKN_TYPE_Q4_K> &raw) {
+    if (!valid) return;
+    const int p = (k0 >> 6) & 3;
+    const uint8_t *bp = rp + (size_t)(k0 >> 8) * 144;
+    raw.hdr = __ldg(reinterpret_cast<const uint4 *>(bp));
+    raw.qa = __ldg(reinterpret_cast<const uint4 *>(bp + 16 + 32 * p));
+    raw.qb = __ldg(reinterpret_cast<const uint4 *>(bp + 32 + 32 * p));
+}
+
+template <int TYPE>
+__device__ __forceinline__ void tc_decode_row(const TcRaw<TYPE> &, const uint8_t *rp, int k0, uint8_t *tile, int r, bool valid) {
+    tc_dequant_row<TYPE>(rp, k0, tile, r, valid);
+}
+
+template <>
+__device__ __forceinline__ void tc_decode_row<SKN_TYPE_Q4_K>(const TcRaw<SKN_TYPE_Q4_K> &raw, const uint8_t *, int k0,
+                                                             uint8_t *tile, int r, bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(0u, 0u, 0u, 0u));
+        return;
+    }
+    const int p = (k0 >> 6) & 3;
+    const uint4 hdr = raw.hdr, qa = raw.qa, qb = raw.qb;
+    // scales / mins of sub-blocks 2p, 2p+1 (p is the same for every thread of the CTA)
+    const int sh = (p & 1) * 16;
+    const uint32_t a2 = (hdr.y >> sh) & 0xFFFFu, b2 = (hdr.z >> sh) & 0xFFFFu, c2 = (hdr.w >> sh) & 0xFFFFu;
+    const uint32_t sc2 = (p < 2) ? (a2 & 0x3F3Fu) : ((c2 & 0x0F0Fu) | ((a2 >> 2) & 0x3030u));
+    const uint32_t mn2 = (p < 2) ? (b2 & 0x3F3Fu) : (((c2 >> 4) & 0x0F0Fu) | ((b2 >> 2) & 0x3030u));
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+    const float dl0 = __fmul_rn(dd.x, (float)(sc2 & 0xFFu)), dl1 = __fmul_rn(dd.x, (float)(sc2 >> 8));
+    const float ml0 = __fmul_rn(dd.y, (float)(mn2 & 0xFFu)), ml1 = __fmul_rn(dd.y, (float)(mn2 >> 8));
+    const float l0 = dl0, l8 = dl0 * (1.f / 256.f), l16 = dl0 * (1.f / 65536.f);
+    const float h4 = dl1 * (1.f / 16.f), h12 = dl1 * (1.f / 4096.f), h8 = dl1 * (1.f / 256.f), h16 = dl1 * (1.f / 65536.f);
+    const uint32_t M = 0x4B000000u;
+    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    uint32_t lo[16], hi[16];   // bf16 pairs: lo = sub-block 2p (weights 0..31), hi = sub-block 2p+1
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t w = qw[i], w8 = w >> 8, w12 = w >> 12;
+        const float a0 = tc_field((w & 0x0000000Fu) | M, l0, ml0), a1 = tc_field((w & 0x00000F00u) | M, l8, ml0);
+        const float a2f = tc_field((w & 0x000F0000u) | M, l16, ml0), a3 = tc_field((w8 & 0x000F0000u) | M, l16, ml0);
+        const float b0 = tc_field((w & 0x000000F0u) | M, h4, ml1), b1 = tc_field((w & 0x0000F000u) | M, h12, ml1);
+        const float b2f = tc_field((w12 & 0x00000F00u) | M, h8, ml1), b3 = tc_field((w12 & 0x000F0000u) | M, h16, ml1);
+        lo[2 * i] = tc_pack_bf16(a0, a1);
+        lo[2 * i + 1] = tc_pack_bf16(a2f, a3);
+        hi[2 * i] = tc_pack_bf16(b0, b1);
+        hi[2 * i + 1] = tc_pack_bf16(b2f, b3);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        tc_store_chunk(tile, r, c, make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]));
+        tc_store_chunk(tile, r, 4 + c, make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]));
+    }
+}
+
+// Q6_K: 64 weights at k0 = quarter u of a 210-byte super-block: half h = u/2, groups g0 = 2*(u&1)
+// and g0+1.  Blocks start on 2-byte boundaries, so the 64 ql bytes, 32 qh bytes, 4 scales and d
+// are read as aligned words and re-aligned with funnel shifts (the shift is the same for all
+// threads: every thread of the CTA works on the same k0).
+template <>
+__device__ __forceinline__ void tc_load_row<SKN_TYPE_Q6_K>(const uint8_t *rp, int k0, bool valid, TcRaw<SKN_TYPE_Q6_K> &raw) {
+    if (!valid) return;
+    const int b = k0 >> 8, u = (k0 >> 6) & 3, h = u >> 1, g0 = 2 * (u & 1);
+    const uint8_t *bp = rp + (size_t)b * 210;
+    const uint32_t *wq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(bp + 64 * h) & ~(uintptr_t)3);
+    const uint32_t *wh = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(bp + 128 + 32 * h) & ~(uintptr_t)3);
+    const uint32_t *ws = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(bp + 192 + 8 * h + 2 * g0) & ~(uintptr_t)3);
+    const uint32_t *wd = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(bp + 208) & ~(uintptr_t)3);
+#pragma unroll
+    for (int i = 0; i < 17; ++i) raw.rq[i] = __ldg(wq + i);
+#pragma unroll
+    for (int i = 0; i < 9; ++i) raw.rh[i] = __ldg(wh + i);
+    raw.s_lo = __ldg(ws);
+    raw.s_hi = __ldg(ws + 1);
+    raw.dword = __ldg(wd);
+}
+
+template <>
+__device__ __forceinline__ void tc_decode_row<SKN_TYPE_Q6_K>(const TcRaw<SKN_TYPE_Q6_K> &raw, const uint8_t *rp, int k0,
+                                                             uint8_t *tile, int r, bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(0u, 0u, 0u, 0u));
+        return;
+    }
+    const int b = k0 >> 8, u = (k0 >> 6) & 3, g0 = 2 * (u & 1);
+    const uint32_t sh = (uint32_t)((reinterpret_cast<uintptr_t>(rp + (size_t)b * 210) & 2) * 8);     // 0 or 16
+    const uint32_t *rq = raw.rq, *rh = raw.rh;
+    const uint32_t s_lo = raw.s_lo, s_hi = raw.s_hi, dword = raw.dword;
+    const uint32_t sc4 = __funnelshift_rc(s_lo, s_hi, sh);                        // four int8 scales
+    const float d = skn_half_bits_to_float((dword >> sh) & 0xFFFFu);
+    float dl[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dl[i] = __fmul_rn(d, (float)(int8_t)((sc4 >> (8 * i)) & 0xFFu));
+    const int sn = (g0 == 2) ? 4 : 0;           // low nibbles for groups 0/1, high nibbles for 2/3
+    const int sq = 2 * g0;
+    uint32_t out[32];                           // bf16 pairs, weights 0..63
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t qh = __funnelshift_rc(rh[i], rh[i + 1], sh);
+        const uint32_t qa = __funnelshift_rc(rq[i], rq[i + 1], sh);            // ql[4i..4i+3]      -> group g0
+        const uint32_t qb = __funnelshift_rc(rq[8 + i], rq[9 + i], sh);        // ql[32+4i..]       -> group g0+1
+        const uint32_t a4 = ((qa >> sn) & 0x0F0F0F0Fu) | (((qh >> sq) & 0x03030303u) << 4);
+        const uint32_t b4 = ((qb >> sn) & 0x0F0F0F0Fu) | (((qh >> (sq + 2)) & 0x03030303u) << 4);
+        const float da = dl[i >> 2], db = dl[2 + (i >> 2)];                    // l/16 = i/4
+        float fa[4], fb[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            fa[k] = __fmul_rn(__uint_as_float(__byte_perm(a4, 0x4B000000u, 0x7440 + k)) - 8388640.f, da);
+            fb[k] = __fmul_rn(__uint_as_float(__byte_perm(b4, 0x4B000000u, 0x7440 + k)) - 8388640.f, db);
+        }
+        out[2 * i] = tc_pack_bf16(fa[0], fa[1]);
+        out[2 * i + 1] = tc_pack_bf16(fa[2], fa[3]);
+        out[16 + 2 * i] = tc_pack_bf16(fb[0], fb[1]);
+        out[16 + 2 * i + 1] = tc_pack_bf16(fb[2], fb[3]);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]));
+}
+
 __global__ void skn_f32_to_bf16_kernel(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n4) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         const float4 v = __ldg(reinterpret_cast<const float4 *>(in) + i);
@@ -128,33 +266,36 @@ __global__ void skn_f32_to_bf16_kernel(const float *__restrict__ in, __nv_bfloat
 
 // TYPE: block type of W (and W2).  DUAL: out_bf16[m][n] = silu(A.W^T) * (A.W2^T), else
 // out_f32[m][n] = A.W^T (+ bias[n]).
+// A CTA owns 256 token rows (two 128-row accumulators that share every dequantised weight
+// tile) x 128 features.  TMEM columns: [0,128) rows 0-127, [128,256) rows 128-255 and, DUAL,
+// [256,512) the same for W2.
 template <int TYPE, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const uint8_t *__restrict__ W,
                      const uint8_t *__restrict__ W2, int64_t pitch, int N, const float *__restrict__ bias,
                      float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_bf16, int64_t ld_out,
-                     int32_t *__restrict__ status) {
+                     int32_t *__restrict__ status, int halves) {
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NB = DUAL ? 2 : 1;
-    constexpr int STAGE_BYTES = (1 + NB) * TC_TILE_BYTES;
-    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], accum_bar;
+    constexpr int STAGES = DUAL ? 3 : 4;
+    constexpr int STAGE_BYTES = (2 + NB) * TC_TILE_BYTES;     // A0 | A1 | B [| B2]
+    __shared__ uint64_t full_bar[4], empty_bar[4], accum_bar;
     __shared__ uint32_t tmem_slot;
-    __shared__ int fail_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int m0 = blockIdx.x * (halves * TC_BM), n0 = blockIdx.y * TC_BN;
     const int ksteps = K / TC_BK;
-    constexpr uint32_t TMEM_COLS = DUAL ? 256 : 128;
+    const bool two = halves == 2 && M - m0 > TC_BM;            // second 128-row half in use
+    constexpr uint32_t TMEM_COLS = DUAL ? 512 : 256;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             skn_mbar_init(&full_bar[s], 8);      // one arrival per producer warp
             skn_mbar_init(&empty_bar[s], 1);     // one tcgen05.commit
         }
         skn_mbar_init(&accum_bar, 1);
-        fail_flag = 0;
         skn_fence_mbar_init();
     }
     if (warp == 8) tc_alloc(&tmem_slot, TMEM_COLS);
@@ -167,31 +308,49 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
         // ---------------- producers ----------------
         const bool is_b = warp < 4;
         const int r = threadIdx.x & 127;                    // row of the tile this thread fills
-        const int grow = is_b ? n0 + r : m0 + r;            // weight row / activation row
-        const bool valid = is_b ? (grow < N) : (grow < M);
-        const uint8_t *wrow = W + (int64_t)(valid ? grow : 0) * pitch;
-        const uint8_t *wrow2 = DUAL ? W2 + (int64_t)(valid ? grow : 0) * pitch : nullptr;
-        const __nv_bfloat16 *arow = A + (int64_t)(valid ? grow : 0) * K;
+        const bool b_valid = n0 + r < N;
+        const uint8_t *wrow = W + (int64_t)(b_valid ? n0 + r : 0) * pitch;
+        const uint8_t *wrow2 = DUAL ? W2 + (int64_t)(b_valid ? n0 + r : 0) * pitch : nullptr;
+        const bool a0_valid = m0 + r < M, a1_valid = m0 + TC_BM + r < M;
+        const __nv_bfloat16 *arow0 = A + (int64_t)(a0_valid ? m0 + r : 0) * K;
+        const __nv_bfloat16 *arow1 = A + (int64_t)(a1_valid ? m0 + TC_BM + r : 0) * K;
         bool failed = false;
+        TcRaw<TYPE> raw, raw2, nraw, nraw2;      // this stage's raw weights and the next stage's
+        if (is_b) {
+            tc_load_row<TYPE>(wrow, 0, b_valid, raw);
+            if (DUAL) tc_load_row<TYPE>(wrow2, 0, b_valid, raw2);
+        }
         for (int it = 0; it < ksteps; ++it) {
-            const int s = it % TC_STAGES;
-            const uint32_t ph = (uint32_t)(it / TC_STAGES) & 1u;
+            const int s = it % STAGES;
+            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+            const int k0 = it * TC_BK;
+            if (is_b && it + 1 < ksteps) {       // the loads of the next stage fly during this decode
+                tc_load_row<TYPE>(wrow, k0 + TC_BK, b_valid, nraw);
+                if (DUAL) tc_load_row<TYPE>(wrow2, k0 + TC_BK, b_valid, nraw2);
+            }
             if (!failed && !skn_mbar_wait(&empty_bar[s], ph ^ 1u)) {
                 failed = true;
                 atomicExch(status, SKN_ERR_TIMEOUT);
-                atomicExch(&fail_flag, 1);
             }
             uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
-            const int k0 = it * TC_BK;
             if (is_b) {
-                tc_dequant_row<TYPE>(wrow, k0, stage + TC_TILE_BYTES, r, valid);
-                if (DUAL) tc_dequant_row<TYPE>(wrow2, k0, stage + 2 * TC_TILE_BYTES, r, valid);
+                tc_decode_row<TYPE>(raw, wrow, k0, stage + 2 * TC_TILE_BYTES, r, b_valid);
+                if (DUAL) tc_decode_row<TYPE>(raw2, wrow2, k0, stage + 3 * TC_TILE_BYTES, r, b_valid);
+                raw = nraw;
+                if (DUAL) raw2 = nraw2;
             } else {
-                const uint4 *src = reinterpret_cast<const uint4 *>(arow + k0);
+                const uint4 *src0 = reinterpret_cast<const uint4 *>(arow0 + k0);
+                const uint4 *src1 = reinterpret_cast<const uint4 *>(arow1 + k0);
+                uint4 v0[8], v1[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 v = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
-                    tc_store_chunk(stage, r, c, v);
+                    v0[c] = a0_valid ? __ldg(src0 + c) : make_uint4(0u, 0u, 0u, 0u);
+                    v1[c] = (two && a1_valid) ? __ldg(src1 + c) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    tc_store_chunk(stage, r, c, v0[c]);
+                    if (two) tc_store_chunk(stage + TC_TILE_BYTES, r, c, v1[c]);
                 }
             }
             skn_fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async proxy
@@ -203,57 +362,62 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
         const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
         bool failed = false;
         for (int it = 0; it < ksteps; ++it) {
-            const int s = it % TC_STAGES;
-            const uint32_t ph = (uint32_t)(it / TC_STAGES) & 1u;
+            const int s = it % STAGES;
+            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
             if (!failed && !skn_mbar_wait(&full_bar[s], ph)) {
                 failed = true;
                 atomicExch(status, SKN_ERR_TIMEOUT);
-                atomicExch(&fail_flag, 1);
             }
             tc_fence_after();
-            const uint32_t a_addr = skn_smem_u32(smem + (size_t)s * STAGE_BYTES);
-            const uint64_t adesc = tc_smem_desc(a_addr);
-            const uint64_t bdesc = tc_smem_desc(a_addr + TC_TILE_BYTES);
-            const uint64_t bdesc2 = tc_smem_desc(a_addr + 2 * TC_TILE_BYTES);
+            const uint32_t base = skn_smem_u32(smem + (size_t)s * STAGE_BYTES);
+            const uint64_t a0desc = tc_smem_desc(base), a1desc = tc_smem_desc(base + TC_TILE_BYTES);
+            const uint64_t bdesc = tc_smem_desc(base + 2 * TC_TILE_BYTES);
+            const uint64_t b2desc = tc_smem_desc(base + 3 * TC_TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; ++k) {
                 const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
                 // advancing 16 bf16 (32 bytes) along K inside the swizzle atom = +2 in the address field
-                tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
-                if (DUAL) tc_mma_bf16(tmem_base + 128, adesc + 2 * k, bdesc2 + 2 * k, idesc, acc);
+                tc_mma_bf16(tmem_base, a0desc + 2 * k, bdesc + 2 * k, idesc, acc);
+                if (two) tc_mma_bf16(tmem_base + 128, a1desc + 2 * k, bdesc + 2 * k, idesc, acc);
+                if (DUAL) {
+                    tc_mma_bf16(tmem_base + 256, a0desc + 2 * k, b2desc + 2 * k, idesc, acc);
+                    if (two) tc_mma_bf16(tmem_base + 384, a1desc + 2 * k, b2desc + 2 * k, idesc, acc);
+                }
             }
             tc_commit(&empty_bar[s]);    // frees the stage once these MMAs have read it
         }
-        tc_commit(&accum_bar);           // all MMAs done: the accumulator is complete
+        tc_commit(&accum_bar);           // all MMAs done: the accumulators are complete
     }
 
     // ---------------- epilogue: warps 0-3, TMEM lane = token row ----------------
     if (warp < 4) {
-        bool ok = skn_mbar_wait(&accum_bar, 0u);
-        if (!ok) {
-            atomicExch(status, SKN_ERR_TIMEOUT);
-            atomicExch(&fail_flag, 1);
-        }
+        const bool ok = skn_mbar_wait(&accum_bar, 0u);
+        if (!ok) atomicExch(status, SKN_ERR_TIMEOUT);
         tc_fence_after();
-        const int m = m0 + warp * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        if (ok) {
+        for (int half = 0; half < (two ? 2 : 1) && ok; ++half) {
+            const int m = m0 + half * TC_BM + warp * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < TC_BN; c0 += 32) {
                 uint32_t acc[32];
-                tc_ld32(lane_addr + c0, acc);
+                tc_ld32(lane_addr + half * 128 + c0, acc);
                 if (DUAL) {
                     uint32_t up[32];
-                    tc_ld32(lane_addr + 128 + c0, up);
+                    tc_ld32(lane_addr + 256 + half * 128 + c0, up);
                     if (m < M) {
                         __nv_bfloat16 *dst = out_bf16 + (int64_t)m * ld_out + n0 + c0;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            if (n0 + c0 + i < N) {      // N is even
-                                const float g0 = __uint_as_float(acc[i]), g1 = __uint_as_float(acc[i + 1]);
-                                const float h0 = g0 / (1.f + expf(-g0)) * __uint_as_float(up[i]);
-                                const float h1 = g1 / (1.f + expf(-g1)) * __uint_as_float(up[i + 1]);
-                                *reinterpret_cast<uint32_t *>(dst + i) = tc_pack_bf16(h0, h1);
+                        for (int i = 0; i < 32; i += 8) {
+                            if (n0 + c0 + i < N) {      // N is a multiple of 8 on this path
+                                uint32_t hv[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float g0 = __uint_as_float(acc[i + 2 * j]), g1 = __uint_as_float(acc[i + 2 * j + 1]);
+                                    const float h0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(up[i + 2 * j]);
+                                    const float h1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(up[i + 2 * j + 1]);
+                                    hv[j] = tc_pack_bf16(h0, h1);
+                                }
+                                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
                             }
                         }
                     }
@@ -265,8 +429,8 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
                             float4 v = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
                                                    __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
                             if (bias) {
-                                const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + n0 + c0 + i));
-                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                                const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n0 + c0 + i));
+                                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
                             }
                             *reinterpret_cast<float4 *>(dst + i) = v;
                         }
@@ -290,7 +454,7 @@ static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_ten
                              const float *bias, float *out_f32, __nv_bfloat16 *out_bf16, int64_t ld_out,
                              int32_t *status, cudaStream_t stream) {
     auto kern = skn_matmul_tc_kernel<TYPE, DUAL>;
-    const size_t smem = (size_t)TC_STAGES * (DUAL ? 3 : 2) * TC_TILE_BYTES + 1024;
+    const size_t smem = (size_t)(DUAL ? 3 * 4 : 4 * 3) * TC_TILE_BYTES + 1024;
     static bool attr_done[64] = {false};   // per device
     int dev = 0;
     cudaError_t e0 = cudaGetDevice(&dev);
@@ -300,9 +464,15 @@ static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_ten
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    const dim3 grid((unsigned)((M + TC_BM - 1) / TC_BM), (unsigned)((w->n_rows + TC_BN - 1) / TC_BN));
+    // 256-row CTAs share each dequantised weight tile between two accumulators; when that leaves
+    // SMs idle (few feature tiles), 128-row CTAs double the CTA count instead
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t ntiles = (w->n_rows + TC_BN - 1) / TC_BN;
+    int halves = (M > TC_BM && ntiles * ((M + 2 * TC_BM - 1) / (2 * TC_BM)) >= sms) ? 2 : 1;
+    const dim3 grid((unsigned)((M + halves * TC_BM - 1) / (halves * TC_BM)), (unsigned)ntiles);
     kern<<<grid, TC_THREADS, smem, stream>>>(A, M, K, w->d_blocks, w2 ? w2->d_blocks : nullptr, w->pitch, (int)w->n_rows,
-                                             bias, out_f32, out_bf16, ld_out, status);
+                                             bias, out_f32, out_bf16, ld_out, status, halves);
     return cudaGetLastError();
 }
 
@@ -320,7 +490,7 @@ static cudaError_t dispatch_tc(const __nv_bfloat16 *A, int M, int K, const skn_t
 }
 
 bool skn_tc_supported(const skn_tensor *w, int32_t M) {
-    return M >= 1 && (w->n_cols % TC_BK) == 0 && w->n_cols >= TC_BK && (w->n_rows % 4) == 0 &&
+    return M >= 1 && (w->n_cols % TC_BK) == 0 && w->n_cols >= TC_BK && (w->n_rows % 8) == 0 && (w->pitch % 16) == 0 &&
            (reinterpret_cast<uintptr_t>(w->d_blocks) & 1) == 0;
 }
 
