@@ -18,11 +18,12 @@
 #include "skn_blocks.cuh"
 #include "skn_ptx.cuh"
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;   // 16 KB, one operand tile
-constexpr int TC_THREADS = 9 * 32;
+constexpr int TC_THREADS = 10 * 32;   // 8 dequant warps, 1 MMA warp, 1 TMA warp
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ void tc_alloc(uint32_t *slot_smem, uint32_t ncols) {
@@ -63,6 +64,15 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 2-D tiled TMA load (no multicast) of a box at element coordinates (x = column, y = row); the
+// tensor map's 128-byte swizzle lays the box out exactly as tc_store_chunk does
+__device__ __forceinline__ void tc_tma_load_2d(void *dst_smem, const CUtensorMap *tmap, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(skn_smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(skn_smem_u32(bar))
+        : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major operand, rows of 64 bf16 (128 bytes) in 8-row
@@ -271,7 +281,7 @@ __global__ void skn_f32_to_bf16_kernel(const float *__restrict__ in, __nv_bfloat
 // [256,512) the same for W2.
 template <int TYPE, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const uint8_t *__restrict__ W,
+skn_matmul_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, int M, int K, const uint8_t *__restrict__ W,
                      const uint8_t *__restrict__ W2, int64_t pitch, int N, const float *__restrict__ bias,
                      float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_bf16, int64_t ld_out,
                      int32_t *__restrict__ status, int halves) {
@@ -292,7 +302,7 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            skn_mbar_init(&full_bar[s], 8);      // one arrival per producer warp
+            skn_mbar_init(&full_bar[s], DUAL ? 9 : 5);   // dequant warps of the stage + the TMA thread
             skn_mbar_init(&empty_bar[s], 1);     // one tcgen05.commit
         }
         skn_mbar_init(&accum_bar, 1);
@@ -305,60 +315,54 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
     const uint32_t tmem_base = tmem_slot;
 
     if (warp < 8) {
-        // ---------------- producers ----------------
-        const bool is_b = warp < 4;
-        const int r = threadIdx.x & 127;                    // row of the tile this thread fills
+        // ---------------- weight producers ----------------
+        // DUAL: warps 0-3 dequantise W, warps 4-7 W2, every stage.  Otherwise the two groups
+        // of four warps take the stages in turn.  Thread t fills tile row t & 127.
+        const int grp = warp >> 2;
+        const int r = threadIdx.x & 127;
         const bool b_valid = n0 + r < N;
-        const uint8_t *wrow = W + (int64_t)(b_valid ? n0 + r : 0) * pitch;
-        const uint8_t *wrow2 = DUAL ? W2 + (int64_t)(b_valid ? n0 + r : 0) * pitch : nullptr;
-        const bool a0_valid = m0 + r < M, a1_valid = m0 + TC_BM + r < M;
-        const __nv_bfloat16 *arow0 = A + (int64_t)(a0_valid ? m0 + r : 0) * K;
-        const __nv_bfloat16 *arow1 = A + (int64_t)(a1_valid ? m0 + TC_BM + r : 0) * K;
+        const uint8_t *wrow = ((DUAL && grp == 1) ? W2 : W) + (int64_t)(b_valid ? n0 + r : 0) * pitch;
+        const int tile_off = (DUAL && grp == 1) ? 3 * TC_TILE_BYTES : 2 * TC_TILE_BYTES;
+        const int step = DUAL ? 1 : 2, first = DUAL ? 0 : grp;
         bool failed = false;
-        TcRaw<TYPE> raw, raw2, nraw, nraw2;      // this stage's raw weights and the next stage's
-        if (is_b) {
-            tc_load_row<TYPE>(wrow, 0, b_valid, raw);
-            if (DUAL) tc_load_row<TYPE>(wrow2, 0, b_valid, raw2);
-        }
-        for (int it = 0; it < ksteps; ++it) {
+        TcRaw<TYPE> raw, nraw;                   // this turn's raw weights and the next turn's
+        if (first < ksteps) tc_load_row<TYPE>(wrow, first * TC_BK, b_valid, raw);
+        for (int it = first; it < ksteps; it += step) {
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
             const int k0 = it * TC_BK;
-            if (is_b && it + 1 < ksteps) {       // the loads of the next stage fly during this decode
-                tc_load_row<TYPE>(wrow, k0 + TC_BK, b_valid, nraw);
-                if (DUAL) tc_load_row<TYPE>(wrow2, k0 + TC_BK, b_valid, nraw2);
-            }
+            if (it + step < ksteps) tc_load_row<TYPE>(wrow, k0 + step * TC_BK, b_valid, nraw);   // flies during this decode
             if (!failed && !skn_mbar_wait(&empty_bar[s], ph ^ 1u)) {
                 failed = true;
                 atomicExch(status, SKN_ERR_TIMEOUT);
             }
-            uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
-            if (is_b) {
-                tc_decode_row<TYPE>(raw, wrow, k0, stage + 2 * TC_TILE_BYTES, r, b_valid);
-                if (DUAL) tc_decode_row<TYPE>(raw2, wrow2, k0, stage + 3 * TC_TILE_BYTES, r, b_valid);
-                raw = nraw;
-                if (DUAL) raw2 = nraw2;
-            } else {
-                const uint4 *src0 = reinterpret_cast<const uint4 *>(arow0 + k0);
-                const uint4 *src1 = reinterpret_cast<const uint4 *>(arow1 + k0);
-                uint4 v0[8], v1[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    v0[c] = a0_valid ? __ldg(src0 + c) : make_uint4(0u, 0u, 0u, 0u);
-                    v1[c] = (two && a1_valid) ? __ldg(src1 + c) : make_uint4(0u, 0u, 0u, 0u);
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    tc_store_chunk(stage, r, c, v0[c]);
-                    if (two) tc_store_chunk(stage + TC_TILE_BYTES, r, c, v1[c]);
-                }
-            }
+            tc_decode_row<TYPE>(raw, wrow, k0, smem + (size_t)s * STAGE_BYTES + tile_off, r, b_valid);
+            raw = nraw;
             skn_fence_proxy_async();     // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) skn_mbar_arrive(&full_bar[s]);
         }
+    } else if (warp == 9) {
+        // ---------------- activation producer: one thread, TMA ----------------
+        if (lane == 0) {
+            bool failed = false;
+            const uint32_t bytes = (two ? 2u : 1u) * TC_TILE_BYTES;
+            for (int it = 0; it < ksteps; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!failed && !skn_mbar_wait(&empty_bar[s], ph ^ 1u)) {
+                    failed = true;
+                    atomicExch(status, SKN_ERR_TIMEOUT);
+                }
+                uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
+                skn_mbar_expect_tx(&full_bar[s], bytes);
+                // rows beyond M are filled with zeros by the tensor map
+                tc_tma_load_2d(stage, &tmap_a, it * TC_BK, m0, &full_bar[s]);
+                if (two) tc_tma_load_2d(stage + TC_TILE_BYTES, &tmap_a, it * TC_BK, m0 + TC_BM, &full_bar[s]);
+            }
+        }
     } else if (lane == 0) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer (warp 8) ----------------
         const uint32_t idesc = tc_idesc(TC_BM, TC_BN);
         bool failed = false;
         for (int it = 0; it < ksteps; ++it) {
@@ -449,6 +453,32 @@ skn_matmul_tc_kernel(const __nv_bfloat16 *__restrict__ A, int M, int K, const ui
 }
 
 // ---------------------------------------------------------------------------------------------
+typedef CUresult (*skn_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                        const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map of the bf16 activations [M][K]: boxes of 64 columns x 128 rows, 128-byte swizzle,
+// rows past M read as zeros.
+static cudaError_t make_a_tmap(const __nv_bfloat16 *A, int M, int K, CUtensorMap *out) {
+    static skn_encode_tiled_fn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        encode = (skn_encode_tiled_fn)fn;
+    }
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(A), gdim, gstride, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <int TYPE, bool DUAL>
 static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_tensor *w, const skn_tensor *w2,
                              const float *bias, float *out_f32, __nv_bfloat16 *out_bf16, int64_t ld_out,
@@ -464,6 +494,9 @@ static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_ten
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
+    CUtensorMap tmap;
+    e0 = make_a_tmap(A, M, K, &tmap);
+    if (e0 != cudaSuccess) return e0;
     // 256-row CTAs share each dequantised weight tile between two accumulators; when that leaves
     // SMs idle (few feature tiles), 128-row CTAs double the CTA count instead
     int sms = 148;
@@ -471,7 +504,7 @@ static cudaError_t launch_tc(const __nv_bfloat16 *A, int M, int K, const skn_ten
     const int64_t ntiles = (w->n_rows + TC_BN - 1) / TC_BN;
     int halves = (M > TC_BM && ntiles * ((M + 2 * TC_BM - 1) / (2 * TC_BM)) >= sms) ? 2 : 1;
     const dim3 grid((unsigned)((M + halves * TC_BM - 1) / (halves * TC_BM)), (unsigned)ntiles);
-    kern<<<grid, TC_THREADS, smem, stream>>>(A, M, K, w->d_blocks, w2 ? w2->d_blocks : nullptr, w->pitch, (int)w->n_rows,
+    kern<<<grid, TC_THREADS, smem, stream>>>(tmap, M, K, w->d_blocks, w2 ? w2->d_blocks : nullptr, w->pitch, (int)w->n_rows,
                                              bias, out_f32, out_bf16, ld_out, status, halves);
     return cudaGetLastError();
 }
