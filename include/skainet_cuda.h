@@ -221,6 +221,47 @@ int64_t skn_attn_scratch_bytes(const skn_kvcache *kv, int32_t n_q_heads);
 int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, float scale,
                                     float *out_dev);
 
+/* Multi-token forms used by prefill (no counterpart in the reference).
+ * skn_kv_append_many_dev: T tokens per sequence, k_new / v_new [batch][T][n_kv_heads][head_dim];
+ *   never wraps the ring: host_len_upper (the caller's bound on the current lengths) + T must
+ *   fit the capacity.
+ * skn_attn_causal_dev: q, out [batch][T][n_q_heads][head_dim]; query t of the T most recent
+ *   positions attends to the cache up to its own token (T = 1 is skn_attn_decode_dev).  Scratch:
+ *   T * skn_attn_scratch_bytes() bytes, or NULL for the context's own. */
+int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const float *v_new_dev, int32_t T,
+                               int32_t host_len_upper);
+int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                            float *out_dev, void *scratch_dev);
+
+/* ---- Llama-style decoder ---------------------------------------------------------------------
+ * RMSNorm -> Q/K/V -> rotary embedding (interleaved pairs) -> KV append -> grouped-query
+ * attention -> output projection -> residual -> RMSNorm -> SwiGLU FFN -> residual; final norm,
+ * LM head, greedy argmax.  The reference contains no decoder, attention, RoPE or RMSNorm
+ * (model-zoo holds only an MNIST loader, model-zoo/src/commonMain/kotlin/sk/ai/net/io/data/mnist);
+ * this is the loop of Module.forward calls (core/src/commonMain/kotlin/sk/ai/net/nn/Module.kt:6-16,
+ * nn/topology/MLP.kt:13-19) a caller would write, kept in the library so that a step is a
+ * fixed launch sequence.  Every forward processes all `max_batch` sequences with the same
+ * number of new tokens.  Weight tensors are borrowed and must outlive the decoder. */
+typedef struct skn_llama skn_llama;
+int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
+                         int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
+                         int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_llama **out);
+int32_t skn_llama_destroy(skn_llama *m);
+int32_t skn_llama_set_layer(skn_llama *m, int32_t layer, const skn_tensor *wq, const skn_tensor *wk,
+                            const skn_tensor *wv, const skn_tensor *wo, const skn_tensor *w_gate,
+                            const skn_tensor *w_up, const skn_tensor *w_down, const float *attn_norm_host,
+                            const float *ffn_norm_host);
+int32_t skn_llama_set_head(skn_llama *m, const skn_tensor *tok_embd, const float *out_norm_host,
+                           const skn_tensor *output);
+int32_t skn_llama_reset(skn_llama *m);
+/* tokens [max_batch][T] int32; NULL with T == 1 feeds back the ids of the previous forward.
+ * next (greedy token per sequence) and logits ([max_batch][vocab], last position) may be NULL. */
+int32_t skn_llama_forward(skn_llama *m, const int32_t *tokens_host, int32_t T, int32_t *next_host,
+                          float *logits_host);
+int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T);
+/* tokens cached per sequence so far (-1 on a bad handle) */
+int32_t skn_llama_position(const skn_llama *m);
+
 #ifdef __cplusplus
 }
 #endif

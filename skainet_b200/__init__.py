@@ -8,3 +8,6 @@ from .tensor import (Context, KVCache, GGML_QUANT_SIZES, GGMLQuantizationType, Q
 
 __all__ = ["Context", "KVCache", "GGML_QUANT_SIZES", "GGMLQuantizationType", "QK_K", "QuantLinear", "QuantTensor", "Shape",
            "SknError", "ffn_swiglu", "quant_shape_to_byte_shape"]
+from .llama import LlamaConfig, LlamaDecoder  # noqa: E402
+
+__all__ += ["LlamaConfig", "LlamaDecoder"]

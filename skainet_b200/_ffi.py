@@ -50,6 +50,17 @@ SIGNATURES = {
     "skn_attn_decode": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
     "skn_attn_decode_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp, c_vp]),
     "skn_attn_scratch_bytes": (c_i64, [c_vp, c_i32]),
+    "skn_kv_append_many_dev": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i32]),
+    "skn_attn_causal_dev": (c_i32, [c_vp, c_vp, c_i32, c_i32, ctypes.c_float, c_vp, c_vp]),
+    "skn_llama_create": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.c_float, ctypes.c_float,
+                                 c_i32, c_i32, c_i32, P(c_vp)]),
+    "skn_llama_destroy": (c_i32, [c_vp]),
+    "skn_llama_set_layer": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "skn_llama_set_head": (c_i32, [c_vp, c_vp, c_vp, c_vp]),
+    "skn_llama_reset": (c_i32, [c_vp]),
+    "skn_llama_forward": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
+    "skn_llama_forward_dev": (c_i32, [c_vp, c_vp, c_i32]),
+    "skn_llama_position": (c_i32, [c_vp]),
     "skn_attn_decode_noalloc_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
 }
 

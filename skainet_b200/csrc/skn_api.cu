@@ -100,6 +100,7 @@ int32_t skn_ctx_destroy(skn_ctx *ctx) {
     if (ctx->d_stage_in) cudaFree(ctx->d_stage_in);
     if (ctx->d_stage_out) cudaFree(ctx->d_stage_out);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    if (ctx->d_scratch2) cudaFree(ctx->d_scratch2);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);

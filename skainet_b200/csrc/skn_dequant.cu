@@ -37,3 +37,32 @@ cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitc
     }
     return cudaGetLastError();
 }
+
+// out[m][:] = dequantised row ids[m] of a quantized [vocab][d] table (token embedding lookup)
+template <int TYPE>
+__global__ void __launch_bounds__(128)
+skn_embed_kernel(const uint8_t *__restrict__ blocks, int64_t pitch, int64_t n_rows, int64_t groups_per_row,
+                 const int32_t *__restrict__ ids, float *__restrict__ out) {
+    int64_t row = ids[blockIdx.x];
+    if (row < 0 || row >= n_rows) row = 0;         // out-of-range ids read row 0 (no fault)
+    for (int64_t g = threadIdx.x; g < groups_per_row; g += blockDim.x) {
+        float w[32];
+        decode_group<TYPE>(blocks + row * pitch, g, w);
+        float4 *o = reinterpret_cast<float4 *>(out + ((int64_t)blockIdx.x * groups_per_row + g) * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[q] = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+}
+
+cudaError_t skn_launch_embed(const skn_tensor *emb, const int32_t *ids, int M, float *out, cudaStream_t st) {
+    if (M == 0) return cudaSuccess;
+    const int64_t gpr = emb->n_cols / 32;
+    switch (emb->type) {
+    case SKN_TYPE_Q4_0: skn_embed_kernel<SKN_TYPE_Q4_0><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_Q8_0: skn_embed_kernel<SKN_TYPE_Q8_0><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_Q4_K: skn_embed_kernel<SKN_TYPE_Q4_K><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_Q6_K: skn_embed_kernel<SKN_TYPE_Q6_K><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}

@@ -18,3 +18,125 @@ cudaError_t skn_launch_silu_mul(const float *g, const float *u, float *h, int64_
     skn_silu_mul_kernel<<<(unsigned)blocks, 256, 0, stream>>>(g, u, h, n);
     return cudaGetLastError();
 }
+
+// ---- decoder glue (K8) ---------------------------------------------------------------------
+// y[m][:] = x[m][:] / sqrt(mean(x[m]^2) + eps) * gain[:]; one CTA per row
+__global__ void __launch_bounds__(256)
+skn_rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ gain, float *__restrict__ y, int D, float eps) {
+    __shared__ float red[8];
+    const float *xr = x + (size_t)blockIdx.x * D;
+    float *yr = y + (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    const float r = rsqrtf(tot / (float)D + eps);
+    for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        const float4 g = *reinterpret_cast<const float4 *>(gain + i);
+        *reinterpret_cast<float4 *>(yr + i) = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+    }
+}
+
+// Rotary embedding in place on x [M][H][D]: pairs (2i, 2i+1) of every head rotate by
+// pos * theta^(-2i/D); row m = b * T + t has position len[b] + t (len = tokens already cached).
+__global__ void skn_rope_kernel(float *__restrict__ x, const int32_t *__restrict__ len, int T, int H, int D,
+                                double log2_theta, int64_t total_pairs) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_pairs; i += (int64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(i % (D / 2));
+        const int64_t mh = i / (D / 2);
+        const int64_t m = mh / H;
+        const int pos = len[m / T] + (int)(m % T);
+        // angle in double: at position 4096 an fp32 angle is already off by ~5e-4 rad
+        const double ang = (double)pos * exp2(-(double)log2_theta * (2.0 * (double)p / (double)D));
+        double sd, cd;
+        sincos(ang, &sd, &cd);
+        const float sn = (float)sd, cs = (float)cd;
+        float2 *v = reinterpret_cast<float2 *>(x) + i;
+        const float2 a = *v;
+        *v = make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+    }
+}
+
+__global__ void skn_add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 u = reinterpret_cast<const float4 *>(a)[i], v = reinterpret_cast<const float4 *>(b)[i];
+        reinterpret_cast<float4 *>(out)[i] = make_float4(u.x + v.x, u.y + v.y, u.z + v.z, u.w + v.w);
+    }
+}
+
+// out[m][:] = rows[src[m]][:] (row gather of fp32 matrices; used to pick the last position of
+// every sequence before the LM head)
+__global__ void skn_gather_rows_kernel(const float *__restrict__ in, float *__restrict__ out, int D, int T) {
+    const float *src = in + ((size_t)blockIdx.x * T + (T - 1)) * D;
+    float *dst = out + (size_t)blockIdx.x * D;
+    for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4)
+        *reinterpret_cast<float4 *>(dst + i) = *reinterpret_cast<const float4 *>(src + i);
+}
+
+// ids[m] = argmax_v logits[m][v] (first maximum wins, as a sequential scan would give)
+__global__ void __launch_bounds__(256)
+skn_argmax_kernel(const float *__restrict__ logits, int V, int32_t *__restrict__ ids) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const float *row = logits + (size_t)blockIdx.x * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        ids[blockIdx.x] = bi;
+    }
+}
+
+static int glue_blocks(int64_t n, int sm_count) {
+    int64_t b = (n + 255) / 256;
+    if (b > (int64_t)sm_count * 8) b = (int64_t)sm_count * 8;
+    return (int)(b < 1 ? 1 : b);
+}
+
+cudaError_t skn_launch_rmsnorm(const float *x, const float *gain, float *y, int M, int D, float eps, cudaStream_t st) {
+    if (M == 0) return cudaSuccess;
+    skn_rmsnorm_kernel<<<M, 256, 0, st>>>(x, gain, y, D, eps);
+    return cudaGetLastError();
+}
+cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, int D, float theta, int sm_count, cudaStream_t st) {
+    const int64_t pairs = (int64_t)M * H * (D / 2);
+    if (pairs == 0) return cudaSuccess;
+    skn_rope_kernel<<<glue_blocks(pairs, sm_count), 256, 0, st>>>(x, len, T, H, D, log2((double)theta), pairs);
+    return cudaGetLastError();
+}
+cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    skn_add_kernel<<<glue_blocks(n / 4, sm_count), 256, 0, st>>>(a, b, out, n / 4);
+    return cudaGetLastError();
+}
+cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int D, cudaStream_t st) {
+    if (B == 0) return cudaSuccess;
+    skn_gather_rows_kernel<<<B, 256, 0, st>>>(in, out, D, T);
+    return cudaGetLastError();
+}
+cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, cudaStream_t st) {
+    if (M == 0) return cudaSuccess;
+    skn_argmax_kernel<<<M, 256, 0, st>>>(logits, V, ids);
+    return cudaGetLastError();
+}

@@ -25,7 +25,8 @@ struct skn_ctx {
     // staging for the host-pointer entry points (grown on demand)
     void *d_stage_in;  size_t d_stage_in_bytes;
     void *d_stage_out; size_t d_stage_out_bytes;
-    void *d_scratch;   size_t d_scratch_bytes;   // kernel scratch (split partials etc.)
+    void *d_scratch;   size_t d_scratch_bytes;   // kernel scratch (bf16 operands, FFN intermediates)
+    void *d_scratch2;  size_t d_scratch2_bytes;  // attention split partials
     char err[512];
 };
 
@@ -86,3 +87,11 @@ cudaError_t skn_launch_matmul_tc(skn_ctx *ctx, const skn_tensor *w, const void *
 cudaError_t skn_launch_gate_up_tc(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const void *a_bf16,
                                   int32_t M, void *h_bf16, cudaStream_t stream);
 cudaError_t skn_launch_silu_mul(const float *g, const float *u, float *h, int64_t n, int sm_count, cudaStream_t stream);
+
+// decoder glue (skn_glue.cu)
+cudaError_t skn_launch_rmsnorm(const float *x, const float *gain, float *y, int M, int D, float eps, cudaStream_t st);
+cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, int D, float theta, int sm_count, cudaStream_t st);
+cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st);
+cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int D, cudaStream_t st);
+cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, cudaStream_t st);
+cudaError_t skn_launch_embed(const skn_tensor *emb, const int32_t *ids, int M, float *out, cudaStream_t st);

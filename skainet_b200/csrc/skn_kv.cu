@@ -59,6 +59,29 @@ __global__ void skn_kv_append_kernel(float *__restrict__ kc, float *__restrict__
     }
 }
 
+// T new tokens per sequence: k_new, v_new are [batch][T][Hkv][D]; token t goes to ring slot
+// (start + len + t) % cap.  The lengths are advanced afterwards by skn_kv_advance_kernel, so
+// every CTA of this launch reads the same old length.  The caller guarantees len + T <= cap.
+__global__ void skn_kv_append_many_kernel(float *__restrict__ kc, float *__restrict__ vc, const int32_t *__restrict__ len,
+                                          const int32_t *__restrict__ start, const float *__restrict__ k_new,
+                                          const float *__restrict__ v_new, int Hkv, int D, int cap, int T) {
+    const int b = blockIdx.y, t = blockIdx.x;
+    const int slot = (start[b] + len[b] + t) % cap;
+    const int n4 = Hkv * D / 4;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const int h = (i * 4) / D, d = (i * 4) % D;
+        const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t src = (((size_t)b * T + t) * Hkv + h) * D + d;
+        *reinterpret_cast<float4 *>(kc + dst) = *reinterpret_cast<const float4 *>(k_new + src);
+        *reinterpret_cast<float4 *>(vc + dst) = *reinterpret_cast<const float4 *>(v_new + src);
+    }
+}
+
+__global__ void skn_kv_advance_kernel(int32_t *__restrict__ len, int B, int T, int cap) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) len[b] = min(cap, len[b] + T);
+}
+
 __global__ void skn_kv_gather_kernel(const float *__restrict__ kc, const float *__restrict__ vc,
                                      const int32_t *__restrict__ start, int b, int Hkv, int D, int cap, int pos0,
                                      int count, float *__restrict__ k_out, float *__restrict__ v_out) {
@@ -154,7 +177,7 @@ template <int D, int G, int TT>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
                       const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
-                      float scale, float *__restrict__ part, int S) {
+                      float scale, float *__restrict__ part, int S, int tq) {
     constexpr int VEC = D / 32;
     constexpr int NV = TT * G;
     constexpr int REP = 32 / NV;                 // lanes holding the same (token, head) score
@@ -164,9 +187,11 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_o[ATT_WARPS][G][D];
 
-    const int sp = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // blockIdx.z = sequence * tq + t: query t of the tq most recent positions of its sequence
+    // sees the cache up to and including its own token (tq = 1: plain decode)
+    const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = len[b];
+    const int L = max(0, len[b] - (tq - 1 - bq % tq));
     const int t0 = sp * ATT_CHUNK;
     if (t0 >= L) return;
     const int nt = min(ATT_CHUNK, L - t0);
@@ -178,7 +203,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     float qv[G][VEC];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        VecLoad<VEC>::ld(q + ((size_t)b * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
+        VecLoad<VEC>::ld(q + ((size_t)bq * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) qv[g][e] *= scale;
     }
@@ -297,7 +322,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
         float a = 0.f;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; ++w) a += s_o[w][g][d];
-        float *rec = part + (((size_t)b * Hq + kvh * G + g) * S + sp) * (D + 2);
+        float *rec = part + (((size_t)bq * Hq + kvh * G + g) * S + sp) * (D + 2);
         rec[2 + d] = a;
         if (d == 0) { rec[0] = s_m[g]; rec[1] = s_l[g]; }
     }
@@ -305,9 +330,9 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
 
 template <int D>
 __global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
-                                      float *__restrict__ out) {
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int L = len[b];
+                                      float *__restrict__ out, int tq) {
+    const int h = blockIdx.x, b = blockIdx.y;          // b = sequence * tq + t
+    const int L = max(0, len[b / tq] - (tq - 1 - b % tq));
     const int ns = (L + ATT_CHUNK - 1) / ATT_CHUNK;
     const float *rec = part + ((size_t)b * Hq + h) * S * (D + 2);
     float m = -INFINITY;
@@ -325,33 +350,33 @@ __global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int3
 
 template <int D, int G>
 static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scale, float *part, int S, float *out,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int tq) {
     constexpr int TT = (G >= 8) ? 4 : 8;
-    const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)kv->batch);
+    const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)(kv->batch * tq));
     skn_attn_split_kernel<D, G, TT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
-                                                                        kv->n_kv_heads, kv->capacity, scale, part, S);
+                                                                        kv->n_kv_heads, kv->capacity, scale, part, S, tq);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)kv->batch);
-    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out);
+    const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)(kv->batch * tq));
+    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq);
     return cudaGetLastError();
 }
 
 static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int S,
-                                 float *out, cudaStream_t st) {
+                                 float *out, cudaStream_t st, int tq = 1) {
     if (kv->head_dim == 128) {
         switch (G) {
-        case 1: return launch_attn<128, 1>(kv, q, scale, part, S, out, st);
-        case 2: return launch_attn<128, 2>(kv, q, scale, part, S, out, st);
-        case 4: return launch_attn<128, 4>(kv, q, scale, part, S, out, st);
-        case 8: return launch_attn<128, 8>(kv, q, scale, part, S, out, st);
+        case 1: return launch_attn<128, 1>(kv, q, scale, part, S, out, st, tq);
+        case 2: return launch_attn<128, 2>(kv, q, scale, part, S, out, st, tq);
+        case 4: return launch_attn<128, 4>(kv, q, scale, part, S, out, st, tq);
+        case 8: return launch_attn<128, 8>(kv, q, scale, part, S, out, st, tq);
         }
     } else if (kv->head_dim == 64) {
         switch (G) {
-        case 1: return launch_attn<64, 1>(kv, q, scale, part, S, out, st);
-        case 2: return launch_attn<64, 2>(kv, q, scale, part, S, out, st);
-        case 4: return launch_attn<64, 4>(kv, q, scale, part, S, out, st);
-        case 8: return launch_attn<64, 8>(kv, q, scale, part, S, out, st);
+        case 1: return launch_attn<64, 1>(kv, q, scale, part, S, out, st, tq);
+        case 2: return launch_attn<64, 2>(kv, q, scale, part, S, out, st, tq);
+        case 4: return launch_attn<64, 4>(kv, q, scale, part, S, out, st, tq);
+        case 8: return launch_attn<64, 8>(kv, q, scale, part, S, out, st, tq);
         }
     }
     return cudaErrorInvalidValue;
@@ -537,9 +562,9 @@ int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
     const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
     float *part = (float *)scratch_dev;
     if (!part) {
-        rc = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads));
+        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads));
         if (rc) return rc;
-        part = (float *)ctx->d_scratch;
+        part = (float *)ctx->d_scratch2;
     }
     SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream));
     return SKN_OK;
@@ -561,6 +586,53 @@ int32_t skn_attn_decode(skn_kvcache *kv, const float *q_host, int32_t n_q_heads,
     if (rc) return rc;
     SKN_CUDA(ctx, cudaMemcpyAsync(out_host, ctx->d_stage_out, n, cudaMemcpyDeviceToHost, ctx->stream));
     return skn_sync(ctx);
+}
+
+// Append T tokens per sequence (k_new, v_new: [batch][T][n_kv_heads][head_dim] on the device).
+// host_len_upper is the caller's knowledge of the longest sequence before the call; the call
+// is refused when host_len_upper + T would not fit the ring (a multi-token append never wraps).
+int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const float *v_new_dev, int32_t T,
+                               int32_t host_len_upper) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if (T < 0 || host_len_upper < 0) return skn_fail(ctx, SKN_ERR_ARG, "negative argument");
+    if (T == 0) return SKN_OK;
+    if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    if ((((uintptr_t)k_new_dev) | ((uintptr_t)v_new_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "k/v must be 16-byte aligned");
+    if ((int64_t)host_len_upper + T > kv->capacity)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    skn_kv_append_many_kernel<<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
+        kv->d_k, kv->d_v, kv->d_len, kv->d_start, k_new_dev, v_new_dev, kv->n_kv_heads, kv->head_dim, kv->capacity, T);
+    SKN_CUDA(ctx, cudaGetLastError());
+    skn_kv_advance_kernel<<<(kv->batch + 127) / 128, 128, 0, ctx->stream>>>(kv->d_len, kv->batch, T, kv->capacity);
+    SKN_CUDA(ctx, cudaGetLastError());
+    return SKN_OK;
+}
+
+// Causal attention of the T most recent positions of every sequence (after their K/V have been
+// appended): q, out are [batch][T][n_q_heads][head_dim]; query t attends to the cache up to its
+// own token.  T = 1 is skn_attn_decode_dev.  Scratch: T times skn_attn_scratch_bytes().
+int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                            float *out_dev, void *scratch_dev) {
+    int G = 0;
+    int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
+    if (rc) return rc;
+    skn_ctx *ctx = kv->ctx;
+    if (T < 1) return skn_fail(ctx, SKN_ERR_ARG, "T must be positive");
+    if ((int64_t)T * kv->batch > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch * T exceeds 65535");
+    if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
+        return skn_fail(ctx, SKN_ERR_ALIGN, "q, out and scratch must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    float *part = (float *)scratch_dev;
+    if (!part) {
+        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads) * T);
+        if (rc) return rc;
+        part = (float *)ctx->d_scratch2;
+    }
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream, T));
+    return SKN_OK;
 }
 
 // ---- decode attention without any allocation -----------------------------------------------

@@ -1,0 +1,258 @@
+// Llama-style decoder over the quantized kernels (configuration 5): RMSNorm -> Q/K/V ->
+// RoPE -> KV append -> attention -> output projection -> residual -> RMSNorm -> SwiGLU FFN ->
+// residual, then final norm, LM head and greedy argmax.  The reference has no decoder of
+// any kind (model-zoo holds only an MNIST loader); this is the host-side loop a Kotlin
+// caller would otherwise write over the individual entry points, kept in the library so
+// that one forward is a fixed sequence of launches on the context's stream (capturable in a
+// CUDA graph once the first call has sized the scratch buffers).
+#include "skn_internal.cuh"
+
+#include <new>
+#include <vector>
+
+#define SKN_MAGIC_LLAMA 0x736b6e6cu   // 'sknl'
+
+struct skn_llama_layer {
+    const skn_tensor *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    float *attn_norm, *ffn_norm;      // device, [d_model]
+    skn_kvcache *kv;
+};
+
+struct skn_llama {
+    uint32_t magic;
+    skn_ctx *ctx;
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn_dim, vocab, max_batch, max_ctx;
+    float rope_theta, rms_eps;
+    std::vector<skn_llama_layer> layers;
+    const skn_tensor *tok_embd, *output;
+    float *out_norm;
+    // activations for up to max_rows = max_batch * max_tokens rows
+    int32_t max_rows;
+    float *x, *h, *q, *k, *v, *att, *proj, *last, *logits;
+    int32_t *ids_in, *ids_out;
+    int32_t host_len;                 // tokens cached so far (the same for every sequence)
+};
+
+// from skn_kv.cu
+extern "C" int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k, const float *v, int32_t T, int32_t host_len_upper);
+extern "C" int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q, int32_t n_q_heads, int32_t T, float scale,
+                                       float *out, void *scratch);
+extern "C" int32_t skn_kv_info(const skn_kvcache *kv, int32_t *, int32_t *, int32_t *, int32_t *, void **, void **,
+                               void **len_dev, void **);
+
+static bool llama_ok(const skn_llama *m) { return m && m->magic == SKN_MAGIC_LLAMA && skn_ctx_ok(m->ctx); }
+
+static cudaError_t dev_alloc(float **p, size_t n) { return cudaMalloc((void **)p, n * sizeof(float)); }
+
+extern "C" {
+
+int32_t skn_llama_destroy(skn_llama *m);
+
+int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
+                         int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
+                         int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_llama **out) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    if (n_layers < 1 || d_model < 4 || n_heads < 1 || n_kv_heads < 1 || ffn_dim < 1 || vocab < 1 || max_batch < 1 ||
+        max_tokens < 1 || max_ctx < max_tokens)
+        return skn_fail(ctx, SKN_ERR_ARG, "invalid model geometry");
+    if (d_model % 4 || n_heads % n_kv_heads || (head_dim != 64 && head_dim != 128))
+        return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    skn_llama *m = new (std::nothrow) skn_llama();
+    if (!m) return skn_fail(ctx, SKN_ERR_OOM, "host allocation failed");
+    m->magic = SKN_MAGIC_LLAMA;
+    m->ctx = ctx;
+    m->n_layers = n_layers; m->d_model = d_model; m->n_heads = n_heads; m->n_kv_heads = n_kv_heads;
+    m->head_dim = head_dim; m->ffn_dim = ffn_dim; m->vocab = vocab; m->max_batch = max_batch; m->max_ctx = max_ctx;
+    m->rope_theta = rope_theta; m->rms_eps = rms_eps;
+    m->tok_embd = m->output = nullptr;
+    m->out_norm = nullptr;
+    m->max_rows = max_batch * max_tokens;
+    m->host_len = 0;
+    m->x = m->h = m->q = m->k = m->v = m->att = m->proj = m->last = m->logits = nullptr;
+    m->ids_in = m->ids_out = nullptr;
+    m->layers.resize(n_layers);
+    for (auto &l : m->layers) l = skn_llama_layer{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    cudaError_t e = cudaSetDevice(ctx->device);
+    const size_t R = (size_t)m->max_rows, qd = (size_t)n_heads * head_dim, kd = (size_t)n_kv_heads * head_dim;
+    if (e == cudaSuccess) e = dev_alloc(&m->x, R * d_model);
+    if (e == cudaSuccess) e = dev_alloc(&m->h, R * d_model);
+    if (e == cudaSuccess) e = dev_alloc(&m->q, R * qd);
+    if (e == cudaSuccess) e = dev_alloc(&m->k, R * kd);
+    if (e == cudaSuccess) e = dev_alloc(&m->v, R * kd);
+    if (e == cudaSuccess) e = dev_alloc(&m->att, R * qd);
+    if (e == cudaSuccess) e = dev_alloc(&m->proj, R * d_model);
+    if (e == cudaSuccess) e = dev_alloc(&m->last, (size_t)max_batch * d_model);
+    if (e == cudaSuccess) e = dev_alloc(&m->logits, (size_t)max_batch * vocab);
+    if (e == cudaSuccess) e = dev_alloc(&m->out_norm, d_model);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_in, sizeof(int32_t) * R);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_out, sizeof(int32_t) * max_batch);
+    int32_t rc = SKN_OK;
+    if (e != cudaSuccess) rc = skn_check_cuda(ctx, e, "decoder activation buffers");
+    for (int l = 0; l < n_layers && rc == SKN_OK; ++l) {
+        e = dev_alloc(&m->layers[l].attn_norm, d_model);
+        if (e == cudaSuccess) e = dev_alloc(&m->layers[l].ffn_norm, d_model);
+        if (e != cudaSuccess) { rc = skn_check_cuda(ctx, e, "decoder norm gains"); break; }
+        rc = skn_kv_create(ctx, max_batch, n_kv_heads, head_dim, max_ctx, &m->layers[l].kv);
+    }
+    if (rc != SKN_OK) {
+        skn_llama_destroy(m);
+        return rc;
+    }
+    *out = m;
+    return SKN_OK;
+}
+
+int32_t skn_llama_destroy(skn_llama *m) {
+    if (!m || m->magic != SKN_MAGIC_LLAMA) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    if (skn_ctx_ok(m->ctx)) {
+        cudaSetDevice(m->ctx->device);
+        cudaStreamSynchronize(m->ctx->stream);
+    }
+    float *bufs[] = {m->x, m->h, m->q, m->k, m->v, m->att, m->proj, m->last, m->logits, m->out_norm};
+    for (float *b : bufs) if (b) cudaFree(b);
+    if (m->ids_in) cudaFree(m->ids_in);
+    if (m->ids_out) cudaFree(m->ids_out);
+    for (auto &l : m->layers) {
+        if (l.attn_norm) cudaFree(l.attn_norm);
+        if (l.ffn_norm) cudaFree(l.ffn_norm);
+        if (l.kv) skn_kv_destroy(l.kv);
+    }
+    m->magic = 0;
+    delete m;
+    return SKN_OK;
+}
+
+}  // extern "C"
+
+static int32_t upload_gain(skn_llama *m, float *dst, const float *host) {
+    skn_ctx *ctx = m->ctx;
+    SKN_CUDA(ctx, cudaMemcpyAsync(dst, host, sizeof(float) * m->d_model, cudaMemcpyHostToDevice, ctx->stream));
+    SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SKN_OK;
+}
+
+static bool shape_is(const skn_tensor *t, const skn_ctx *ctx, int64_t rows, int64_t cols) {
+    return skn_tensor_ok(t) && t->ctx == ctx && t->n_rows == rows && t->n_cols == cols;
+}
+
+extern "C" {
+
+// Weights of one layer (borrowed: the tensors must outlive the decoder).  Norm gains are fp32
+// host vectors of length d_model.
+int32_t skn_llama_set_layer(skn_llama *m, int32_t layer, const skn_tensor *wq, const skn_tensor *wk,
+                            const skn_tensor *wv, const skn_tensor *wo, const skn_tensor *w_gate,
+                            const skn_tensor *w_up, const skn_tensor *w_down, const float *attn_norm_host,
+                            const float *ffn_norm_host) {
+    if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    skn_ctx *ctx = m->ctx;
+    if (layer < 0 || layer >= m->n_layers) return skn_fail(ctx, SKN_ERR_ARG, "layer index out of range");
+    if (!attn_norm_host || !ffn_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
+    const int64_t d = m->d_model, qd = (int64_t)m->n_heads * m->head_dim, kd = (int64_t)m->n_kv_heads * m->head_dim;
+    if (!shape_is(wq, ctx, qd, d) || !shape_is(wk, ctx, kd, d) || !shape_is(wv, ctx, kd, d) || !shape_is(wo, ctx, d, qd) ||
+        !shape_is(w_gate, ctx, m->ffn_dim, d) || !shape_is(w_up, ctx, m->ffn_dim, d) || !shape_is(w_down, ctx, d, m->ffn_dim))
+        return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    skn_llama_layer &l = m->layers[layer];
+    l.wq = wq; l.wk = wk; l.wv = wv; l.wo = wo; l.wg = w_gate; l.wu = w_up; l.wd = w_down;
+    int32_t rc = upload_gain(m, l.attn_norm, attn_norm_host);
+    if (rc) return rc;
+    return upload_gain(m, l.ffn_norm, ffn_norm_host);
+}
+
+// Token embedding table [vocab, d_model], final norm gain and LM head [vocab, d_model].
+int32_t skn_llama_set_head(skn_llama *m, const skn_tensor *tok_embd, const float *out_norm_host,
+                           const skn_tensor *output) {
+    if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    skn_ctx *ctx = m->ctx;
+    if (!out_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
+    if (!shape_is(tok_embd, ctx, m->vocab, m->d_model) || !shape_is(output, ctx, m->vocab, m->d_model))
+        return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    m->tok_embd = tok_embd;
+    m->output = output;
+    return upload_gain(m, m->out_norm, out_norm_host);
+}
+
+// Forget all cached tokens.
+int32_t skn_llama_reset(skn_llama *m) {
+    if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    for (auto &l : m->layers) {
+        int32_t rc = skn_kv_reset(l.kv);
+        if (rc) return rc;
+    }
+    m->host_len = 0;
+    return SKN_OK;
+}
+
+// Enqueue one forward over T new tokens for each of the max_batch sequences.  tokens_dev
+// ([batch][T] int32 on the device) may be NULL with T == 1: the ids produced by the previous
+// forward are then fed back (greedy decoding without a host round trip).
+int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T) {
+    if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    skn_ctx *ctx = m->ctx;
+    const int B = m->max_batch;
+    if (T < 1 || (int64_t)B * T > m->max_rows) return skn_fail(ctx, SKN_ERR_SHAPE, "T outside [1, max_tokens]");
+    if (!tokens_dev && T != 1) return skn_fail(ctx, SKN_ERR_ARG, "tokens may be NULL only for single-token steps");
+    if (m->host_len + T > m->max_ctx) return skn_fail(ctx, SKN_ERR_SHAPE, "context of %d tokens exceeded", m->max_ctx);
+    if (!m->tok_embd || !m->output) return skn_fail(ctx, SKN_ERR_ARG, "model head not set");
+    for (auto &l : m->layers)
+        if (!l.wq) return skn_fail(ctx, SKN_ERR_ARG, "a layer has no weights");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    const int M = B * T, d = m->d_model, Hq = m->n_heads, Hkv = m->n_kv_heads, D = m->head_dim;
+    const float scale = 1.0f / sqrtf((float)D);
+    const int32_t *ids = tokens_dev ? tokens_dev : m->ids_out;
+    SKN_CUDA(ctx, skn_launch_embed(m->tok_embd, ids, M, m->x, st));
+    int32_t rc;
+    for (auto &l : m->layers) {
+        void *len_dev = nullptr;
+        rc = skn_kv_info(l.kv, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &len_dev, nullptr);
+        if (rc) return rc;
+        SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
+        if ((rc = skn_matmul_dev(ctx, l.wq, m->h, M, d, nullptr, m->q))) return rc;
+        if ((rc = skn_matmul_dev(ctx, l.wk, m->h, M, d, nullptr, m->k))) return rc;
+        if ((rc = skn_matmul_dev(ctx, l.wv, m->h, M, d, nullptr, m->v))) return rc;
+        SKN_CUDA(ctx, skn_launch_rope(m->q, (const int32_t *)len_dev, M, T, Hq, D, m->rope_theta, ctx->sm_count, st));
+        SKN_CUDA(ctx, skn_launch_rope(m->k, (const int32_t *)len_dev, M, T, Hkv, D, m->rope_theta, ctx->sm_count, st));
+        if ((rc = skn_kv_append_many_dev(l.kv, m->k, m->v, T, m->host_len))) return rc;
+        if ((rc = skn_attn_causal_dev(l.kv, m->q, Hq, T, scale, m->att, nullptr))) return rc;
+        if ((rc = skn_matmul_dev(ctx, l.wo, m->att, M, (int64_t)Hq * D, nullptr, m->proj))) return rc;
+        SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+        SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+        if ((rc = skn_ffn_swiglu_dev(ctx, l.wg, l.wu, l.wd, m->h, M, m->proj))) return rc;
+        SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+    }
+    m->host_len += T;
+    SKN_CUDA(ctx, skn_launch_last_rows(m->x, m->last, B, T, d, st));
+    SKN_CUDA(ctx, skn_launch_rmsnorm(m->last, m->out_norm, m->h, B, d, m->rms_eps, st));
+    if ((rc = skn_matmul_dev(ctx, m->output, m->h, B, d, nullptr, m->logits))) return rc;
+    SKN_CUDA(ctx, skn_launch_argmax(m->logits, B, m->vocab, m->ids_out, st));
+    return SKN_OK;
+}
+
+// Host-pointer form: tokens_host [batch][T] (NULL with T == 1 feeds back the previous ids);
+// returns the greedy next token of every sequence and, optionally, the logits of the last
+// position ([batch][vocab]).
+int32_t skn_llama_forward(skn_llama *m, const int32_t *tokens_host, int32_t T, int32_t *next_host, float *logits_host) {
+    if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    skn_ctx *ctx = m->ctx;
+    const int B = m->max_batch;
+    if (T < 1 || (int64_t)B * T > m->max_rows) return skn_fail(ctx, SKN_ERR_SHAPE, "T outside [1, max_tokens]");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (tokens_host)
+        SKN_CUDA(ctx, cudaMemcpyAsync(m->ids_in, tokens_host, sizeof(int32_t) * B * T, cudaMemcpyHostToDevice, ctx->stream));
+    int32_t rc = skn_llama_forward_dev(m, tokens_host ? m->ids_in : nullptr, T);
+    if (rc) return rc;
+    if (next_host)
+        SKN_CUDA(ctx, cudaMemcpyAsync(next_host, m->ids_out, sizeof(int32_t) * B, cudaMemcpyDeviceToHost, ctx->stream));
+    if (logits_host)
+        SKN_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * B * m->vocab, cudaMemcpyDeviceToHost, ctx->stream));
+    return skn_sync(ctx);
+}
+
+// number of tokens cached per sequence
+int32_t skn_llama_position(const skn_llama *m) { return llama_ok(m) ? m->host_len : -1; }
+
+}  // extern "C"

@@ -524,6 +524,160 @@ struct Q80Stream {
     }
 };
 
+// ---- Q6_K ------------------------------------------------------------------------------
+// chunk = 8 super-blocks (2048 weights, 1680 bytes); lane = (block cb = lane/4, quarter u =
+// lane%4): half h = u/2, groups g0 = 2*(u&1) and g0+1, i.e. the 64 consecutive weights starting
+// at 256*cb + 64*u.  They use 64 ql bytes (low nibbles for groups 0/1, high for 2/3), 32 qh
+// bytes (two bits per group), four int8 scales and d.  Blocks start on 2-byte boundaries:
+// everything is read as aligned words and re-aligned with a per-lane funnel shift.
+// The 6-bit quant q = nibble | (two bits << 4) is assembled four at a time with integer
+// ops; each byte of the result, masked in place, is the fp32 operand q * 2^(8k) * 2^-149.
+// A 16-weight sub-group with scale sc contributes d * sc * (sum q*x - 32 * sum x).
+//
+// Shared x layout per group of 64 activations: 32 packed pairs, pair grp*16 + j*4 + k =
+// {x[32grp + 8j + k], x[32grp + 8j + 4 + k]} * 2^(S - pos(k)), pos = 0, 8, 16, 16 (sixteen
+// 16-byte slots rotated by the group index); gsum[4G + i] = sum of activations 16i..16i+15;
+// gun[G] = 2^(149 - S).
+struct Q6KStream {
+    static constexpr int CHUNK_BLOCKS = 8;
+    static constexpr int BLOCK_BYTES = 210;
+    static constexpr int BLOCK_WEIGHTS = 256;
+    static constexpr int CHUNK_BYTES = CHUNK_BLOCKS * BLOCK_BYTES;
+    static constexpr int CHUNK_WEIGHTS = CHUNK_BLOCKS * BLOCK_WEIGHTS;
+    static __host__ __device__ size_t xprep_bytes(int64_t kpad) { return (size_t)kpad * 4 + (size_t)kpad / 4 + (size_t)kpad / 16; }
+
+    struct Raw { uint32_t ql[17], qh[9], sc[2], dw; };
+
+    uint64_t x2[32];
+    float sums[4], unscale;
+    int o_ql, o_qh, o_sc, o_d;    // aligned byte offsets inside a staged chunk
+    uint32_t sh;                  // 0 or 16: the block's misalignment in bits
+    int sn, sq;                   // nibble shift (0 / 4) and qh shift (0 / 4) of group g0
+    bool active;
+
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+        float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
+        float *gun = gsum + kpad / 16;
+        const int nf = kpad / 4;
+        const int lane = threadIdx.x & 31;
+        constexpr int B = 4;
+        for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
+            float4 v[B];
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;
+                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const int f = f0 + b * blockDim.x + threadIdx.x;   // 16 consecutive f = one group
+                float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+                float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+                for (int o = 2; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                int S = 217 - (int)(__float_as_uint(mx) >> 23);
+                S = S > 120 ? 120 : (S < 23 ? 23 : S);
+                if (f < nf) {
+                    const int G = f >> 4, idx = f & 15;
+                    const int grp = idx >> 3, word = idx & 7, j = word >> 1, comp = word & 1;
+                    float *g32 = reinterpret_cast<float *>(xs + (size_t)G * 256);
+                    // byte k -> pair grp*16 + j*4 + k -> slot grp*8 + j*2 + (k>>1), float 2*(k&1) + comp
+                    const int sl = grp * 8 + j * 2;
+                    g32[((sl + 0 + G) & 15) * 4 + 0 + comp] = v[b].x * skn_pow2f(S);
+                    g32[((sl + 0 + G) & 15) * 4 + 2 + comp] = v[b].y * skn_pow2f(S - 8);
+                    g32[((sl + 1 + G) & 15) * 4 + 0 + comp] = v[b].z * skn_pow2f(S - 16);
+                    g32[((sl + 1 + G) & 15) * 4 + 2 + comp] = v[b].w * skn_pow2f(S - 16);
+                    if ((lane & 3) == 0) gsum[4 * G + (idx >> 2)] = sm;
+                    if ((lane & 15) == 0) gun[G] = skn_pow2f(149 - S);
+                }
+            }
+        }
+    }
+
+    __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
+        const int cb = lane >> 2, u = lane & 3, h = u >> 1, g0 = 2 * (u & 1);
+        active = cb < nblocks_in_chunk;
+        const int base = cb * BLOCK_BYTES;            // chunk starts are 16-byte aligned
+        sh = (uint32_t)(base & 2) * 8;
+        o_ql = (base + 64 * h) & ~3;
+        o_qh = (base + 128 + 32 * h) & ~3;
+        o_sc = (base + 192 + 8 * h + 2 * g0) & ~3;
+        o_d = (base + 208) & ~3;
+        sn = (g0 == 2) ? 4 : 0;
+        sq = 2 * g0;
+        const int G = (chunk * CHUNK_BLOCKS + cb) * 4 + u;
+        const ulonglong2 *g = reinterpret_cast<const ulonglong2 *>(xs + (size_t)G * 256);
+        const float *gsum = reinterpret_cast<const float *>(xs + (size_t)kpad * 4);
+        const float *gun = gsum + kpad / 16;
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+            const ulonglong2 v = g[(s + G) & 15];
+            x2[2 * s] = v.x;
+            x2[2 * s + 1] = v.y;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sums[i] = gsum[4 * G + i];
+        unscale = gun[G];
+    }
+
+    __device__ __forceinline__ Raw fetch(const uint8_t *sb) const {
+        Raw r;
+        const uint32_t *pq = reinterpret_cast<const uint32_t *>(sb + o_ql);
+        const uint32_t *ph = reinterpret_cast<const uint32_t *>(sb + o_qh);
+        const uint32_t *ps = reinterpret_cast<const uint32_t *>(sb + o_sc);
+#pragma unroll
+        for (int i = 0; i < 17; ++i) r.ql[i] = pq[i];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) r.qh[i] = ph[i];
+        r.sc[0] = ps[0];
+        r.sc[1] = ps[1];
+        r.dw = *reinterpret_cast<const uint32_t *>(sb + o_d);
+        return r;
+    }
+
+    __device__ __forceinline__ float dot(const Raw &r) const {
+        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};        // (group, 16-weight half)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t h0 = __funnelshift_rc(r.qh[2 * j], r.qh[2 * j + 1], sh);
+            const uint32_t h1 = __funnelshift_rc(r.qh[2 * j + 1], r.qh[2 * j + 2], sh);
+            const uint64_t H = (((uint64_t)h1 << 32) | h0) >> sq;
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+                const uint32_t a0 = __funnelshift_rc(r.ql[8 * grp + 2 * j], r.ql[8 * grp + 2 * j + 1], sh);
+                const uint32_t a1 = __funnelshift_rc(r.ql[8 * grp + 2 * j + 1], r.ql[8 * grp + 2 * j + 2], sh);
+                const uint64_t P = (((uint64_t)a1 << 32) | a0) >> sn;
+                // bits 4-5 of every byte from qh (group g0: bits 0-1 after the shift, g0+1: bits 2-3)
+                const uint64_t hb = grp ? ((H << 2) & 0x3030303030303030ull) : ((H << 4) & 0x3030303030303030ull);
+                const uint64_t Q = (P & 0x0F0F0F0F0F0F0F0Full) | hb;
+                const uint64_t Q8 = Q >> 8;
+                uint64_t a = acc[2 * grp + (j >> 1)];
+                a = skn_fma2(Q & 0x000000FF000000FFull, x2[grp * 16 + j * 4 + 0], a);
+                a = skn_fma2(Q & 0x0000FF000000FF00ull, x2[grp * 16 + j * 4 + 1], a);
+                a = skn_fma2(Q & 0x00FF000000FF0000ull, x2[grp * 16 + j * 4 + 2], a);
+                a = skn_fma2(Q8 & 0x00FF000000FF0000ull, x2[grp * 16 + j * 4 + 3], a);
+                acc[2 * grp + (j >> 1)] = a;
+            }
+        }
+        const uint32_t sc4 = __funnelshift_rc(r.sc[0], r.sc[1], sh);
+        const float d = skn_half_bits_to_float((r.dw >> sh) & 0xFFFFu);
+        float res = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            skn_unpack2(acc[i], lo, hi);
+            // signed 8-bit scale -> float without the conversion pipe: (2^23 + 128 + s) - (2^23 + 128)
+            const uint32_t sb8 = ((sc4 >> (8 * i)) & 0xFFu) ^ 0x80u;
+            const float scf = __uint_as_float(0x4B000000u | sb8) - 8388736.f;
+            res = fmaf(scf, fmaf(lo + hi, unscale, -32.f * sums[i]), res);
+        }
+        res *= d;
+        return active ? res : 0.f;
+    }
+};
+
 // One kernel for every streaming decoder S.
 //   grid  : CTA b owns rows [b*N/grid, (b+1)*N/grid)
 //   block : nch * wg warps; warp w -> chunk c = w % nch, row slot g = w / nch
@@ -676,18 +830,22 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
     if (wg < 1) wg = 1;
     while (nch * wg > 16) --wg;
     if (wg < 1) return cudaSuccess;
-    const int warps = nch * wg;
-    const int threads = warps * 32;
-    const int kpad = nch * S::CHUNK_WEIGHTS;
-    const size_t fixed = (size_t)warps * MV_NST * S::CHUNK_BYTES + (S::xprep_bytes(kpad) + 127) / 128 * 128 +
-                         (size_t)warps * MV_NST * sizeof(uint64_t);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
     int64_t grid = ctx->sm_count;
     if (grid > w->n_rows) grid = w->n_rows;
     const int64_t rows_max = (w->n_rows + grid - 1) / grid;
-    const size_t smem = fixed + (size_t)rows_max * nch * sizeof(float);
-    if (smem > 220 * 1024) return cudaSuccess;
+    const int kpad = nch * S::CHUNK_WEIGHTS;
+    int threads = 0;
+    size_t smem = 0;
+    for (;; --wg) {       // fewer row slots until the ring, the prepared x and the partials fit
+        if (wg < 1) return cudaSuccess;
+        const int warps = nch * wg;
+        threads = warps * 32;
+        smem = (size_t)warps * MV_NST * S::CHUNK_BYTES + (S::xprep_bytes(kpad) + 127) / 128 * 128 +
+               (size_t)warps * MV_NST * sizeof(uint64_t) + (size_t)rows_max * nch * sizeof(float);
+        if (smem <= 220 * 1024) break;
+    }
     int occ = 0;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem);
     if (e != cudaSuccess) return e;
@@ -744,6 +902,7 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
             if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q4_0) took = try_stream<Q40Stream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q8_0) took = try_stream<Q80Stream>(ctx, w, xm, bias, ym, stream, err);
+            else if (w->type == SKN_TYPE_Q6_K) took = try_stream<Q6KStream>(ctx, w, xm, bias, ym, stream, err);
             if (!took) break;               // shape not covered: the generic kernel below does all rows
             if (err != cudaSuccess) return err;
             done = (m == M - 1);
