@@ -505,6 +505,96 @@ def run_sweep(args):
                       "peak": peak, "peak_kind": kind, "cases": rows}), flush=True)
 
 
+def run_decode(args):
+    """Configuration 5: Llama-style decoder, 32 layers, d_model 4096, FFN 14336, 32q/8kv heads,
+    head_dim 128, vocab 32000, Q4_K projections, Q6_K embedding / LM head.  512-token prefill of
+    uniform-random ids, then 128 greedy decode steps (ids fed back on the device, one CUDA graph
+    replay per step).  One layer's random blocks are uploaded 32 times (distinct device buffers).
+    4 GB of weights per step far exceed L2."""
+    import torch
+    import skainet_b200 as skn
+    from skainet_b200 import synth
+    from skainet_b200.llama import LlamaConfig, LlamaDecoder
+    B, T, steps = args.batch, 512, min(args.steps, 128)
+    cfg = LlamaConfig(n_layers=args.layers if args.layers != 128 else 32)
+    dev = torch.device("cuda", 0)
+    ctx = skn.Context(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    g = synth.rng(4)
+    qd, kd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    shapes = {"wq": (qd, cfg.d_model), "wk": (kd, cfg.d_model), "wv": (kd, cfg.d_model), "wo": (cfg.d_model, qd),
+              "w_gate": (cfg.ffn_dim, cfg.d_model), "w_up": (cfg.ffn_dim, cfg.d_model), "w_down": (cfg.d_model, cfg.ffn_dim)}
+    layer = {k: synth.make_weight(g, cfg.proj_type, *shp) for k, shp in shapes.items()}
+    emb = synth.make_weight(g, cfg.head_type, cfg.vocab, cfg.d_model)
+    dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=T + 136)
+    ones = np.ones(cfg.d_model, dtype=np.float32)
+    for i in range(cfg.n_layers):
+        dec.set_layer(i, layer, ones, ones)
+    dec.set_head(emb, ones, np.roll(emb, 1, axis=0))
+    prompt = torch.from_numpy(g.integers(0, cfg.vocab, size=(B, T)).astype(np.int32)).to(dev)
+
+    def prefill():
+        dec.reset()
+        dec.forward_dev(prompt, T)
+
+    prefill()
+    dec.forward_dev(None, 1)          # sizes every scratch buffer of the decode path
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    prefill()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    graph = None
+    if not args.no_graph:
+        try:
+            cap = torch.cuda.Stream()
+            cap.wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap):
+                ctx.set_stream(cap.cuda_stream)
+                with torch.cuda.graph(graph, stream=cap):
+                    dec.forward_dev(None, 1)
+        except Exception as exc:
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); launching eagerly\n")
+            graph = None
+        finally:
+            ctx.set_stream(stream.cuda_stream)
+        torch.cuda.synchronize()
+    # the capture itself advanced the host-side position by one: start over
+    prefill()
+    torch.cuda.synchronize()
+    step = graph.replay if graph is not None else (lambda: dec.forward_dev(None, 1))
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    ctx.sync()
+    wbytes = cfg.n_layers * sum(n * (k // 256) * 144 for n, k in shapes.values()) + cfg.vocab * (cfg.d_model // 256) * 210
+    peak, kind = measured_peak()
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode_tok_s", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 1,
+        "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg5: Llama-style decoder, {cfg.n_layers} layers, Q4_K / Q6_K, batch {B}, "
+                               f"{T}-token prefill then greedy decode",
+                   "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
+                   "prefill_ms": prefill_ms, "prefill_tok_s": B * T * 1e3 / prefill_ms,
+                   "weight_bytes_per_step": wbytes},
+        "roofline": {"bound": "hbm", "kernel": "decode step (weight stream)", "achieved": gbs, "peak": peak,
+                     "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "traffic": None},
+        "clocks": clocks}), flush=True)
+    dec.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -518,11 +608,12 @@ def main():
     ap.add_argument("--order", default="relaxed", choices=["relaxed", "stream"],
                     help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
                          "may overlap; stream: each launch waits for the one before it")
-    ap.add_argument("--workload", default="matvec", choices=["matvec", "ffn", "attn", "sweep"],
+    ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences per step")
+    ap.add_argument("--workload", default="matvec", choices=["matvec", "ffn", "attn", "sweep", "decode"],
                     help="matvec is the headline line; the others print one secondary JSON line (1 GPU)")
     args = ap.parse_args()
     if args.impl == "ours" and args.workload != "matvec":
-        return {"ffn": run_ffn, "attn": run_attn, "sweep": run_sweep}[args.workload](args)
+        return {"ffn": run_ffn, "attn": run_attn, "sweep": run_sweep, "decode": run_decode}[args.workload](args)
     if args.impl == "reference":
         run_reference(args)
     else:
