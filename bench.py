@@ -17,7 +17,8 @@ weights from HBM).  One step = one pass over the stack: LAYERS matvec launches b
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank streams its own row
 shard of an N-times taller stack (column-parallel: rank r owns rows [r*4096, (r+1)*4096) of
-each [N*4096, 4096] layer) and the y slices are all-gathered over NCCL once per layer;
+each [N*4096, 4096] layer) and the y slices of the whole stack are all-gathered over NCCL once
+per step (the layers of this stack are independent of one another);
 per-GPU work is fixed, so scaling is weak.
 
 --impl reference times the CPU oracle alone (all host threads) and prints the same line.
@@ -42,6 +43,9 @@ N_ROWS, N_COLS = 4096, 4096
 Q4_K = 12
 W_BYTES = N_ROWS * (N_COLS // 256) * 144
 ALG_BYTES = W_BYTES + 4 * N_COLS + 4 * N_ROWS      # 9 469 952 per matvec
+# dram__bytes_read.sum + dram__bytes_write.sum of one skn_matvec_stream<Q4KStream> launch on this
+# workload, from the ncu capture summarised in profiles/q4k_matvec_cfg1.md
+DRAM_TRAFFIC_PER_LAUNCH = 9507328
 METRIC = "q4k_matvec_gbs"
 UNIT = "GB/s"
 
@@ -207,14 +211,15 @@ def run_ours(args):
         tensors.append(skn.QuantTensor(ctx, (N_ROWS, N_COLS), Q4_K, wi))
     x_dev = x_host.to(dev)
     y_dev = torch.empty((layers, N_ROWS), dtype=torch.float32, device=dev)
-    y_all = torch.empty((layers, world * N_ROWS), dtype=torch.float32, device=dev) if world > 1 else None
+    y_all = torch.empty((world, layers, N_ROWS), dtype=torch.float32, device=dev) if world > 1 else None
     y_host = torch.empty(N_ROWS, dtype=torch.float32).pin_memory()
 
     def step_device():
         for i, t in enumerate(tensors):
             t.matmul_t_dev(x_dev, 1, y_dev[i])
-            if world > 1:
-                dist.all_gather_into_tensor(y_all[i], y_dev[i])
+        if world > 1:
+            # the layers of the stack are independent: their y slices are exchanged once per step
+            dist.all_gather_into_tensor(y_all, y_dev)
 
     from skainet_b200 import _ffi
     L = _ffi.lib()
@@ -236,44 +241,51 @@ def run_ours(args):
     # microseconds, less than a host-side launch); the timed region replays the graph.
     step_device()          # first call plans each tensor's launch geometry (not capturable)
     barrier()
-    graph = None
-    run_step = step_device
-    if not args.no_graph:
-        cap_stream = torch.cuda.Stream()
-        cap_stream.wait_stream(stream)
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(cap_stream):
-                ctx.set_stream(cap_stream.cuda_stream)
-                with torch.cuda.graph(graph, stream=cap_stream):
-                    step_device()
-            run_step = graph.replay
-        except Exception as exc:   # capture unsupported for this configuration: launch eagerly
-            sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); launching eagerly\n")
-            graph = None
-            run_step = step_device
-        finally:
-            ctx.set_stream(stream.cuda_stream)
-        torch.cuda.synchronize()
-    for _ in range(max(3, args.warmup)):
-        run_step()
-    barrier()
+
+    def time_device(order):
+        ctx.set_relaxed_order(order == "relaxed")
+        graph, run = None, step_device
+        if not args.no_graph:
+            cap_stream = torch.cuda.Stream()
+            cap_stream.wait_stream(stream)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(cap_stream):
+                    ctx.set_stream(cap_stream.cuda_stream)
+                    with torch.cuda.graph(graph, stream=cap_stream):
+                        step_device()
+                run = graph.replay
+            except Exception as exc:   # capture unsupported for this configuration: launch eagerly
+                sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); launching eagerly\n")
+                graph, run = None, step_device
+            finally:
+                ctx.set_stream(stream.cuda_stream)
+            torch.cuda.synchronize()
+        for _ in range(max(3, args.warmup)):
+            run()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        barrier()
+        ctx.sync()
+        t = e0.elapsed_time(e1)
+        if world > 1:
+            tt = torch.tensor([t], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        return t, graph is not None
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        run_step()
-    ev1.record(stream)
-    barrier()
-    ctx.sync()
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        tms = torch.tensor([ms], device=dev)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = float(tms.item())
+    other = "stream" if args.order == "relaxed" else "relaxed"
+    ms_other, _ = time_device(other) if world == 1 else (None, False)
+    ms, graphed = time_device(args.order)
+    graph = graphed or None
 
     # ---- end to end through the host-pointer ABI ----------------------------------------
     for _ in range(2):
@@ -316,14 +328,16 @@ def run_ours(args):
                        "l2_policy": f"inputs larger than L2: {layers} distinct weights = "
                                     f"{layers * W_BYTES / 1e6:.0f} MB streamed per step",
                        "sharding": "none" if world == 1 else
-                       f"column-parallel rows over {world} ranks, NCCL all-gather of y slices per layer",
-                       "pct_of_8TBs": 100.0 * value / world / 8000.0},
+                       f"column-parallel rows over {world} ranks, one NCCL all-gather of the y slices per step",
+                       "pct_of_8TBs": 100.0 * value / world / 8000.0,
+                       "other_order": None if ms_other is None else
+                       {"order": other, "value": total_bytes * args.steps / (ms_other * 1e-3) / 1e9, "unit": UNIT}},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": layers * 4 * N_COLS,
                     "d2h_bytes_per_step": layers * 4 * N_ROWS, "steps": e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "skn_matvec_stream<Q4KStream>", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": UNIT, "frac": achieved / peak,
-                         "us_per_launch": per_launch_us, "traffic": None},
+                         "us_per_launch": per_launch_us, "traffic": DRAM_TRAFFIC_PER_LAUNCH},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
