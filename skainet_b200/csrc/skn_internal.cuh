@@ -46,7 +46,7 @@ struct skn_tensor {
     int64_t row_bytes;   // n_cols / block_elems * block_bytes
     int64_t pitch;       // device row pitch in bytes (multiple of 16)
     uint8_t *d_blocks;
-    skn_mv_plan mv_plan;
+    skn_mv_plan mv_plan[2];      // [0] stream order, [1] relaxed order
 };
 
 // error plumbing (skn_api.cu)

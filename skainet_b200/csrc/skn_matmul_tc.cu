@@ -137,6 +137,8 @@ __device__ __forceinline__ float tc_field(uint32_t masked_or_magic, float scale_
 // sub-block 2p+1) plus the block header; three 16-byte loads.
 template <int TYPE> struct TcRaw { };                       // generic types: nothing is prefetched
 template <> struct TcRaw<SKN_TYPE_Q4_K> { uint4 hdr, qa, qb; };
+template <> struct TcRaw<SKN_TYPE_Q4_0> { uint32_t w[9]; };
+template <> struct TcRaw<SKN_TYPE_Q8_0> { uint32_t w[17]; };
 template <> struct TcRaw<SKN_TYPE_Q6_K> { uint32_t rq[17], rh[9], s_lo, s_hi, dword; };
 
 // raw bytes of the 64 weights at k0 into registers (issued one stage ahead of their decode)
@@ -197,6 +199,89 @@ __device__ __forceinline__ void tc_decode_row<SKN_TYPE_Q4_K>(const TcRaw<SKN_TYP
         tc_store_chunk(tile, r, c, make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]));
         tc_store_chunk(tile, r, 4 + c, make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]));
     }
+}
+
+// Q4_0: 64 weights at k0 = two 18-byte blocks = nine aligned words; block A's quants straddle
+// the words by two bytes.  Byte e of a block: low nibble = weight e, high nibble = weight e+16.
+template <>
+__device__ __forceinline__ void tc_load_row<SKN_TYPE_Q4_0>(const uint8_t *rp, int k0, bool valid, TcRaw<SKN_TYPE_Q4_0> &raw) {
+    if (!valid) return;
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(rp + (size_t)(k0 >> 6) * 36);
+#pragma unroll
+    for (int i = 0; i < 9; ++i) raw.w[i] = __ldg(p + i);
+}
+
+// four quant words of one Q4_0 block -> 32 bf16 (16 packed pairs) at out[0..15]
+__device__ __forceinline__ void tc_q40_block(const uint32_t (&q)[4], float d, uint32_t *out) {
+    const float off = 8.f * d;
+    const float l0 = d, l8 = d * (1.f / 256.f), l16 = d * (1.f / 65536.f);
+    const float h4 = d * (1.f / 16.f), h12 = d * (1.f / 4096.f);
+    const uint32_t M = 0x4B000000u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = q[i], w8 = w >> 8, w12 = w >> 12;
+        out[2 * i] = tc_pack_bf16(tc_field((w & 0x0000000Fu) | M, l0, off), tc_field((w & 0x00000F00u) | M, l8, off));
+        out[2 * i + 1] = tc_pack_bf16(tc_field((w & 0x000F0000u) | M, l16, off), tc_field((w8 & 0x000F0000u) | M, l16, off));
+        out[8 + 2 * i] = tc_pack_bf16(tc_field((w & 0x000000F0u) | M, h4, off), tc_field((w & 0x0000F000u) | M, h12, off));
+        out[8 + 2 * i + 1] = tc_pack_bf16(tc_field((w12 & 0x00000F00u) | M, l8, off), tc_field((w12 & 0x000F0000u) | M, l16, off));
+    }
+}
+
+template <>
+__device__ __forceinline__ void tc_decode_row<SKN_TYPE_Q4_0>(const TcRaw<SKN_TYPE_Q4_0> &raw, const uint8_t *, int,
+                                                             uint8_t *tile, int r, bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(0u, 0u, 0u, 0u));
+        return;
+    }
+    const uint32_t qa[4] = {__funnelshift_r(raw.w[0], raw.w[1], 16), __funnelshift_r(raw.w[1], raw.w[2], 16),
+                            __funnelshift_r(raw.w[2], raw.w[3], 16), __funnelshift_r(raw.w[3], raw.w[4], 16)};
+    const uint32_t qb[4] = {raw.w[5], raw.w[6], raw.w[7], raw.w[8]};
+    uint32_t out[32];
+    tc_q40_block(qa, skn_half_bits_to_float(raw.w[0] & 0xFFFFu), out);
+    tc_q40_block(qb, skn_half_bits_to_float(raw.w[4] >> 16), out + 16);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]));
+}
+
+// Q8_0: 64 weights at k0 = two 34-byte blocks = seventeen aligned words.  A signed byte b is
+// widened as (2^23 + (b ^ 0x80)) - (2^23 + 128) = b, then multiplied by d.
+template <>
+__device__ __forceinline__ void tc_load_row<SKN_TYPE_Q8_0>(const uint8_t *rp, int k0, bool valid, TcRaw<SKN_TYPE_Q8_0> &raw) {
+    if (!valid) return;
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(rp + (size_t)(k0 >> 6) * 68);
+#pragma unroll
+    for (int i = 0; i < 17; ++i) raw.w[i] = __ldg(p + i);
+}
+
+__device__ __forceinline__ void tc_q80_word(uint32_t w, float d, uint32_t *out) {
+    const uint32_t u = w ^ 0x80808080u;
+    const float f0 = __fmul_rn(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.f, d);
+    const float f1 = __fmul_rn(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.f, d);
+    const float f2 = __fmul_rn(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.f, d);
+    const float f3 = __fmul_rn(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.f, d);
+    out[0] = tc_pack_bf16(f0, f1);
+    out[1] = tc_pack_bf16(f2, f3);
+}
+
+template <>
+__device__ __forceinline__ void tc_decode_row<SKN_TYPE_Q8_0>(const TcRaw<SKN_TYPE_Q8_0> &raw, const uint8_t *, int,
+                                                             uint8_t *tile, int r, bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(0u, 0u, 0u, 0u));
+        return;
+    }
+    const float da = skn_half_bits_to_float(raw.w[0] & 0xFFFFu), db = skn_half_bits_to_float(raw.w[8] >> 16);
+    uint32_t out[32];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        tc_q80_word(__funnelshift_r(raw.w[i], raw.w[i + 1], 16), da, out + 2 * i);
+        tc_q80_word(raw.w[9 + i], db, out + 16 + 2 * i);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) tc_store_chunk(tile, r, c, make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]));
 }
 
 // Q6_K: 64 weights at k0 = quarter u of a 210-byte super-block: half h = u/2, groups g0 = 2*(u&1)

@@ -815,7 +815,7 @@ static int env_int(const char *name, int dflt) {
 //     one computes);
 //   - warps = nch * wg with wg chosen for about 8 warps.
 template <class S>
-static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &pl) {
+static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &pl, bool relaxed) {
     auto kern = skn_matvec_stream<S>;
     pl.state = -1;  // "no streaming plan" unless everything below works out
     if (w->n_cols % S::BLOCK_WEIGHTS || w->n_cols > (1 << 20)) return cudaSuccess;
@@ -823,7 +823,11 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
     const int nch = (int)((nb + S::CHUNK_BLOCKS - 1) / S::CHUNK_BLOCKS);
     if (nch < 1 || nch > 16 || w->n_rows < 1) return cudaSuccess;
     static const int wg_env = env_int("SKN_MV_WG", 0);
-    static const int warps_env = env_int("SKN_MV_WARPS", 8);
+    // Stream order: 8 warps per CTA (one launch computes while the next one only prefetches).
+    // Relaxed order: 4 warps per CTA, so that CTAs of up to four consecutive launches share an
+    // SM and their phases (prefetch, x preparation, arithmetic, epilogue) overlap.
+    static const int warps_env_cfg = env_int("SKN_MV_WARPS", 0);
+    const int warps_env = warps_env_cfg > 0 ? warps_env_cfg : (relaxed ? 4 : 8);
     // about `warps_env` warps per CTA; long rows (nch > 4) get two row slots when they fit
     int wg = wg_env > 0 ? wg_env : (nch <= warps_env ? warps_env / nch : 1);
     if (wg_env <= 0 && nch > 4 && nch <= 8) wg = 2;
@@ -832,7 +836,8 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
     if (wg < 1) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
-    int64_t grid = ctx->sm_count;
+    static const int ctas_env = env_int("SKN_MV_CTAS_PER_SM", 1);
+    int64_t grid = (int64_t)ctx->sm_count * (ctas_env > 0 ? ctas_env : 1);
     if (grid > w->n_rows) grid = w->n_rows;
     const int64_t rows_max = (w->n_rows + grid - 1) / grid;
     const int kpad = nch * S::CHUNK_WEIGHTS;
@@ -877,9 +882,9 @@ static cudaError_t launch_stream(skn_ctx *ctx, const skn_tensor *w, const float 
 template <class S>
 static bool try_stream(skn_ctx *ctx, const skn_tensor *w, const float *x, const float *bias, float *y,
                        cudaStream_t stream, cudaError_t &err) {
-    skn_mv_plan &pl = const_cast<skn_tensor *>(w)->mv_plan;
+    skn_mv_plan &pl = const_cast<skn_tensor *>(w)->mv_plan[ctx->relaxed_order ? 1 : 0];
     if (pl.state == 0) {
-        err = plan_stream<S>(ctx, w, pl);
+        err = plan_stream<S>(ctx, w, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) { pl.state = 0; return true; }
     }
     if (pl.state != 1) return false;
