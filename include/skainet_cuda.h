@@ -262,6 +262,33 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
 /* tokens cached per sequence so far (-1 on a bad handle) */
 int32_t skn_llama_position(const skn_llama *m);
 
+/* ---- GGUF container --------------------------------------------------------------------------
+ * Memory-mapped GGUF v2 / v3 reader with 64-bit offsets; tensor data is handed out as pointers
+ * into the mapping (no copy, no boxing) and quantized tensors upload straight from it.  Stands
+ * where the reference parses the file, gguf/src/commonMain/kotlin/sk/ai/net/gguf/GGUFReader.kt:82-112
+ * (fields: GGUFReader.kt:285-318, tensors: GGUFReader.kt:332-401), without its whole-file
+ * ByteArray (:83), Int byte counts (:359) and F16 rejection (:363).  Host code; needs no GPU
+ * except skn_gguf_upload. */
+typedef struct skn_gguf skn_gguf;
+int32_t skn_gguf_open(const char *path, skn_gguf **out);
+int32_t skn_gguf_close(skn_gguf *g);
+int32_t skn_gguf_counts(const skn_gguf *g, int32_t *version, int64_t *n_tensors, int64_t *n_kv, int64_t *alignment,
+                        int64_t *data_offset);
+/* Metadata entry i: key (NUL-terminated), GGUFValueType ids (Constants.kt, GGUFValueType; elem_type
+ * is -1 unless the value is an array), a pointer to the value inside the mapping and a count
+ * (string: byte length; array: elements, string elements being u64 length + bytes each). */
+int32_t skn_gguf_kv(const skn_gguf *g, int64_t i, const char **key, int32_t *value_type, int32_t *elem_type,
+                    const void **value, int64_t *count);
+/* Tensor i: name, dims in file order (dims[0] contiguous; unused dims are 1), GGML type id, absolute
+ * file offset, byte length and a pointer to the data inside the mapping: ReaderTensor,
+ * GGUFReader.kt:35-44. */
+int32_t skn_gguf_tensor(const skn_gguf *g, int64_t i, const char **name, int32_t *n_dims, int64_t *dims4,
+                        int32_t *ggml_type, int64_t *data_offset, int64_t *n_bytes, const void **data);
+int32_t skn_gguf_find_tensor(const skn_gguf *g, const char *name, int64_t *index);
+/* Upload quantized tensor i as a [dims[1], dims[0]] weight (the step the reference's loader
+ * skips, samples/mnist-mlp-cli/src/jvmMain/kotlin/sk/ai/net/samples/mnist/mlp/Main.kt:229-232). */
+int32_t skn_gguf_upload(skn_ctx *ctx, const skn_gguf *g, int64_t i, skn_tensor **out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,13 @@ SIGNATURES = {
     "skn_llama_forward": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
     "skn_llama_forward_dev": (c_i32, [c_vp, c_vp, c_i32]),
     "skn_llama_position": (c_i32, [c_vp]),
+    "skn_gguf_open": (c_i32, [ctypes.c_char_p, P(c_vp)]),
+    "skn_gguf_close": (c_i32, [c_vp]),
+    "skn_gguf_counts": (c_i32, [c_vp, P(c_i32), P(c_i64), P(c_i64), P(c_i64), P(c_i64)]),
+    "skn_gguf_kv": (c_i32, [c_vp, c_i64, P(ctypes.c_char_p), P(c_i32), P(c_i32), P(c_vp), P(c_i64)]),
+    "skn_gguf_tensor": (c_i32, [c_vp, c_i64, P(ctypes.c_char_p), P(c_i32), P(c_i64), P(c_i32), P(c_i64), P(c_i64), P(c_vp)]),
+    "skn_gguf_find_tensor": (c_i32, [c_vp, ctypes.c_char_p, P(c_i64)]),
+    "skn_gguf_upload": (c_i32, [c_vp, c_vp, c_i64, P(c_vp)]),
     "skn_attn_decode_noalloc_dev": (c_i32, [c_vp, c_vp, c_i32, ctypes.c_float, c_vp]),
 }
 
