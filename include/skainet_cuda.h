@@ -147,6 +147,13 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
 int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
                        const float *bias_dev, float *y_dev);
 
+/* y[t] = W[t] . x (+ add[t]) for n <= 3 weights that multiply the same activation vector x (Q/K/V,
+ * gate/up): one launch when the weights share type and K, separate launches otherwise.  add[t]
+ * ([n_rows of W[t]], may be NULL, the array itself may be NULL) is a bias or a residual; y[t] may
+ * alias add[t].  Several Linear.forward calls on one input (nn/Linear.kt:43-49) in one step. */
+int32_t skn_matvec_group_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
+                             float *const *y_dev, const float *const *add_dev);
+
 /* Y[M, N] = (silu(X . Wg^T) * (X . Wu^T)) . Wd^T -- the SwiGLU feed-forward block; Wg, Wu are
  * [F, K] (same block type), Wd is [N, F].  The reference has neither SiLU nor SwiGLU (its
  * sigmoid(), core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:448-449, computes

@@ -307,6 +307,22 @@ int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, in
     return SKN_OK;
 }
 
+// y[t] = W[t] . x (+ add[t]) for up to three weights that share the activation vector x
+int32_t skn_matvec_group_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
+                             float *const *y_dev, const float *const *add_dev) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (n < 1 || n > 3 || !w || !y_dev || !x_dev) return skn_fail(ctx, SKN_ERR_ARG, "1 to 3 tensors, non-NULL arrays");
+    for (int32_t t = 0; t < n; ++t) {
+        if (!skn_tensor_ok(w[t]) || w[t]->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+        if (w[t]->n_cols != w[0]->n_cols) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+        if (!y_dev[t] || (((uintptr_t)y_dev[t]) & 15)) return skn_fail(ctx, SKN_ERR_ALIGN, "outputs must be 16-byte aligned");
+    }
+    if (((uintptr_t)x_dev) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "x must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SKN_CUDA(ctx, skn_launch_matvec_group(ctx, n, w, x_dev, y_dev, add_dev, ctx->stream));
+    return SKN_OK;
+}
+
 int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
                            const float *x_dev, int32_t M, float *y_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");

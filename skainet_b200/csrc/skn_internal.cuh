@@ -78,6 +78,8 @@ cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitc
                                int64_t n_cols, float *out, cudaStream_t stream);
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M,
                               const float *bias, float *y, cudaStream_t stream);
+cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                                    const float *const *add, cudaStream_t stream);
 
 // tensor-core prefill path (skn_matmul_tc.cu)
 bool skn_tc_supported(const skn_tensor *w, int32_t M);

@@ -28,7 +28,7 @@ struct skn_llama {
     float *out_norm;
     // activations for up to max_rows = max_batch * max_tokens rows
     int32_t max_rows;
-    float *x, *h, *q, *k, *v, *att, *proj, *last, *logits;
+    float *x, *h, *q, *k, *v, *att, *proj, *last, *logits, *ffn_g, *ffn_u;
     int32_t *ids_in, *ids_out;
     int32_t host_len;                 // tokens cached so far (the same for every sequence)
 };
@@ -70,7 +70,7 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     m->out_norm = nullptr;
     m->max_rows = max_batch * max_tokens;
     m->host_len = 0;
-    m->x = m->h = m->q = m->k = m->v = m->att = m->proj = m->last = m->logits = nullptr;
+    m->x = m->h = m->q = m->k = m->v = m->att = m->proj = m->last = m->logits = m->ffn_g = m->ffn_u = nullptr;
     m->ids_in = m->ids_out = nullptr;
     m->layers.resize(n_layers);
     for (auto &l : m->layers) l = skn_llama_layer{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -86,6 +86,10 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     if (e == cudaSuccess) e = dev_alloc(&m->last, (size_t)max_batch * d_model);
     if (e == cudaSuccess) e = dev_alloc(&m->logits, (size_t)max_batch * vocab);
     if (e == cudaSuccess) e = dev_alloc(&m->out_norm, d_model);
+    // gate / up outputs of the decode-size path (rows below the prefill threshold only)
+    const size_t small_rows = R < 64 ? R : 64;
+    if (e == cudaSuccess) e = dev_alloc(&m->ffn_g, small_rows * ffn_dim);
+    if (e == cudaSuccess) e = dev_alloc(&m->ffn_u, small_rows * ffn_dim);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_in, sizeof(int32_t) * R);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_out, sizeof(int32_t) * max_batch);
     int32_t rc = SKN_OK;
@@ -110,7 +114,7 @@ int32_t skn_llama_destroy(skn_llama *m) {
         cudaSetDevice(m->ctx->device);
         cudaStreamSynchronize(m->ctx->stream);
     }
-    float *bufs[] = {m->x, m->h, m->q, m->k, m->v, m->att, m->proj, m->last, m->logits, m->out_norm};
+    float *bufs[] = {m->x, m->h, m->q, m->k, m->v, m->att, m->proj, m->last, m->logits, m->out_norm, m->ffn_g, m->ffn_u};
     for (float *b : bufs) if (b) cudaFree(b);
     if (m->ids_in) cudaFree(m->ids_in);
     if (m->ids_out) cudaFree(m->ids_out);
@@ -204,6 +208,8 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     const int M = B * T, d = m->d_model, Hq = m->n_heads, Hkv = m->n_kv_heads, D = m->head_dim;
     const float scale = 1.0f / sqrtf((float)D);
     const int32_t *ids = tokens_dev ? tokens_dev : m->ids_out;
+    // below the prefill threshold every product is an fp32 streaming matvec per activation row
+    const bool small = M <= 64 && !(ctx->prefill_min_m > 0 && M >= ctx->prefill_min_m);
     SKN_CUDA(ctx, skn_launch_embed(m->tok_embd, ids, M, m->x, st));
     int32_t rc;
     for (auto &l : m->layers) {
@@ -211,18 +217,45 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         rc = skn_kv_info(l.kv, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &len_dev, nullptr);
         if (rc) return rc;
         SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
-        if ((rc = skn_matmul_dev(ctx, l.wq, m->h, M, d, nullptr, m->q))) return rc;
-        if ((rc = skn_matmul_dev(ctx, l.wk, m->h, M, d, nullptr, m->k))) return rc;
-        if ((rc = skn_matmul_dev(ctx, l.wv, m->h, M, d, nullptr, m->v))) return rc;
+        const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_dim;
+        if (small) {
+            // decode-size batches: Q/K/V in one launch per activation row
+            for (int r = 0; r < M; ++r) {
+                const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
+                float *ys[3] = {m->q + r * qd, m->k + r * kd, m->v + r * kd};
+                SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 3, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+            }
+        } else {
+            if ((rc = skn_matmul_dev(ctx, l.wq, m->h, M, d, nullptr, m->q))) return rc;
+            if ((rc = skn_matmul_dev(ctx, l.wk, m->h, M, d, nullptr, m->k))) return rc;
+            if ((rc = skn_matmul_dev(ctx, l.wv, m->h, M, d, nullptr, m->v))) return rc;
+        }
         SKN_CUDA(ctx, skn_launch_rope(m->q, (const int32_t *)len_dev, M, T, Hq, D, m->rope_theta, ctx->sm_count, st));
         SKN_CUDA(ctx, skn_launch_rope(m->k, (const int32_t *)len_dev, M, T, Hkv, D, m->rope_theta, ctx->sm_count, st));
         if ((rc = skn_kv_append_many_dev(l.kv, m->k, m->v, T, m->host_len))) return rc;
         if ((rc = skn_attn_causal_dev(l.kv, m->q, Hq, T, scale, m->att, nullptr))) return rc;
-        if ((rc = skn_matmul_dev(ctx, l.wo, m->att, M, (int64_t)Hq * D, nullptr, m->proj))) return rc;
-        SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
-        SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
-        if ((rc = skn_ffn_swiglu_dev(ctx, l.wg, l.wu, l.wd, m->h, M, m->proj))) return rc;
-        SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+        if (small) {
+            // output projection with the residual added in its epilogue (x += att . Wo^T)
+            for (int r = 0; r < M; ++r)
+                SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wo, m->att + r * qd, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+            SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+            // gate and up in one launch per row (q and att are free again: they hold g and u)
+            float *gbuf = m->ffn_g, *ubuf = m->ffn_u;
+            for (int r = 0; r < M; ++r) {
+                const skn_tensor *ws[2] = {l.wg, l.wu};
+                float *ys[2] = {gbuf + r * F, ubuf + r * F};
+                SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 2, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+            }
+            SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
+            for (int r = 0; r < M; ++r)
+                SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+        } else {
+            if ((rc = skn_matmul_dev(ctx, l.wo, m->att, M, qd, nullptr, m->proj))) return rc;
+            SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+            SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+            if ((rc = skn_ffn_swiglu_dev(ctx, l.wg, l.wu, l.wd, m->h, M, m->proj))) return rc;
+            SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+        }
     }
     m->host_len += T;
     SKN_CUDA(ctx, skn_launch_last_rows(m->x, m->last, B, T, d, st));

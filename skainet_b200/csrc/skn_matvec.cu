@@ -683,11 +683,30 @@ struct Q6KStream {
 //   block : nch * wg warps; warp w -> chunk c = w % nch, row slot g = w / nch
 //   smem  : [warps][MV_NST][CHUNK_BYTES] ring | prepared x | [warps][MV_NST] mbarriers | [rows][nch] partials
 // Each warp walks its rows two at a time; stage s of its ring holds row i with i % MV_NST == s.
+//
+// A launch may cover up to three weight tensors of the same type, K and pitch that multiply the
+// same x (Q/K/V, gate/up): their rows are concatenated, row r of the concatenation belongs to
+// the first tensor whose cumulative end exceeds r.  `add[t]` (may be NULL) is added to tensor
+// t's outputs: a bias, or the residual stream when y aliases it.
+struct skn_mv_group {
+    const uint8_t *W[3];
+    float *y[3];
+    const float *add[3];
+    int64_t n_end[3];       // cumulative row counts
+    int count;
+};
+
+__device__ __forceinline__ int skn_group_find(const skn_mv_group &grp, int64_t r, int64_t &local) {
+    const int t = (r >= grp.n_end[0] ? 1 : 0) + ((grp.count > 2 && r >= grp.n_end[1]) ? 1 : 0);
+    local = r - (t ? grp.n_end[t - 1] : 0);
+    return t;
+}
+
 template <class S>
 __global__ void __launch_bounds__(512, 1)
-skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K, int nch, int wg,
-                  const float *__restrict__ x, const float *__restrict__ bias, float *__restrict__ y,
+skn_matvec_stream(const skn_mv_group grp, int64_t pitch, int K, int nch, int wg, const float *__restrict__ x,
                   int32_t *__restrict__ status, int relaxed) {
+    const int64_t N = grp.n_end[grp.count - 1];
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -714,8 +733,12 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K
     // a short last chunk may end off a 16-byte boundary: the copy runs a few bytes into the
     // next row (or the slack after the last one); those bytes are never decoded
     const uint32_t bytes = ((uint32_t)nbc * S::BLOCK_BYTES + 15u) & ~15u;
-    const uint8_t *src0 = W + (row_begin + g) * pitch + (size_t)c * S::CHUNK_BYTES;
-    const int64_t src_step = (int64_t)wg * pitch;
+    // global address of the chunk this warp reads from its i-th row
+    auto row_src = [&](int i) -> const uint8_t * {
+        int64_t local;
+        const int t = skn_group_find(grp, row_begin + g + (int64_t)i * wg, local);
+        return grp.W[t] + local * pitch + (size_t)c * S::CHUNK_BYTES;
+    };
 
     MV_STAMP(0);
     // weights never depend on the previous kernel: start streaming them right away, one
@@ -726,7 +749,7 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K
         skn_fence_proxy_async();
         if (lane < cnt) {
             skn_mbar_expect_tx(&bars[lane], bytes);
-            skn_bulk_g2s(ring + lane * S::CHUNK_BYTES, src0 + lane * src_step, bytes, &bars[lane]);
+            skn_bulk_g2s(ring + lane * S::CHUNK_BYTES, row_src(lane), bytes, &bars[lane]);
         }
     }
     __syncwarp();
@@ -769,7 +792,7 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K
             const int st = lane ? s1 : s0;
             skn_fence_proxy_async();
             skn_mbar_expect_tx(&bars[st], bytes);
-            skn_bulk_g2s(ring + st * S::CHUNK_BYTES, src0 + (int64_t)(i + lane + MV_NST) * src_step, bytes, &bars[st]);
+            skn_bulk_g2s(ring + st * S::CHUNK_BYTES, row_src(i + lane + MV_NST), bytes, &bars[st]);
         }
         pend += __shfl_xor_sync(0xffffffffu, pend, 2);
         const float v0 = dec.dot(r0);
@@ -797,8 +820,10 @@ skn_matvec_stream(const uint8_t *__restrict__ W, int64_t pitch, int64_t N, int K
     for (int lr = threadIdx.x; lr < rows; lr += blockDim.x) {
         float s = 0.f;
         for (int cc = 0; cc < nch; ++cc) s += part[(size_t)lr * nch + cc];
-        if (bias) s += bias[row_begin + lr];
-        y[row_begin + lr] = s;
+        int64_t local;
+        const int t = skn_group_find(grp, row_begin + lr, local);
+        if (grp.add[t]) s += grp.add[t][local];
+        grp.y[t][local] = s;
     }
     MV_STAMP(7);
 }
@@ -815,13 +840,13 @@ static int env_int(const char *name, int dflt) {
 //     one computes);
 //   - warps = nch * wg with wg chosen for about 8 warps.
 template <class S>
-static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &pl, bool relaxed) {
+static cudaError_t plan_stream(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_plan &pl, bool relaxed) {
     auto kern = skn_matvec_stream<S>;
     pl.state = -1;  // "no streaming plan" unless everything below works out
-    if (w->n_cols % S::BLOCK_WEIGHTS || w->n_cols > (1 << 20)) return cudaSuccess;
-    const int64_t nb = w->n_cols / S::BLOCK_WEIGHTS;
+    if (n_cols % S::BLOCK_WEIGHTS || n_cols > (1 << 20)) return cudaSuccess;
+    const int64_t nb = n_cols / S::BLOCK_WEIGHTS;
     const int nch = (int)((nb + S::CHUNK_BLOCKS - 1) / S::CHUNK_BLOCKS);
-    if (nch < 1 || nch > 16 || w->n_rows < 1) return cudaSuccess;
+    if (nch < 1 || nch > 16 || n_rows < 1) return cudaSuccess;
     static const int wg_env = env_int("SKN_MV_WG", 0);
     // Stream order: 8 warps per CTA (one launch computes while the next one only prefetches).
     // Relaxed order: 4 warps per CTA, so that CTAs of up to four consecutive launches share an
@@ -838,8 +863,8 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
     if (e != cudaSuccess) return e;
     static const int ctas_env = env_int("SKN_MV_CTAS_PER_SM", 1);
     int64_t grid = (int64_t)ctx->sm_count * (ctas_env > 0 ? ctas_env : 1);
-    if (grid > w->n_rows) grid = w->n_rows;
-    const int64_t rows_max = (w->n_rows + grid - 1) / grid;
+    if (grid > n_rows) grid = n_rows;
+    const int64_t rows_max = (n_rows + grid - 1) / grid;
     const int kpad = nch * S::CHUNK_WEIGHTS;
     int threads = 0;
     size_t smem = 0;
@@ -861,7 +886,7 @@ static cudaError_t plan_stream(skn_ctx *ctx, const skn_tensor *w, skn_mv_plan &p
 }
 
 template <class S>
-static cudaError_t launch_stream(skn_ctx *ctx, const skn_tensor *w, const float *x, const float *bias, float *y,
+static cudaError_t launch_stream(skn_ctx *ctx, const skn_mv_group &grp, int64_t pitch, int K, const float *x,
                                  const skn_mv_plan &pl, cudaStream_t stream) {
     auto kern = skn_matvec_stream<S>;
     cudaLaunchConfig_t cfg = {};
@@ -875,8 +900,7 @@ static cudaError_t launch_stream(skn_ctx *ctx, const skn_tensor *w, const float 
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, (const uint8_t *)w->d_blocks, w->pitch, w->n_rows, (int)w->n_cols, pl.nch,
-                              pl.wg, x, bias, y, ctx->d_status, ctx->relaxed_order);
+    return cudaLaunchKernelEx(&cfg, kern, grp, pitch, K, pl.nch, pl.wg, x, ctx->d_status, ctx->relaxed_order);
 }
 
 template <class S>
@@ -884,12 +908,72 @@ static bool try_stream(skn_ctx *ctx, const skn_tensor *w, const float *x, const 
                        cudaStream_t stream, cudaError_t &err) {
     skn_mv_plan &pl = const_cast<skn_tensor *>(w)->mv_plan[ctx->relaxed_order ? 1 : 0];
     if (pl.state == 0) {
-        err = plan_stream<S>(ctx, w, pl, ctx->relaxed_order != 0);
+        err = plan_stream<S>(ctx, w->n_rows, w->n_cols, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) { pl.state = 0; return true; }
     }
     if (pl.state != 1) return false;
-    err = launch_stream<S>(ctx, w, x, bias, y, pl, stream);
+    skn_mv_group grp = {};
+    grp.W[0] = w->d_blocks; grp.y[0] = y; grp.add[0] = bias; grp.n_end[0] = w->n_rows; grp.count = 1;
+    err = launch_stream<S>(ctx, grp, w->pitch, (int)w->n_cols, x, pl, stream);
     return true;
+}
+
+// Up to three tensors sharing x in one launch (M = 1).  Returns false when the shapes are not
+// covered by the streaming kernel (the caller then issues separate products).
+template <class S>
+static bool try_stream_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                             const float *const *add, cudaStream_t stream, cudaError_t &err) {
+    skn_mv_group grp = {};
+    int64_t tot = 0;
+    for (int t = 0; t < n; ++t) {
+        tot += w[t]->n_rows;
+        grp.W[t] = w[t]->d_blocks; grp.y[t] = y[t]; grp.add[t] = add ? add[t] : nullptr; grp.n_end[t] = tot;
+    }
+    for (int t = n; t < 3; ++t) grp.n_end[t] = tot;
+    grp.count = n;
+    // plans of grouped launches are cached by (rows, columns, order, device)
+    struct Cached { int64_t rows, cols; int relaxed, device; skn_mv_plan pl; };
+    static Cached cache[32];
+    static int n_cached = 0;
+    skn_mv_plan pl;
+    pl.state = 0;
+    for (int i = 0; i < n_cached; ++i)
+        if (cache[i].rows == tot && cache[i].cols == w[0]->n_cols && cache[i].relaxed == ctx->relaxed_order &&
+            cache[i].device == ctx->device) { pl = cache[i].pl; break; }
+    if (pl.state == 0) {
+        err = plan_stream<S>(ctx, tot, w[0]->n_cols, pl, ctx->relaxed_order != 0);
+        if (err != cudaSuccess) return true;
+        if (n_cached < 32) cache[n_cached++] = Cached{tot, w[0]->n_cols, ctx->relaxed_order, ctx->device, pl};
+    }
+    if (pl.state != 1) return false;
+    err = launch_stream<S>(ctx, grp, w[0]->pitch, (int)w[0]->n_cols, x, pl, stream);
+    return true;
+}
+
+// y[t] = W[t] . x (+ add[t]) for n <= 3 tensors of one type, K and pitch, one launch when the
+// streaming kernel covers the shape, separate launches otherwise.
+cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                                    const float *const *add, cudaStream_t stream) {
+    bool same = n >= 1 && n <= 3;
+    for (int t = 1; t < n && same; ++t)
+        same = w[t]->type == w[0]->type && w[t]->n_cols == w[0]->n_cols && w[t]->pitch == w[0]->pitch;
+    if (same && n > 1 && (w[0]->pitch % 16) == 0) {
+        cudaError_t err = cudaSuccess;
+        bool took = false;
+        switch (w[0]->type) {
+        case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, stream, err); break;
+        case SKN_TYPE_Q4_0: took = try_stream_group<Q40Stream>(ctx, n, w, x, y, add, stream, err); break;
+        case SKN_TYPE_Q8_0: took = try_stream_group<Q80Stream>(ctx, n, w, x, y, add, stream, err); break;
+        case SKN_TYPE_Q6_K: took = try_stream_group<Q6KStream>(ctx, n, w, x, y, add, stream, err); break;
+        default: break;
+        }
+        if (took) return err;
+    }
+    for (int t = 0; t < n; ++t) {
+        cudaError_t e = skn_launch_matvec(ctx, w[t], x, 1, add ? add[t] : nullptr, y[t], stream);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M, const float *bias,
