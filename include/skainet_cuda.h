@@ -154,6 +154,17 @@ int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, in
 int32_t skn_matvec_group_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
                              float *const *y_dev, const float *const *add_dev);
 
+/* skn_matvec_group_dev with an element-wise step folded into the preparation of x (no extra
+ * launch, no intermediate vector in HBM).  Exactly one of:
+ *   norm_gain_dev != NULL : x <- x / sqrt(mean(x^2) + norm_eps) * gain   (RMSNorm before Q/K/V or gate/up)
+ *   silu_u_dev    != NULL : x <- silu(x) * u                              (SwiGLU before the down projection)
+ * or neither (then identical to skn_matvec_group_dev).  x itself is not modified, so y[t] may
+ * alias add[t] but not x.  The reference would run these as separate tensor ops around
+ * Linear.forward (nn/Linear.kt:43-49); it has neither RMSNorm nor SiLU. */
+int32_t skn_matvec_fused_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
+                             float *const *y_dev, const float *const *add_dev, const float *norm_gain_dev,
+                             float norm_eps, const float *silu_u_dev);
+
 /* Y[M, N] = (silu(X . Wg^T) * (X . Wu^T)) . Wd^T -- the SwiGLU feed-forward block; Wg, Wu are
  * [F, K] (same block type), Wd is [N, F].  The reference has neither SiLU nor SwiGLU (its
  * sigmoid(), core/src/commonMain/kotlin/sk/ai/net/impl/DoublesTensor.kt:448-449, computes

@@ -323,6 +323,40 @@ int32_t skn_matvec_group_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w
     return SKN_OK;
 }
 
+int32_t skn_matvec_fused_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
+                             float *const *y_dev, const float *const *add_dev, const float *norm_gain_dev,
+                             float norm_eps, const float *silu_u_dev) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (n < 1 || n > 3 || !w || !y_dev || !x_dev) return skn_fail(ctx, SKN_ERR_ARG, "1 to 3 tensors, non-NULL arrays");
+    if (norm_gain_dev && silu_u_dev) return skn_fail(ctx, SKN_ERR_ARG, "either a norm gain or a SwiGLU partner, not both");
+    for (int32_t t = 0; t < n; ++t) {
+        if (!skn_tensor_ok(w[t]) || w[t]->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
+        if (w[t]->n_cols != w[0]->n_cols) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+        if (!y_dev[t] || (((uintptr_t)y_dev[t]) & 15)) return skn_fail(ctx, SKN_ERR_ALIGN, "outputs must be 16-byte aligned");
+    }
+    if ((((uintptr_t)x_dev) | ((uintptr_t)norm_gain_dev) | ((uintptr_t)silu_u_dev)) & 15)
+        return skn_fail(ctx, SKN_ERR_ALIGN, "x, gain and partner must be 16-byte aligned");
+    const int64_t K = w[0]->n_cols;
+    if (K % 4) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaError_t e = skn_launch_matvec_fused(ctx, n, w, x_dev, y_dev, add_dev, norm_gain_dev, norm_eps, silu_u_dev, ctx->stream);
+    if (e == cudaErrorNotSupported) {
+        // shapes outside the streaming kernel: transform x with the element-wise kernels first
+        const float *xin = x_dev;
+        if (norm_gain_dev || silu_u_dev) {
+            int32_t rc = skn_stage_reserve(ctx, &ctx->d_scratch, &ctx->d_scratch_bytes, (size_t)K * sizeof(float));
+            if (rc) return rc;
+            float *t = (float *)ctx->d_scratch;
+            if (norm_gain_dev) SKN_CUDA(ctx, skn_launch_rmsnorm(x_dev, norm_gain_dev, t, 1, (int)K, norm_eps, ctx->stream));
+            else SKN_CUDA(ctx, skn_launch_silu_mul(x_dev, silu_u_dev, t, K, ctx->sm_count, ctx->stream));
+            xin = t;
+        }
+        e = skn_launch_matvec_group(ctx, n, w, xin, y_dev, add_dev, ctx->stream);
+    }
+    SKN_CUDA(ctx, e);
+    return SKN_OK;
+}
+
 int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
                            const float *x_dev, int32_t M, float *y_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");

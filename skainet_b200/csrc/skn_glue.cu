@@ -81,30 +81,62 @@ __global__ void skn_gather_rows_kernel(const float *__restrict__ in, float *__re
         *reinterpret_cast<float4 *>(dst + i) = *reinterpret_cast<const float4 *>(src + i);
 }
 
-// ids[m] = argmax_v logits[m][v] (first maximum wins, as a sequential scan would give)
+// ids[m] = argmax_v logits[m][v] (first maximum wins, as a sequential scan would give).
+// Grid (ARGMAX_SPLIT, M): every CTA scans one slice of the row and leaves its candidate in
+// scratch; the CTA that draws the last ticket of its row (threadfence + atomic counter, no
+// waiting) picks the winner among the candidates and hands the ticket counter back as zero.
+constexpr int ARGMAX_SPLIT = 64;
+
+__device__ __forceinline__ void argmax_take(float &best, int &bi, float v, int i) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+
 __global__ void __launch_bounds__(256)
-skn_argmax_kernel(const float *__restrict__ logits, int V, int32_t *__restrict__ ids) {
+skn_argmax_kernel(const float *__restrict__ logits, int V, int32_t *__restrict__ ids, float *__restrict__ cand_v,
+                  int *__restrict__ cand_i, unsigned *__restrict__ tickets) {
     __shared__ float sv[8];
     __shared__ int si[8];
-    const float *row = logits + (size_t)blockIdx.x * V;
+    __shared__ bool last;
+    const int m = blockIdx.y, sp = blockIdx.x;
+    const float *row = logits + (size_t)m * V;
+    const int per = (V + ARGMAX_SPLIT - 1) / ARGMAX_SPLIT;
+    const int lo = sp * per, hi = min(V, lo + per);
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-    }
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_take(best, bi, row[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        argmax_take(best, bi, ov, oi);
     }
     if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
-        ids[blockIdx.x] = bi;
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) argmax_take(best, bi, sv[w], si[w]);
+        cand_v[m * ARGMAX_SPLIT + sp] = best;
+        cand_i[m * ARGMAX_SPLIT + sp] = bi;
+        __threadfence();
+        last = atomicAdd(&tickets[m], 1u) == (unsigned)(ARGMAX_SPLIT - 1);
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        best = -INFINITY;
+        bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < ARGMAX_SPLIT; i += 32)
+            argmax_take(best, bi, __ldcg(cand_v + m * ARGMAX_SPLIT + i), __ldcg(cand_i + m * ARGMAX_SPLIT + i));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_take(best, bi, ov, oi);
+        }
+        if (threadIdx.x == 0) {
+            ids[m] = (bi == 0x7fffffff) ? 0 : bi;   // a row of NaNs or -inf: token 0
+            tickets[m] = 0;
+        }
     }
 }
 
@@ -135,8 +167,14 @@ cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int 
     skn_gather_rows_kernel<<<B, 256, 0, st>>>(in, out, D, T);
     return cudaGetLastError();
 }
-cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, cudaStream_t st) {
+size_t skn_argmax_scratch_bytes(int M) { return (size_t)M * (ARGMAX_SPLIT * 8 + 4); }
+// scratch: skn_argmax_scratch_bytes(M) bytes whose ticket part was zeroed once (the kernel
+// leaves it zeroed)
+cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, void *scratch, cudaStream_t st) {
     if (M == 0) return cudaSuccess;
-    skn_argmax_kernel<<<M, 256, 0, st>>>(logits, V, ids);
+    float *cv = (float *)scratch;
+    int *ci = (int *)(cv + (size_t)M * ARGMAX_SPLIT);
+    unsigned *tk = (unsigned *)(ci + (size_t)M * ARGMAX_SPLIT);
+    skn_argmax_kernel<<<dim3(ARGMAX_SPLIT, (unsigned)M), 256, 0, st>>>(logits, V, ids, cv, ci, tk);
     return cudaGetLastError();
 }

@@ -78,6 +78,9 @@ cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitc
                                int64_t n_cols, float *out, cudaStream_t stream);
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M,
                               const float *bias, float *y, cudaStream_t stream);
+cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                                    const float *const *add, const float *norm_gain, float norm_eps,
+                                    const float *silu_u, cudaStream_t stream);
 cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                                     const float *const *add, cudaStream_t stream);
 
@@ -95,5 +98,16 @@ cudaError_t skn_launch_rmsnorm(const float *x, const float *gain, float *y, int 
 cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, int D, float theta, int sm_count, cudaStream_t st);
 cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st);
 cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int D, cudaStream_t st);
-cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, cudaStream_t st);
+size_t skn_argmax_scratch_bytes(int M);
+cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, void *scratch, cudaStream_t st);
 cudaError_t skn_launch_embed(const skn_tensor *emb, const int32_t *ids, int M, float *out, cudaStream_t st);
+
+// decoder-internal forms of the cache operations (skn_kv.cu): K/V rotated and written without
+// advancing the lengths, attention over the cache plus those T pending tokens, and one advance
+// for all layers at the end of a step
+int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k_new_dev, const float *v_new_dev,
+                                   int32_t n_q_heads, int32_t T, float theta, int32_t host_len_upper);
+int32_t skn_attn_causal_pending(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                                float *out_dev);
+int32_t *skn_kv_len_dev(const skn_kvcache *kv);
+cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, cudaStream_t st);

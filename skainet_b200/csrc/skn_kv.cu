@@ -32,7 +32,7 @@ struct skn_kvcache {
     int32_t *d_len, *d_start;
 };
 
-constexpr int ATT_CHUNK = 256;   // cached tokens per CTA
+constexpr int ATT_CHUNK = 256;   // cached tokens per CTA (64 when the grid would otherwise leave SMs idle)
 constexpr int ATT_WARPS = 4;
 
 static bool kv_ok(const skn_kvcache *kv) { return kv && kv->magic == SKN_MAGIC_KV && skn_ctx_ok(kv->ctx); }
@@ -80,6 +80,54 @@ __global__ void skn_kv_append_many_kernel(float *__restrict__ kc, float *__restr
 __global__ void skn_kv_advance_kernel(int32_t *__restrict__ len, int B, int T, int cap) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < B) len[b] = min(cap, len[b] + T);
+}
+
+// Decoder step, one CTA per new token (grid: T x batch): rotary embedding of the token's query
+// heads in place and of its key heads on their way into the ring, V copied alongside.  Pairs
+// (2i, 2i+1) of a head rotate by pos * theta^(-2i/D) with pos = len[b] + t (angle in double:
+// at position 4096 an fp32 angle is already off by ~5e-4 rad).  The lengths are NOT advanced
+// here: the decoder runs attention with `len_extra = T` and advances every layer's lengths
+// with one launch at the end of the step.
+__global__ void __launch_bounds__(256)
+skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, const float *__restrict__ v_new,
+                       float *__restrict__ kc, float *__restrict__ vc, const int32_t *__restrict__ len,
+                       const int32_t *__restrict__ start, int Hq, int Hkv, int D, int cap, int T, double log2_theta) {
+    const int b = blockIdx.y, t = blockIdx.x;
+    const int pos = len[b] + t;
+    const int slot = (start[b] + pos) % cap;
+    const int half = D / 2;
+    const size_t row = (size_t)b * T + t;
+    for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
+        const int p = i % half, h = i / half;
+        const double ang = (double)pos * exp2(-log2_theta * (2.0 * (double)p / (double)D));
+        double sd, cd;
+        sincos(ang, &sd, &cd);
+        const float sn = (float)sd, cs = (float)cd;
+        if (h < Hq) {
+            float2 *v = reinterpret_cast<float2 *>(q + (row * Hq + h) * D) + p;
+            const float2 a = *v;
+            *v = make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+        } else {
+            const int hk = h - Hq;
+            const float2 a = reinterpret_cast<const float2 *>(k_new + (row * Hkv + hk) * D)[p];
+            reinterpret_cast<float2 *>(kc + (((size_t)b * Hkv + hk) * cap + slot) * D)[p] =
+                make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+        }
+    }
+    for (int i = threadIdx.x; i < Hkv * D / 4; i += blockDim.x) {
+        const int h = (i * 4) / D, d = (i * 4) % D;
+        *reinterpret_cast<float4 *>(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d) =
+            *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d);
+    }
+}
+
+// len[l][b] += T for every layer's cache of a decoder (lens: device array of n_layers pointers)
+__global__ void skn_kv_advance_all_kernel(int32_t *const *__restrict__ lens, int n_layers, int B, int T, int cap) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_layers * B) {
+        int32_t *len = lens[i / B] + (i % B);
+        *len = min(cap, *len + T);
+    }
 }
 
 __global__ void skn_kv_gather_kernel(const float *__restrict__ kc, const float *__restrict__ vc,
@@ -173,16 +221,16 @@ template <> struct VecLoad<2> {
 };
 
 // D: head dim (64 or 128); G: query heads per kv head; TT: tokens per warp tile (TT*G <= 32)
-template <int D, int G, int TT>
+template <int D, int G, int TT, int CHUNK>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
                       const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
-                      float scale, float *__restrict__ part, int S, int tq) {
+                      float scale, float *__restrict__ part, int S, int tq, int len_extra) {
     constexpr int VEC = D / 32;
     constexpr int NV = TT * G;
     constexpr int REP = 32 / NV;                 // lanes holding the same (token, head) score
-    constexpr int TILES = ATT_CHUNK / (ATT_WARPS * TT);
-    __shared__ float s_sc[ATT_CHUNK][G];         // scores, then probabilities
+    constexpr int TILES = CHUNK / (ATT_WARPS * TT);
+    __shared__ float s_sc[CHUNK][G];         // scores, then probabilities
     __shared__ float s_red[ATT_WARPS][G];
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_o[ATT_WARPS][G][D];
@@ -191,10 +239,10 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     // sees the cache up to and including its own token (tq = 1: plain decode)
     const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = max(0, len[b] - (tq - 1 - bq % tq));
-    const int t0 = sp * ATT_CHUNK;
+    const int L = max(0, len[b] + len_extra - (tq - 1 - bq % tq));
+    const int t0 = sp * CHUNK;
     if (t0 >= L) return;
-    const int nt = min(ATT_CHUNK, L - t0);
+    const int nt = min(CHUNK, L - t0);
     const int s0 = start[b];
     const int Hq = Hkv * G;
     const float *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
@@ -330,10 +378,10 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
 
 template <int D>
 __global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
-                                      float *__restrict__ out, int tq) {
+                                      float *__restrict__ out, int tq, int chunk, int len_extra) {
     const int h = blockIdx.x, b = blockIdx.y;          // b = sequence * tq + t
-    const int L = max(0, len[b / tq] - (tq - 1 - b % tq));
-    const int ns = (L + ATT_CHUNK - 1) / ATT_CHUNK;
+    const int L = max(0, len[b / tq] + len_extra - (tq - 1 - b % tq));
+    const int ns = (L + chunk - 1) / chunk;
     const float *rec = part + ((size_t)b * Hq + h) * S * (D + 2);
     float m = -INFINITY;
     for (int s = 0; s < ns; ++s) m = fmaxf(m, rec[(size_t)s * (D + 2)]);
@@ -349,34 +397,47 @@ __global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int3
 }
 
 template <int D, int G>
-static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scale, float *part, int S, float *out,
-                               cudaStream_t stream, int tq) {
+static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scale, float *part, int chunk, float *out,
+                               cudaStream_t stream, int tq, int len_extra) {
     constexpr int TT = (G >= 8) ? 4 : 8;
+    const int S = (kv->capacity + chunk - 1) / chunk;
     const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)(kv->batch * tq));
-    skn_attn_split_kernel<D, G, TT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
-                                                                        kv->n_kv_heads, kv->capacity, scale, part, S, tq);
+    if (chunk == 64)
+        skn_attn_split_kernel<D, G, TT, 64><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+                                                                                kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra);
+    else
+        skn_attn_split_kernel<D, G, TT, ATT_CHUNK><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+                                                                                       kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)(kv->batch * tq));
-    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq);
+    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq, chunk, len_extra);
     return cudaGetLastError();
 }
 
-static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int S,
-                                 float *out, cudaStream_t st, int tq = 1) {
+// 64-token chunks when 256-token chunks would give fewer CTAs than two per SM (short contexts,
+// small batches) and the partials of the finer split fit `scratch_cap` bytes
+static int attn_pick_chunk(const skn_kvcache *kv, int n_q_heads, int tq, size_t scratch_cap) {
+    const int64_t ctas = (int64_t)kv->batch * tq * kv->n_kv_heads * ((kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK);
+    const int64_t need64 = (int64_t)kv->batch * tq * n_q_heads * ((kv->capacity + 63) / 64) * (kv->head_dim + 2) * 4;
+    return (ctas < 2 * (int64_t)kv->ctx->sm_count && (size_t)need64 <= scratch_cap) ? 64 : ATT_CHUNK;
+}
+
+static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,
+                                 float *out, cudaStream_t st, int tq = 1, int len_extra = 0) {
     if (kv->head_dim == 128) {
         switch (G) {
-        case 1: return launch_attn<128, 1>(kv, q, scale, part, S, out, st, tq);
-        case 2: return launch_attn<128, 2>(kv, q, scale, part, S, out, st, tq);
-        case 4: return launch_attn<128, 4>(kv, q, scale, part, S, out, st, tq);
-        case 8: return launch_attn<128, 8>(kv, q, scale, part, S, out, st, tq);
+        case 1: return launch_attn<128, 1>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 2: return launch_attn<128, 2>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 4: return launch_attn<128, 4>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 8: return launch_attn<128, 8>(kv, q, scale, part, chunk, out, st, tq, len_extra);
         }
     } else if (kv->head_dim == 64) {
         switch (G) {
-        case 1: return launch_attn<64, 1>(kv, q, scale, part, S, out, st, tq);
-        case 2: return launch_attn<64, 2>(kv, q, scale, part, S, out, st, tq);
-        case 4: return launch_attn<64, 4>(kv, q, scale, part, S, out, st, tq);
-        case 8: return launch_attn<64, 8>(kv, q, scale, part, S, out, st, tq);
+        case 1: return launch_attn<64, 1>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 2: return launch_attn<64, 2>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 4: return launch_attn<64, 4>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 8: return launch_attn<64, 8>(kv, q, scale, part, chunk, out, st, tq, len_extra);
         }
     }
     return cudaErrorInvalidValue;
@@ -559,14 +620,17 @@ int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
     if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
         return skn_fail(ctx, SKN_ERR_ALIGN, "q, out and scratch must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    int chunk = ATT_CHUNK;
     float *part = (float *)scratch_dev;
     if (!part) {
-        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads));
+        chunk = attn_pick_chunk(kv, n_q_heads, 1, (size_t)64 << 20);
+        const int S = (kv->capacity + chunk - 1) / chunk;
+        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes,
+                               (size_t)kv->batch * n_q_heads * S * (kv->head_dim + 2) * sizeof(float));
         if (rc) return rc;
         part = (float *)ctx->d_scratch2;
     }
-    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream));
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, chunk, out_dev, ctx->stream));
     return SKN_OK;
 }
 
@@ -613,8 +677,8 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
 // Causal attention of the T most recent positions of every sequence (after their K/V have been
 // appended): q, out are [batch][T][n_q_heads][head_dim]; query t attends to the cache up to its
 // own token.  T = 1 is skn_attn_decode_dev.  Scratch: T times skn_attn_scratch_bytes().
-int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
-                            float *out_dev, void *scratch_dev) {
+static int32_t attn_causal_impl(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                                float *out_dev, void *scratch_dev, int len_extra) {
     int G = 0;
     int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
     if (rc) return rc;
@@ -624,16 +688,57 @@ int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
     if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
         return skn_fail(ctx, SKN_ERR_ALIGN, "q, out and scratch must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
+    int chunk = ATT_CHUNK;
     float *part = (float *)scratch_dev;
     if (!part) {
-        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes, (size_t)skn_attn_scratch_bytes(kv, n_q_heads) * T);
+        chunk = attn_pick_chunk(kv, n_q_heads, T, (size_t)64 << 20);
+        const int S = (kv->capacity + chunk - 1) / chunk;
+        rc = skn_stage_reserve(ctx, &ctx->d_scratch2, &ctx->d_scratch2_bytes,
+                               (size_t)kv->batch * T * n_q_heads * S * (kv->head_dim + 2) * sizeof(float));
         if (rc) return rc;
         part = (float *)ctx->d_scratch2;
     }
-    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream, T));
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, chunk, out_dev, ctx->stream, T, len_extra));
     return SKN_OK;
 }
+
+int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                            float *out_dev, void *scratch_dev) {
+    return attn_causal_impl(kv, q_dev, n_q_heads, T, scale, out_dev, scratch_dev, 0);
+}
+
+}  // extern "C"
+
+// ---- decoder-internal forms (skn_llama.cu): append without advancing, attention over the
+// cache plus the T pending tokens, one advance for all layers
+int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k_new_dev, const float *v_new_dev,
+                                   int32_t n_q_heads, int32_t T, float theta, int32_t host_len_upper) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    skn_ctx *ctx = kv->ctx;
+    if ((int64_t)host_len_upper + T > kv->capacity)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
+    skn_rope_append_kernel<<<dim3((unsigned)T, (unsigned)kv->batch), 256, 0, ctx->stream>>>(
+        q_dev, k_new_dev, v_new_dev, kv->d_k, kv->d_v, kv->d_len, kv->d_start, n_q_heads, kv->n_kv_heads, kv->head_dim,
+        kv->capacity, T, log2((double)theta));
+    SKN_CUDA(ctx, cudaGetLastError());
+    return SKN_OK;
+}
+
+int32_t skn_attn_causal_pending(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
+                                float *out_dev) {
+    return attn_causal_impl(kv, q_dev, n_q_heads, T, scale, out_dev, nullptr, T);
+}
+
+int32_t *skn_kv_len_dev(const skn_kvcache *kv) { return kv_ok(kv) ? kv->d_len : nullptr; }
+
+cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, cudaStream_t st) {
+    const int n = n_layers * B;
+    if (n == 0) return cudaSuccess;
+    skn_kv_advance_all_kernel<<<(n + 127) / 128, 128, 0, st>>>(lens_dev, n_layers, B, T, cap);
+    return cudaGetLastError();
+}
+
+extern "C" {
 
 // ---- decode attention without any allocation -----------------------------------------------
 // Some hosts may not allocate device memory at the moment they need attention: a serving loop
@@ -671,8 +776,8 @@ int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t
         if (!p) return skn_fail(ctx, SKN_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
         part = g_attn_static_ptr[ctx->device] = (float *)p;
     }
-    const int S = (kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK;
-    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, S, out_dev, ctx->stream));
+    SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, attn_pick_chunk(kv, n_q_heads, 1, SKN_ATTN_STATIC_SCRATCH_BYTES),
+                                out_dev, ctx->stream));
     return SKN_OK;
 }
 

@@ -30,6 +30,8 @@ struct skn_llama {
     int32_t max_rows;
     float *x, *h, *q, *k, *v, *att, *proj, *last, *logits, *ffn_g, *ffn_u;
     int32_t *ids_in, *ids_out;
+    int32_t **len_ptrs;               // device array: the length vector of every layer's cache
+    void *argmax_scratch;             // candidates and tickets of the two-level argmax
     int32_t host_len;                 // tokens cached so far (the same for every sequence)
 };
 
@@ -72,6 +74,8 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     m->host_len = 0;
     m->x = m->h = m->q = m->k = m->v = m->att = m->proj = m->last = m->logits = m->ffn_g = m->ffn_u = nullptr;
     m->ids_in = m->ids_out = nullptr;
+    m->len_ptrs = nullptr;
+    m->argmax_scratch = nullptr;
     m->layers.resize(n_layers);
     for (auto &l : m->layers) l = skn_llama_layer{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaError_t e = cudaSetDevice(ctx->device);
@@ -92,6 +96,9 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     if (e == cudaSuccess) e = dev_alloc(&m->ffn_u, small_rows * ffn_dim);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_in, sizeof(int32_t) * R);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_out, sizeof(int32_t) * max_batch);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&m->len_ptrs, sizeof(int32_t *) * n_layers);
+    if (e == cudaSuccess) e = cudaMalloc(&m->argmax_scratch, skn_argmax_scratch_bytes(max_batch));
+    if (e == cudaSuccess) e = cudaMemset(m->argmax_scratch, 0, skn_argmax_scratch_bytes(max_batch));
     int32_t rc = SKN_OK;
     if (e != cudaSuccess) rc = skn_check_cuda(ctx, e, "decoder activation buffers");
     for (int l = 0; l < n_layers && rc == SKN_OK; ++l) {
@@ -99,6 +106,12 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
         if (e == cudaSuccess) e = dev_alloc(&m->layers[l].ffn_norm, d_model);
         if (e != cudaSuccess) { rc = skn_check_cuda(ctx, e, "decoder norm gains"); break; }
         rc = skn_kv_create(ctx, max_batch, n_kv_heads, head_dim, max_ctx, &m->layers[l].kv);
+    }
+    if (rc == SKN_OK) {
+        std::vector<int32_t *> lens(n_layers);
+        for (int l = 0; l < n_layers; ++l) lens[l] = skn_kv_len_dev(m->layers[l].kv);
+        e = cudaMemcpy(m->len_ptrs, lens.data(), sizeof(int32_t *) * n_layers, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = skn_check_cuda(ctx, e, "decoder length table");
     }
     if (rc != SKN_OK) {
         skn_llama_destroy(m);
@@ -118,6 +131,8 @@ int32_t skn_llama_destroy(skn_llama *m) {
     for (float *b : bufs) if (b) cudaFree(b);
     if (m->ids_in) cudaFree(m->ids_in);
     if (m->ids_out) cudaFree(m->ids_out);
+    if (m->len_ptrs) cudaFree(m->len_ptrs);
+    if (m->argmax_scratch) cudaFree(m->argmax_scratch);
     for (auto &l : m->layers) {
         if (l.attn_norm) cudaFree(l.attn_norm);
         if (l.ffn_norm) cudaFree(l.ffn_norm);
@@ -210,45 +225,90 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     const int32_t *ids = tokens_dev ? tokens_dev : m->ids_out;
     // below the prefill threshold every product is an fp32 streaming matvec per activation row
     const bool small = M <= 64 && !(ctx->prefill_min_m > 0 && M >= ctx->prefill_min_m);
+    // the step is a dependent chain: every launch keeps stream order whatever the context's
+    // launch-order option says
+    struct OrderGuard {
+        skn_ctx *c; int saved;
+        explicit OrderGuard(skn_ctx *cx) : c(cx), saved(cx->relaxed_order) { c->relaxed_order = 0; }
+        ~OrderGuard() { c->relaxed_order = saved; }
+    } guard(ctx);
     SKN_CUDA(ctx, skn_launch_embed(m->tok_embd, ids, M, m->x, st));
     int32_t rc;
+    const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_dim;
+    // fused form of one matvec launch; `fell_back` reports a shape the streaming kernel does not
+    // cover.  Folding the norm / SwiGLU into the preparation of x saves a launch per layer but
+    // adds a few microseconds to every row's launch: it pays for one or two rows, beyond that
+    // one batched element-wise launch is cheaper.
+    const bool fold = M <= 2;
+    auto fused = [&](int n, const skn_tensor *const *ws, const float *x, float *const *ys, const float *const *add,
+                     const float *gain, const float *silu_u, bool &fell_back) -> cudaError_t {
+        if (!fold) { fell_back = true; return cudaSuccess; }
+        const cudaError_t e = skn_launch_matvec_fused(ctx, n, ws, x, ys, add, gain, m->rms_eps, silu_u, st);
+        fell_back = (e == cudaErrorNotSupported);
+        return fell_back ? cudaSuccess : e;
+    };
     for (auto &l : m->layers) {
-        void *len_dev = nullptr;
-        rc = skn_kv_info(l.kv, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &len_dev, nullptr);
-        if (rc) return rc;
-        SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
-        const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_dim;
         if (small) {
-            // decode-size batches: Q/K/V in one launch per activation row
-            for (int r = 0; r < M; ++r) {
+            // decode-size batches, per activation row: RMSNorm folded into the preparation of x
+            // for Q/K/V (one launch) ...
+            bool fb = false;
+            for (int r = 0; r < M && !fb; ++r) {
                 const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
                 float *ys[3] = {m->q + r * qd, m->k + r * kd, m->v + r * kd};
-                SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 3, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+                SKN_CUDA(ctx, fused(3, ws, m->x + (int64_t)r * d, ys, nullptr, l.attn_norm, nullptr, fb));
+            }
+            if (fb) {
+                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
+                for (int r = 0; r < M; ++r) {
+                    const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
+                    float *ys[3] = {m->q + r * qd, m->k + r * kd, m->v + r * kd};
+                    SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 3, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+                }
             }
         } else {
+            SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
             if ((rc = skn_matmul_dev(ctx, l.wq, m->h, M, d, nullptr, m->q))) return rc;
             if ((rc = skn_matmul_dev(ctx, l.wk, m->h, M, d, nullptr, m->k))) return rc;
             if ((rc = skn_matmul_dev(ctx, l.wv, m->h, M, d, nullptr, m->v))) return rc;
         }
-        SKN_CUDA(ctx, skn_launch_rope(m->q, (const int32_t *)len_dev, M, T, Hq, D, m->rope_theta, ctx->sm_count, st));
-        SKN_CUDA(ctx, skn_launch_rope(m->k, (const int32_t *)len_dev, M, T, Hkv, D, m->rope_theta, ctx->sm_count, st));
-        if ((rc = skn_kv_append_many_dev(l.kv, m->k, m->v, T, m->host_len))) return rc;
-        if ((rc = skn_attn_causal_dev(l.kv, m->q, Hq, T, scale, m->att, nullptr))) return rc;
+        // rotary embedding of q in place and of k on its way into the cache, v alongside; the
+        // lengths advance once for all layers at the end of the step
+        if ((rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
+        if ((rc = skn_attn_causal_pending(l.kv, m->q, Hq, T, scale, m->att))) return rc;
         if (small) {
-            // output projection with the residual added in its epilogue (x += att . Wo^T)
+            // ... output projection with the residual added in its epilogue (x += att . Wo^T) ...
             for (int r = 0; r < M; ++r)
                 SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wo, m->att + r * qd, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
-            SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
-            // gate and up in one launch per row (q and att are free again: they hold g and u)
+            // ... gate and up with the second RMSNorm folded in (one launch) ...
             float *gbuf = m->ffn_g, *ubuf = m->ffn_u;
-            for (int r = 0; r < M; ++r) {
+            bool fb = false;
+            for (int r = 0; r < M && !fb; ++r) {
                 const skn_tensor *ws[2] = {l.wg, l.wu};
                 float *ys[2] = {gbuf + r * F, ubuf + r * F};
-                SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 2, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+                SKN_CUDA(ctx, fused(2, ws, m->x + (int64_t)r * d, ys, nullptr, l.ffn_norm, nullptr, fb));
             }
-            SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
-            for (int r = 0; r < M; ++r)
-                SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+            if (fb) {
+                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+                for (int r = 0; r < M; ++r) {
+                    const skn_tensor *ws[2] = {l.wg, l.wu};
+                    float *ys[2] = {gbuf + r * F, ubuf + r * F};
+                    SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 2, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+                }
+            }
+            // ... and the down projection of silu(g) * u, formed while x is prepared, with the
+            // residual in its epilogue
+            fb = false;
+            for (int r = 0; r < M && !fb; ++r) {
+                const skn_tensor *ws[1] = {l.wd};
+                float *ys[1] = {m->x + (int64_t)r * d};
+                const float *adds[1] = {m->x + (int64_t)r * d};
+                SKN_CUDA(ctx, fused(1, ws, gbuf + r * F, ys, adds, nullptr, ubuf + r * F, fb));
+            }
+            if (fb) {
+                SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
+                for (int r = 0; r < M; ++r)
+                    SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+            }
         } else {
             if ((rc = skn_matmul_dev(ctx, l.wo, m->att, M, qd, nullptr, m->proj))) return rc;
             SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
@@ -257,11 +317,21 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
             SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
         }
     }
+    SKN_CUDA(ctx, skn_kv_advance_all(m->len_ptrs, m->n_layers, B, T, m->max_ctx, st));
     m->host_len += T;
-    SKN_CUDA(ctx, skn_launch_last_rows(m->x, m->last, B, T, d, st));
-    SKN_CUDA(ctx, skn_launch_rmsnorm(m->last, m->out_norm, m->h, B, d, m->rms_eps, st));
-    if ((rc = skn_matmul_dev(ctx, m->output, m->h, B, d, nullptr, m->logits))) return rc;
-    SKN_CUDA(ctx, skn_launch_argmax(m->logits, B, m->vocab, m->ids_out, st));
+    // final norm + LM head on the last position of every sequence
+    bool fb = !(B <= 64 && !(ctx->prefill_min_m > 0 && B >= ctx->prefill_min_m));
+    for (int b = 0; b < B && !fb; ++b) {
+        const skn_tensor *ws[1] = {m->output};
+        float *ys[1] = {m->logits + (int64_t)b * m->vocab};
+        SKN_CUDA(ctx, fused(1, ws, m->x + ((int64_t)b * T + (T - 1)) * d, ys, nullptr, m->out_norm, nullptr, fb));
+    }
+    if (fb) {
+        SKN_CUDA(ctx, skn_launch_last_rows(m->x, m->last, B, T, d, st));
+        SKN_CUDA(ctx, skn_launch_rmsnorm(m->last, m->out_norm, m->h, B, d, m->rms_eps, st));
+        if ((rc = skn_matmul_dev(ctx, m->output, m->h, B, d, nullptr, m->logits))) return rc;
+    }
+    SKN_CUDA(ctx, skn_launch_argmax(m->logits, B, m->vocab, m->ids_out, m->argmax_scratch, st));
     return SKN_OK;
 }
 

@@ -137,6 +137,36 @@ __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane)
     return c;
 }
 
+// Optional transforms applied to x while it is prepared, so that the element-wise ops that
+// precede a projection in a decoder need no launch of their own:
+//   silu_u != NULL : x <- silu(x) * silu_u      (SwiGLU product feeding the down projection)
+//   gain   != NULL : x <- x * scale * gain      (RMSNorm; scale = rsqrt(mean(x^2) + eps) is
+//                                                computed by the CTA before the preparation)
+struct skn_xform {
+    const float *gain;
+    const float *silu_u;
+    float scale;
+};
+
+__device__ __forceinline__ float4 skn_load_x4(const float *__restrict__ x, int f, const skn_xform &xf) {
+    float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
+    if (xf.silu_u) {
+        const float4 u = __ldg(reinterpret_cast<const float4 *>(xf.silu_u) + f);
+        v.x = v.x / (1.f + expf(-v.x)) * u.x;
+        v.y = v.y / (1.f + expf(-v.y)) * u.y;
+        v.z = v.z / (1.f + expf(-v.z)) * u.z;
+        v.w = v.w / (1.f + expf(-v.w)) * u.w;
+    }
+    if (xf.gain) {
+        const float4 g = __ldg(reinterpret_cast<const float4 *>(xf.gain) + f);
+        v.x = v.x * xf.scale * g.x;
+        v.y = v.y * xf.scale * g.y;
+        v.z = v.z * xf.scale * g.z;
+        v.w = v.w * xf.scale * g.w;
+    }
+    return v;
+}
+
 // CTA-cooperative preparation of x for the 4-bit decoders: K activations from global memory ->
 // per group of 64: 32 packed pairs (pre-scaled by 2^(S - nibble position)), the two 32-element
 // sums and the factor 2^(149 - S).  kpad (a multiple of 2048) is the padded length; columns
@@ -147,7 +177,8 @@ __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane)
 // The pair of word-pair j, nibble position n = 2k+h is {x[word 2j], x[word 2j+1]} and sits in
 // 16-byte slot j*4 + k (rotated by the group index, see load_x), float 2h + (word & 1).
 template <bool Q40>
-static __device__ __forceinline__ void skn_prep_nibble_groups(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+static __device__ __forceinline__ void skn_prep_nibble_groups(const float *__restrict__ x, int K, int kpad, uint8_t *xs,
+                                                              const skn_xform &xf) {
     float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
     float *gun = gsum + kpad / 32;
     const int nf = kpad / 4;
@@ -158,7 +189,7 @@ static __device__ __forceinline__ void skn_prep_nibble_groups(const float *__res
 #pragma unroll
         for (int b = 0; b < B; ++b) {
             const int f = f0 + b * blockDim.x + threadIdx.x;
-            v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[b] = (f < nf && 4 * f < K) ? skn_load_x4(x, f, xf) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int b = 0; b < B; ++b) {
@@ -251,8 +282,8 @@ struct Q4KStream {
     uint32_t sel, m_low, m_top, m_nib;   // per-lane constants of the scale decode
     bool active;
 
-    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
-        skn_prep_nibble_groups<false>(x, K, kpad, xs);
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs, const skn_xform &xf) {
+        skn_prep_nibble_groups<false>(x, K, kpad, xs, xf);
     }
 
     __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
@@ -353,8 +384,8 @@ struct Q40Stream {
     int off;
     bool act_a, act_b;
 
-    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
-        skn_prep_nibble_groups<true>(x, K, kpad, xs);
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs, const skn_xform &xf) {
+        skn_prep_nibble_groups<true>(x, K, kpad, xs, xf);
     }
 
     __device__ __forceinline__ void load_x(const uint8_t *xs, int kpad, int chunk, int lane, int nblocks_in_chunk) {
@@ -432,7 +463,7 @@ struct Q80Stream {
     int sh;         // 0 or 16: bit offset of the block inside the window
     bool active;
 
-    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs, const skn_xform &xf) {
         float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
         float *gun = gsum + kpad / 32;
         const int nf = kpad / 4;
@@ -443,7 +474,7 @@ struct Q80Stream {
 #pragma unroll
             for (int b = 0; b < B; ++b) {
                 const int f = f0 + b * blockDim.x + threadIdx.x;
-                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[b] = (f < nf && 4 * f < K) ? skn_load_x4(x, f, xf) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int b = 0; b < B; ++b) {
@@ -555,7 +586,7 @@ struct Q6KStream {
     int sn, sq;                   // nibble shift (0 / 4) and qh shift (0 / 4) of group g0
     bool active;
 
-    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs) {
+    static __device__ __forceinline__ void prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *xs, const skn_xform &xf) {
         float *gsum = reinterpret_cast<float *>(xs + (size_t)kpad * 4);
         float *gun = gsum + kpad / 16;
         const int nf = kpad / 4;
@@ -566,7 +597,7 @@ struct Q6KStream {
 #pragma unroll
             for (int b = 0; b < B; ++b) {
                 const int f = f0 + b * blockDim.x + threadIdx.x;
-                v[b] = (f < nf && 4 * f < K) ? __ldg(reinterpret_cast<const float4 *>(x) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[b] = (f < nf && 4 * f < K) ? skn_load_x4(x, f, xf) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int b = 0; b < B; ++b) {
@@ -694,6 +725,9 @@ struct skn_mv_group {
     const float *add[3];
     int64_t n_end[3];       // cumulative row counts
     int count;
+    const float *norm_gain; // RMSNorm of x fused into its preparation (NULL: none)
+    float norm_eps;
+    const float *silu_u;    // x <- silu(x) * silu_u fused into its preparation (NULL: none)
 };
 
 __device__ __forceinline__ int skn_group_find(const skn_mv_group &grp, int64_t r, int64_t &local) {
@@ -760,7 +794,24 @@ skn_matvec_stream(const skn_mv_group grp, int64_t pitch, int K, int nch, int wg,
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
 
-    S::prep_x(x, K, kpad, xs);
+    skn_xform xf{grp.norm_gain, grp.silu_u, 1.f};
+    if (grp.norm_gain) {
+        // RMSNorm scale of the whole vector: every CTA reads all of x anyway
+        __shared__ float red[16];
+        float ss = 0.f;
+        for (int f = threadIdx.x; f < K / 4; f += blockDim.x) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w2 = 0; w2 < nwarps; ++w2) tot += red[w2];
+        xf.scale = rsqrtf(tot / (float)K + grp.norm_eps);
+    }
+    S::prep_x(x, K, kpad, xs, xf);
     __syncthreads();
     MV_STAMP(3);
     S dec;
@@ -922,8 +973,10 @@ static bool try_stream(skn_ctx *ctx, const skn_tensor *w, const float *x, const 
 // covered by the streaming kernel (the caller then issues separate products).
 template <class S>
 static bool try_stream_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
-                             const float *const *add, cudaStream_t stream, cudaError_t &err) {
+                             const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
+                             cudaStream_t stream, cudaError_t &err) {
     skn_mv_group grp = {};
+    grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
         tot += w[t]->n_rows;
@@ -950,24 +1003,35 @@ static bool try_stream_group(skn_ctx *ctx, int n, const skn_tensor *const *w, co
     return true;
 }
 
-// y[t] = W[t] . x (+ add[t]) for n <= 3 tensors of one type, K and pitch, one launch when the
-// streaming kernel covers the shape, separate launches otherwise.
-cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
-                                    const float *const *add, cudaStream_t stream) {
+// y[t] = W[t] . f(x) (+ add[t]) for n <= 3 tensors of one type, K and pitch in ONE launch of the
+// streaming kernel; f is the identity, an RMSNorm (norm_gain) and / or x <- silu(x) * silu_u.
+// Returns cudaErrorNotSupported when the shapes are not covered (nothing has been launched).
+cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                                    const float *const *add, const float *norm_gain, float norm_eps,
+                                    const float *silu_u, cudaStream_t stream) {
     bool same = n >= 1 && n <= 3;
     for (int t = 1; t < n && same; ++t)
         same = w[t]->type == w[0]->type && w[t]->n_cols == w[0]->n_cols && w[t]->pitch == w[0]->pitch;
-    if (same && n > 1 && (w[0]->pitch % 16) == 0) {
-        cudaError_t err = cudaSuccess;
-        bool took = false;
-        switch (w[0]->type) {
-        case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, stream, err); break;
-        case SKN_TYPE_Q4_0: took = try_stream_group<Q40Stream>(ctx, n, w, x, y, add, stream, err); break;
-        case SKN_TYPE_Q8_0: took = try_stream_group<Q80Stream>(ctx, n, w, x, y, add, stream, err); break;
-        case SKN_TYPE_Q6_K: took = try_stream_group<Q6KStream>(ctx, n, w, x, y, add, stream, err); break;
-        default: break;
-        }
-        if (took) return err;
+    if (!same || (w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
+    cudaError_t err = cudaSuccess;
+    bool took = false;
+    switch (w[0]->type) {
+    case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
+    case SKN_TYPE_Q4_0: took = try_stream_group<Q40Stream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
+    case SKN_TYPE_Q8_0: took = try_stream_group<Q80Stream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
+    case SKN_TYPE_Q6_K: took = try_stream_group<Q6KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
+    default: break;
+    }
+    return took ? err : cudaErrorNotSupported;
+}
+
+// y[t] = W[t] . x (+ add[t]): one launch when the streaming kernel covers the shapes, separate
+// launches otherwise.
+cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                                    const float *const *add, cudaStream_t stream) {
+    if (n > 1) {
+        const cudaError_t e = skn_launch_matvec_fused(ctx, n, w, x, y, add, nullptr, 0.f, nullptr, stream);
+        if (e != cudaErrorNotSupported) return e;
     }
     for (int t = 0; t < n; ++t) {
         cudaError_t e = skn_launch_matvec(ctx, w[t], x, 1, add ? add[t] : nullptr, y[t], stream);

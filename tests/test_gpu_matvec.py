@@ -171,3 +171,47 @@ def test_grouped_matvec_equals_separate_products(ctx):
             assert torch.equal(a, b)
         for w in ws:
             w.close()
+
+
+def test_fused_norm_and_swiglu_preparation(ctx):
+    """RMSNorm or silu(x) * u folded into the matvec's preparation of x, against the oracle's
+    product over the separately transformed vector (fp32 tolerance on sum |w . x|); a group of
+    mixed block types takes the element-wise kernels plus separate launches instead."""
+    import ctypes
+    import torch
+    from skainet_b200 import _ffi
+    L = _ffi.lib()
+    g = synth.rng(77)
+    K, eps = 4096, 1e-5
+    for types in ((synth.Q4_K, synth.Q4_K), (synth.Q6_K, synth.Q6_K), (synth.Q8_0, synth.Q8_0), (synth.Q4_0, synth.Q4_0),
+                  (synth.Q4_K, synth.Q8_0)):
+        shapes = [(192, K), (72, K)]
+        blocks = [synth.make_weight(g, qt, *s) for qt, s in zip(types, shapes)]
+        ws = [skn.QuantTensor(ctx, s, qt, b) for qt, s, b in zip(types, shapes, blocks)]
+        x = synth.make_activations(g, 1, K)[0].astype(np.float32)
+        gain = (1.0 + 0.1 * g.standard_normal(K)).astype(np.float32)
+        u = g.standard_normal(K).astype(np.float32)
+        res = g.standard_normal(shapes[0][0]).astype(np.float32)
+        x64 = x.astype(np.float64)
+        x_norm = (x64 / np.sqrt(np.mean(x64 * x64) + eps) * gain).astype(np.float32)
+        x_silu = (x64 / (1.0 + np.exp(-x64)) * u).astype(np.float32)
+        xd, gd, ud = (torch.from_numpy(a.copy()).cuda() for a in (x, gain, u))
+        wp = (ctypes.c_void_p * 2)(*[w.handle.value for w in ws])
+        for name, xin, gp, up in (("norm", x_norm, gd.data_ptr(), None), ("swiglu", x_silu, None, ud.data_ptr())):
+            ys = [torch.from_numpy(res.copy()).cuda(), torch.empty(shapes[1][0], device="cuda")]
+            yp = (ctypes.c_void_p * 2)(*[y.data_ptr() for y in ys])
+            ap = (ctypes.c_void_p * 2)(ys[0].data_ptr(), None)
+            rc = L.skn_matvec_fused_dev(ctx.handle, 2, wp, xd.data_ptr(), yp, ap, gp, eps, up)
+            assert rc == 0, L.skn_last_error(ctx.handle)
+            ctx.sync()
+            for t, (qt, s, b) in enumerate(zip(types, shapes, blocks)):
+                y_ref, absdot = oracle.matmul(qt, b, s[0], K, xin[None, :])
+                if t == 0:
+                    y_ref = y_ref + res[None, :]
+                    absdot = absdot + np.abs(res)[None, :]
+                # the in-kernel transform rounds x once more than the reference vector does
+                assert_close_dot(ys[t].cpu().numpy()[None, :], y_ref, absdot, 4 * FP32_TOL, f"{name} types {types} tensor {t}")
+        rc = L.skn_matvec_fused_dev(ctx.handle, 2, wp, xd.data_ptr(), yp, ap, gd.data_ptr(), eps, ud.data_ptr())
+        assert rc == 8 and "not both" in L.skn_last_error(ctx.handle).decode()
+        for w in ws:
+            w.close()
