@@ -251,6 +251,31 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
 int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
                             float *out_dev, void *scratch_dev);
 
+/* ---- Exchange between the GPUs of one box ------------------------------------------------------
+ * Sum of per-rank partial products of a K-sharded (row-parallel) layer, and, with zero-filled
+ * slots, the concatenation of the slices of an N-sharded (column-parallel) one.  The reference
+ * has no multi-device notion (core/src/commonMain/kotlin/sk/ai/net/Tensor.kt:6-33): new surface.
+ * Every rank owns an inbox that its peers write with ordinary peer stores; one kernel per rank
+ * pushes, waits (bounded: about two seconds, then SKN_ERR_TIMEOUT is reported by the next
+ * skn_sync and later exchanges stop waiting) and sums in rank order, so every rank obtains the
+ * same bits.  No library collective is involved and the sequence is CUDA-graph capturable.
+ *   one process per GPU : skn_comm_create on every rank, exchange skn_comm_handle() blobs
+ *                         (skn_comm_handle_bytes() each) by any host channel, skn_comm_connect;
+ *   one process, n GPUs : skn_comm_create per device, then skn_comm_connect_local(all of them).
+ * capacity_floats bounds the element count of one skn_allreduce_dev call. */
+typedef struct skn_comm skn_comm;
+int32_t skn_comm_create(skn_ctx *ctx, int32_t rank, int32_t world, int64_t capacity_floats, skn_comm **out);
+int32_t skn_comm_destroy(skn_comm *c);
+int32_t skn_comm_handle_bytes(void);
+int32_t skn_comm_handle(skn_comm *c, void *handle_out);
+int32_t skn_comm_connect(skn_comm *c, const void *handles_in_rank_order);
+int32_t skn_comm_connect_local(skn_comm *const *comms, int32_t n);
+int32_t skn_comm_info(const skn_comm *c, int32_t *rank, int32_t *world, int64_t *capacity_floats);
+/* out = resid + sum over ranks of partial: n floats (multiple of 4), 16-byte aligned device
+ * pointers; resid may be NULL; out may alias resid or partial.  Collective: every rank calls it
+ * the same number of times with the same n. */
+int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *resid_dev, float *out_dev, int64_t n);
+
 /* ---- Llama-style decoder ---------------------------------------------------------------------
  * RMSNorm -> Q/K/V -> rotary embedding (interleaved pairs) -> KV append -> grouped-query
  * attention -> output projection -> residual -> RMSNorm -> SwiGLU FFN -> residual; final norm,
@@ -264,6 +289,20 @@ typedef struct skn_llama skn_llama;
 int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
                          int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
                          int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_llama **out);
+/* Tensor-parallel form: the geometry arguments stay those of the WHOLE model; rank r of the
+ * exchange owns n_heads / world query heads and n_kv_heads / world KV heads (with their cache),
+ * ffn_dim / world FFN columns and vocab / world LM-head rows, all contiguous ranges in rank
+ * order.  skn_llama_set_layer then takes wq [n_heads*head_dim/world, d_model], wk, wv
+ * [n_kv_heads*head_dim/world, d_model], wo [d_model, n_heads*head_dim/world] (a K-shard),
+ * w_gate, w_up [ffn_dim/world, d_model], w_down [d_model, ffn_dim/world] (a K-shard);
+ * skn_llama_set_head takes the full embedding table and output [vocab/world, d_model].  The
+ * partial products of wo and w_down are summed through the exchange (two per layer), the
+ * greedy token is chosen across the ranks' vocabulary slices, and logits_host of
+ * skn_llama_forward receives this rank's slice [max_batch][vocab/world].  comm == NULL or a
+ * world of one is skn_llama_create. */
+int32_t skn_llama_create_tp(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
+                            int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
+                            int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_comm *comm, skn_llama **out);
 int32_t skn_llama_destroy(skn_llama *m);
 int32_t skn_llama_set_layer(skn_llama *m, int32_t layer, const skn_tensor *wq, const skn_tensor *wk,
                             const skn_tensor *wv, const skn_tensor *wo, const skn_tensor *w_gate,

@@ -54,6 +54,16 @@ SIGNATURES = {
     "skn_attn_scratch_bytes": (c_i64, [c_vp, c_i32]),
     "skn_kv_append_many_dev": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i32]),
     "skn_attn_causal_dev": (c_i32, [c_vp, c_vp, c_i32, c_i32, ctypes.c_float, c_vp, c_vp]),
+    "skn_comm_create": (c_i32, [c_vp, c_i32, c_i32, c_i64, P(c_vp)]),
+    "skn_comm_destroy": (c_i32, [c_vp]),
+    "skn_comm_handle_bytes": (c_i32, []),
+    "skn_comm_handle": (c_i32, [c_vp, c_vp]),
+    "skn_comm_connect": (c_i32, [c_vp, c_vp]),
+    "skn_comm_connect_local": (c_i32, [c_vp, c_i32]),
+    "skn_comm_info": (c_i32, [c_vp, c_vp, c_vp, c_vp]),
+    "skn_allreduce_dev": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64]),
+    "skn_llama_create_tp": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.c_float, ctypes.c_float,
+                                    c_i32, c_i32, c_i32, c_vp, P(c_vp)]),
     "skn_llama_create": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, ctypes.c_float, ctypes.c_float,
                                  c_i32, c_i32, c_i32, P(c_vp)]),
     "skn_llama_destroy": (c_i32, [c_vp]),

@@ -1,0 +1,292 @@
+// C1/C2: exchange between the GPUs of one box without a library collective.
+//
+// Every rank owns one "inbox" allocation that its peers map (CUDA IPC between processes, peer
+// access inside one process):
+//
+//   [ flags : uint32 flag[NBUF][MAX_WORLD] ]  4 KiB
+//   [ data  : float  inbox[NBUF][world][capacity] ]
+//
+// Reduce number q (q = 0, 1, 2, ... counted on the device, so that a captured CUDA graph can be
+// replayed) uses buffer q % NBUF.  One kernel per rank does the whole exchange:
+//   1. push    every CTA copies its share of the local partial into inbox[q % NBUF][rank] of
+//              every peer with plain peer stores, then a system-wide fence and a ticket; the CTA
+//              that draws the last ticket releases flag[q % NBUF][rank] = q + 1 on every peer;
+//   2. wait    one thread per peer polls the local flags with acquire loads; the wait is bounded
+//              (about two seconds, then SKN_ERR_TIMEOUT lands in the context's status word and
+//              later exchanges do not wait at all);
+//   3. sum     out = resid + partial_0 + partial_1 + ... in rank order, the same on every rank,
+//              so the replicated residual stream stays bit-identical across ranks.
+// The kernel runs with one CTA per SM at most, so all its CTAs are resident while any of them
+// waits.  Two buffers suffice: a peer can push reduce q + 2 only after it has finished reduce
+// q + 1, which needs this rank's push of q + 1, which this rank issues after its own reduce q
+// has completed.
+//
+// No multicast, no bulk-async loads from peer memory: only ordinary stores to peers and loads
+// from local memory.
+#include "skn_internal.cuh"
+#include "skn_ptx.cuh"
+
+#include <new>
+
+#define SKN_MAGIC_COMM 0x736b6e6du   // 'sknm'
+
+constexpr int COMM_NBUF = 2;
+constexpr int COMM_MAX_WORLD = 8;
+constexpr size_t COMM_FLAG_BYTES = 4096;
+
+struct skn_comm {
+    uint32_t magic;
+    skn_ctx *ctx;
+    int32_t rank, world;
+    int64_t capacity;                  // floats per (buffer, source rank)
+    uint8_t *local;                    // this rank's inbox allocation
+    uint8_t *peer[COMM_MAX_WORLD];     // peers' inboxes as mapped here (peer[rank] == local)
+    bool ipc_mapped[COMM_MAX_WORLD];
+    uint32_t *d_state;                 // [0] reduce counter q, [1] push tickets, [2] finish tickets
+    bool connected;
+};
+
+struct comm_peers {
+    uint8_t *base[COMM_MAX_WORLD];
+};
+
+static bool comm_ok(const skn_comm *c) { return c && c->magic == SKN_MAGIC_COMM && skn_ctx_ok(c->ctx); }
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float *comm_inbox(uint8_t *base, int buf, int world, int src, int64_t cap) {
+    return reinterpret_cast<float *>(base + COMM_FLAG_BYTES) + ((int64_t)buf * world + src) * cap;
+}
+__device__ __forceinline__ uint32_t *comm_flag(uint8_t *base, int buf, int src) {
+    return reinterpret_cast<uint32_t *>(base) + buf * COMM_MAX_WORLD + src;
+}
+
+// out[i] = resid[i] + sum over ranks of partial_r[i]   (resid may be NULL, out may alias resid
+// or partial); n is a multiple of 4.
+__global__ void __launch_bounds__(256)
+skn_allreduce_push_kernel(comm_peers peers, int rank, int world, int64_t cap, uint32_t *__restrict__ state,
+                          int32_t *__restrict__ status, const float *__restrict__ partial,
+                          const float *__restrict__ resid, float *__restrict__ out, int64_t n) {
+    __shared__ uint32_t s_q;
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) s_q = *reinterpret_cast<volatile uint32_t *>(state);
+    __syncthreads();
+    const uint32_t q = s_q;
+    const int buf = (int)(q % COMM_NBUF);
+    const int64_t n4 = n / 4;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
+
+    // 1. push
+    for (int p = 1; p < world; ++p) {
+        const int dst = (rank + p) % world;           // start with a different peer on every rank
+        float4 *to = reinterpret_cast<float4 *>(comm_inbox(peers.base[dst], buf, world, rank, cap));
+        for (int64_t i = tid; i < n4; i += nthr) to[i] = reinterpret_cast<const float4 *>(partial)[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
+        if (s_last) {
+            state[1] = 0;
+            __threadfence_system();
+            for (int p = 1; p < world; ++p) st_release_sys(comm_flag(peers.base[(rank + p) % world], buf, rank), q + 1);
+        }
+    }
+
+    // 2. wait for every peer's push of reduce q
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        const uint32_t *flag = comm_flag(peers.base[rank], buf, threadIdx.x);
+        if (*reinterpret_cast<volatile int32_t *>(status) == 0) {
+            const uint64_t t0 = skn_globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys(flag) != q + 1) {
+                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > 2000000000ull) {
+                    atomicExch(status, SKN_ERR_TIMEOUT);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // 3. sum in rank order
+    for (int64_t i = tid; i < n4; i += nthr) {
+        float4 acc = resid ? reinterpret_cast<const float4 *>(resid)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int src = 0; src < world; ++src) {
+            const float4 v = (src == rank)
+                                 ? reinterpret_cast<const float4 *>(partial)[i]
+                                 : __ldcg(reinterpret_cast<const float4 *>(comm_inbox(peers.base[rank], buf, world, src, cap)) + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4 *>(out)[i] = acc;
+    }
+    __syncthreads();
+    // the CTA that finishes last moves the counter on
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {
+            state[2] = 0;
+            *reinterpret_cast<volatile uint32_t *>(state) = q + 1;
+        }
+    }
+}
+
+extern "C" {
+
+int32_t skn_comm_destroy(skn_comm *c);
+
+int32_t skn_comm_create(skn_ctx *ctx, int32_t rank, int32_t world, int64_t capacity_floats, skn_comm **out) {
+    if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
+    *out = nullptr;
+    if (world < 1 || world > COMM_MAX_WORLD || rank < 0 || rank >= world)
+        return skn_fail(ctx, SKN_ERR_ARG, "rank %d outside a world of %d (at most %d ranks)", rank, world, COMM_MAX_WORLD);
+    if (capacity_floats < 4) return skn_fail(ctx, SKN_ERR_ARG, "capacity must be at least 4 floats");
+    skn_comm *c = new (std::nothrow) skn_comm();
+    if (!c) return skn_fail(ctx, SKN_ERR_OOM, "host allocation failed");
+    c->magic = SKN_MAGIC_COMM;
+    c->ctx = ctx;
+    c->rank = rank;
+    c->world = world;
+    c->capacity = (capacity_floats + 63) / 64 * 64;
+    c->local = nullptr;
+    c->d_state = nullptr;
+    c->connected = (world == 1);
+    for (int i = 0; i < COMM_MAX_WORLD; ++i) { c->peer[i] = nullptr; c->ipc_mapped[i] = false; }
+    const size_t bytes = COMM_FLAG_BYTES + (size_t)COMM_NBUF * world * c->capacity * sizeof(float);
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&c->local, bytes);
+    if (e == cudaSuccess) e = cudaMemset(c->local, 0, COMM_FLAG_BYTES);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&c->d_state, 64);
+    if (e == cudaSuccess) e = cudaMemset(c->d_state, 0, 64);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        const int32_t rc = skn_check_cuda(ctx, e, "exchange buffers");
+        skn_comm_destroy(c);
+        return rc;
+    }
+    c->peer[rank] = c->local;
+    *out = c;
+    return SKN_OK;
+}
+
+int32_t skn_comm_destroy(skn_comm *c) {
+    if (!c || c->magic != SKN_MAGIC_COMM) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+    if (skn_ctx_ok(c->ctx)) {
+        cudaSetDevice(c->ctx->device);
+        cudaStreamSynchronize(c->ctx->stream);
+    }
+    for (int i = 0; i < COMM_MAX_WORLD; ++i)
+        if (c->ipc_mapped[i] && c->peer[i]) cudaIpcCloseMemHandle(c->peer[i]);
+    if (c->local) cudaFree(c->local);
+    if (c->d_state) cudaFree(c->d_state);
+    c->magic = 0;
+    delete c;
+    return SKN_OK;
+}
+
+int32_t skn_comm_handle_bytes(void) { return (int32_t)sizeof(cudaIpcMemHandle_t); }
+
+// Writes the inter-process handle of this rank's inbox (skn_comm_handle_bytes() bytes).
+int32_t skn_comm_handle(skn_comm *c, void *handle_out) {
+    if (!comm_ok(c)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+    if (!handle_out) return skn_fail(c->ctx, SKN_ERR_ARG, "handle_out is NULL");
+    SKN_CUDA(c->ctx, cudaSetDevice(c->ctx->device));
+    cudaIpcMemHandle_t h;
+    SKN_CUDA(c->ctx, cudaIpcGetMemHandle(&h, c->local));
+    memcpy(handle_out, &h, sizeof(h));
+    return SKN_OK;
+}
+
+// One process per GPU: `handles` holds the world's handles in rank order (this rank's own
+// entry is ignored).  Every rank must have created its exchange with the same capacity.
+int32_t skn_comm_connect(skn_comm *c, const void *handles) {
+    if (!comm_ok(c)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+    skn_ctx *ctx = c->ctx;
+    if (!handles) return skn_fail(ctx, SKN_ERR_ARG, "handles is NULL");
+    if (c->connected) return skn_fail(ctx, SKN_ERR_ARG, "exchange already connected");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + (size_t)r * sizeof(h), sizeof(h));
+        void *p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return skn_fail(ctx, SKN_ERR_COMM, "cannot map the inbox of rank %d: %s", r, cudaGetErrorString(e));
+        }
+        c->peer[r] = (uint8_t *)p;
+        c->ipc_mapped[r] = true;
+    }
+    c->connected = true;
+    return SKN_OK;
+}
+
+// One process driving several GPUs: connects the n = world exchanges of that process (rank
+// order) through peer access.
+int32_t skn_comm_connect_local(skn_comm *const *comms, int32_t n) {
+    if (!comms || n < 1 || n > COMM_MAX_WORLD) return skn_fail(nullptr, SKN_ERR_ARG, "1 to %d exchanges", COMM_MAX_WORLD);
+    for (int i = 0; i < n; ++i)
+        if (!comm_ok(comms[i]) || comms[i]->world != n || comms[i]->rank != i || comms[i]->capacity != comms[0]->capacity)
+            return skn_fail(nullptr, SKN_ERR_ARG, "exchanges must be given in rank order with equal world and capacity");
+    for (int i = 0; i < n; ++i) {
+        skn_ctx *ctx = comms[i]->ctx;
+        SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+        for (int j = 0; j < n; ++j) {
+            if (j == i) continue;
+            if (comms[j]->ctx->device != ctx->device) {
+                int can = 0;
+                SKN_CUDA(ctx, cudaDeviceCanAccessPeer(&can, ctx->device, comms[j]->ctx->device));
+                if (!can) return skn_fail(ctx, SKN_ERR_COMM, "device %d cannot access device %d", ctx->device, comms[j]->ctx->device);
+                const cudaError_t e = cudaDeviceEnablePeerAccess(comms[j]->ctx->device, 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return skn_check_cuda(ctx, e, "peer access");
+                cudaGetLastError();
+            }
+            comms[i]->peer[j] = comms[j]->local;
+        }
+        comms[i]->connected = true;
+    }
+    return SKN_OK;
+}
+
+int32_t skn_comm_info(const skn_comm *c, int32_t *rank, int32_t *world, int64_t *capacity_floats) {
+    if (!comm_ok(c)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+    if (rank) *rank = c->rank;
+    if (world) *world = c->world;
+    if (capacity_floats) *capacity_floats = c->capacity;
+    return SKN_OK;
+}
+
+// out = resid + sum over ranks of partial (all device pointers, n floats, n % 4 == 0, 16-byte
+// aligned; resid may be NULL; out may alias resid or partial).  Every rank must call this the
+// same number of times with the same n.  Enqueued on the context's stream.
+int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *resid_dev, float *out_dev, int64_t n) {
+    if (!comm_ok(c)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+    skn_ctx *ctx = c->ctx;
+    if (!c->connected) return skn_fail(ctx, SKN_ERR_COMM, "exchange not connected");
+    if (n < 0 || n % 4) return skn_fail(ctx, SKN_ERR_SHAPE, "element count must be a non-negative multiple of 4");
+    if (n > c->capacity) return skn_fail(ctx, SKN_ERR_SHAPE, "%lld floats exceed the exchange capacity %lld", (long long)n, (long long)c->capacity);
+    if (n == 0) return SKN_OK;
+    if (!partial_dev || !out_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
+    if ((((uintptr_t)partial_dev) | ((uintptr_t)resid_dev) | ((uintptr_t)out_dev)) & 15)
+        return skn_fail(ctx, SKN_ERR_ALIGN, "buffers must be 16-byte aligned");
+    SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    comm_peers peers;
+    for (int i = 0; i < COMM_MAX_WORLD; ++i) peers.base[i] = c->peer[i];
+    int64_t blocks = (n / 4 + 255) / 256;
+    if (blocks > ctx->sm_count) blocks = ctx->sm_count;    // every CTA resident while any of them waits
+    skn_allreduce_push_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(peers, c->rank, c->world, c->capacity, c->d_state,
+                                                                       ctx->d_status, partial_dev, resid_dev, out_dev, n);
+    SKN_CUDA(ctx, cudaGetLastError());
+    return SKN_OK;
+}
+
+}  // extern "C"

@@ -178,3 +178,45 @@ cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, v
     skn_argmax_kernel<<<dim3(ARGMAX_SPLIT, (unsigned)M), 256, 0, st>>>(logits, V, ids, cv, ci, tk);
     return cudaGetLastError();
 }
+
+// Cross-rank greedy choice.  offer: cand[world][B][2] is zero except this rank's slots, which
+// hold (best logit of the local slice, its global token id as a float; ids stay below 2^24).
+// pick (after the slots of all ranks have been summed together): highest value wins, ties go
+// to the lowest id; a slice whose best is NaN never wins.
+__global__ void skn_argmax_offer_kernel(const float *__restrict__ logits, const int32_t *__restrict__ ids, int B, int V_local,
+                                        int rank, int world, float *__restrict__ cand) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = (world * B * 2 + 3) / 4 * 4;
+    if (i >= n) return;
+    float v = 0.f;
+    const int slot = i / 2, r = slot / B, b = slot % B;
+    if (slot < world * B && r == rank) {
+        const int id = ids[b];
+        v = (i & 1) ? (float)(id + rank * V_local) : logits[(size_t)b * V_local + id];
+    }
+    cand[i] = v;
+}
+
+__global__ void skn_argmax_pick_kernel(const float *__restrict__ cand, int B, int world, int32_t *__restrict__ ids) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < world; ++r) {
+        const float v = cand[((size_t)r * B + b) * 2];
+        const int id = (int)cand[((size_t)r * B + b) * 2 + 1];
+        argmax_take(best, bi, v, id);
+    }
+    ids[b] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+cudaError_t skn_launch_argmax_offer(const float *logits, const int32_t *ids, int B, int V_local, int rank, int world,
+                                    float *cand, cudaStream_t st) {
+    const int n = (world * B * 2 + 3) / 4 * 4;
+    skn_argmax_offer_kernel<<<(n + 127) / 128, 128, 0, st>>>(logits, ids, B, V_local, rank, world, cand);
+    return cudaGetLastError();
+}
+cudaError_t skn_launch_argmax_pick(const float *cand, int B, int world, int32_t *ids, cudaStream_t st) {
+    skn_argmax_pick_kernel<<<(B + 127) / 128, 128, 0, st>>>(cand, B, world, ids);
+    return cudaGetLastError();
+}

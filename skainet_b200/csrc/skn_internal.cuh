@@ -12,6 +12,22 @@
 #define SKN_MAGIC_TENSOR 0x736b6e74u  // 'sknt'
 #define SKN_MAGIC_KV 0x736b6e6bu      // 'sknk'
 
+// cached launch geometry of the streaming matvec (state: 0 = not planned yet,
+// 1 = valid, -1 = shape not covered by the streaming kernel)
+struct skn_mv_plan {
+    int state;
+    int nch, wg, grid, threads;
+    size_t smem;
+};
+
+// plan of a grouped launch, cached in the context by (block type, total rows, columns, order)
+struct skn_group_plan {
+    int32_t type;
+    int relaxed;
+    int64_t rows, cols;
+    skn_mv_plan pl;
+};
+
 struct skn_ctx {
     uint32_t magic;
     int device;
@@ -27,15 +43,9 @@ struct skn_ctx {
     void *d_stage_out; size_t d_stage_out_bytes;
     void *d_scratch;   size_t d_scratch_bytes;   // kernel scratch (bf16 operands, FFN intermediates)
     void *d_scratch2;  size_t d_scratch2_bytes;  // attention split partials
+    skn_group_plan group_plans[32];
+    int n_group_plans;
     char err[512];
-};
-
-// cached launch geometry of the streaming matvec (state: 0 = not planned yet,
-// 1 = valid, -1 = shape not covered by the streaming kernel)
-struct skn_mv_plan {
-    int state;
-    int nch, wg, grid, threads;
-    size_t smem;
 };
 
 struct skn_tensor {
@@ -100,6 +110,9 @@ cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n
 cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int D, cudaStream_t st);
 size_t skn_argmax_scratch_bytes(int M);
 cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, void *scratch, cudaStream_t st);
+cudaError_t skn_launch_argmax_offer(const float *logits, const int32_t *ids, int B, int V_local, int rank, int world,
+                                    float *cand, cudaStream_t st);
+cudaError_t skn_launch_argmax_pick(const float *cand, int B, int world, int32_t *ids, cudaStream_t st);
 cudaError_t skn_launch_embed(const skn_tensor *emb, const int32_t *ids, int M, float *out, cudaStream_t st);
 
 // decoder-internal forms of the cache operations (skn_kv.cu): K/V rotated and written without

@@ -33,12 +33,18 @@ struct skn_llama {
     int32_t **len_ptrs;               // device array: the length vector of every layer's cache
     void *argmax_scratch;             // candidates and tickets of the two-level argmax
     int32_t host_len;                 // tokens cached so far (the same for every sequence)
+    // tensor parallelism: this rank's share of heads, FFN columns and vocabulary rows
+    skn_comm *comm;
+    int32_t world, rank, heads_l, kv_heads_l, ffn_l, vocab_l;
+    float *cand;                      // [world][max_batch][2] (value, global id) of the cross-rank argmax
 };
 
 // from skn_kv.cu
 extern "C" int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k, const float *v, int32_t T, int32_t host_len_upper);
 extern "C" int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q, int32_t n_q_heads, int32_t T, float scale,
                                        float *out, void *scratch);
+extern "C" int32_t skn_comm_info(const skn_comm *c, int32_t *rank, int32_t *world, int64_t *capacity_floats);
+extern "C" int32_t skn_allreduce_dev(skn_comm *c, const float *partial, const float *resid, float *out, int64_t n);
 extern "C" int32_t skn_kv_info(const skn_kvcache *kv, int32_t *, int32_t *, int32_t *, int32_t *, void **, void **,
                                void **len_dev, void **);
 
@@ -53,14 +59,32 @@ int32_t skn_llama_destroy(skn_llama *m);
 int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
                          int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
                          int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_llama **out) {
+    return skn_llama_create_tp(ctx, n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn_dim, vocab, rope_theta, rms_eps,
+                               max_batch, max_tokens, max_ctx, nullptr, out);
+}
+
+int32_t skn_llama_create_tp(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_t n_heads, int32_t n_kv_heads,
+                            int32_t head_dim, int32_t ffn_dim, int32_t vocab, float rope_theta, float rms_eps,
+                            int32_t max_batch, int32_t max_tokens, int32_t max_ctx, skn_comm *comm, skn_llama **out) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
     if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     *out = nullptr;
+    int32_t world = 1, rank = 0;
+    int64_t comm_cap = 0;
+    if (comm) {
+        if (skn_comm_info(comm, &rank, &world, &comm_cap)) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad exchange handle");
+        if (world == 1) comm = nullptr;
+    }
     if (n_layers < 1 || d_model < 4 || n_heads < 1 || n_kv_heads < 1 || ffn_dim < 1 || vocab < 1 || max_batch < 1 ||
         max_tokens < 1 || max_ctx < max_tokens)
         return skn_fail(ctx, SKN_ERR_ARG, "invalid model geometry");
     if (d_model % 4 || n_heads % n_kv_heads || (head_dim != 64 && head_dim != 128))
         return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
+    if (n_heads % world || n_kv_heads % world || ffn_dim % world || vocab % world)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "heads, FFN width and vocabulary must divide by the %d ranks", world);
+    if (comm && comm_cap < (int64_t)max_batch * max_tokens * d_model)
+        return skn_fail(ctx, SKN_ERR_SHAPE, "exchange capacity %lld below max_batch * max_tokens * d_model = %lld floats",
+                        (long long)comm_cap, (long long)max_batch * max_tokens * d_model);
     skn_llama *m = new (std::nothrow) skn_llama();
     if (!m) return skn_fail(ctx, SKN_ERR_OOM, "host allocation failed");
     m->magic = SKN_MAGIC_LLAMA;
@@ -68,6 +92,9 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     m->n_layers = n_layers; m->d_model = d_model; m->n_heads = n_heads; m->n_kv_heads = n_kv_heads;
     m->head_dim = head_dim; m->ffn_dim = ffn_dim; m->vocab = vocab; m->max_batch = max_batch; m->max_ctx = max_ctx;
     m->rope_theta = rope_theta; m->rms_eps = rms_eps;
+    m->comm = comm; m->world = world; m->rank = rank;
+    m->heads_l = n_heads / world; m->kv_heads_l = n_kv_heads / world; m->ffn_l = ffn_dim / world; m->vocab_l = vocab / world;
+    m->cand = nullptr;
     m->tok_embd = m->output = nullptr;
     m->out_norm = nullptr;
     m->max_rows = max_batch * max_tokens;
@@ -79,7 +106,7 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     m->layers.resize(n_layers);
     for (auto &l : m->layers) l = skn_llama_layer{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaError_t e = cudaSetDevice(ctx->device);
-    const size_t R = (size_t)m->max_rows, qd = (size_t)n_heads * head_dim, kd = (size_t)n_kv_heads * head_dim;
+    const size_t R = (size_t)m->max_rows, qd = (size_t)m->heads_l * head_dim, kd = (size_t)m->kv_heads_l * head_dim;
     if (e == cudaSuccess) e = dev_alloc(&m->x, R * d_model);
     if (e == cudaSuccess) e = dev_alloc(&m->h, R * d_model);
     if (e == cudaSuccess) e = dev_alloc(&m->q, R * qd);
@@ -88,12 +115,13 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
     if (e == cudaSuccess) e = dev_alloc(&m->att, R * qd);
     if (e == cudaSuccess) e = dev_alloc(&m->proj, R * d_model);
     if (e == cudaSuccess) e = dev_alloc(&m->last, (size_t)max_batch * d_model);
-    if (e == cudaSuccess) e = dev_alloc(&m->logits, (size_t)max_batch * vocab);
+    if (e == cudaSuccess) e = dev_alloc(&m->logits, (size_t)max_batch * m->vocab_l);
+    if (e == cudaSuccess) e = dev_alloc(&m->cand, ((size_t)world * max_batch * 2 + 3) / 4 * 4);
     if (e == cudaSuccess) e = dev_alloc(&m->out_norm, d_model);
     // gate / up outputs of the decode-size path (rows below the prefill threshold only)
     const size_t small_rows = R < 64 ? R : 64;
-    if (e == cudaSuccess) e = dev_alloc(&m->ffn_g, small_rows * ffn_dim);
-    if (e == cudaSuccess) e = dev_alloc(&m->ffn_u, small_rows * ffn_dim);
+    if (e == cudaSuccess) e = dev_alloc(&m->ffn_g, small_rows * m->ffn_l);
+    if (e == cudaSuccess) e = dev_alloc(&m->ffn_u, small_rows * m->ffn_l);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_in, sizeof(int32_t) * R);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->ids_out, sizeof(int32_t) * max_batch);
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->len_ptrs, sizeof(int32_t *) * n_layers);
@@ -105,7 +133,7 @@ int32_t skn_llama_create(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int32_
         e = dev_alloc(&m->layers[l].attn_norm, d_model);
         if (e == cudaSuccess) e = dev_alloc(&m->layers[l].ffn_norm, d_model);
         if (e != cudaSuccess) { rc = skn_check_cuda(ctx, e, "decoder norm gains"); break; }
-        rc = skn_kv_create(ctx, max_batch, n_kv_heads, head_dim, max_ctx, &m->layers[l].kv);
+        rc = skn_kv_create(ctx, max_batch, m->kv_heads_l, head_dim, max_ctx, &m->layers[l].kv);
     }
     if (rc == SKN_OK) {
         std::vector<int32_t *> lens(n_layers);
@@ -127,7 +155,7 @@ int32_t skn_llama_destroy(skn_llama *m) {
         cudaSetDevice(m->ctx->device);
         cudaStreamSynchronize(m->ctx->stream);
     }
-    float *bufs[] = {m->x, m->h, m->q, m->k, m->v, m->att, m->proj, m->last, m->logits, m->out_norm, m->ffn_g, m->ffn_u};
+    float *bufs[] = {m->x, m->h, m->q, m->k, m->v, m->att, m->proj, m->last, m->logits, m->out_norm, m->ffn_g, m->ffn_u, m->cand};
     for (float *b : bufs) if (b) cudaFree(b);
     if (m->ids_in) cudaFree(m->ids_in);
     if (m->ids_out) cudaFree(m->ids_out);
@@ -168,9 +196,9 @@ int32_t skn_llama_set_layer(skn_llama *m, int32_t layer, const skn_tensor *wq, c
     skn_ctx *ctx = m->ctx;
     if (layer < 0 || layer >= m->n_layers) return skn_fail(ctx, SKN_ERR_ARG, "layer index out of range");
     if (!attn_norm_host || !ffn_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
-    const int64_t d = m->d_model, qd = (int64_t)m->n_heads * m->head_dim, kd = (int64_t)m->n_kv_heads * m->head_dim;
+    const int64_t d = m->d_model, qd = (int64_t)m->heads_l * m->head_dim, kd = (int64_t)m->kv_heads_l * m->head_dim;
     if (!shape_is(wq, ctx, qd, d) || !shape_is(wk, ctx, kd, d) || !shape_is(wv, ctx, kd, d) || !shape_is(wo, ctx, d, qd) ||
-        !shape_is(w_gate, ctx, m->ffn_dim, d) || !shape_is(w_up, ctx, m->ffn_dim, d) || !shape_is(w_down, ctx, d, m->ffn_dim))
+        !shape_is(w_gate, ctx, m->ffn_l, d) || !shape_is(w_up, ctx, m->ffn_l, d) || !shape_is(w_down, ctx, d, m->ffn_l))
         return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     skn_llama_layer &l = m->layers[layer];
@@ -186,7 +214,7 @@ int32_t skn_llama_set_head(skn_llama *m, const skn_tensor *tok_embd, const float
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
     skn_ctx *ctx = m->ctx;
     if (!out_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
-    if (!shape_is(tok_embd, ctx, m->vocab, m->d_model) || !shape_is(output, ctx, m->vocab, m->d_model))
+    if (!shape_is(tok_embd, ctx, m->vocab, m->d_model) || !shape_is(output, ctx, m->vocab_l, m->d_model))
         return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     m->tok_embd = tok_embd;
@@ -220,7 +248,8 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         if (!l.wq) return skn_fail(ctx, SKN_ERR_ARG, "a layer has no weights");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaStream_t st = ctx->stream;
-    const int M = B * T, d = m->d_model, Hq = m->n_heads, Hkv = m->n_kv_heads, D = m->head_dim;
+    const int M = B * T, d = m->d_model, Hq = m->heads_l, Hkv = m->kv_heads_l, D = m->head_dim;
+    const bool tp = m->comm != nullptr;
     const float scale = 1.0f / sqrtf((float)D);
     const int32_t *ids = tokens_dev ? tokens_dev : m->ids_out;
     // below the prefill threshold every product is an fp32 streaming matvec per activation row
@@ -234,7 +263,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     } guard(ctx);
     SKN_CUDA(ctx, skn_launch_embed(m->tok_embd, ids, M, m->x, st));
     int32_t rc;
-    const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_dim;
+    const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_l;
     // fused form of one matvec launch; `fell_back` reports a shape the streaming kernel does not
     // cover.  Folding the norm / SwiGLU into the preparation of x saves a launch per layer but
     // adds a few microseconds to every row's launch: it pays for one or two rows, beyond that
@@ -276,9 +305,13 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         if ((rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
         if ((rc = skn_attn_causal_pending(l.kv, m->q, Hq, T, scale, m->att))) return rc;
         if (small) {
-            // ... output projection with the residual added in its epilogue (x += att . Wo^T) ...
-            for (int r = 0; r < M; ++r)
-                SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wo, m->att + r * qd, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+            // ... output projection with the residual added in its epilogue (x += att . Wo^T); with
+            // K-sharded weights the partial products meet in the exchange, which adds the residual ...
+            for (int r = 0; r < M; ++r) {
+                float *xr = m->x + (int64_t)r * d;
+                SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wo, m->att + r * qd, 1, tp ? nullptr : xr, tp ? m->proj + (int64_t)r * d : xr, st));
+            }
+            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
             // ... gate and up with the second RMSNorm folded in (one launch) ...
             float *gbuf = m->ffn_g, *ubuf = m->ffn_u;
             bool fb = false;
@@ -300,21 +333,26 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
             fb = false;
             for (int r = 0; r < M && !fb; ++r) {
                 const skn_tensor *ws[1] = {l.wd};
-                float *ys[1] = {m->x + (int64_t)r * d};
-                const float *adds[1] = {m->x + (int64_t)r * d};
+                float *ys[1] = {tp ? m->proj + (int64_t)r * d : m->x + (int64_t)r * d};
+                const float *adds[1] = {tp ? nullptr : m->x + (int64_t)r * d};
                 SKN_CUDA(ctx, fused(1, ws, gbuf + r * F, ys, adds, nullptr, ubuf + r * F, fb));
             }
             if (fb) {
                 SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
-                for (int r = 0; r < M; ++r)
-                    SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, m->x + (int64_t)r * d, m->x + (int64_t)r * d, st));
+                for (int r = 0; r < M; ++r) {
+                    float *xr = m->x + (int64_t)r * d;
+                    SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, tp ? nullptr : xr, tp ? m->proj + (int64_t)r * d : xr, st));
+                }
             }
+            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
         } else {
             if ((rc = skn_matmul_dev(ctx, l.wo, m->att, M, qd, nullptr, m->proj))) return rc;
-            SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+            if (tp) { if ((rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc; }
+            else SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
             SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
             if ((rc = skn_ffn_swiglu_dev(ctx, l.wg, l.wu, l.wd, m->h, M, m->proj))) return rc;
-            SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
+            if (tp) { if ((rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc; }
+            else SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
         }
     }
     SKN_CUDA(ctx, skn_kv_advance_all(m->len_ptrs, m->n_layers, B, T, m->max_ctx, st));
@@ -323,7 +361,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     bool fb = !(B <= 64 && !(ctx->prefill_min_m > 0 && B >= ctx->prefill_min_m));
     for (int b = 0; b < B && !fb; ++b) {
         const skn_tensor *ws[1] = {m->output};
-        float *ys[1] = {m->logits + (int64_t)b * m->vocab};
+        float *ys[1] = {m->logits + (int64_t)b * m->vocab_l};
         SKN_CUDA(ctx, fused(1, ws, m->x + ((int64_t)b * T + (T - 1)) * d, ys, nullptr, m->out_norm, nullptr, fb));
     }
     if (fb) {
@@ -331,7 +369,15 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         SKN_CUDA(ctx, skn_launch_rmsnorm(m->last, m->out_norm, m->h, B, d, m->rms_eps, st));
         if ((rc = skn_matmul_dev(ctx, m->output, m->h, B, d, nullptr, m->logits))) return rc;
     }
-    SKN_CUDA(ctx, skn_launch_argmax(m->logits, B, m->vocab, m->ids_out, m->argmax_scratch, st));
+    SKN_CUDA(ctx, skn_launch_argmax(m->logits, B, m->vocab_l, m->ids_out, m->argmax_scratch, st));
+    if (tp) {
+        // every rank offers the best token of its vocabulary slice; zero-filled slots make the
+        // exchange's sum a concatenation, and every rank then picks the same winner
+        const int64_t nc = ((int64_t)m->world * B * 2 + 3) / 4 * 4;
+        SKN_CUDA(ctx, skn_launch_argmax_offer(m->logits, m->ids_out, B, m->vocab_l, m->rank, m->world, m->cand, st));
+        if ((rc = skn_allreduce_dev(m->comm, m->cand, nullptr, m->cand, nc))) return rc;
+        SKN_CUDA(ctx, skn_launch_argmax_pick(m->cand, B, m->world, m->ids_out, st));
+    }
     return SKN_OK;
 }
 
@@ -351,7 +397,7 @@ int32_t skn_llama_forward(skn_llama *m, const int32_t *tokens_host, int32_t T, i
     if (next_host)
         SKN_CUDA(ctx, cudaMemcpyAsync(next_host, m->ids_out, sizeof(int32_t) * B, cudaMemcpyDeviceToHost, ctx->stream));
     if (logits_host)
-        SKN_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * B * m->vocab, cudaMemcpyDeviceToHost, ctx->stream));
+        SKN_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * B * m->vocab_l, cudaMemcpyDeviceToHost, ctx->stream));
     return skn_sync(ctx);
 }
 

@@ -984,19 +984,18 @@ static bool try_stream_group(skn_ctx *ctx, int n, const skn_tensor *const *w, co
     }
     for (int t = n; t < 3; ++t) grp.n_end[t] = tot;
     grp.count = n;
-    // plans of grouped launches are cached by (rows, columns, order, device)
-    struct Cached { int64_t rows, cols; int relaxed, device; skn_mv_plan pl; };
-    static Cached cache[32];
-    static int n_cached = 0;
+    // plans of grouped launches live in the context (one host thread drives a context at a time)
     skn_mv_plan pl;
     pl.state = 0;
-    for (int i = 0; i < n_cached; ++i)
-        if (cache[i].rows == tot && cache[i].cols == w[0]->n_cols && cache[i].relaxed == ctx->relaxed_order &&
-            cache[i].device == ctx->device) { pl = cache[i].pl; break; }
+    for (int i = 0; i < ctx->n_group_plans; ++i) {
+        const skn_group_plan &c = ctx->group_plans[i];
+        if (c.type == w[0]->type && c.rows == tot && c.cols == w[0]->n_cols && c.relaxed == ctx->relaxed_order) { pl = c.pl; break; }
+    }
     if (pl.state == 0) {
         err = plan_stream<S>(ctx, tot, w[0]->n_cols, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) return true;
-        if (n_cached < 32) cache[n_cached++] = Cached{tot, w[0]->n_cols, ctx->relaxed_order, ctx->device, pl};
+        if (ctx->n_group_plans < 32)
+            ctx->group_plans[ctx->n_group_plans++] = skn_group_plan{w[0]->type, ctx->relaxed_order, tot, w[0]->n_cols, pl};
     }
     if (pl.state != 1) return false;
     err = launch_stream<S>(ctx, grp, w[0]->pitch, (int)w[0]->n_cols, x, pl, stream);

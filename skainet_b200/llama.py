@@ -32,13 +32,20 @@ class LlamaConfig:
 class LlamaDecoder:
     """Owns the quantized weights (uploaded from raw blocks) and the native decoder."""
 
-    def __init__(self, ctx: Context, cfg: LlamaConfig, batch: int, max_tokens: int, max_ctx: int):
+    def __init__(self, ctx: Context, cfg: LlamaConfig, batch: int, max_tokens: int, max_ctx: int, exchange=None):
+        """exchange (parallel.Exchange): tensor-parallel decoder; this rank then keeps only its
+        share of every weight (set_layer / set_head still take the WHOLE tensors' raw blocks and
+        upload the rank's shard)."""
         self.ctx, self.cfg, self.batch = ctx, cfg, batch
         self._h = ctypes.c_void_p()
         self._tensors = []
-        rc = _ffi.lib().skn_llama_create(ctx.handle, cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads,
-                                         cfg.head_dim, cfg.ffn_dim, cfg.vocab, cfg.rope_theta, cfg.rms_eps, batch,
-                                         max_tokens, max_ctx, ctypes.byref(self._h))
+        self.exchange = exchange
+        self.world = exchange.world if exchange is not None else 1
+        self.rank = exchange.rank if exchange is not None else 0
+        rc = _ffi.lib().skn_llama_create_tp(ctx.handle, cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads,
+                                            cfg.head_dim, cfg.ffn_dim, cfg.vocab, cfg.rope_theta, cfg.rms_eps, batch,
+                                            max_tokens, max_ctx, None if exchange is None else exchange.handle,
+                                            ctypes.byref(self._h))
         if rc != SKN_OK:
             self._h = ctypes.c_void_p()
             _raise(ctx.handle, rc)
@@ -47,8 +54,15 @@ class LlamaDecoder:
     def handle(self):
         return self._h
 
-    def _up(self, qtype, shape, blocks) -> QuantTensor:
-        t = QuantTensor(self.ctx, shape, qtype, blocks)
+    def _up(self, qtype, shape, blocks, split=None) -> QuantTensor:
+        """split: None (whole tensor), "rows" (this rank's contiguous range of output rows) or
+        "cols" (its range of input columns, in whole blocks)."""
+        shard = None
+        if self.world > 1 and split == "rows":
+            shard = (self.rank * (shape[0] // self.world), shape[0] // self.world, 0, shape[1])
+        elif self.world > 1 and split == "cols":
+            shard = (0, shape[0], self.rank * (shape[1] // self.world), shape[1] // self.world)
+        t = QuantTensor(self.ctx, shape, qtype, blocks, shard=shard)
         self._tensors.append(t)
         return t
 
@@ -58,7 +72,8 @@ class LlamaDecoder:
         qd, kd = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         shapes = {"wq": (qd, c.d_model), "wk": (kd, c.d_model), "wv": (kd, c.d_model), "wo": (c.d_model, qd),
                   "w_gate": (c.ffn_dim, c.d_model), "w_up": (c.ffn_dim, c.d_model), "w_down": (c.d_model, c.ffn_dim)}
-        ts = {k: self._up(c.proj_type, shapes[k], w[k]) for k in shapes}
+        split = {"wq": "rows", "wk": "rows", "wv": "rows", "wo": "cols", "w_gate": "rows", "w_up": "rows", "w_down": "cols"}
+        ts = {k: self._up(c.proj_type, shapes[k], w[k], split[k]) for k in shapes}
         an = np.ascontiguousarray(attn_norm, dtype=np.float32)
         fn = np.ascontiguousarray(ffn_norm, dtype=np.float32)
         _check(self.ctx.handle, _ffi.lib().skn_llama_set_layer(
@@ -68,7 +83,7 @@ class LlamaDecoder:
     def set_head(self, tok_embd: np.ndarray, out_norm: np.ndarray, output: np.ndarray):
         c = self.cfg
         te = self._up(c.head_type, (c.vocab, c.d_model), tok_embd)
-        ot = self._up(c.head_type, (c.vocab, c.d_model), output)
+        ot = self._up(c.head_type, (c.vocab, c.d_model), output, "rows")
         on = np.ascontiguousarray(out_norm, dtype=np.float32)
         _check(self.ctx.handle, _ffi.lib().skn_llama_set_head(self._h, te.handle, on.ctypes.data, ot.handle))
 
@@ -81,7 +96,8 @@ class LlamaDecoder:
 
     def forward(self, tokens: Optional[np.ndarray], want_logits: bool = False):
         """tokens [batch, T] int32 (None: feed back the previous greedy ids, T = 1).
-        Returns next ids [batch] (and the last-position logits [batch, vocab])."""
+        Returns next ids [batch] (and the last-position logits [batch, vocab]; under tensor
+        parallelism this rank's vocabulary slice [batch, vocab / world])."""
         if tokens is None:
             tp, T = None, 1
         else:
@@ -90,7 +106,7 @@ class LlamaDecoder:
                 raise ValueError("Shapes do not align.")
             tp, T = tokens.ctypes.data, tokens.shape[1]
         nxt = np.empty(self.batch, dtype=np.int32)
-        logits = np.empty((self.batch, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        logits = np.empty((self.batch, self.cfg.vocab // self.world), dtype=np.float32) if want_logits else None
         _check(self.ctx.handle, _ffi.lib().skn_llama_forward(self._h, tp, T, nxt.ctypes.data,
                                                             None if logits is None else logits.ctypes.data))
         return (nxt, logits) if want_logits else nxt
