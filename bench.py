@@ -324,7 +324,8 @@ def run_ours(args):
                        "launch_order": ("relaxed: the layers of a step are independent and declared so "
                                         "(SKN_OPT_RELAXED_ORDER)") if args.order == "relaxed" else
                        "stream order: every launch waits for the previous one",
-                       "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
+                       "parallelism": f"tp{world}" if world > 1 else "none",
+                   "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                        "l2_policy": f"inputs larger than L2: {layers} distinct weights = "
                                     f"{layers * W_BYTES / 1e6:.0f} MB streamed per step",
                        "sharding": "none" if world == 1 else
@@ -524,15 +525,29 @@ def run_decode(args):
     head_dim 128, vocab 32000, Q4_K projections, Q6_K embedding / LM head.  512-token prefill of
     uniform-random ids, then 128 greedy decode steps (ids fed back on the device, one CUDA graph
     replay per step).  One layer's random blocks are uploaded 32 times (distinct device buffers).
-    4 GB of weights per step far exceed L2."""
+    4 GB of weights per step far exceed L2.
+
+    Under torchrun (WORLD_SIZE > 1) the decoder is tensor-parallel: every rank keeps its share of
+    the heads, FFN columns and vocabulary and the partial products meet in the library's own
+    exchange (two per layer); the step time is the maximum over the ranks ("strong" scaling:
+    the model and batch are fixed)."""
     import torch
+    import torch.distributed as dist
     import skainet_b200 as skn
     from skainet_b200 import synth
     from skainet_b200.llama import LlamaConfig, LlamaDecoder
+    from skainet_b200.parallel import Exchange
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     B, T, steps = args.batch, 512, min(args.steps, 128)
     cfg = LlamaConfig(n_layers=args.layers if args.layers != 128 else 32)
-    dev = torch.device("cuda", 0)
-    ctx = skn.Context(0)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = skn.Context(local)
+    exchange = Exchange.connect_processes(ctx, B * T * cfg.d_model) if world > 1 else None
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
@@ -542,7 +557,7 @@ def run_decode(args):
               "w_gate": (cfg.ffn_dim, cfg.d_model), "w_up": (cfg.ffn_dim, cfg.d_model), "w_down": (cfg.d_model, cfg.ffn_dim)}
     layer = {k: synth.make_weight(g, cfg.proj_type, *shp) for k, shp in shapes.items()}
     emb = synth.make_weight(g, cfg.head_type, cfg.vocab, cfg.d_model)
-    dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=T + 136)
+    dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=T + 136, exchange=exchange)
     ones = np.ones(cfg.d_model, dtype=np.float32)
     for i in range(cfg.n_layers):
         dec.set_layer(i, layer, ones, ones)
@@ -553,15 +568,27 @@ def run_decode(args):
         dec.reset()
         dec.forward_dev(prompt, T)
 
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     prefill()
     dec.forward_dev(None, 1)          # sizes every scratch buffer of the decode path
-    torch.cuda.synchronize()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     prefill()
     e1.record(stream)
-    torch.cuda.synchronize()
-    prefill_ms = e0.elapsed_time(e1)
+    barrier()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
     graph = None
     if not args.no_graph:
         try:
@@ -580,33 +607,43 @@ def run_decode(args):
         torch.cuda.synchronize()
     # the capture itself advanced the host-side position by one: start over
     prefill()
-    torch.cuda.synchronize()
     step = graph.replay if graph is not None else (lambda: dec.forward_dev(None, 1))
-    sampler = ClockSampler(0)
+    for _ in range(3):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
     sampler.start()
     e0.record(stream)
     for _ in range(steps):
         step()
     e1.record(stream)
-    torch.cuda.synchronize()
+    barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / steps
+    ms = max_over_ranks(e0.elapsed_time(e1) / steps)
     ctx.sync()
+    if rank != 0:
+        dec.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     wbytes = cfg.n_layers * sum(n * (k // 256) * 144 for n, k in shapes.values()) + cfg.vocab * (cfg.d_model // 256) * 210
     peak, kind = measured_peak()
     gbs = wbytes / (ms * 1e-3) / 1e9
     print(json.dumps({
-        "metric": "decode_tok_s", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 1,
-        "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "metric": "decode_tok_s", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": 3,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg5: Llama-style decoder, {cfg.n_layers} layers, Q4_K / Q6_K, batch {B}, "
                                f"{T}-token prefill then greedy decode",
+                   "parallelism": f"tp{world}" if world > 1 else "none",
                    "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                    "prefill_ms": prefill_ms, "prefill_tok_s": B * T * 1e3 / prefill_ms,
                    "weight_bytes_per_step": wbytes},
-        "roofline": {"bound": "hbm", "kernel": "decode step (weight stream)", "achieved": gbs, "peak": peak,
-                     "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "traffic": None},
+        "roofline": {"bound": "hbm", "kernel": "decode step (weight stream, all GPUs)", "achieved": gbs, "peak": peak * world,
+                     "peak_kind": kind, "unit": "GB/s", "frac": gbs / (peak * world), "traffic": None},
         "clocks": clocks}), flush=True)
     dec.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():

@@ -91,6 +91,10 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
 cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                                     const float *const *add, const float *norm_gain, float norm_eps,
                                     const float *silu_u, cudaStream_t stream);
+// integer tensor-core matvec (skn_matvec_mma.cu); false = shapes or type not covered
+bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
+                       const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
+                       cudaStream_t stream, cudaError_t &err);
 cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                                     const float *const *add, cudaStream_t stream);
 

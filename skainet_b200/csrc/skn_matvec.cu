@@ -19,24 +19,7 @@
 //    per output row, byte-granular decode, MT activation rows per pass.
 #include "skn_blocks.cuh"
 #include "skn_ptx.cuh"
-
-#include <stdlib.h>
-
-// SKN_MV_TRACE builds record per-CTA phase timestamps (SM clock and global timer) after the
-// status word; used only for profiling experiments, never in the shipped library.
-#ifdef SKN_MV_TRACE
-#define MV_STAMP(k)                                                                        \
-    do {                                                                                   \
-        if (threadIdx.x == 0) {                                                            \
-            long long *tr = reinterpret_cast<long long *>(status) + 16 + blockIdx.x * 16;  \
-            tr[2 * (k)] = clock64();                                                       \
-            tr[2 * (k) + 1] = (long long)skn_globaltimer_ns();                             \
-        }                                                                                  \
-    } while (0)
-#else
-#define MV_STAMP(k) do {} while (0)
-#endif
-
+#include "skn_mv_common.cuh"
 
 // ----------------------------------------------------------------------------------------
 // generic kernel
@@ -111,8 +94,6 @@ static cudaError_t launch_generic(const skn_tensor *w, const float *x, int M, co
 // ----------------------------------------------------------------------------------------
 constexpr int MV_NST = 8;          // ring stages per warp == rows per reduction group
 
-__device__ __forceinline__ float skn_pow2f(int e) { return __int_as_float((e + 127) << 23); }
-
 // Sum 8 per-lane values across the warp in 9 shuffles.  On return the lanes whose
 // (lane >> 2) == r hold the total of v[r].
 __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane) {
@@ -135,36 +116,6 @@ __device__ __forceinline__ float skn_warp_reduce8(const float (&v)[8], int lane)
     c += __shfl_xor_sync(0xffffffffu, c, 2);
     c += __shfl_xor_sync(0xffffffffu, c, 1);
     return c;
-}
-
-// Optional transforms applied to x while it is prepared, so that the element-wise ops that
-// precede a projection in a decoder need no launch of their own:
-//   silu_u != NULL : x <- silu(x) * silu_u      (SwiGLU product feeding the down projection)
-//   gain   != NULL : x <- x * scale * gain      (RMSNorm; scale = rsqrt(mean(x^2) + eps) is
-//                                                computed by the CTA before the preparation)
-struct skn_xform {
-    const float *gain;
-    const float *silu_u;
-    float scale;
-};
-
-__device__ __forceinline__ float4 skn_load_x4(const float *__restrict__ x, int f, const skn_xform &xf) {
-    float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
-    if (xf.silu_u) {
-        const float4 u = __ldg(reinterpret_cast<const float4 *>(xf.silu_u) + f);
-        v.x = v.x / (1.f + expf(-v.x)) * u.x;
-        v.y = v.y / (1.f + expf(-v.y)) * u.y;
-        v.z = v.z / (1.f + expf(-v.z)) * u.z;
-        v.w = v.w / (1.f + expf(-v.w)) * u.w;
-    }
-    if (xf.gain) {
-        const float4 g = __ldg(reinterpret_cast<const float4 *>(xf.gain) + f);
-        v.x = v.x * xf.scale * g.x;
-        v.y = v.y * xf.scale * g.y;
-        v.z = v.z * xf.scale * g.z;
-        v.w = v.w * xf.scale * g.w;
-    }
-    return v;
 }
 
 // CTA-cooperative preparation of x for the 4-bit decoders: K activations from global memory ->
@@ -715,27 +666,6 @@ struct Q6KStream {
 //   smem  : [warps][MV_NST][CHUNK_BYTES] ring | prepared x | [warps][MV_NST] mbarriers | [rows][nch] partials
 // Each warp walks its rows two at a time; stage s of its ring holds row i with i % MV_NST == s.
 //
-// A launch may cover up to three weight tensors of the same type, K and pitch that multiply the
-// same x (Q/K/V, gate/up): their rows are concatenated, row r of the concatenation belongs to
-// the first tensor whose cumulative end exceeds r.  `add[t]` (may be NULL) is added to tensor
-// t's outputs: a bias, or the residual stream when y aliases it.
-struct skn_mv_group {
-    const uint8_t *W[3];
-    float *y[3];
-    const float *add[3];
-    int64_t n_end[3];       // cumulative row counts
-    int count;
-    const float *norm_gain; // RMSNorm of x fused into its preparation (NULL: none)
-    float norm_eps;
-    const float *silu_u;    // x <- silu(x) * silu_u fused into its preparation (NULL: none)
-};
-
-__device__ __forceinline__ int skn_group_find(const skn_mv_group &grp, int64_t r, int64_t &local) {
-    const int t = (r >= grp.n_end[0] ? 1 : 0) + ((grp.count > 2 && r >= grp.n_end[1]) ? 1 : 0);
-    local = r - (t ? grp.n_end[t - 1] : 0);
-    return t;
-}
-
 template <class S>
 __global__ void __launch_bounds__(512, 1)
 skn_matvec_stream(const skn_mv_group grp, int64_t pitch, int K, int nch, int wg, const float *__restrict__ x,
@@ -879,11 +809,6 @@ skn_matvec_stream(const skn_mv_group grp, int64_t pitch, int K, int nch, int wg,
     MV_STAMP(7);
 }
 
-static int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
-}
-
 // Launch geometry of the streaming kernel for one weight tensor; computed on first use and
 // cached in the tensor (it depends only on the tensor's shape and the device).
 //   - one CTA per SM (a second CTA slot is left free so that, under programmatic dependent
@@ -1013,6 +938,7 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
         same = w[t]->type == w[0]->type && w[t]->n_cols == w[0]->n_cols && w[t]->pitch == w[0]->pitch;
     if (!same || (w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
     cudaError_t err = cudaSuccess;
+    if (skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
     bool took = false;
     switch (w[0]->type) {
     case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
@@ -1051,7 +977,11 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
             const float *xm = x + (int64_t)m * w->n_cols;
             float *ym = y + (int64_t)m * w->n_rows;
             bool took = false;
-            if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
+            const skn_tensor *w1[1] = {w};
+            float *y1[1] = {ym};
+            const float *b1[1] = {bias};
+            if (skn_mma_try_group(ctx, 1, w1, xm, y1, b1, nullptr, 0.f, nullptr, stream, err)) took = true;
+            else if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q4_0) took = try_stream<Q40Stream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q8_0) took = try_stream<Q80Stream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q6_K) took = try_stream<Q6KStream>(ctx, w, xm, bias, ym, stream, err);
