@@ -3,38 +3,40 @@
 // The CUDA-core kernels of skn_matvec.cu spend one logic operation and half a packed FMA per
 // weight and end up bound by instruction issue at about half of the HBM rate.  Here the dot
 // product of a 32-weight sub-block with its 32 activations is an EXACT integer dot product
-// on the tensor cores (mma.sync m16n8k32, u8 x s8 -> s32), so the per-weight work shrinks to
-// a fraction of an instruction and the kernel waits for HBM instead:
+// on the tensor cores (mma.sync m16n8k32, u8 x s8 -> s32), and the 6-bit sub-block scales are
+// applied in integers as well, so the per-weight work shrinks to a fraction of an instruction:
 //
-//   * x, per group of 32 activations, becomes a 23-bit fixed-point number with a power-of-two
-//     group scale: X = rint(x * 2^(21-e)), e = exponent of the group's largest |x|, split into
-//     three balanced signed byte digits X = d0 + 256 d1 + 65536 d2.  The digit planes are the
-//     columns 0..2 of the B operand (columns 3..7 are zero), in shared memory, prepared once per
-//     CTA.  The rounding error per activation is at most 2^-23 of the group's largest one.
-//   * the A operand is the quant bytes as they lie in the block: `word & 0x0F0F0F0F` are four
-//     low-nibble weights (sub-block 2p), `word & 0xF0F0F0F0` four high-nibble weights times 16
-//     (sub-block 2p+1; the 1/16 goes into the scale).  One MMA = 16 rows x one sub-block.
-//   * per (row, sub-block) the s32 results of the three digit columns are recombined
-//     (c0 + 256 c1 in integers, the third digit through a factor 65536 applied once per tile)
-//     and scaled by d * sc * 2^(e-21); the -dmin * m * sum(x) term is added per row and
-//     super-block by the lane that decodes that block's header.
+//   * x, per super-block of 256 activations, becomes a 23-bit fixed-point number with a
+//     power-of-two scale: X = rint(x * 2^(21-e)), e = exponent of the super-block's largest |x|,
+//     split into three balanced signed byte digits X = d0 + 256 d1 + 65536 d2 (the bytes of
+//     (X + 0x808080) ^ 0x808080).  The digit planes are columns 0..2 of the B operand (columns
+//     3..7 are zero), prepared once per CTA in shared memory.  The rounding error per
+//     activation is at most 2^-23 of the super-block's largest one.
+//   * the A operand is the quant bytes as they lie in the block.  For the byte pair p of a
+//     super-block (sub-block 2p in the low nibbles, 2p+1 in the high ones) two MMAs run: one on
+//     `word & 0x0F0F0F0F` (L = the low-nibble dot) and one on the raw bytes (L + 16 H).  With
+//     the integer scales s0, s1 of the two sub-blocks, 16 (s0 L + s1 H) = (16 s0 - s1) L +
+//     s1 (L + 16 H): two integer multiply-adds per result, accumulated over the super-block in
+//     s32 (at most 2^29 in magnitude).
+//   * once per (row, super-block) the digit columns are recombined in fp32 and scaled by
+//     d * 2^(e-21) / 16; the -dmin * m * sum(x) term is added per row and super-block.
 //
 // Work split: CTA b owns rows [b*N/grid, (b+1)*N/grid).  A tile is 16 rows x one K super-chunk
 // (up to 16 super-blocks, i.e. one bulk async copy of at most 2304 bytes per row: few, large
-// copies).  The CTA walks its tiles through a ring of `nst` stages; the sixteen row copies of a
-// tile are issued by sixteen lanes of warp 0 and signal the stage's "full" mbarrier, every warp
-// takes the super-blocks warp, warp + W, ... of the tile and arrives on the stage's "empty"
-// mbarrier when it has read its share.  Rows are padded by 32 bytes in shared memory, which
-// makes the 64-bit fragment loads of the eight row groups conflict-free.  Weights are
-// prefetched before the programmatic dependent-launch wait, x is read after it.  Partial sums
-// per (row, super-chunk, warp) meet in shared memory and are added in a fixed order.
+// copies).  The CTA walks its tiles through a ring of `nst` stages.  A producer warp issues the
+// sixteen row copies of a tile (they signal the stage's "full" mbarrier) and refills a stage
+// when the W compute warps have arrived on its "empty" mbarrier; issuing blocks while the copy
+// queue is full, i.e. at the speed of HBM, which is why it has a warp of its own.  Compute warp
+// w takes the super-blocks w, w + W, ... of every tile.  Rows are padded by 32 bytes in shared
+// memory, which makes the 64-bit fragment loads of the eight row groups conflict-free.  Weights
+// are prefetched before the programmatic dependent-launch wait, x is read after it.  Partial
+// sums per (row, super-chunk, warp) meet in shared memory and are added in a fixed order.
 #include "skn_mv_common.cuh"
 
 constexpr int MM_KS = 16;                       // super-blocks per K super-chunk (one row copy)
 constexpr int MM_BLOCK_BYTES = 144;
 constexpr int MM_ROW_STRIDE = MM_KS * MM_BLOCK_BYTES + 32;   // 2336 B = 584 words = 8 mod 32
 constexpr int MM_STAGE = 16 * MM_ROW_STRIDE;
-constexpr int MM_FROW = 12;                     // floats per row of the scale scratch (8 used): 48 B stride, no bank conflicts
 
 __device__ __forceinline__ void skn_mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
@@ -43,98 +45,84 @@ __device__ __forceinline__ void skn_mma_u8s8(int (&c)[4], uint32_t a0, uint32_t 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// |v| < 2^22 as a float without the conversion pipe: (1.5 * 2^23 + v) - 1.5 * 2^23
-__device__ __forceinline__ float mm_int_f(int v) { return __int_as_float(0x4B400000 + v) - 12582912.f; }
 
 // byte i (0..3) of w as a float without the conversion pipe: (2^23 + b) - 2^23
-__device__ __forceinline__ float mm_byte_f(uint32_t w, int i) {
+__device__ __forceinline__ float mm_byte_f(uint32_t w, uint32_t i) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u + i)) - 8388608.f;
 }
+__device__ __forceinline__ int mm_byte_i(uint32_t w, uint32_t i) { return (int)__byte_perm(w, 0u, 0x4440u + i); }
 
-// CTA-cooperative preparation of x: digit planes, group scales and group sums.
-//   dig  : 3 planes of PL bytes, byte k of a plane = that digit of activation k (the MMA's k index
-//          is mapped so that thread-in-group t owns activations 8t..8t+7 of a group: one 64-bit load)
-//   sgrp : 2^(e-21) per group (NaN when the group holds a NaN or an infinity)
-//   xsum : plain fp32 sum of the group
-// Columns >= K are zero.
-template <int B>                                // float4 loads in flight per thread
-static __device__ __forceinline__ void mm_prep_x(const float *__restrict__ x, int K, int kpad, uint8_t *dig, int PL,
-                                                 float *sgrp, float *xsum, const skn_xform &xf) {
-    const int nf = kpad / 4;
-    for (int f0 = 0; f0 < nf; f0 += B * blockDim.x) {
-        float4 v[B];
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-            const int f = f0 + b * blockDim.x + threadIdx.x;
-            v[b] = (f < nf && 4 * f < K) ? skn_load_x4(x, f, xf) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-            const int f = f0 + b * blockDim.x + threadIdx.x;      // 8 consecutive f = one group
-            float mx = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
-            float sm = (v[b].x + v[b].y) + (v[b].z + v[b].w);
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                sm += __shfl_xor_sync(0xffffffffu, sm, o);
-            }
-            int E = (int)(__float_as_uint(mx) >> 23);
-            E = E < 22 ? 22 : (E > 254 ? 254 : E);
-            const float mul = __int_as_float((275 - E) << 23);          // 2^(21-e)
-            const int X[4] = {__float2int_rn(v[b].x * mul), __float2int_rn(v[b].y * mul), __float2int_rn(v[b].z * mul),
-                              __float2int_rn(v[b].w * mul)};
-            uint32_t p0 = 0, p1 = 0, p2 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int d0 = (int)(int8_t)(X[i] & 0xFF);
-                const int X1 = (X[i] - d0) >> 8;
-                const int d1 = (int)(int8_t)(X1 & 0xFF);
-                const int d2 = (X1 - d1) >> 8;
-                p0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
-                p1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
-                p2 |= (uint32_t)(d2 & 0xFF) << (8 * i);
-            }
-            if (f < nf) {
-                const int G = f >> 3, q = f & 7;
-                const int off = 4 * f;
-                *reinterpret_cast<uint32_t *>(dig + off) = p0;
-                *reinterpret_cast<uint32_t *>(dig + PL + off) = p1;
-                *reinterpret_cast<uint32_t *>(dig + 2 * PL + off) = p2;
-                if (q == 0) {
-                    const bool finite = fabsf(sm) <= 3.4028234e38f;       // false for NaN and infinities
-                    sgrp[G] = finite ? __int_as_float((E - 21) << 23) : __int_as_float(0x7FC00000);
-                    xsum[G] = sm;
-                }
-            }
-        }
-    }
+__device__ __forceinline__ void mm_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// One super-block (256 activations, two float4 per lane: elements 4*lane.. and 128 + 4*lane..)
+// -> three digit planes (byte k of a plane = that digit of activation k), the scale 2^(e-21)
+// (NaN when the block holds a NaN or an infinity) and the eight 32-element sums.
+static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4 v1, int sbi, int lane, uint8_t *dig, int PL,
+                                                   float *sgrp, float *xsum) {
+    float mx = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                     fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    float s0 = (v0.x + v0.y) + (v0.z + v0.w), s1 = (v1.x + v1.y) + (v1.z + v1.w);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float tot = s0 + s1;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 8);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 16);
+    int E = (int)(__float_as_uint(mx) >> 23);
+    E = E < 22 ? 22 : (E > 254 ? 254 : E);
+    const float mul = __int_as_float((275 - E) << 23);          // 2^(21-e)
+    // rint(v * mul) sits in the mantissa of v * mul + 1.5 * 2^23; adding 0x808080 and flipping
+    // the three sign bits leaves the three balanced digits in bytes 0..2
+    constexpr int C = 0x808080 - 0x4B400000;
+    const float in[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t D[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) D[i] = (uint32_t)(__float_as_int(fmaf(in[i], mul, 12582912.f)) + C) ^ 0x808080u;
+    const int f = sbi * 64 + lane;
+#pragma unroll
+    for (int n = 0; n < 3; ++n) {
+        const uint32_t sel = 0x0040u + 0x11u * n;               // byte n of both operands
+        const uint32_t a = __byte_perm(__byte_perm(D[0], D[1], sel), __byte_perm(D[2], D[3], sel), 0x5410u);
+        const uint32_t b = __byte_perm(__byte_perm(D[4], D[5], sel), __byte_perm(D[6], D[7], sel), 0x5410u);
+        *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * f) = a;
+        *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * (f + 32)) = b;
+    }
+    if ((lane & 7) == 0) {
+        xsum[sbi * 8 + (lane >> 3)] = s0;
+        xsum[sbi * 8 + 4 + (lane >> 3)] = s1;
+    }
+    if (lane == 0) sgrp[sbi] = (fabsf(tot) <= 3.4028234e38f) ? __int_as_float((E - 21) << 23) : __int_as_float(0x7FC00000);
+}
 
-template <int SPW>                              // super-blocks of a tile per warp: blockDim = 32 * ceil(16 / SPW)
-__global__ void __launch_bounds__(512 / SPW, 1)
+// Register caps: the register file is split over the SM's four schedulers (16K registers each), so
+// two resident CTAs of 9 warps need five warps per scheduler, i.e. at most 102 registers per
+// thread; three CTAs of 5 warps need four per scheduler (at most 128).
+template <int SPW>                              // super-blocks of a tile per compute warp: W = 16 / SPW compute warps
+__global__ void __launch_bounds__(SPW == 1 ? 544 : (SPW == 2 ? 320 : 256), SPW == 1 ? 1 : 2)
 skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
                    int32_t *__restrict__ status, int relaxed) {
+    constexpr int W = 16 / SPW;
     const int64_t N = grp.n_end[grp.count - 1];
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int W = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5;          // 0..W-1 compute, W = producer
     const int g = lane >> 2, t = lane & 3;
     const int nb = K / 256;
     const int nks = (nb + MM_KS - 1) / MM_KS;   // K super-chunks
-    constexpr int spw = SPW;
-    const int kpad = nb * 256;
-    const int PL = kpad + 32;                   // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
+    const int PL = nb * 256 + 32;               // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
 
-    // shared memory: ring | digit planes | group scales | group sums | F scratch | barriers | partials
+    // shared memory: ring | digit planes | block scales | group sums | barriers | partials
     uint8_t *ring = smem;
     uint8_t *dig = smem + (size_t)nst * MM_STAGE;
     float *sgrp = reinterpret_cast<float *>(dig + ((size_t)3 * PL + 127) / 128 * 128);
-    float *xsum = sgrp + (kpad / 32 + 3) / 4 * 4;
-    float *Fs_all = xsum + (kpad / 32 + 3) / 4 * 4;
-    float *Fs = Fs_all + (size_t)warp * spw * MM_FROW * 16;               // [own super-block][row][MM_FROW]
-    uint64_t *full = reinterpret_cast<uint64_t *>(Fs_all + (size_t)W * spw * MM_FROW * 16);
+    float *xsum = sgrp + (nb + 3) / 4 * 4;
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + nb * 8);
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
@@ -145,97 +133,89 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     const int ntiles = nrt * nks;               // tile i -> super-chunk i / nrt, row tile i % nrt
     const int pw = nks * W;                     // partial slots per row
 
-    // warp 0: stage i % nst <- tile i (one copy per valid row, all on the stage's full barrier)
-    auto issue = [&](int ks, int rt, int stg) {
-        int nsb = nb - ks * MM_KS;
-        nsb = nsb > MM_KS ? MM_KS : nsb;
-        const uint32_t bytes = (uint32_t)nsb * MM_BLOCK_BYTES;
-        int nvalid = rows - rt * 16;
-        nvalid = nvalid > 16 ? 16 : nvalid;
-        if (lane == 0) skn_mbar_expect_tx(&full[stg], bytes * (uint32_t)nvalid);
-        __syncwarp();
-        if (lane < nvalid) {
-            int64_t local;
-            const int tt = skn_group_find(grp, row_begin + rt * 16 + lane, local);
-            skn_fence_proxy_async();
-            skn_bulk_g2s(ring + (size_t)stg * MM_STAGE + lane * MM_ROW_STRIDE,
-                         grp.W[tt] + local * pitch + (size_t)ks * MM_KS * MM_BLOCK_BYTES, bytes, &full[stg]);
-        }
-    };
-
     MV_STAMP(0);
-    int iks = 0, irt = 0;                       // warp 0: the next tile to issue
-    if (warp == 0) {
-        if (lane < nst) {
-            skn_mbar_init(&full[lane], 1);
-            skn_mbar_init(&empty[lane], (uint32_t)W);
-        }
-        skn_fence_mbar_init();
-        skn_fence_proxy_async();
-        __syncwarp();
-#ifdef MM_FINE2
-        MV_STAMP(5);
-#endif
-        for (int i = 0; i < nst && i < ntiles; ++i) {
-#ifdef MM_FINE2
-            if (i == 1) MV_STAMP(6);
-#endif
-            issue(iks, irt, i);
-            if (++irt == nrt) { irt = 0; ++iks; }
-        }
+    if (warp == W && lane < nst) {
+        skn_mbar_init(&full[lane], 1);
+        skn_mbar_init(&empty[lane], (uint32_t)W);
     }
-    MV_STAMP(1);
+    if (warp == W) skn_fence_mbar_init();
+    __syncthreads();                            // barriers are initialised for everyone
+
+    if (warp == W) {
+        // ---- producer: one copy per valid row of a tile, all on the stage's full barrier ----
+        int ks = 0, rt = 0, stg = 0;
+        uint32_t par = 0;                       // parity of the stage's previous use
+        bool failed = false;
+        for (int i = 0; i < ntiles; ++i) {
+            if (i >= nst && !failed && !skn_mbar_wait(&empty[stg], par ^ 1u)) {
+                failed = true;
+                atomicExch(status, SKN_ERR_TIMEOUT);
+            }
+            int nsb = nb - ks * MM_KS;
+            nsb = nsb > MM_KS ? MM_KS : nsb;
+            const uint32_t bytes = (uint32_t)nsb * MM_BLOCK_BYTES;
+            int nvalid = rows - rt * 16;
+            nvalid = nvalid > 16 ? 16 : nvalid;
+            if (lane == 0) skn_mbar_expect_tx(&full[stg], bytes * (uint32_t)nvalid);
+            __syncwarp();
+            if (lane < nvalid) {
+                int64_t local;
+                const int tt = skn_group_find(grp, row_begin + rt * 16 + lane, local);
+                skn_fence_proxy_async();
+                skn_bulk_g2s(ring + (size_t)stg * MM_STAGE + lane * MM_ROW_STRIDE,
+                             grp.W[tt] + local * pitch + (size_t)ks * MM_KS * MM_BLOCK_BYTES, bytes, &full[stg]);
+            }
+            if (i == nst - 1 || i == ntiles - 1) skn_pdl_launch_dependents();   // the first ring-full is on its way
+            if (++rt == nrt) { rt = 0; ++ks; }
+            if (++stg == nst) { stg = 0; par ^= 1u; }
+        }
+        return;
+    }
+
+    // ---- compute warps ----
     skn_pdl_launch_dependents();
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
-
     skn_xform xf{grp.norm_gain, grp.silu_u, 1.f};
     if (grp.norm_gain) {
         __shared__ float red[16];
         float ss = 0.f;
-        for (int f = threadIdx.x; f < K / 4; f += blockDim.x) {
+        for (int f = threadIdx.x; f < K / 4; f += W * 32) {
             const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) red[warp] = ss;
-        __syncthreads();
+        mm_bar_sync(1, W * 32);
         float tot = 0.f;
         for (int w2 = 0; w2 < W; ++w2) tot += red[w2];
         xf.scale = rsqrtf(tot / (float)K + grp.norm_eps);
     }
-    mm_prep_x<2 * SPW>(x, K, kpad, dig, PL, sgrp, xsum, xf);
-    __syncthreads();     // also publishes the barrier initialisation to the other warps
+    // x -> digit planes: a warp takes whole super-blocks, two at a time (four loads in flight)
+    for (int sbi = warp; sbi < nb; sbi += 2 * W) {
+        const int sb2 = sbi + W;
+        const float4 a0 = skn_load_x4(x, sbi * 64 + lane, xf), a1 = skn_load_x4(x, sbi * 64 + 32 + lane, xf);
+        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+        if (sb2 < nb) {
+            b0 = skn_load_x4(x, sb2 * 64 + lane, xf);
+            b1 = skn_load_x4(x, sb2 * 64 + 32 + lane, xf);
+        }
+        mm_digitize(a0, a1, sbi, lane, dig, PL, sgrp, xsum);
+        if (sb2 < nb) mm_digitize(b0, b1, sb2, lane, dig, PL, sgrp, xsum);
+    }
+    mm_bar_sync(1, W * 32);
     MV_STAMP(3);
 
     bool failed = false;
     uint2 bq[SPW * 8];                          // B fragments of this warp's super-blocks in the current super-chunk
     int cur_ks = -1;
-    // tile i = (super-chunk ks, row tile rt) sits in stage stg with barrier parity par; the same
-    // for the tile issued nst - 1 tiles ahead (n*) and for the stage of the previous tile (p*)
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
-    int pstg = 0;
-    uint32_t ppar = 0;
     for (int i = 0; i < ntiles; ++i) {
         const uint8_t *st = ring + (size_t)stg * MM_STAGE;
         int nsb = nb - ks * MM_KS;
         nsb = nsb > MM_KS ? MM_KS : nsb;
-        // refill the stage the previous tile used, once every warp has read its share of it
-        if (warp == 0 && i > 0 && i - 1 + nst < ntiles) {
-            if (!failed && !skn_mbar_wait(&empty[pstg], ppar)) {
-                failed = true;
-                atomicExch(status, SKN_ERR_TIMEOUT);
-            }
-            issue(iks, irt, pstg);
-            if (++irt == nrt) { irt = 0; ++iks; }
-        }
-        if (!failed && !skn_mbar_wait(&full[stg], par)) {
-            failed = true;
-            atomicExch(status, SKN_ERR_TIMEOUT);
-        }
-        if (i == 0) MV_STAMP(4);
         if (ks != cur_ks) {
             // column n = g of the B operand holds digit plane n (n < 3), zero otherwise
             cur_ks = ks;
@@ -250,108 +230,77 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
                 }
             }
         }
-        // ---- block headers of this warp's super-blocks: lane -> row lane & 15, own block (lane >> 4) + 2h
-        float ms = 0.f;
-        {
-            const int hr = lane & 15;
-#pragma unroll
-            for (int h2 = 0; h2 < (SPW + 1) / 2; ++h2) {
-                const int hh = (lane >> 4) + 2 * h2;
-                const int sb = warp + W * hh;
-                if (hh < spw && sb < nsb) {
-                    const uint4 hd = *reinterpret_cast<const uint4 *>(st + hr * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES);
-                    const int G0 = (ks * MM_KS + sb) * 8;
-                    const float4 sg0 = *reinterpret_cast<const float4 *>(sgrp + G0), sg1 = *reinterpret_cast<const float4 *>(sgrp + G0 + 4);
-                    const float4 xs0 = *reinterpret_cast<const float4 *>(xsum + G0), xs1 = *reinterpret_cast<const float4 *>(xsum + G0 + 4);
-                    const uint32_t sc_lo = hd.y & 0x3F3F3F3Fu, mn_lo = hd.z & 0x3F3F3F3Fu;
-                    const uint32_t sc_hi = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
-                    const uint32_t mn_hi = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
-                    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hd.x));   // {d, dmin}
-                    const float d = dd.x, d16 = dd.x * 0.0625f;
-                    float4 f0, f1;
-                    f0.x = (d * mm_byte_f(sc_lo, 0)) * sg0.x;
-                    f0.y = (d16 * mm_byte_f(sc_lo, 1)) * sg0.y;
-                    f0.z = (d * mm_byte_f(sc_lo, 2)) * sg0.z;
-                    f0.w = (d16 * mm_byte_f(sc_lo, 3)) * sg0.w;
-                    f1.x = (d * mm_byte_f(sc_hi, 0)) * sg1.x;
-                    f1.y = (d16 * mm_byte_f(sc_hi, 1)) * sg1.y;
-                    f1.z = (d * mm_byte_f(sc_hi, 2)) * sg1.z;
-                    f1.w = (d16 * mm_byte_f(sc_hi, 3)) * sg1.w;
-                    float *fd = Fs + ((size_t)hh * 16 + hr) * MM_FROW;
-                    *reinterpret_cast<float4 *>(fd) = f0;
-                    *reinterpret_cast<float4 *>(fd + 4) = f1;
-                    float m = mm_byte_f(mn_lo, 0) * xs0.x;
-                    m = fmaf(mm_byte_f(mn_lo, 1), xs0.y, m);
-                    m = fmaf(mm_byte_f(mn_lo, 2), xs0.z, m);
-                    m = fmaf(mm_byte_f(mn_lo, 3), xs0.w, m);
-                    m = fmaf(mm_byte_f(mn_hi, 0), xs1.x, m);
-                    m = fmaf(mm_byte_f(mn_hi, 1), xs1.y, m);
-                    m = fmaf(mm_byte_f(mn_hi, 2), xs1.z, m);
-                    m = fmaf(mm_byte_f(mn_hi, 3), xs1.w, m);
-                    ms = fmaf(dd.y, m, ms);
-                }
-            }
+        if (!failed && !skn_mbar_wait(&full[stg], par)) {
+            failed = true;
+            atomicExch(status, SKN_ERR_TIMEOUT);
         }
-        __syncwarp();
-#ifdef MM_FINE
-        if (i == 0) MV_STAMP(5);
-#endif
-        // ---- integer dot products: rows g and g + 8, one MMA per sub-block
-        float acc0 = 0.f, acc1 = 0.f;
+        if (i == 0) MV_STAMP(4);
+        float acc0 = 0.f, acc1 = 0.f;           // rows g, g + 8: this lane's digit columns, all own super-blocks
+        float ms = 0.f;                         // min term of row g + 8 * (t & 1), sub-blocks 4 * (t >> 1) .. + 3
 #pragma unroll
-        for (int hh = 0; hh < spw; ++hh) {
+        for (int hh = 0; hh < SPW; ++hh) {
             const int sb = warp + W * hh;
             if (sb >= nsb) break;
-            const float4 fa0 = *reinterpret_cast<const float4 *>(Fs + ((size_t)hh * 16 + g) * MM_FROW);
-            const float4 fa1 = *reinterpret_cast<const float4 *>(Fs + ((size_t)hh * 16 + g) * MM_FROW + 4);
-            const float4 fb0 = *reinterpret_cast<const float4 *>(Fs + ((size_t)hh * 16 + g + 8) * MM_FROW);
-            const float4 fb1 = *reinterpret_cast<const float4 *>(Fs + ((size_t)hh * 16 + g + 8) * MM_FROW + 4);
-            const float fa[8] = {fa0.x, fa0.y, fa0.z, fa0.w, fa1.x, fa1.y, fa1.z, fa1.w};
-            const float fb[8] = {fb0.x, fb0.y, fb0.z, fb0.w, fb1.x, fb1.y, fb1.z, fb1.w};
-            const uint8_t *q = st + sb * MM_BLOCK_BYTES + 16 + 8 * t;
+            const uint8_t *ba = st + g * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES;
+            const uint8_t *bb = ba + 8 * MM_ROW_STRIDE;
+            const uint4 ha = *reinterpret_cast<const uint4 *>(ba), hb = *reinterpret_cast<const uint4 *>(bb);
+            const int sbi = ks * MM_KS + sb;
+            // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
+            const uint32_t sa[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u)};
+            const uint32_t sq[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u)};
+            int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};       // [row g col 0, col 1, row g+8 col 0, col 1]
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                const uint2 wa = *reinterpret_cast<const uint2 *>(q + 32 * p + g * MM_ROW_STRIDE);
-                const uint2 wb = *reinterpret_cast<const uint2 *>(q + 32 * p + (g + 8) * MM_ROW_STRIDE);
-                const uint2 b0 = bq[hh * 8 + 2 * p], b1 = bq[hh * 8 + 2 * p + 1];
-                int cc[4];
-                skn_mma_u8s8(cc, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, b0.x, b0.y);
-                acc0 = fmaf(fa[2 * p], fmaf(mm_int_f(cc[1]), 256.f, mm_int_f(cc[0])), acc0);
-                acc1 = fmaf(fb[2 * p], fmaf(mm_int_f(cc[3]), 256.f, mm_int_f(cc[2])), acc1);
-                skn_mma_u8s8(cc, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, b1.x, b1.y);
-                acc0 = fmaf(fa[2 * p + 1], fmaf(mm_int_f(cc[1]), 256.f, mm_int_f(cc[0])), acc0);
-                acc1 = fmaf(fb[2 * p + 1], fmaf(mm_int_f(cc[3]), 256.f, mm_int_f(cc[2])), acc1);
+                const uint2 wa = *reinterpret_cast<const uint2 *>(ba + 16 + 32 * p + 8 * t);
+                const uint2 wb = *reinterpret_cast<const uint2 *>(bb + 16 + 32 * p + 8 * t);
+                const int s0a = mm_byte_i(sa[p >> 1], 2 * (p & 1)), s1a = mm_byte_i(sa[p >> 1], 2 * (p & 1) + 1);
+                const int s0b = mm_byte_i(sq[p >> 1], 2 * (p & 1)), s1b = mm_byte_i(sq[p >> 1], 2 * (p & 1) + 1);
+                int cl[4], ch[4];
+                skn_mma_u8s8(cl, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, bq[hh * 8 + 2 * p].x,
+                             bq[hh * 8 + 2 * p].y);
+                skn_mma_u8s8(ch, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, bq[hh * 8 + 2 * p + 1].x,
+                             bq[hh * 8 + 2 * p + 1].y);
+                lo[0] += s0a * cl[0]; lo[1] += s0a * cl[1]; lo[2] += s0b * cl[2]; lo[3] += s0b * cl[3];
+                hi[0] += s1a * ch[0]; hi[1] += s1a * ch[1]; hi[2] += s1b * ch[2]; hi[3] += s1b * ch[3];
             }
+            // 16 * sum_j sc_j dot_j per digit column (high-nibble results carry a factor 16)
+            const float sg = sgrp[sbi] * 0.0625f;
+            const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&ha.x));   // {d, dmin} of row g
+            const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&hb.x));   // ... of row g + 8
+            const float va = fmaf((float)(lo[1] * 16 + hi[1]), 256.f, (float)(lo[0] * 16 + hi[0]));
+            const float vb = fmaf((float)(lo[3] * 16 + hi[3]), 256.f, (float)(lo[2] * 16 + hi[2]));
+            acc0 = fmaf(da.x * sg, va, acc0);
+            acc1 = fmaf(db.x * sg, vb, acc1);
+            // min term: this lane covers one row and four sub-blocks
+            const uint4 hm = (t & 1) ? hb : ha;
+            const uint32_t mw = (t & 2) ? (((hm.w >> 4) & 0x0F0F0F0Fu) | ((hm.z >> 2) & 0x30303030u)) : (hm.z & 0x3F3F3F3Fu);
+            const float4 xs = *reinterpret_cast<const float4 *>(xsum + sbi * 8 + 4 * (t >> 1));
+            float m = mm_byte_f(mw, 0) * xs.x;
+            m = fmaf(mm_byte_f(mw, 1), xs.y, m);
+            m = fmaf(mm_byte_f(mw, 2), xs.z, m);
+            m = fmaf(mm_byte_f(mw, 3), xs.w, m);
+            ms = fmaf((t & 1) ? db.y : da.y, m, ms);
         }
-        __syncwarp();      // every lane has read its share of the stage and of Fs
-#ifdef MM_FINE
-        if (i == 0) MV_STAMP(6);
-#endif
+        __syncwarp();      // every lane has read its share of the stage
         if (lane == 0) skn_mbar_arrive(&empty[stg]);
         // ---- tile epilogue: digits 0-1 sit in lanes t = 0, digit 2 in lanes t = 1
         float a0 = (t == 0) ? acc0 : ((t == 1) ? acc0 * 65536.f : 0.f);
         float a1 = (t == 0) ? acc1 : ((t == 1) ? acc1 * 65536.f : 0.f);
         a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
         a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-        ms += __shfl_xor_sync(0xffffffffu, ms, 16);
-        const float m0 = __shfl_sync(0xffffffffu, ms, g), m1 = __shfl_sync(0xffffffffu, ms, g + 8);
+        ms += __shfl_xor_sync(0xffffffffu, ms, 2);          // both sub-block halves: lane t = 0 row g, t = 1 row g + 8
+        const float m1 = __shfl_xor_sync(0xffffffffu, ms, 1);
         if (t == 0) {
             const int r0 = rt * 16 + g;
-            if (r0 < rows) part[(size_t)r0 * pw + ks * W + warp] = a0 - m0;
+            if (r0 < rows) part[(size_t)r0 * pw + ks * W + warp] = a0 - ms;
             if (r0 + 8 < rows) part[(size_t)(r0 + 8) * pw + ks * W + warp] = a1 - m1;
         }
-        pstg = stg;
-        ppar = par;
         if (++rt == nrt) { rt = 0; ++ks; }
         if (++stg == nst) { stg = 0; par ^= 1u; }
     }
-#if !defined(MM_FINE) && !defined(MM_FINE2)
     MV_STAMP(5);
-#endif
-    __syncthreads();
-#if !defined(MM_FINE) && !defined(MM_FINE2)
+    mm_bar_sync(1, W * 32);
     MV_STAMP(6);
-#endif
     // sixteen lanes per row: each adds its share of the row's partials in index order, then a
     // fixed butterfly (the same summation tree on every run)
     for (int lb = warp * 2; lb < rows; lb += W * 2) {          // warp-uniform trip count
@@ -372,7 +321,7 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     MV_STAMP(7);
 }
 
-// Launch geometry: warps per CTA and ring depth that fit the shared-memory budget.  The
+// Launch geometry: compute warps per CTA and ring depth that fit the shared-memory budget.  The
 // budget is half of an SM's shared memory: the CTA of the next launch can then become resident
 // (programmatic dependent launch) and prefetch its weights while this one computes.
 static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_plan &pl, bool relaxed) {
@@ -387,13 +336,11 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
     static const int warps_env = env_int("SKN_MM_WARPS", 0);
     static const int nst_env = env_int("SKN_MM_NST", 0);
     static const int budget_env = env_int("SKN_MM_SMEM_KB", 0);
-    int warps = warps_env > 0 ? warps_env : (relaxed ? 8 : 16);
+    int warps = warps_env > 0 ? warps_env : 8;
     warps = warps >= 16 ? 16 : (warps >= 8 ? 8 : 4);
-    const int spw = (MM_KS + warps - 1) / warps;
-    const int kpad = nb * 256;
     const size_t budget = (size_t)(budget_env > 0 ? budget_env : 110) * 1024;
-    const size_t fixed = ((size_t)3 * (kpad + 32) + 127) / 128 * 128 + (size_t)2 * ((kpad / 32 + 3) / 4 * 4) * 4 +
-                         (size_t)warps * spw * MM_FROW * 16 * 4 + (size_t)rows_max * nks * warps * 4 + 64;
+    const size_t fixed = ((size_t)3 * (nb * 256 + 32) + 127) / 128 * 128 + (size_t)((nb + 3) / 4 * 4) * 4 + (size_t)nb * 8 * 4 +
+                         (size_t)rows_max * nks * warps * 4 + 64;
     int nst = nst_env > 0 ? nst_env : (ntiles < 4 ? ntiles : 4);
     while (nst > 1 && fixed + (size_t)nst * (MM_STAGE + 16) > budget) --nst;
     if (nst < 2 && ntiles > 1 && budget_env <= 0) {
@@ -408,7 +355,13 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
     else if (warps == 8) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     else e = cudaFuncSetAttribute(skn_matvec_q4k_mma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
-    pl.nch = nks; pl.wg = nst; pl.grid = (int)grid; pl.threads = warps * 32; pl.smem = smem;
+    // all of the SM's L1 / shared memory as shared memory, so that two CTAs (consecutive launches) fit
+    if (warps == 16) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    else if (warps == 8) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    else e = cudaFuncSetAttribute(skn_matvec_q4k_mma<4>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    // wg carries the ring depth; threads = compute warps + the producer warp
+    pl.nch = nks; pl.wg = nst; pl.grid = (int)grid; pl.threads = (warps + 1) * 32; pl.smem = smem;
     pl.state = 1;
     return cudaSuccess;
 }
@@ -454,7 +407,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    auto kern = pl.threads == 512 ? skn_matvec_q4k_mma<1> : (pl.threads == 256 ? skn_matvec_q4k_mma<2> : skn_matvec_q4k_mma<4>);
+    auto kern = pl.threads == 17 * 32 ? skn_matvec_q4k_mma<1> : (pl.threads == 9 * 32 ? skn_matvec_q4k_mma<2> : skn_matvec_q4k_mma<4>);
     err = cudaLaunchKernelEx(&cfg, kern, grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status, ctx->relaxed_order);
     return true;
 }
