@@ -301,16 +301,18 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     MV_STAMP(5);
     mm_bar_sync(1, W * 32);
     MV_STAMP(6);
-    // sixteen lanes per row: each adds its share of the row's partials in index order, then a
-    // fixed butterfly (the same summation tree on every run)
-    for (int lb = warp * 2; lb < rows; lb += W * 2) {          // warp-uniform trip count
-        const int lr = lb + (lane >> 4);
-        const int sub = lane & 15;
+    // L lanes per row (16, 4 or 1, the most that still covers the CTA's rows in about one pass):
+    // each adds its share of the row's partials in index order, then a fixed butterfly, so the
+    // summation tree depends on the shape only
+    const int lsh = (rows * 16 <= W * 32) ? 4 : ((rows * 4 <= W * 32) ? 2 : 0);
+    const int L = 1 << lsh;
+    for (int lb = warp * (32 >> lsh); lb < rows; lb += W * (32 >> lsh)) {     // warp-uniform trip count
+        const int lr = lb + (lane >> lsh);
+        const int sub = lane & (L - 1);
         float s = 0.f;
         if (lr < rows)
-            for (int cc = sub; cc < pw; cc += 16) s += part[(size_t)lr * pw + cc];
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            for (int cc = sub; cc < pw; cc += L) s += part[(size_t)lr * pw + cc];
+        for (int o = L >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (sub == 0 && lr < rows) {
             int64_t local;
             const int tt = skn_group_find(grp, row_begin + lr, local);
@@ -338,7 +340,9 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
     static const int budget_env = env_int("SKN_MM_SMEM_KB", 0);
     int warps = warps_env > 0 ? warps_env : 8;
     warps = warps >= 16 ? 16 : (warps >= 8 ? 8 : 4);
-    const size_t budget = (size_t)(budget_env > 0 ? budget_env : 110) * 1024;
+    // few tiles: half an SM, so that the next launch's CTA is resident early; many tiles: a deeper
+    // ring matters more than the neighbour
+    const size_t budget = (size_t)(budget_env > 0 ? budget_env : (ntiles >= 6 ? 200 : 110)) * 1024;
     const size_t fixed = ((size_t)3 * (nb * 256 + 32) + 127) / 128 * 128 + (size_t)((nb + 3) / 4 * 4) * 4 + (size_t)nb * 8 * 4 +
                          (size_t)rows_max * nks * warps * 4 + 64;
     int nst = nst_env > 0 ? nst_env : (ntiles < 4 ? ntiles : 4);
