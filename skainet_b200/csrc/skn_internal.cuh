@@ -94,7 +94,11 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 // integer tensor-core matvec (skn_matvec_mma.cu); false = shapes or type not covered
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err);
+                       cudaStream_t stream, cudaError_t &err, bool swiglu = false);
+// h = silu(Wg . f(x)) * (Wu . f(x)) in one launch (f: optional RMSNorm); cudaErrorNotSupported when
+// the tensor-core matvec does not cover the tensors (nothing launched)
+cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,
+                                      const float *norm_gain, float norm_eps, cudaStream_t stream);
 cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                                     const float *const *add, cudaStream_t stream);
 

@@ -30,6 +30,7 @@ struct skn_kvcache {
     int32_t batch, n_kv_heads, head_dim, capacity;
     float *d_k, *d_v;
     int32_t *d_len, *d_start;
+    unsigned *d_tickets;         // [batch][n_kv_heads], zero between launches: split-attention merge tickets
 };
 
 constexpr int ATT_CHUNK = 256;   // cached tokens per CTA (64 when the grid would otherwise leave SMs idle)
@@ -82,42 +83,45 @@ __global__ void skn_kv_advance_kernel(int32_t *__restrict__ len, int B, int T, i
     if (b < B) len[b] = min(cap, len[b] + T);
 }
 
-// Decoder step, one CTA per new token (grid: T x batch): rotary embedding of the token's query
-// heads in place and of its key heads on their way into the ring, V copied alongside.  Pairs
-// (2i, 2i+1) of a head rotate by pos * theta^(-2i/D) with pos = len[b] + t (angle in double:
-// at position 4096 an fp32 angle is already off by ~5e-4 rad).  The lengths are NOT advanced
-// here: the decoder runs attention with `len_extra = T` and advances every layer's lengths
-// with one launch at the end of the step.
-__global__ void __launch_bounds__(256)
+// Decoder step, grid (pair blocks + one V block, T, batch): rotary embedding of a new token's
+// query heads in place and of its key heads on their way into the ring, V copied alongside.
+// Pairs (2i, 2i+1) of a head rotate by pos * theta^(-2i/D) with pos = len[b] + t (angle in double:
+// at position 4096 an fp32 angle is already off by ~5e-4 rad); one pair per thread.  The
+// lengths are NOT advanced here: the decoder runs attention with `len_extra = T` and advances
+// every layer's lengths with one launch at the end of the step.
+__global__ void __launch_bounds__(128)
 skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, const float *__restrict__ v_new,
                        float *__restrict__ kc, float *__restrict__ vc, const int32_t *__restrict__ len,
                        const int32_t *__restrict__ start, int Hq, int Hkv, int D, int cap, int T, double log2_theta) {
-    const int b = blockIdx.y, t = blockIdx.x;
+    const int b = blockIdx.z, t = blockIdx.y;
     const int pos = len[b] + t;
     const int slot = (start[b] + pos) % cap;
     const int half = D / 2;
     const size_t row = (size_t)b * T + t;
-    for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
-        const int p = i % half, h = i / half;
-        const double ang = (double)pos * exp2(-log2_theta * (2.0 * (double)p / (double)D));
-        double sd, cd;
-        sincos(ang, &sd, &cd);
-        const float sn = (float)sd, cs = (float)cd;
-        if (h < Hq) {
-            float2 *v = reinterpret_cast<float2 *>(q + (row * Hq + h) * D) + p;
-            const float2 a = *v;
-            *v = make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
-        } else {
-            const int hk = h - Hq;
-            const float2 a = reinterpret_cast<const float2 *>(k_new + (row * Hkv + hk) * D)[p];
-            reinterpret_cast<float2 *>(kc + (((size_t)b * Hkv + hk) * cap + slot) * D)[p] =
-                make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+    if (blockIdx.x == gridDim.x - 1) {
+        for (int i = threadIdx.x; i < Hkv * D / 4; i += blockDim.x) {
+            const int h = (i * 4) / D, d = (i * 4) % D;
+            *reinterpret_cast<float4 *>(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d) =
+                *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d);
         }
+        return;
     }
-    for (int i = threadIdx.x; i < Hkv * D / 4; i += blockDim.x) {
-        const int h = (i * 4) / D, d = (i * 4) % D;
-        *reinterpret_cast<float4 *>(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d) =
-            *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (Hq + Hkv) * half) return;
+    const int p = i % half, h = i / half;
+    const double ang = (double)pos * exp2(-log2_theta * (2.0 * (double)p / (double)D));
+    double sd, cd;
+    sincos(ang, &sd, &cd);
+    const float sn = (float)sd, cs = (float)cd;
+    if (h < Hq) {
+        float2 *v = reinterpret_cast<float2 *>(q + (row * Hq + h) * D) + p;
+        const float2 a = *v;
+        *v = make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+    } else {
+        const int hk = h - Hq;
+        const float2 a = reinterpret_cast<const float2 *>(k_new + (row * Hkv + hk) * D)[p];
+        reinterpret_cast<float2 *>(kc + (((size_t)b * Hkv + hk) * cap + slot) * D)[p] =
+            make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
     }
 }
 
@@ -225,7 +229,8 @@ template <int D, int G, int TT, int CHUNK>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
                       const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
-                      float scale, float *__restrict__ part, int S, int tq, int len_extra) {
+                      float scale, float *__restrict__ part, int S, int tq, int len_extra, float *__restrict__ out,
+                      unsigned *__restrict__ tickets) {
     constexpr int VEC = D / 32;
     constexpr int NV = TT * G;
     constexpr int REP = 32 / NV;                 // lanes holding the same (token, head) score
@@ -241,7 +246,12 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int L = max(0, len[b] + len_extra - (tq - 1 - bq % tq));
     const int t0 = sp * CHUNK;
-    if (t0 >= L) return;
+    if (t0 >= L) {
+        // an empty sequence has no split to merge: its output is zero
+        if (tickets && L == 0 && sp == 0)
+            for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) out[((size_t)bq * Hkv * G + kvh * G) * D + i] = 0.f;
+        return;
+    }
     const int nt = min(CHUNK, L - t0);
     const int s0 = start[b];
     const int Hq = Hkv * G;
@@ -374,6 +384,31 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
         rec[2 + d] = a;
         if (d == 0) { rec[0] = s_m[g]; rec[1] = s_l[g]; }
     }
+    if (!tickets) return;
+    // merge without a second launch: the CTA that draws the last ticket of its (query, kv head)
+    // combines the splits (log-sum-exp) and hands the ticket counter back as zero
+    __shared__ bool s_last;
+    __threadfence();
+    __syncthreads();
+    const int ns = (L + CHUNK - 1) / CHUNK;
+    if (threadIdx.x == 0) s_last = atomicAdd(&tickets[bq * Hkv + kvh], 1u) == (unsigned)(ns - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) {
+        const int g = i / D, d = i % D;
+        const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2);
+        float m = -INFINITY;
+        for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(rec + (size_t)s * (D + 2)));
+        float l = 0.f, a = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float w = expf(__ldcg(rec + (size_t)s * (D + 2)) - m);
+            l = fmaf(__ldcg(rec + (size_t)s * (D + 2) + 1), w, l);
+            a = fmaf(__ldcg(rec + (size_t)s * (D + 2) + 2 + d), w, a);
+        }
+        out[((size_t)bq * Hq + kvh * G + g) * D + d] = a / l;
+    }
+    if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
 
 template <int D>
@@ -402,14 +437,19 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     constexpr int TT = (G >= 8) ? 4 : 8;
     const int S = (kv->capacity + chunk - 1) / chunk;
     const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)(kv->batch * tq));
+    // single-token decode: the last split of every (sequence, kv head) merges in the same launch;
+    // sequences without any cached token are left to the merge kernel (it writes their zeros)
+    // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
+    const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
+    unsigned *tickets = (tq == 1 && small_grid) ? kv->d_tickets : nullptr;
     if (chunk == 64)
         skn_attn_split_kernel<D, G, TT, 64><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
-                                                                                kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra);
+                                                                                kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else
         skn_attn_split_kernel<D, G, TT, ATT_CHUNK><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
-                                                                                       kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra);
+                                                                                       kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    if (e != cudaSuccess || tickets) return e;
     const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)(kv->batch * tq));
     skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq, chunk, len_extra);
     return cudaGetLastError();
@@ -463,10 +503,12 @@ int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t h
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_k, n);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_v, n);
-    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_len, 2 * sizeof(int32_t) * batch);
+    const size_t n_ints = (size_t)2 * batch + (size_t)batch * n_kv_heads;     // lengths, starts, merge tickets
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_len, n_ints * sizeof(int32_t));
     if (e == cudaSuccess) {
         kv->d_start = kv->d_len + batch;
-        e = cudaMemsetAsync(kv->d_len, 0, 2 * sizeof(int32_t) * batch, ctx->stream);
+        kv->d_tickets = reinterpret_cast<unsigned *>(kv->d_len + 2 * batch);
+        e = cudaMemsetAsync(kv->d_len, 0, n_ints * sizeof(int32_t), ctx->stream);
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
@@ -717,7 +759,9 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
     skn_ctx *ctx = kv->ctx;
     if ((int64_t)host_len_upper + T > kv->capacity)
         return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
-    skn_rope_append_kernel<<<dim3((unsigned)T, (unsigned)kv->batch), 256, 0, ctx->stream>>>(
+    if ((int64_t)kv->batch > 65535 || T > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch or T exceeds 65535");
+    const int pair_blocks = ((n_q_heads + kv->n_kv_heads) * (kv->head_dim / 2) + 127) / 128;
+    skn_rope_append_kernel<<<dim3((unsigned)pair_blocks + 1, (unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
         q_dev, k_new_dev, v_new_dev, kv->d_k, kv->d_v, kv->d_len, kv->d_start, n_q_heads, kv->n_kv_heads, kv->head_dim,
         kv->capacity, T, log2((double)theta));
     SKN_CUDA(ctx, cudaGetLastError());

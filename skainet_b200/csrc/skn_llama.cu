@@ -312,36 +312,53 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
                 SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wo, m->att + r * qd, 1, tp ? nullptr : xr, tp ? m->proj + (int64_t)r * d : xr, st));
             }
             if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
-            // ... gate and up with the second RMSNorm folded in (one launch) ...
+            // ... gate, up and silu(g) * u in one launch (second RMSNorm folded in for one or two
+            // rows), then the down projection with the residual in its epilogue ...
             float *gbuf = m->ffn_g, *ubuf = m->ffn_u;
-            bool fb = false;
-            for (int r = 0; r < M && !fb; ++r) {
-                const skn_tensor *ws[2] = {l.wg, l.wu};
-                float *ys[2] = {gbuf + r * F, ubuf + r * F};
-                SKN_CUDA(ctx, fused(2, ws, m->x + (int64_t)r * d, ys, nullptr, l.ffn_norm, nullptr, fb));
+            bool fused_ffn = true;
+            if (!fold) SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+            for (int r = 0; r < M && fused_ffn; ++r) {
+                const float *src = fold ? m->x + (int64_t)r * d : m->h + (int64_t)r * d;
+                const cudaError_t e = skn_launch_gate_up_swiglu(ctx, l.wg, l.wu, src, gbuf + r * F, fold ? l.ffn_norm : nullptr,
+                                                                m->rms_eps, st);
+                if (e == cudaErrorNotSupported) fused_ffn = false;       // only ever on the first row
+                else SKN_CUDA(ctx, e);
             }
-            if (fb) {
-                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
-                for (int r = 0; r < M; ++r) {
-                    const skn_tensor *ws[2] = {l.wg, l.wu};
-                    float *ys[2] = {gbuf + r * F, ubuf + r * F};
-                    SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 2, ws, m->h + (int64_t)r * d, ys, nullptr, st));
-                }
-            }
-            // ... and the down projection of silu(g) * u, formed while x is prepared, with the
-            // residual in its epilogue
-            fb = false;
-            for (int r = 0; r < M && !fb; ++r) {
-                const skn_tensor *ws[1] = {l.wd};
-                float *ys[1] = {tp ? m->proj + (int64_t)r * d : m->x + (int64_t)r * d};
-                const float *adds[1] = {tp ? nullptr : m->x + (int64_t)r * d};
-                SKN_CUDA(ctx, fused(1, ws, gbuf + r * F, ys, adds, nullptr, ubuf + r * F, fb));
-            }
-            if (fb) {
-                SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
+            if (fused_ffn) {
                 for (int r = 0; r < M; ++r) {
                     float *xr = m->x + (int64_t)r * d;
                     SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, tp ? nullptr : xr, tp ? m->proj + (int64_t)r * d : xr, st));
+                }
+            } else {
+                // ... or, for block types the fused kernel does not cover: gate and up grouped, the
+                // SwiGLU product formed while the down projection prepares x
+                bool fb = false;
+                for (int r = 0; r < M && !fb; ++r) {
+                    const skn_tensor *ws[2] = {l.wg, l.wu};
+                    float *ys[2] = {gbuf + r * F, ubuf + r * F};
+                    SKN_CUDA(ctx, fused(2, ws, m->x + (int64_t)r * d, ys, nullptr, l.ffn_norm, nullptr, fb));
+                }
+                if (fb) {
+                    if (fold) SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+                    for (int r = 0; r < M; ++r) {
+                        const skn_tensor *ws[2] = {l.wg, l.wu};
+                        float *ys[2] = {gbuf + r * F, ubuf + r * F};
+                        SKN_CUDA(ctx, skn_launch_matvec_group(ctx, 2, ws, m->h + (int64_t)r * d, ys, nullptr, st));
+                    }
+                }
+                fb = false;
+                for (int r = 0; r < M && !fb; ++r) {
+                    const skn_tensor *ws[1] = {l.wd};
+                    float *ys[1] = {tp ? m->proj + (int64_t)r * d : m->x + (int64_t)r * d};
+                    const float *adds[1] = {tp ? nullptr : m->x + (int64_t)r * d};
+                    SKN_CUDA(ctx, fused(1, ws, gbuf + r * F, ys, adds, nullptr, ubuf + r * F, fb));
+                }
+                if (fb) {
+                    SKN_CUDA(ctx, skn_launch_silu_mul(gbuf, ubuf, gbuf, (int64_t)M * F, ctx->sm_count, st));
+                    for (int r = 0; r < M; ++r) {
+                        float *xr = m->x + (int64_t)r * d;
+                        SKN_CUDA(ctx, skn_launch_matvec(ctx, l.wd, gbuf + r * F, 1, tp ? nullptr : xr, tp ? m->proj + (int64_t)r * d : xr, st));
+                    }
                 }
             }
             if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;

@@ -950,6 +950,18 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
     return took ? err : cudaErrorNotSupported;
 }
 
+cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,
+                                      const float *norm_gain, float norm_eps, cudaStream_t stream) {
+    if (wg->type != wu->type || wg->n_cols != wu->n_cols || wg->n_rows != wu->n_rows || wg->pitch != wu->pitch ||
+        (wg->pitch % 16) != 0)
+        return cudaErrorNotSupported;
+    const skn_tensor *ws[2] = {wg, wu};
+    float *ys[2] = {h, h};
+    cudaError_t err = cudaSuccess;
+    if (skn_mma_try_group(ctx, 2, ws, x, ys, nullptr, norm_gain, norm_eps, nullptr, stream, err, true)) return err;
+    return cudaErrorNotSupported;
+}
+
 // y[t] = W[t] . x (+ add[t]): one launch when the streaming kernel covers the shapes, separate
 // launches otherwise.
 cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,

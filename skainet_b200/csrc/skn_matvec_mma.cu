@@ -126,8 +126,10 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
-    const int64_t row_begin = (int64_t)blockIdx.x * N / gridDim.x;
-    const int64_t row_end = (int64_t)(blockIdx.x + 1) * N / gridDim.x;
+    // with interleaved gate / up rows every CTA owns whole (gate, up) pairs: even boundaries
+    const int64_t even = grp.swiglu ? ~(int64_t)1 : ~(int64_t)0;
+    const int64_t row_begin = ((int64_t)blockIdx.x * N / gridDim.x) & even;
+    const int64_t row_end = (blockIdx.x + 1 == gridDim.x) ? N : (((int64_t)(blockIdx.x + 1) * N / gridDim.x) & even);
     const int rows = (int)(row_end - row_begin);
     const int nrt = (rows + 15) >> 4;           // row tiles
     const int ntiles = nrt * nks;               // tile i -> super-chunk i / nrt, row tile i % nrt
@@ -160,7 +162,7 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
             __syncwarp();
             if (lane < nvalid) {
                 int64_t local;
-                const int tt = skn_group_find(grp, row_begin + rt * 16 + lane, local);
+                const int tt = skn_group_row(grp, row_begin + rt * 16 + lane, local);
                 skn_fence_proxy_async();
                 skn_bulk_g2s(ring + (size_t)stg * MM_STAGE + lane * MM_ROW_STRIDE,
                              grp.W[tt] + local * pitch + (size_t)ks * MM_KS * MM_BLOCK_BYTES, bytes, &full[stg]);
@@ -313,11 +315,16 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
         if (lr < rows)
             for (int cc = sub; cc < pw; cc += L) s += part[(size_t)lr * pw + cc];
         for (int o = L >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float up = __shfl_xor_sync(0xffffffffu, s, L);      // the next row: the `up` product of a gate row
         if (sub == 0 && lr < rows) {
             int64_t local;
-            const int tt = skn_group_find(grp, row_begin + lr, local);
-            if (grp.add[tt]) s += grp.add[tt][local];
-            grp.y[tt][local] = s;
+            const int tt = skn_group_row(grp, row_begin + lr, local);
+            if (grp.swiglu) {
+                if (tt == 0) grp.y[0][local] = s / (1.f + expf(-s)) * up;
+            } else {
+                if (grp.add[tt]) s += grp.add[tt][local];
+                grp.y[tt][local] = s;
+            }
         }
     }
     MV_STAMP(7);
@@ -333,7 +340,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
     const int nks = (nb + MM_KS - 1) / MM_KS;
     int64_t grid = ctx->sm_count;
     if (grid > n_rows) grid = n_rows;
-    const int64_t rows_max = (n_rows + grid - 1) / grid;
+    const int64_t rows_max = (n_rows + grid - 1) / grid + 2;      // + 2: interleaved launches round to even boundaries
     const int ntiles = (int)((rows_max + 15) / 16) * nks;
     static const int warps_env = env_int("SKN_MM_WARPS", 0);
     static const int nst_env = env_int("SKN_MM_NST", 0);
@@ -374,12 +381,14 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
 // the shapes are not covered (nothing launched).
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err) {
+                       cudaStream_t stream, cudaError_t &err, bool swiglu) {
     static const int enabled = env_int("SKN_MM", 1);
     err = cudaSuccess;
     if (!enabled || w[0]->type != SKN_TYPE_Q4_K) return false;
+    if (swiglu && (n != 2 || w[0]->n_rows != w[1]->n_rows)) return false;
     skn_mv_group grp = {};
     grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
+    grp.swiglu = swiglu ? 1 : 0;
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
         tot += w[t]->n_rows;

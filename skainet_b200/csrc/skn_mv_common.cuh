@@ -67,12 +67,24 @@ struct skn_mv_group {
     const float *norm_gain; // RMSNorm of x fused into its preparation (NULL: none)
     float norm_eps;
     const float *silu_u;    // x <- silu(x) * silu_u fused into its preparation (NULL: none)
+    int swiglu;             // tensor-core kernel only: W[0] = gate, W[1] = up (equal shapes); rows are
+                            // interleaved (virtual row v = tensor v & 1, row v >> 1) so that a CTA holds
+                            // both products of a column and writes y[0][r] = silu(gate . x) * (up . x)
 };
 
 __device__ __forceinline__ int skn_group_find(const skn_mv_group &grp, int64_t r, int64_t &local) {
     const int t = (r >= grp.n_end[0] ? 1 : 0) + ((grp.count > 2 && r >= grp.n_end[1]) ? 1 : 0);
     local = r - (t ? grp.n_end[t - 1] : 0);
     return t;
+}
+
+// row v of a launch -> (tensor, row inside it)
+__device__ __forceinline__ int skn_group_row(const skn_mv_group &grp, int64_t v, int64_t &local) {
+    if (grp.swiglu) {
+        local = v >> 1;
+        return (int)(v & 1);
+    }
+    return skn_group_find(grp, v, local);
 }
 
 static inline int env_int(const char *name, int dflt) {
