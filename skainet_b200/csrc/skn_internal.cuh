@@ -94,7 +94,15 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 // integer tensor-core matvec (skn_matvec_mma.cu); false = shapes or type not covered
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err, bool swiglu = false);
+                       cudaStream_t stream, cudaError_t &err, bool swiglu = false, int n_act = 1, bool add_per_act = false);
+// activation rows one tensor-core matvec launch can take for this tensor (0: not covered)
+int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols);
+// y[t][m] = W[t] . f(x[m]) (+ add) for M activation rows through the tensor-core matvec, in launches
+// of as many rows as fit; cudaErrorNotSupported (nothing launched) when it does not cover the tensors.
+// x rows are K apart, outputs (and per-row add vectors) n_rows apart.
+cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
+                                   const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
+                                   const float *silu_u, bool swiglu, cudaStream_t stream);
 // h = silu(Wg . f(x)) * (Wu . f(x)) in one launch (f: optional RMSNorm); cudaErrorNotSupported when
 // the tensor-core matvec does not cover the tensors (nothing launched)
 cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,

@@ -277,6 +277,55 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         return fell_back ? cudaSuccess : e;
     };
     for (auto &l : m->layers) {
+        // Decode-size batches whose projections the tensor-core matvec covers: every product takes
+        // all M activation rows (a few rows per launch, the weights of the later launches come
+        // from L2), Q/K/V grouped, gate / up / SwiGLU in one launch, residuals in the epilogues.
+        const bool rows_path =
+            small && skn_mma_max_acts(ctx, l.wq->type, 2 * kd + qd, d) > 0 && l.wk->type == l.wq->type && l.wv->type == l.wq->type &&
+            l.wq->pitch == l.wk->pitch && l.wq->pitch == l.wv->pitch && skn_mma_max_acts(ctx, l.wo->type, d, qd) > 0 &&
+            skn_mma_max_acts(ctx, l.wg->type, 2 * F, d) > 0 && l.wu->type == l.wg->type && l.wu->pitch == l.wg->pitch &&
+            skn_mma_max_acts(ctx, l.wd->type, d, F) > 0;
+        if (rows_path) {
+            const float *src = m->x;
+            if (!fold) {
+                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
+                src = m->h;
+            }
+            {
+                const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
+                float *ys[3] = {m->q, m->k, m->v};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 3, ws, src, M, ys, nullptr, false, fold ? l.attn_norm : nullptr, m->rms_eps,
+                                                     nullptr, false, st));
+            }
+            if ((rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
+            if ((rc = skn_attn_causal_pending(l.kv, m->q, Hq, T, scale, m->att))) return rc;
+            {
+                const skn_tensor *ws[1] = {l.wo};
+                float *ys[1] = {tp ? m->proj : m->x};
+                const float *as[1] = {tp ? nullptr : m->x};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->att, M, ys, as, true, nullptr, 0.f, nullptr, false, st));
+            }
+            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
+            src = m->x;
+            if (!fold) {
+                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+                src = m->h;
+            }
+            {
+                const skn_tensor *ws[2] = {l.wg, l.wu};
+                float *ys[2] = {m->ffn_g, m->ffn_g};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 2, ws, src, M, ys, nullptr, false, fold ? l.ffn_norm : nullptr, m->rms_eps,
+                                                     nullptr, true, st));
+            }
+            {
+                const skn_tensor *ws[1] = {l.wd};
+                float *ys[1] = {tp ? m->proj : m->x};
+                const float *as[1] = {tp ? nullptr : m->x};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->ffn_g, M, ys, as, true, nullptr, 0.f, nullptr, false, st));
+            }
+            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
+            continue;
+        }
         if (small) {
             // decode-size batches, per activation row: RMSNorm folded into the preparation of x
             // for Q/K/V (one launch) ...

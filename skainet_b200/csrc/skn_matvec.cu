@@ -950,6 +950,38 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
     return took ? err : cudaErrorNotSupported;
 }
 
+cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
+                                   const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
+                                   const float *silu_u, bool swiglu, cudaStream_t stream) {
+    if (n < 1 || n > 3 || M < 1) return cudaErrorNotSupported;
+    int64_t tot = 0;
+    for (int t = 0; t < n; ++t) {
+        if (w[t]->type != w[0]->type || w[t]->n_cols != w[0]->n_cols || w[t]->pitch != w[0]->pitch) return cudaErrorNotSupported;
+        tot += w[t]->n_rows;
+    }
+    if ((w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
+    const int maxa = skn_mma_max_acts(ctx, w[0]->type, tot, w[0]->n_cols);
+    if (maxa < 1) return cudaErrorNotSupported;
+    const int launches = (M + maxa - 1) / maxa;
+    const int64_t K = w[0]->n_cols;
+    for (int i = 0, m0 = 0; i < launches; ++i) {
+        const int na = (M - m0 + (launches - i) - 1) / (launches - i);       // even shares
+        float *ys[3] = {nullptr, nullptr, nullptr};
+        const float *as[3] = {nullptr, nullptr, nullptr};
+        for (int t = 0; t < n; ++t) {
+            ys[t] = y[t] + (int64_t)m0 * w[swiglu ? 0 : t]->n_rows;
+            if (add && add[t]) as[t] = add[t] + (add_per_act ? (int64_t)m0 * w[t]->n_rows : 0);
+        }
+        cudaError_t err = cudaSuccess;
+        if (!skn_mma_try_group(ctx, n, w, x + (int64_t)m0 * K, ys, add ? as : nullptr, norm_gain, norm_eps,
+                               silu_u ? silu_u + (int64_t)m0 * K : nullptr, stream, err, swiglu, na, add_per_act))
+            return cudaErrorNotSupported;
+        if (err != cudaSuccess) return err;
+        m0 += na;
+    }
+    return cudaSuccess;
+}
+
 cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,
                                       const float *norm_gain, float norm_eps, cudaStream_t stream) {
     if (wg->type != wu->type || wg->n_cols != wu->n_cols || wg->n_rows != wu->n_rows || wg->pitch != wu->pitch ||
@@ -980,6 +1012,13 @@ cudaError_t skn_launch_matvec_group(skn_ctx *ctx, int n, const skn_tensor *const
 cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x, int32_t M, const float *bias,
                               float *y, cudaStream_t stream) {
     static const int force_generic = env_int("SKN_MV_GENERIC", 0);
+    if (M >= 1 && !force_generic) {
+        const skn_tensor *w1[1] = {w};
+        float *y1[1] = {y};
+        const float *b1[1] = {bias};
+        const cudaError_t e = skn_launch_matvec_acts(ctx, 1, w1, x, M, y1, b1, false, nullptr, 0.f, nullptr, false, stream);
+        if (e != cudaErrorNotSupported) return e;
+    }
     if (M >= 1 && !force_generic && (w->pitch % 16) == 0) {
         // small batches run the streaming matvec once per activation row (the weights of the
         // later rows come from L2); each launch is a complete fp32 fused dequant-dot
@@ -989,11 +1028,7 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
             const float *xm = x + (int64_t)m * w->n_cols;
             float *ym = y + (int64_t)m * w->n_rows;
             bool took = false;
-            const skn_tensor *w1[1] = {w};
-            float *y1[1] = {ym};
-            const float *b1[1] = {bias};
-            if (skn_mma_try_group(ctx, 1, w1, xm, y1, b1, nullptr, 0.f, nullptr, stream, err)) took = true;
-            else if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
+            if (w->type == SKN_TYPE_Q4_K) took = try_stream<Q4KStream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q4_0) took = try_stream<Q40Stream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q8_0) took = try_stream<Q80Stream>(ctx, w, xm, bias, ym, stream, err);
             else if (w->type == SKN_TYPE_Q6_K) took = try_stream<Q6KStream>(ctx, w, xm, bias, ym, stream, err);

@@ -102,27 +102,33 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
 
 // Register caps: the register file is split over the SM's four schedulers (16K registers each), so
 // two resident CTAs of 9 warps need five warps per scheduler, i.e. at most 102 registers per
-// thread; three CTAs of 5 warps need four per scheduler (at most 128).
-template <int SPW>                              // super-blocks of a tile per compute warp: W = 16 / SPW compute warps
+// thread.
+//
+// Several activation rows per launch: one MMA serves TWO rows (digit columns 0..2 and 3..5 of the
+// B operand), NP such pairs share the A fragments, block headers and scale decoding.
+template <int SPW, int NP>                      // super-blocks of a tile per compute warp (W = 16 / SPW warps); row pairs
 __global__ void __launch_bounds__(SPW == 1 ? 544 : (SPW == 2 ? 320 : 256), SPW == 1 ? 1 : 2)
 skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
                    int32_t *__restrict__ status, int relaxed) {
     constexpr int W = 16 / SPW;
+    constexpr int NAMAX = 2 * NP;
     const int64_t N = grp.n_end[grp.count - 1];
+    const int NA = grp.n_act;                   // 1 .. NAMAX activation rows
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;          // 0..W-1 compute, W = producer
     const int g = lane >> 2, t = lane & 3;
     const int nb = K / 256;
+    const int nbp = (nb + 3) / 4 * 4;
     const int nks = (nb + MM_KS - 1) / MM_KS;   // K super-chunks
     const int PL = nb * 256 + 32;               // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
 
-    // shared memory: ring | digit planes | block scales | group sums | barriers | partials
+    // shared memory: ring | digit planes [row][3] | block scales [row] | group sums [row] | barriers | partials [row]
     uint8_t *ring = smem;
     uint8_t *dig = smem + (size_t)nst * MM_STAGE;
-    float *sgrp = reinterpret_cast<float *>(dig + ((size_t)3 * PL + 127) / 128 * 128);
-    float *xsum = sgrp + (nb + 3) / 4 * 4;
-    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + nb * 8);
+    float *sgrp = reinterpret_cast<float *>(dig + ((size_t)NA * 3 * PL + 127) / 128 * 128);
+    float *xsum = sgrp + (size_t)NA * nbp;
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nb * 8);
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
@@ -133,7 +139,7 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     const int rows = (int)(row_end - row_begin);
     const int nrt = (rows + 15) >> 4;           // row tiles
     const int ntiles = nrt * nks;               // tile i -> super-chunk i / nrt, row tile i % nrt
-    const int pw = nks * W;                     // partial slots per row
+    const int pw = nks * W;                     // partial slots per (activation row, weight row)
 
     MV_STAMP(0);
     if (warp == W && lane < nst) {
@@ -178,67 +184,86 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     skn_pdl_launch_dependents();
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
-    skn_xform xf{grp.norm_gain, grp.silu_u, 1.f};
-    if (grp.norm_gain) {
-        __shared__ float red[16];
-        float ss = 0.f;
-        for (int f = threadIdx.x; f < K / 4; f += W * 32) {
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
+    float nscale[NAMAX];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        mm_bar_sync(1, W * 32);
-        float tot = 0.f;
-        for (int w2 = 0; w2 < W; ++w2) tot += red[w2];
-        xf.scale = rsqrtf(tot / (float)K + grp.norm_eps);
-    }
-    // x -> digit planes: a warp takes whole super-blocks, two at a time (four loads in flight)
-    for (int sbi = warp; sbi < nb; sbi += 2 * W) {
-        const int sb2 = sbi + W;
-        const float4 a0 = skn_load_x4(x, sbi * 64 + lane, xf), a1 = skn_load_x4(x, sbi * 64 + 32 + lane, xf);
-        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
-        if (sb2 < nb) {
-            b0 = skn_load_x4(x, sb2 * 64 + lane, xf);
-            b1 = skn_load_x4(x, sb2 * 64 + 32 + lane, xf);
+    for (int a = 0; a < NAMAX; ++a) nscale[a] = 1.f;
+    if (grp.norm_gain) {
+        // RMSNorm scale of every activation row: each CTA reads all of x anyway
+        __shared__ float red[NAMAX][16];
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) {
+            if (a < NA) {
+                float ss = 0.f;
+                for (int f = threadIdx.x; f < K / 4; f += W * 32) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)a * K) + f);
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) red[a][warp] = ss;
+            }
         }
-        mm_digitize(a0, a1, sbi, lane, dig, PL, sgrp, xsum);
-        if (sb2 < nb) mm_digitize(b0, b1, sb2, lane, dig, PL, sgrp, xsum);
+        mm_bar_sync(1, W * 32);
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) {
+            if (a < NA) {
+                float tot = 0.f;
+                for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
+                nscale[a] = rsqrtf(tot / (float)K + grp.norm_eps);
+            }
+        }
+    }
+    // x -> digit planes: a warp takes whole super-blocks, two at a time (four loads in flight);
+    // unit u = activation row u / nb, super-block u % nb
+    {
+        const int units = NA * nb;
+        for (int u = warp; u < units; u += 2 * W) {
+            const int u2 = u + W;
+            const int a0 = u / nb, s0 = u - a0 * nb;
+            const int a1 = u2 < units ? u2 / nb : a0, s1 = u2 < units ? u2 - a1 * nb : s0;
+            skn_xform xf0{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a0 * K : nullptr, 1.f};
+            skn_xform xf1{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a1 * K : nullptr, 1.f};
+#pragma unroll
+            for (int a = 0; a < NAMAX; ++a) {
+                if (a == a0) xf0.scale = nscale[a];
+                if (a == a1) xf1.scale = nscale[a];
+            }
+            const float *x0 = x + (size_t)a0 * K, *x1 = x + (size_t)a1 * K;
+            const float4 p0 = skn_load_x4(x0, s0 * 64 + lane, xf0), p1 = skn_load_x4(x0, s0 * 64 + 32 + lane, xf0);
+            float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
+            if (u2 < units) {
+                q0 = skn_load_x4(x1, s1 * 64 + lane, xf1);
+                q1 = skn_load_x4(x1, s1 * 64 + 32 + lane, xf1);
+            }
+            mm_digitize(p0, p1, s0, lane, dig + (size_t)a0 * 3 * PL, PL, sgrp + (size_t)a0 * nbp, xsum + (size_t)a0 * nb * 8);
+            if (u2 < units)
+                mm_digitize(q0, q1, s1, lane, dig + (size_t)a1 * 3 * PL, PL, sgrp + (size_t)a1 * nbp, xsum + (size_t)a1 * nb * 8);
+        }
     }
     mm_bar_sync(1, W * 32);
     MV_STAMP(3);
 
+    // this lane's two B columns (2t, 2t + 1): column c of a row pair is digit c % 3 of its row c / 3
+    const int bcol_row = g / 3, bcol_dig = g - 3 * bcol_row;          // the column this lane LOADS (g < 6)
+    const int rowA = (t >= 2) ? 1 : 0, rowB = (t >= 1) ? 1 : 0;       // rows (within a pair) of the columns it READS BACK
     bool failed = false;
-    uint2 bq[SPW * 8];                          // B fragments of this warp's super-blocks in the current super-chunk
-    int cur_ks = -1;
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
     for (int i = 0; i < ntiles; ++i) {
         const uint8_t *st = ring + (size_t)stg * MM_STAGE;
         int nsb = nb - ks * MM_KS;
         nsb = nsb > MM_KS ? MM_KS : nsb;
-        if (ks != cur_ks) {
-            // column n = g of the B operand holds digit plane n (n < 3), zero otherwise
-            cur_ks = ks;
-#pragma unroll
-            for (int hh = 0; hh < SPW; ++hh) {
-                const int sb = warp + W * hh;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint2 v = make_uint2(0u, 0u);
-                    if (g < 3 && sb < nsb) v = *reinterpret_cast<const uint2 *>(dig + (size_t)g * PL + ((size_t)(ks * MM_KS + sb) * 8 + j) * 32 + 8 * t);
-                    bq[hh * 8 + j] = v;
-                }
-            }
-        }
         if (!failed && !skn_mbar_wait(&full[stg], par)) {
             failed = true;
             atomicExch(status, SKN_ERR_TIMEOUT);
         }
         if (i == 0) MV_STAMP(4);
-        float acc0 = 0.f, acc1 = 0.f;           // rows g, g + 8: this lane's digit columns, all own super-blocks
-        float ms = 0.f;                         // min term of row g + 8 * (t & 1), sub-blocks 4 * (t >> 1) .. + 3
+        float accA[NP][2], accB[NP][2];         // [pair][weight row g / g + 8]: columns 2t and 2t + 1, all own super-blocks
+        float ms[NAMAX];                        // min term of weight row g + 8 * (t & 1), sub-blocks 4 * (t >> 1) .. + 3
+#pragma unroll
+        for (int ap = 0; ap < NP; ++ap) accA[ap][0] = accA[ap][1] = accB[ap][0] = accB[ap][1] = 0.f;
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) ms[a] = 0.f;
 #pragma unroll
         for (int hh = 0; hh < SPW; ++hh) {
             const int sb = warp + W * hh;
@@ -250,52 +275,103 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
             // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
             const uint32_t sa[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u)};
             const uint32_t sq[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u)};
-            int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};       // [row g col 0, col 1, row g+8 col 0, col 1]
+            int lo[NP][4], hi[NP][4];           // [pair][weight row g col 2t, col 2t+1, weight row g+8 col 2t, col 2t+1]
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) lo[ap][c] = hi[ap][c] = 0;
+            const uint8_t *bsrc[NP];
+            bool bon[NP];
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int arow = 2 * ap + bcol_row;
+                bon[ap] = g < 6 && arow < NA;
+                bsrc[ap] = dig + ((size_t)(bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (size_t)sbi * 256 + 8 * t;
+            }
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
                 const uint2 wa = *reinterpret_cast<const uint2 *>(ba + 16 + 32 * p + 8 * t);
                 const uint2 wb = *reinterpret_cast<const uint2 *>(bb + 16 + 32 * p + 8 * t);
                 const int s0a = mm_byte_i(sa[p >> 1], 2 * (p & 1)), s1a = mm_byte_i(sa[p >> 1], 2 * (p & 1) + 1);
                 const int s0b = mm_byte_i(sq[p >> 1], 2 * (p & 1)), s1b = mm_byte_i(sq[p >> 1], 2 * (p & 1) + 1);
-                int cl[4], ch[4];
-                skn_mma_u8s8(cl, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, bq[hh * 8 + 2 * p].x,
-                             bq[hh * 8 + 2 * p].y);
-                skn_mma_u8s8(ch, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, bq[hh * 8 + 2 * p + 1].x,
-                             bq[hh * 8 + 2 * p + 1].y);
-                lo[0] += s0a * cl[0]; lo[1] += s0a * cl[1]; lo[2] += s0b * cl[2]; lo[3] += s0b * cl[3];
-                hi[0] += s1a * ch[0]; hi[1] += s1a * ch[1]; hi[2] += s1b * ch[2]; hi[3] += s1b * ch[3];
+                const uint32_t al0 = wa.x & 0x0F0F0F0Fu, al1 = wb.x & 0x0F0F0F0Fu, al2 = wa.y & 0x0F0F0F0Fu, al3 = wb.y & 0x0F0F0F0Fu;
+                const uint32_t ah0 = wa.x & 0xF0F0F0F0u, ah1 = wb.x & 0xF0F0F0F0u, ah2 = wa.y & 0xF0F0F0F0u, ah3 = wb.y & 0xF0F0F0F0u;
+#pragma unroll
+                for (int ap = 0; ap < NP; ++ap) {
+                    uint2 b0 = make_uint2(0u, 0u), b1 = make_uint2(0u, 0u);
+                    if (bon[ap]) {
+                        b0 = *reinterpret_cast<const uint2 *>(bsrc[ap] + (2 * p) * 32);
+                        b1 = *reinterpret_cast<const uint2 *>(bsrc[ap] + (2 * p + 1) * 32);
+                    }
+                    int cl[4], ch[4];
+                    skn_mma_u8s8(cl, al0, al1, al2, al3, b0.x, b0.y);
+                    skn_mma_u8s8(ch, ah0, ah1, ah2, ah3, b1.x, b1.y);
+                    lo[ap][0] += s0a * cl[0]; lo[ap][1] += s0a * cl[1]; lo[ap][2] += s0b * cl[2]; lo[ap][3] += s0b * cl[3];
+                    hi[ap][0] += s1a * ch[0]; hi[ap][1] += s1a * ch[1]; hi[ap][2] += s1b * ch[2]; hi[ap][3] += s1b * ch[3];
+                }
             }
-            // 16 * sum_j sc_j dot_j per digit column (high-nibble results carry a factor 16)
-            const float sg = sgrp[sbi] * 0.0625f;
+            // 16 * sum_j sc_j dot_j per digit column (high-nibble results carry a factor 16), scaled
+            // by d of the weight row and the block scale of the column's activation row
             const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&ha.x));   // {d, dmin} of row g
             const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&hb.x));   // ... of row g + 8
-            const float va = fmaf((float)(lo[1] * 16 + hi[1]), 256.f, (float)(lo[0] * 16 + hi[0]));
-            const float vb = fmaf((float)(lo[3] * 16 + hi[3]), 256.f, (float)(lo[2] * 16 + hi[2]));
-            acc0 = fmaf(da.x * sg, va, acc0);
-            acc1 = fmaf(db.x * sg, vb, acc1);
-            // min term: this lane covers one row and four sub-blocks
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
+                const float sgA = sgrp[(size_t)ra * nbp + sbi] * 0.0625f, sgB = sgrp[(size_t)rb * nbp + sbi] * 0.0625f;
+                accA[ap][0] = fmaf(da.x * sgA, (float)(lo[ap][0] * 16 + hi[ap][0]), accA[ap][0]);
+                accB[ap][0] = fmaf(da.x * sgB, (float)(lo[ap][1] * 16 + hi[ap][1]), accB[ap][0]);
+                accA[ap][1] = fmaf(db.x * sgA, (float)(lo[ap][2] * 16 + hi[ap][2]), accA[ap][1]);
+                accB[ap][1] = fmaf(db.x * sgB, (float)(lo[ap][3] * 16 + hi[ap][3]), accB[ap][1]);
+            }
+            // min term: this lane covers one weight row and four sub-blocks, every activation row
             const uint4 hm = (t & 1) ? hb : ha;
             const uint32_t mw = (t & 2) ? (((hm.w >> 4) & 0x0F0F0F0Fu) | ((hm.z >> 2) & 0x30303030u)) : (hm.z & 0x3F3F3F3Fu);
-            const float4 xs = *reinterpret_cast<const float4 *>(xsum + sbi * 8 + 4 * (t >> 1));
-            float m = mm_byte_f(mw, 0) * xs.x;
-            m = fmaf(mm_byte_f(mw, 1), xs.y, m);
-            m = fmaf(mm_byte_f(mw, 2), xs.z, m);
-            m = fmaf(mm_byte_f(mw, 3), xs.w, m);
-            ms = fmaf((t & 1) ? db.y : da.y, m, ms);
+            const float m0 = mm_byte_f(mw, 0), m1 = mm_byte_f(mw, 1), m2 = mm_byte_f(mw, 2), m3 = mm_byte_f(mw, 3);
+            const float dmin = (t & 1) ? db.y : da.y;
+#pragma unroll
+            for (int a = 0; a < NAMAX; ++a) {
+                if (a < NA) {
+                    const float4 xs = *reinterpret_cast<const float4 *>(xsum + ((size_t)a * nb + sbi) * 8 + 4 * (t >> 1));
+                    float m = m0 * xs.x;
+                    m = fmaf(m1, xs.y, m);
+                    m = fmaf(m2, xs.z, m);
+                    m = fmaf(m3, xs.w, m);
+                    ms[a] = fmaf(dmin, m, ms[a]);
+                }
+            }
         }
         __syncwarp();      // every lane has read its share of the stage
         if (lane == 0) skn_mbar_arrive(&empty[stg]);
-        // ---- tile epilogue: digits 0-1 sit in lanes t = 0, digit 2 in lanes t = 1
-        float a0 = (t == 0) ? acc0 : ((t == 1) ? acc0 * 65536.f : 0.f);
-        float a1 = (t == 0) ? acc1 : ((t == 1) ? acc1 * 65536.f : 0.f);
-        a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
-        a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-        ms += __shfl_xor_sync(0xffffffffu, ms, 2);          // both sub-block halves: lane t = 0 row g, t = 1 row g + 8
-        const float m1 = __shfl_xor_sync(0xffffffffu, ms, 1);
-        if (t == 0) {
-            const int r0 = rt * 16 + g;
-            if (r0 < rows) part[(size_t)r0 * pw + ks * W + warp] = a0 - ms;
-            if (r0 + 8 < rows) part[(size_t)(r0 + 8) * pw + ks * W + warp] = a1 - m1;
+        // ---- tile epilogue.  Columns of a pair: lane t = 0 holds (row 0 digit 0, row 0 digit 1),
+        // t = 1 (row 0 digit 2, row 1 digit 0), t = 2 (row 1 digit 1, row 1 digit 2), t = 3 nothing.
+#pragma unroll
+        for (int ap = 0; ap < NP; ++ap) {
+#pragma unroll
+            for (int wr = 0; wr < 2; ++wr) {            // weight rows g, g + 8
+                const float A = accA[ap][wr], B = accB[ap][wr];
+                float e0 = (t == 0) ? fmaf(B, 256.f, A) : ((t == 1) ? A * 65536.f : 0.f);
+                float e1 = (t == 1) ? B : ((t == 2) ? fmaf(B, 65536.f, A * 256.f) : 0.f);
+                e0 += __shfl_xor_sync(0xffffffffu, e0, 1);
+                e1 += __shfl_xor_sync(0xffffffffu, e1, 1);
+                e0 += __shfl_xor_sync(0xffffffffu, e0, 2);
+                e1 += __shfl_xor_sync(0xffffffffu, e1, 2);
+                accA[ap][wr] = e0;                      // now: totals of rows 2 ap and 2 ap + 1 in every lane
+                accB[ap][wr] = e1;
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) {
+            // both sub-block halves: lanes t = 0, 2 hold weight row g, lanes t = 1, 3 row g + 8
+            ms[a] += __shfl_xor_sync(0xffffffffu, ms[a], 2);
+            const float mo = __shfl_xor_sync(0xffffffffu, ms[a], 1);
+            if (t == 0 && a < NA) {
+                const int r0 = rt * 16 + g;
+                const float v0 = (a & 1) ? accB[a >> 1][0] : accA[a >> 1][0];
+                const float v1 = (a & 1) ? accB[a >> 1][1] : accA[a >> 1][1];
+                float *pa = part + (size_t)a * rows * pw;
+                if (r0 < rows) pa[(size_t)r0 * pw + ks * W + warp] = v0 - ms[a];
+                if (r0 + 8 < rows) pa[(size_t)(r0 + 8) * pw + ks * W + warp] = v1 - mo;
+            }
         }
         if (++rt == nrt) { rt = 0; ++ks; }
         if (++stg == nst) { stg = 0; par ^= 1u; }
@@ -308,34 +384,62 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     // summation tree depends on the shape only
     const int lsh = (rows * 16 <= W * 32) ? 4 : ((rows * 4 <= W * 32) ? 2 : 0);
     const int L = 1 << lsh;
-    for (int lb = warp * (32 >> lsh); lb < rows; lb += W * (32 >> lsh)) {     // warp-uniform trip count
-        const int lr = lb + (lane >> lsh);
-        const int sub = lane & (L - 1);
-        float s = 0.f;
-        if (lr < rows)
-            for (int cc = sub; cc < pw; cc += L) s += part[(size_t)lr * pw + cc];
-        for (int o = L >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const float up = __shfl_xor_sync(0xffffffffu, s, L);      // the next row: the `up` product of a gate row
-        if (sub == 0 && lr < rows) {
-            int64_t local;
-            const int tt = skn_group_row(grp, row_begin + lr, local);
-            if (grp.swiglu) {
-                if (tt == 0) grp.y[0][local] = s / (1.f + expf(-s)) * up;
-            } else {
-                if (grp.add[tt]) s += grp.add[tt][local];
-                grp.y[tt][local] = s;
+    for (int a = 0; a < NA; ++a) {
+        const float *pa = part + (size_t)a * rows * pw;
+        for (int lb = warp * (32 >> lsh); lb < rows; lb += W * (32 >> lsh)) {     // warp-uniform trip count
+            const int lr = lb + (lane >> lsh);
+            const int sub = lane & (L - 1);
+            float s = 0.f;
+            if (lr < rows)
+                for (int cc = sub; cc < pw; cc += L) s += pa[(size_t)lr * pw + cc];
+            for (int o = L >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float up = __shfl_xor_sync(0xffffffffu, s, L);      // the next row: the `up` product of a gate row
+            if (sub == 0 && lr < rows) {
+                int64_t local;
+                const int tt = skn_group_row(grp, row_begin + lr, local);
+                if (grp.swiglu) {
+                    if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = s / (1.f + expf(-s)) * up;
+                } else {
+                    if (grp.add[tt]) s += grp.add[tt][(size_t)a * grp.addstride[tt] + local];
+                    grp.y[tt][(size_t)a * grp.ystride[tt] + local] = s;
+                }
             }
         }
     }
     MV_STAMP(7);
 }
 
-// Launch geometry: compute warps per CTA and ring depth that fit the shared-memory budget.  The
-// budget is half of an SM's shared memory: the CTA of the next launch can then become resident
-// (programmatic dependent launch) and prefetch its weights while this one computes.
-static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_plan &pl, bool relaxed) {
+// Launch geometry: compute warps per CTA and ring depth that fit the shared-memory budget.  With
+// few tiles the budget is half of an SM's shared memory: the CTA of the next launch can then
+// become resident (programmatic dependent launch) and prefetch its weights while this one
+// computes.
+typedef void (*mm_kernel_t)(const skn_mv_group, int64_t, int, int, const float *, int32_t *, int);
+
+static mm_kernel_t mm_kernel(int warps, int n_act) {
+    if (n_act > 2) return skn_matvec_q4k_mma<2, 2>;
+    return warps == 16 ? skn_matvec_q4k_mma<1, 1> : (warps == 8 ? skn_matvec_q4k_mma<2, 1> : skn_matvec_q4k_mma<4, 1>);
+}
+
+static size_t mm_fixed_smem(int nb, int n_act, int64_t rows_max, int nks, int warps) {
+    return ((size_t)n_act * 3 * (nb * 256 + 32) + 127) / 128 * 128 + (size_t)n_act * ((nb + 3) / 4 * 4) * 4 +
+           (size_t)n_act * nb * 8 * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
+}
+
+// most activation rows one launch can take for this shape (the digit planes and partial sums of
+// every row sit in shared memory next to at least two ring stages)
+static int mm_max_acts(const skn_ctx *ctx, int64_t n_rows, int64_t n_cols) {
+    const int nb = (int)(n_cols / 256);
+    int64_t grid = ctx->sm_count;
+    if (grid > n_rows) grid = n_rows;
+    const int64_t rows_max = (n_rows + grid - 1) / grid + 2;
+    for (int a = 4; a > 1; --a)
+        if (mm_fixed_smem(nb, a, rows_max, (nb + MM_KS - 1) / MM_KS, 8) + 2 * (MM_STAGE + 16) <= 200 * 1024) return a;
+    return 1;
+}
+
+static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, int n_act, skn_mv_plan &pl, bool relaxed) {
     pl = skn_mv_plan{-1, 0, 0, 0, 0, 0};
-    if (n_cols % 256 || n_cols > (1 << 18) || n_rows < 1) return cudaSuccess;
+    if (n_cols % 256 || n_cols > (1 << 18) || n_rows < 1 || n_act < 1 || n_act > 4) return cudaSuccess;
     const int nb = (int)(n_cols / 256);
     const int nks = (nb + MM_KS - 1) / MM_KS;
     int64_t grid = ctx->sm_count;
@@ -347,41 +451,40 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, skn_mv_
     static const int budget_env = env_int("SKN_MM_SMEM_KB", 0);
     int warps = warps_env > 0 ? warps_env : 8;
     warps = warps >= 16 ? 16 : (warps >= 8 ? 8 : 4);
+    if (n_act > 2) warps = 8;
+    (void)relaxed;
     // few tiles: half an SM, so that the next launch's CTA is resident early; many tiles: a deeper
     // ring matters more than the neighbour
     const size_t budget = (size_t)(budget_env > 0 ? budget_env : (ntiles >= 6 ? 200 : 110)) * 1024;
-    const size_t fixed = ((size_t)3 * (nb * 256 + 32) + 127) / 128 * 128 + (size_t)((nb + 3) / 4 * 4) * 4 + (size_t)nb * 8 * 4 +
-                         (size_t)rows_max * nks * warps * 4 + 64;
+    const size_t fixed = mm_fixed_smem(nb, n_act, rows_max, nks, warps);
     int nst = nst_env > 0 ? nst_env : (ntiles < 4 ? ntiles : 4);
     while (nst > 1 && fixed + (size_t)nst * (MM_STAGE + 16) > budget) --nst;
     if (nst < 2 && ntiles > 1 && budget_env <= 0) {
-        // long rows: the digit planes leave no room for two stages in half an SM; take all of it
+        // long rows or several activation rows: the digit planes leave no room for two stages in
+        // half an SM; take all of it
         nst = ntiles < 4 ? ntiles : 4;
         while (nst > 1 && fixed + (size_t)nst * (MM_STAGE + 16) > 200 * 1024) --nst;
     }
     const size_t smem = fixed + (size_t)nst * (MM_STAGE + 16);
     if (smem > 220 * 1024) return cudaSuccess;
-    cudaError_t e = cudaSuccess;
-    if (warps == 16) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    else if (warps == 8) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    else e = cudaFuncSetAttribute(skn_matvec_q4k_mma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    mm_kernel_t kern = mm_kernel(warps, n_act);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
     // all of the SM's L1 / shared memory as shared memory, so that two CTAs (consecutive launches) fit
-    if (warps == 16) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    else if (warps == 8) e = cudaFuncSetAttribute(skn_matvec_q4k_mma<2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    else e = cudaFuncSetAttribute(skn_matvec_q4k_mma<4>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    // wg carries the ring depth; threads = compute warps + the producer warp
-    pl.nch = nks; pl.wg = nst; pl.grid = (int)grid; pl.threads = (warps + 1) * 32; pl.smem = smem;
+    // wg carries the ring depth, nch the compute warps; threads = compute warps + the producer warp
+    pl.nch = warps; pl.wg = nst; pl.grid = (int)grid; pl.threads = (warps + 1) * 32; pl.smem = smem;
     pl.state = 1;
     return cudaSuccess;
 }
 
-// y[t] = W[t] . f(x) (+ add[t]) for n <= 3 Q4_K tensors of one K and pitch.  Returns false when
-// the shapes are not covered (nothing launched).
+// y[t][a] = W[t] . f(x[a]) (+ add[t]) for n <= 3 Q4_K tensors of one K and pitch and n_act <= 4
+// activation rows (x rows K apart, outputs n_rows apart; add_per_act: add vectors n_rows apart,
+// otherwise one bias for all rows).  Returns false when the shapes are not covered (nothing launched).
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err, bool swiglu) {
+                       cudaStream_t stream, cudaError_t &err, bool swiglu, int n_act, bool add_per_act) {
     static const int enabled = env_int("SKN_MM", 1);
     err = cudaSuccess;
     if (!enabled || w[0]->type != SKN_TYPE_Q4_K) return false;
@@ -389,21 +492,25 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     skn_mv_group grp = {};
     grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
     grp.swiglu = swiglu ? 1 : 0;
+    grp.n_act = n_act;
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
         tot += w[t]->n_rows;
         grp.W[t] = w[t]->d_blocks; grp.y[t] = y[t]; grp.add[t] = add ? add[t] : nullptr; grp.n_end[t] = tot;
+        grp.ystride[t] = w[t]->n_rows;
+        grp.addstride[t] = add_per_act ? w[t]->n_rows : 0;
     }
     for (int t = n; t < 3; ++t) grp.n_end[t] = tot;
     grp.count = n;
+    if (n_act < 1 || n_act > mm_max_acts(ctx, tot, w[0]->n_cols)) return false;
     skn_mv_plan pl = skn_mv_plan{0, 0, 0, 0, 0, 0};
-    const int32_t key_type = 1000 + w[0]->type;       // distinct from the CUDA-core kernels' plans
+    const int32_t key_type = 1000 + 16 * n_act + w[0]->type;       // distinct from the CUDA-core kernels' plans
     for (int i = 0; i < ctx->n_group_plans; ++i) {
         const skn_group_plan &c = ctx->group_plans[i];
         if (c.type == key_type && c.rows == tot && c.cols == w[0]->n_cols && c.relaxed == ctx->relaxed_order) { pl = c.pl; break; }
     }
     if (pl.state == 0) {
-        err = mm_plan(ctx, tot, w[0]->n_cols, pl, ctx->relaxed_order != 0);
+        err = mm_plan(ctx, tot, w[0]->n_cols, n_act, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) return true;
         if (ctx->n_group_plans < 32)
             ctx->group_plans[ctx->n_group_plans++] = skn_group_plan{key_type, ctx->relaxed_order, tot, w[0]->n_cols, pl};
@@ -420,7 +527,13 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    auto kern = pl.threads == 17 * 32 ? skn_matvec_q4k_mma<1> : (pl.threads == 9 * 32 ? skn_matvec_q4k_mma<2> : skn_matvec_q4k_mma<4>);
-    err = cudaLaunchKernelEx(&cfg, kern, grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status, ctx->relaxed_order);
+    err = cudaLaunchKernelEx(&cfg, mm_kernel(pl.nch, n_act), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
+                             ctx->relaxed_order);
     return true;
+}
+
+int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols) {
+    static const int enabled = env_int("SKN_MM", 1);
+    if (!enabled || type != SKN_TYPE_Q4_K || n_cols % 256 || n_cols > (1 << 18) || n_rows_total < 1) return 0;
+    return mm_max_acts(ctx, n_rows_total, n_cols);
 }

@@ -67,6 +67,9 @@ struct skn_mv_group {
     const float *norm_gain; // RMSNorm of x fused into its preparation (NULL: none)
     float norm_eps;
     const float *silu_u;    // x <- silu(x) * silu_u fused into its preparation (NULL: none)
+    int n_act;              // tensor-core kernel only: activation rows per launch (x rows K apart, 0 means 1)
+    int64_t ystride[3];     // ... distance between the outputs of consecutive activation rows
+    int64_t addstride[3];   // ... and between their `add` vectors (0: one bias shared by all rows)
     int swiglu;             // tensor-core kernel only: W[0] = gate, W[1] = up (equal shapes); rows are
                             // interleaved (virtual row v = tensor v & 1, row v >> 1) so that a CTA holds
                             // both products of a column and writes y[0][r] = silu(gate . x) * (up . x)
