@@ -52,6 +52,29 @@ __device__ __forceinline__ float mm_byte_f(uint32_t w, uint32_t i) {
 }
 __device__ __forceinline__ int mm_byte_i(uint32_t w, uint32_t i) { return (int)__byte_perm(w, 0u, 0x4440u + i); }
 
+// loads from a 32-bit shared-memory address (explicit state space: no generic addressing, no
+// 64-bit address arithmetic in the inner loops)
+__device__ __forceinline__ uint2 mm_lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 mm_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float mm_lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float4 mm_lds128f(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+
 __device__ __forceinline__ void mm_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -107,7 +130,7 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
 // Several activation rows per launch: one MMA serves TWO rows (digit columns 0..2 and 3..5 of the
 // B operand), NP such pairs share the A fragments, block headers and scale decoding.
 template <int SPW, int NP>                      // super-blocks of a tile per compute warp (W = 16 / SPW warps); row pairs
-__global__ void __launch_bounds__(SPW == 1 ? 544 : (SPW == 2 ? 320 : 256), SPW == 1 ? 1 : 2)
+__global__ void __launch_bounds__(SPW == 1 ? 544 : (SPW == 2 ? 320 : 256), (SPW == 1 || NP > 1) ? 1 : 2)
 skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
                    int32_t *__restrict__ status, int relaxed) {
     constexpr int W = 16 / SPW;
@@ -249,8 +272,9 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
     bool failed = false;
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
+    const uint32_t ring_s = skn_smem_u32(ring), dig_s = skn_smem_u32(dig), sgrp_s = skn_smem_u32(sgrp), xsum_s = skn_smem_u32(xsum);
     for (int i = 0; i < ntiles; ++i) {
-        const uint8_t *st = ring + (size_t)stg * MM_STAGE;
+        const uint32_t st = ring_s + (uint32_t)stg * MM_STAGE;
         int nsb = nb - ks * MM_KS;
         nsb = nsb > MM_KS ? MM_KS : nsb;
         if (!failed && !skn_mbar_wait(&full[stg], par)) {
@@ -268,9 +292,9 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
         for (int hh = 0; hh < SPW; ++hh) {
             const int sb = warp + W * hh;
             if (sb >= nsb) break;
-            const uint8_t *ba = st + g * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES;
-            const uint8_t *bb = ba + 8 * MM_ROW_STRIDE;
-            const uint4 ha = *reinterpret_cast<const uint4 *>(ba), hb = *reinterpret_cast<const uint4 *>(bb);
+            const uint32_t ba = st + g * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES;
+            const uint32_t bb = ba + 8 * MM_ROW_STRIDE;
+            const uint4 ha = mm_lds128(ba), hb = mm_lds128(bb);
             const int sbi = ks * MM_KS + sb;
             // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
             const uint32_t sa[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u)};
@@ -280,34 +304,44 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
             for (int ap = 0; ap < NP; ++ap)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) lo[ap][c] = hi[ap][c] = 0;
-            const uint8_t *bsrc[NP];
+            uint32_t bsrc[NP];
             bool bon[NP];
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
                 bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig + ((size_t)(bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (size_t)sbi * 256 + 8 * t;
+                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + sbi * 256 + 8 * t);
             }
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const uint2 wa = *reinterpret_cast<const uint2 *>(ba + 16 + 32 * p + 8 * t);
-                const uint2 wb = *reinterpret_cast<const uint2 *>(bb + 16 + 32 * p + 8 * t);
-                const int s0a = mm_byte_i(sa[p >> 1], 2 * (p & 1)), s1a = mm_byte_i(sa[p >> 1], 2 * (p & 1) + 1);
-                const int s0b = mm_byte_i(sq[p >> 1], 2 * (p & 1)), s1b = mm_byte_i(sq[p >> 1], 2 * (p & 1) + 1);
+            // The MMAs of byte pair p + 1 are issued before the results of pair p are consumed, so
+            // that their latency overlaps the integer multiply-adds.
+            int cl[2][NP][4], ch[2][NP][4];
+            auto issue_pair = [&](int p, int buf) {
+                const uint2 wa = mm_lds64(ba + 16 + 32 * p + 8 * t);
+                const uint2 wb = mm_lds64(bb + 16 + 32 * p + 8 * t);
                 const uint32_t al0 = wa.x & 0x0F0F0F0Fu, al1 = wb.x & 0x0F0F0F0Fu, al2 = wa.y & 0x0F0F0F0Fu, al3 = wb.y & 0x0F0F0F0Fu;
                 const uint32_t ah0 = wa.x & 0xF0F0F0F0u, ah1 = wb.x & 0xF0F0F0F0u, ah2 = wa.y & 0xF0F0F0F0u, ah3 = wb.y & 0xF0F0F0F0u;
 #pragma unroll
                 for (int ap = 0; ap < NP; ++ap) {
                     uint2 b0 = make_uint2(0u, 0u), b1 = make_uint2(0u, 0u);
                     if (bon[ap]) {
-                        b0 = *reinterpret_cast<const uint2 *>(bsrc[ap] + (2 * p) * 32);
-                        b1 = *reinterpret_cast<const uint2 *>(bsrc[ap] + (2 * p + 1) * 32);
+                        b0 = mm_lds64(bsrc[ap] + (2 * p) * 32);
+                        b1 = mm_lds64(bsrc[ap] + (2 * p + 1) * 32);
                     }
-                    int cl[4], ch[4];
-                    skn_mma_u8s8(cl, al0, al1, al2, al3, b0.x, b0.y);
-                    skn_mma_u8s8(ch, ah0, ah1, ah2, ah3, b1.x, b1.y);
-                    lo[ap][0] += s0a * cl[0]; lo[ap][1] += s0a * cl[1]; lo[ap][2] += s0b * cl[2]; lo[ap][3] += s0b * cl[3];
-                    hi[ap][0] += s1a * ch[0]; hi[ap][1] += s1a * ch[1]; hi[ap][2] += s1b * ch[2]; hi[ap][3] += s1b * ch[3];
+                    skn_mma_u8s8(cl[buf][ap], al0, al1, al2, al3, b0.x, b0.y);
+                    skn_mma_u8s8(ch[buf][ap], ah0, ah1, ah2, ah3, b1.x, b1.y);
+                }
+            };
+            issue_pair(0, 0);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                if (p < 3) issue_pair(p + 1, (p + 1) & 1);
+                const int s0a = mm_byte_i(sa[p >> 1], 2 * (p & 1)), s1a = mm_byte_i(sa[p >> 1], 2 * (p & 1) + 1);
+                const int s0b = mm_byte_i(sq[p >> 1], 2 * (p & 1)), s1b = mm_byte_i(sq[p >> 1], 2 * (p & 1) + 1);
+#pragma unroll
+                for (int ap = 0; ap < NP; ++ap) {
+                    const int *c = cl[p & 1][ap], *h = ch[p & 1][ap];
+                    lo[ap][0] += s0a * c[0]; lo[ap][1] += s0a * c[1]; lo[ap][2] += s0b * c[2]; lo[ap][3] += s0b * c[3];
+                    hi[ap][0] += s1a * h[0]; hi[ap][1] += s1a * h[1]; hi[ap][2] += s1b * h[2]; hi[ap][3] += s1b * h[3];
                 }
             }
             // 16 * sum_j sc_j dot_j per digit column (high-nibble results carry a factor 16), scaled
@@ -317,7 +351,8 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
-                const float sgA = sgrp[(size_t)ra * nbp + sbi] * 0.0625f, sgB = sgrp[(size_t)rb * nbp + sbi] * 0.0625f;
+                const float sgA = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sbi)) * 0.0625f;
+                const float sgB = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sbi)) * 0.0625f;
                 accA[ap][0] = fmaf(da.x * sgA, (float)(lo[ap][0] * 16 + hi[ap][0]), accA[ap][0]);
                 accB[ap][0] = fmaf(da.x * sgB, (float)(lo[ap][1] * 16 + hi[ap][1]), accB[ap][0]);
                 accA[ap][1] = fmaf(db.x * sgA, (float)(lo[ap][2] * 16 + hi[ap][2]), accA[ap][1]);
@@ -331,7 +366,7 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
 #pragma unroll
             for (int a = 0; a < NAMAX; ++a) {
                 if (a < NA) {
-                    const float4 xs = *reinterpret_cast<const float4 *>(xsum + ((size_t)a * nb + sbi) * 8 + 4 * (t >> 1));
+                    const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nb + sbi) * 8 + 4 * (t >> 1)));
                     float m = m0 * xs.x;
                     m = fmaf(m1, xs.y, m);
                     m = fmaf(m2, xs.z, m);
