@@ -35,6 +35,7 @@ struct skn_kvcache {
 
 constexpr int ATT_CHUNK = 256;   // cached tokens per CTA (64 when the grid would otherwise leave SMs idle)
 constexpr int ATT_WARPS = 4;
+constexpr int ATT_MERGE_MAX_SPLITS = 64;   // most splits the in-kernel merge handles (its weights reuse the score buffer)
 
 static bool kv_ok(const skn_kvcache *kv) { return kv && kv->magic == SKN_MAGIC_KV && skn_ctx_ok(kv->ctx); }
 
@@ -395,18 +396,29 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) {
-        const int g = i / D, d = i % D;
+    // weights of the splits once per (head, split), reusing the score buffer: w = exp(max_s - max) / sum
+    float *s_w = &s_sc[0][0];                       // CHUNK * G floats >= G * ns (the launcher admits ns <= min(CHUNK, ATT_MERGE_MAX_SPLITS))
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
         const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2);
         float m = -INFINITY;
         for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(rec + (size_t)s * (D + 2)));
-        float l = 0.f, a = 0.f;
+        float l = 0.f;
         for (int s = 0; s < ns; ++s) {
             const float w = expf(__ldcg(rec + (size_t)s * (D + 2)) - m);
+            s_w[g * ns + s] = w;
             l = fmaf(__ldcg(rec + (size_t)s * (D + 2) + 1), w, l);
-            a = fmaf(__ldcg(rec + (size_t)s * (D + 2) + 2 + d), w, a);
         }
-        out[((size_t)bq * Hq + kvh * G + g) * D + d] = a / l;
+        const float inv = 1.f / l;
+        for (int s = 0; s < ns; ++s) s_w[g * ns + s] *= inv;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) {
+        const int g = i / D, d = i % D;
+        const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2) + 2 + d;
+        float a = 0.f;
+        for (int s = 0; s < ns; ++s) a = fmaf(__ldcg(rec + (size_t)s * (D + 2)), s_w[g * ns + s], a);
+        out[((size_t)bq * Hq + kvh * G + g) * D + d] = a;
     }
     if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
@@ -441,8 +453,11 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     // sequences without any cached token are left to the merge kernel (it writes their zeros)
     // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
     const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
-    unsigned *tickets = (tq == 1 && small_grid) ? kv->d_tickets : nullptr;
-    if (chunk == 64)
+    unsigned *tickets = (tq == 1 && small_grid && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
+    if (chunk == 32)
+        skn_attn_split_kernel<D, G, TT, 32><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+                                                                                kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
+    else if (chunk == 64)
         skn_attn_split_kernel<D, G, TT, 64><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
                                                                                 kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else
@@ -458,9 +473,19 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
 // 64-token chunks when 256-token chunks would give fewer CTAs than two per SM (short contexts,
 // small batches) and the partials of the finer split fit `scratch_cap` bytes
 static int attn_pick_chunk(const skn_kvcache *kv, int n_q_heads, int tq, size_t scratch_cap) {
-    const int64_t ctas = (int64_t)kv->batch * tq * kv->n_kv_heads * ((kv->capacity + ATT_CHUNK - 1) / ATT_CHUNK);
-    const int64_t need64 = (int64_t)kv->batch * tq * n_q_heads * ((kv->capacity + 63) / 64) * (kv->head_dim + 2) * 4;
-    return (ctas < 2 * (int64_t)kv->ctx->sm_count && (size_t)need64 <= scratch_cap) ? 64 : ATT_CHUNK;
+    // finer splits while 256-token (then 64-token) chunks leave SMs idle (short contexts, small
+    // batches) and the partials of the finer split fit `scratch_cap` bytes
+    const int chunks[3] = {ATT_CHUNK, 64, 32};
+    int pick = ATT_CHUNK;
+    for (int i = 0; i < 3; ++i) {
+        const int c = chunks[i];
+        const int64_t S = (kv->capacity + c - 1) / c;
+        const int64_t need = (int64_t)kv->batch * tq * n_q_heads * S * (kv->head_dim + 2) * 4;
+        if ((size_t)need > scratch_cap) break;
+        pick = c;
+        if ((int64_t)kv->batch * tq * kv->n_kv_heads * S >= 2 * (int64_t)kv->ctx->sm_count) break;
+    }
+    return pick;
 }
 
 static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,

@@ -962,6 +962,10 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
     if ((w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
     const int maxa = skn_mma_max_acts(ctx, w[0]->type, tot, w[0]->n_cols);
     if (maxa < 1) return cudaErrorNotSupported;
+    // the 32-weight-block formats take this route from two activation rows on (a single row is as
+    // fast or faster on their CUDA-core streaming kernels)
+    static const int simple_min_m = env_int("SKN_MM_SIMPLE_MIN_M", 2);
+    if (w[0]->type != SKN_TYPE_Q4_K && M < simple_min_m) return cudaErrorNotSupported;
     const int launches = (M + maxa - 1) / maxa;
     const int64_t K = w[0]->n_cols;
     for (int i = 0, m0 = 0; i < launches; ++i) {

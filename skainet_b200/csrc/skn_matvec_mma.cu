@@ -33,11 +33,25 @@
 // sums per (row, super-chunk, warp) meet in shared memory and are added in a fixed order.
 #include "skn_mv_common.cuh"
 
-constexpr int MM_KS = 16;                       // super-blocks per K super-chunk (one row copy)
-constexpr int MM_BLOCK_BYTES = 144;
-constexpr int MM_ROW_STRIDE = MM_KS * MM_BLOCK_BYTES + 32;   // 2336 B = 584 words = 8 mod 32
-constexpr int MM_STAGE = 16 * MM_ROW_STRIDE;
+// Block formats of this kernel.  A "super-block" is 256 weights: one Q4_K block, or eight of the
+// 32-weight blocks of Q8_0 / Q4_0 (each with its own fp16 scale).  KS super-blocks (one bulk copy
+// per row) make a K super-chunk; rows are padded by 32 bytes in shared memory, which puts the
+// eight row groups of a fragment load on disjoint banks (row stride = 8 words mod 32).
+constexpr int MM_FMT_Q4K = 0, MM_FMT_Q80 = 1, MM_FMT_Q40 = 2;
+template <int FMT> struct MmFmt;
+template <> struct MmFmt<MM_FMT_Q4K> { static constexpr int KS = 16, SB_BYTES = 144; };
+template <> struct MmFmt<MM_FMT_Q80> { static constexpr int KS = 8, SB_BYTES = 272; };
+template <> struct MmFmt<MM_FMT_Q40> { static constexpr int KS = 16, SB_BYTES = 144; };
+static constexpr int mm_ks(int fmt) { return fmt == MM_FMT_Q80 ? 8 : 16; }
+static constexpr int mm_sb_bytes(int fmt) { return fmt == MM_FMT_Q80 ? 272 : 144; }
+static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + 32); }
 
+__device__ __forceinline__ void skn_mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 __device__ __forceinline__ void skn_mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
     asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -63,6 +77,17 @@ __device__ __forceinline__ uint4 mm_lds128(uint32_t a) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
+}
+__device__ __forceinline__ uint32_t mm_lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// fp16 at a 2-byte aligned shared address, widened
+__device__ __forceinline__ float mm_lds_half(uint32_t a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return __half2float(__ushort_as_half(v));
 }
 __device__ __forceinline__ float mm_lds32f(uint32_t a) {
     float v;
@@ -129,11 +154,14 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
 //
 // Several activation rows per launch: one MMA serves TWO rows (digit columns 0..2 and 3..5 of the
 // B operand), NP such pairs share the A fragments, block headers and scale decoding.
-template <int SPW, int NP>                      // super-blocks of a tile per compute warp (W = 16 / SPW warps); row pairs
-__global__ void __launch_bounds__(SPW == 1 ? 544 : (SPW == 2 ? 320 : 256), (SPW == 1 || NP > 1) ? 1 : 2)
-skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
-                   int32_t *__restrict__ status, int relaxed) {
-    constexpr int W = 16 / SPW;
+template <int FMT, int SPW, int NP>             // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs
+__global__ void __launch_bounds__(MmFmt<FMT>::KS / SPW == 16 ? 544 : (MmFmt<FMT>::KS / SPW == 8 ? 320 : 256),
+                                  (MmFmt<FMT>::KS / SPW == 16 || NP > 1) ? 1 : 2)
+skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
+               int32_t *__restrict__ status, int relaxed) {
+    constexpr int MM_KS = MmFmt<FMT>::KS, MM_BLOCK_BYTES = MmFmt<FMT>::SB_BYTES;
+    constexpr int MM_ROW_STRIDE = MM_KS * MM_BLOCK_BYTES + 32, MM_STAGE = 16 * MM_ROW_STRIDE;
+    constexpr int W = MM_KS / SPW;
     constexpr int NAMAX = 2 * NP;
     const int64_t N = grp.n_end[grp.count - 1];
     const int NA = grp.n_act;                   // 1 .. NAMAX activation rows
@@ -294,6 +322,7 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
             if (sb >= nsb) break;
             const uint32_t ba = st + g * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES;
             const uint32_t bb = ba + 8 * MM_ROW_STRIDE;
+            if constexpr (FMT == MM_FMT_Q4K) {
             const uint4 ha = mm_lds128(ba), hb = mm_lds128(bb);
             const int sbi = ks * MM_KS + sb;
             // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
@@ -374,6 +403,96 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
                     ms[a] = fmaf(dmin, m, ms[a]);
                 }
             }
+            } else {
+            const int sbi = ks * MM_KS + sb;
+            uint32_t bsrc[NP];
+            bool bon[NP];
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int arow = 2 * ap + bcol_row;
+                bon[ap] = g < 6 && arow < NA;
+                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + sbi * 256) +
+                           (FMT == MM_FMT_Q80 ? 8 * t : 4 * t);
+            }
+            float sgA[NP], sgB[NP];
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
+                sgA[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sbi));
+                sgB[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sbi));
+            }
+            // eight 32-weight blocks, one MMA each; block j of a row starts 2-byte aligned, its
+            // quants are word aligned for odd j and two bytes off for even j
+            constexpr int BB = MM_BLOCK_BYTES / 8;          // 34 (Q8_0) or 18 (Q4_0)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t a0, a1, a2, a3;                    // rows g / g+8, k 0..15 / 16..31 of the fragment
+                const float d_a = mm_lds_half(ba + BB * j), d_b = mm_lds_half(bb + BB * j);
+                if constexpr (FMT == MM_FMT_Q80) {
+                    // lane t: quant bytes 8t .. 8t+7 of the block
+                    const uint32_t oa = ba + BB * j + 2 + 8 * t, ob = bb + BB * j + 2 + 8 * t;
+                    if (j & 1) {
+                        a0 = mm_lds32(oa); a2 = mm_lds32(oa + 4);
+                        a1 = mm_lds32(ob); a3 = mm_lds32(ob + 4);
+                    } else {
+                        const uint32_t u0 = mm_lds32(oa - 2), u1 = mm_lds32(oa + 2), u2 = mm_lds32(oa + 6);
+                        const uint32_t v0 = mm_lds32(ob - 2), v1 = mm_lds32(ob + 2), v2 = mm_lds32(ob + 6);
+                        a0 = __byte_perm(u0, u1, 0x5432); a2 = __byte_perm(u1, u2, 0x5432);
+                        a1 = __byte_perm(v0, v1, 0x5432); a3 = __byte_perm(v1, v2, 0x5432);
+                    }
+                } else {
+                    // lane t: quant bytes 4t .. 4t+3: low nibbles = weights 4t.., high nibbles = weights 16 + 4t..
+                    const uint32_t oa = ba + BB * j + 2 + 4 * t, ob = bb + BB * j + 2 + 4 * t;
+                    uint32_t wa, wb;
+                    if (j & 1) {
+                        wa = mm_lds32(oa); wb = mm_lds32(ob);
+                    } else {
+                        wa = __byte_perm(mm_lds32(oa - 2), mm_lds32(oa + 2), 0x5432);
+                        wb = __byte_perm(mm_lds32(ob - 2), mm_lds32(ob + 2), 0x5432);
+                    }
+                    a0 = wa & 0x0F0F0F0Fu; a2 = (wa >> 4) & 0x0F0F0F0Fu;
+                    a1 = wb & 0x0F0F0F0Fu; a3 = (wb >> 4) & 0x0F0F0F0Fu;
+                }
+#pragma unroll
+                for (int ap = 0; ap < NP; ++ap) {
+                    uint32_t b0 = 0u, b1 = 0u;
+                    if (bon[ap]) {
+                        if constexpr (FMT == MM_FMT_Q80) {
+                            const uint2 b = mm_lds64(bsrc[ap] + j * 32);
+                            b0 = b.x; b1 = b.y;
+                        } else {
+                            b0 = mm_lds32(bsrc[ap] + j * 32);
+                            b1 = mm_lds32(bsrc[ap] + j * 32 + 16);
+                        }
+                    }
+                    int c[4];
+                    if constexpr (FMT == MM_FMT_Q80) skn_mma_s8s8(c, a0, a1, a2, a3, b0, b1);
+                    else skn_mma_u8s8(c, a0, a1, a2, a3, b0, b1);
+                    accA[ap][0] = fmaf(d_a * sgA[ap], (float)c[0], accA[ap][0]);
+                    accB[ap][0] = fmaf(d_a * sgB[ap], (float)c[1], accB[ap][0]);
+                    accA[ap][1] = fmaf(d_b * sgA[ap], (float)c[2], accA[ap][1]);
+                    accB[ap][1] = fmaf(d_b * sgB[ap], (float)c[3], accB[ap][1]);
+                }
+            }
+            if constexpr (FMT == MM_FMT_Q40) {
+                // offset term 8 * d * sum(x) per block: this lane covers one weight row and four blocks
+                const uint32_t hrow = (t & 1) ? bb : ba;
+                const int j0 = 4 * (t >> 1);
+                const float d0 = mm_lds_half(hrow + BB * j0), d1 = mm_lds_half(hrow + BB * (j0 + 1));
+                const float d2 = mm_lds_half(hrow + BB * (j0 + 2)), d3 = mm_lds_half(hrow + BB * (j0 + 3));
+#pragma unroll
+                for (int a = 0; a < NAMAX; ++a) {
+                    if (a < NA) {
+                        const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nb + sbi) * 8 + j0));
+                        float m = d0 * xs.x;
+                        m = fmaf(d1, xs.y, m);
+                        m = fmaf(d2, xs.z, m);
+                        m = fmaf(d3, xs.w, m);
+                        ms[a] = fmaf(8.f, m, ms[a]);
+                    }
+                }
+            }
+            }
         }
         __syncwarp();      // every lane has read its share of the stage
         if (lane == 0) skn_mbar_arrive(&empty[stg]);
@@ -450,9 +569,21 @@ skn_matvec_q4k_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const 
 // computes.
 typedef void (*mm_kernel_t)(const skn_mv_group, int64_t, int, int, const float *, int32_t *, int);
 
-static mm_kernel_t mm_kernel(int warps, int n_act) {
-    if (n_act > 2) return skn_matvec_q4k_mma<2, 2>;
-    return warps == 16 ? skn_matvec_q4k_mma<1, 1> : (warps == 8 ? skn_matvec_q4k_mma<2, 1> : skn_matvec_q4k_mma<4, 1>);
+static int mm_fmt_of(int32_t type) {
+    switch (type) {
+    case SKN_TYPE_Q4_K: return MM_FMT_Q4K;
+    case SKN_TYPE_Q8_0: return MM_FMT_Q80;
+    case SKN_TYPE_Q4_0: return MM_FMT_Q40;
+    default: return -1;
+    }
+}
+
+static mm_kernel_t mm_kernel(int fmt, int warps, int n_act) {
+    if (fmt == MM_FMT_Q80) return n_act > 2 ? skn_matvec_mma<MM_FMT_Q80, 1, 2> : skn_matvec_mma<MM_FMT_Q80, 1, 1>;
+    if (fmt == MM_FMT_Q40) return n_act > 2 ? skn_matvec_mma<MM_FMT_Q40, 2, 2> : skn_matvec_mma<MM_FMT_Q40, 2, 1>;
+    if (n_act > 2) return skn_matvec_mma<MM_FMT_Q4K, 2, 2>;
+    return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1>
+                       : (warps == 8 ? skn_matvec_mma<MM_FMT_Q4K, 2, 1> : skn_matvec_mma<MM_FMT_Q4K, 4, 1>);
 }
 
 static size_t mm_fixed_smem(int nb, int n_act, int64_t rows_max, int nks, int warps) {
@@ -462,21 +593,23 @@ static size_t mm_fixed_smem(int nb, int n_act, int64_t rows_max, int nks, int wa
 
 // most activation rows one launch can take for this shape (the digit planes and partial sums of
 // every row sit in shared memory next to at least two ring stages)
-static int mm_max_acts(const skn_ctx *ctx, int64_t n_rows, int64_t n_cols) {
+static int mm_max_acts(const skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols) {
     const int nb = (int)(n_cols / 256);
     int64_t grid = ctx->sm_count;
     if (grid > n_rows) grid = n_rows;
     const int64_t rows_max = (n_rows + grid - 1) / grid + 2;
     for (int a = 4; a > 1; --a)
-        if (mm_fixed_smem(nb, a, rows_max, (nb + MM_KS - 1) / MM_KS, 8) + 2 * (MM_STAGE + 16) <= 200 * 1024) return a;
+        if (mm_fixed_smem(nb, a, rows_max, (nb + mm_ks(fmt) - 1) / mm_ks(fmt), 8) + 2 * (size_t)(mm_stage_bytes(fmt) + 16) <= 200 * 1024)
+            return a;
     return 1;
 }
 
-static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, int n_act, skn_mv_plan &pl, bool relaxed) {
+static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols, int n_act, skn_mv_plan &pl, bool relaxed) {
     pl = skn_mv_plan{-1, 0, 0, 0, 0, 0};
     if (n_cols % 256 || n_cols > (1 << 18) || n_rows < 1 || n_act < 1 || n_act > 4) return cudaSuccess;
     const int nb = (int)(n_cols / 256);
-    const int nks = (nb + MM_KS - 1) / MM_KS;
+    const int nks = (nb + mm_ks(fmt) - 1) / mm_ks(fmt);
+    const size_t stage = (size_t)mm_stage_bytes(fmt) + 16;
     int64_t grid = ctx->sm_count;
     if (grid > n_rows) grid = n_rows;
     const int64_t rows_max = (n_rows + grid - 1) / grid + 2;      // + 2: interleaved launches round to even boundaries
@@ -486,23 +619,23 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, int n_a
     static const int budget_env = env_int("SKN_MM_SMEM_KB", 0);
     int warps = warps_env > 0 ? warps_env : 8;
     warps = warps >= 16 ? 16 : (warps >= 8 ? 8 : 4);
-    if (n_act > 2) warps = 8;
+    if (n_act > 2 || fmt != MM_FMT_Q4K) warps = 8;
     (void)relaxed;
     // few tiles: half an SM, so that the next launch's CTA is resident early; many tiles: a deeper
     // ring matters more than the neighbour
     const size_t budget = (size_t)(budget_env > 0 ? budget_env : (ntiles >= 6 ? 200 : 110)) * 1024;
     const size_t fixed = mm_fixed_smem(nb, n_act, rows_max, nks, warps);
     int nst = nst_env > 0 ? nst_env : (ntiles < 4 ? ntiles : 4);
-    while (nst > 1 && fixed + (size_t)nst * (MM_STAGE + 16) > budget) --nst;
+    while (nst > 1 && fixed + (size_t)nst * stage > budget) --nst;
     if (nst < 2 && ntiles > 1 && budget_env <= 0) {
         // long rows or several activation rows: the digit planes leave no room for two stages in
         // half an SM; take all of it
         nst = ntiles < 4 ? ntiles : 4;
-        while (nst > 1 && fixed + (size_t)nst * (MM_STAGE + 16) > 200 * 1024) --nst;
+        while (nst > 1 && fixed + (size_t)nst * stage > 200 * 1024) --nst;
     }
-    const size_t smem = fixed + (size_t)nst * (MM_STAGE + 16);
+    const size_t smem = fixed + (size_t)nst * stage;
     if (smem > 220 * 1024) return cudaSuccess;
-    mm_kernel_t kern = mm_kernel(warps, n_act);
+    mm_kernel_t kern = mm_kernel(fmt, warps, n_act);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
     // all of the SM's L1 / shared memory as shared memory, so that two CTAs (consecutive launches) fit
@@ -514,7 +647,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int64_t n_rows, int64_t n_cols, int n_a
     return cudaSuccess;
 }
 
-// y[t][a] = W[t] . f(x[a]) (+ add[t]) for n <= 3 Q4_K tensors of one K and pitch and n_act <= 4
+// y[t][a] = W[t] . f(x[a]) (+ add[t]) for n <= 3 Q4_K / Q8_0 / Q4_0 tensors of one type, K and pitch and n_act <= 4
 // activation rows (x rows K apart, outputs n_rows apart; add_per_act: add vectors n_rows apart,
 // otherwise one bias for all rows).  Returns false when the shapes are not covered (nothing launched).
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
@@ -522,7 +655,8 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
                        cudaStream_t stream, cudaError_t &err, bool swiglu, int n_act, bool add_per_act) {
     static const int enabled = env_int("SKN_MM", 1);
     err = cudaSuccess;
-    if (!enabled || w[0]->type != SKN_TYPE_Q4_K) return false;
+    const int fmt = mm_fmt_of(w[0]->type);
+    if (!enabled || fmt < 0) return false;
     if (swiglu && (n != 2 || w[0]->n_rows != w[1]->n_rows)) return false;
     skn_mv_group grp = {};
     grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
@@ -537,7 +671,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     }
     for (int t = n; t < 3; ++t) grp.n_end[t] = tot;
     grp.count = n;
-    if (n_act < 1 || n_act > mm_max_acts(ctx, tot, w[0]->n_cols)) return false;
+    if (n_act < 1 || n_act > mm_max_acts(ctx, fmt, tot, w[0]->n_cols)) return false;
     skn_mv_plan pl = skn_mv_plan{0, 0, 0, 0, 0, 0};
     const int32_t key_type = 1000 + 16 * n_act + w[0]->type;       // distinct from the CUDA-core kernels' plans
     for (int i = 0; i < ctx->n_group_plans; ++i) {
@@ -545,7 +679,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
         if (c.type == key_type && c.rows == tot && c.cols == w[0]->n_cols && c.relaxed == ctx->relaxed_order) { pl = c.pl; break; }
     }
     if (pl.state == 0) {
-        err = mm_plan(ctx, tot, w[0]->n_cols, n_act, pl, ctx->relaxed_order != 0);
+        err = mm_plan(ctx, fmt, tot, w[0]->n_cols, n_act, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) return true;
         if (ctx->n_group_plans < 32)
             ctx->group_plans[ctx->n_group_plans++] = skn_group_plan{key_type, ctx->relaxed_order, tot, w[0]->n_cols, pl};
@@ -562,13 +696,14 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    err = cudaLaunchKernelEx(&cfg, mm_kernel(pl.nch, n_act), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
+    err = cudaLaunchKernelEx(&cfg, mm_kernel(fmt, pl.nch, n_act), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
                              ctx->relaxed_order);
     return true;
 }
 
 int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols) {
     static const int enabled = env_int("SKN_MM", 1);
-    if (!enabled || type != SKN_TYPE_Q4_K || n_cols % 256 || n_cols > (1 << 18) || n_rows_total < 1) return 0;
-    return mm_max_acts(ctx, n_rows_total, n_cols);
+    const int fmt = mm_fmt_of(type);
+    if (!enabled || fmt < 0 || n_cols % 256 || n_cols > (1 << 18) || n_rows_total < 1) return 0;
+    return mm_max_acts(ctx, fmt, n_rows_total, n_cols);
 }
