@@ -938,7 +938,10 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
         same = w[t]->type == w[0]->type && w[t]->n_cols == w[0]->n_cols && w[t]->pitch == w[0]->pitch;
     if (!same || (w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
     cudaError_t err = cudaSuccess;
-    if (skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
+    // a single activation row: Q4_K on the tensor-core kernel, the 32-weight-block formats on
+    // their CUDA-core streaming kernels (the same routes skn_launch_matvec takes, so grouped and
+    // separate launches give identical bits)
+    if (w[0]->type == SKN_TYPE_Q4_K && skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
     bool took = false;
     switch (w[0]->type) {
     case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;

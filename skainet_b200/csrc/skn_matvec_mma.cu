@@ -154,7 +154,8 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
 //
 // Several activation rows per launch: one MMA serves TWO rows (digit columns 0..2 and 3..5 of the
 // B operand), NP such pairs share the A fragments, block headers and scale decoding.
-template <int FMT, int SPW, int NP>             // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs
+template <int FMT, int SPW, int NP, bool ODD>   // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs;
+                                                // ODD: the last pair has one row only (its odd columns are skipped)
 __global__ void __launch_bounds__(MmFmt<FMT>::KS / SPW == 16 ? 544 : (MmFmt<FMT>::KS / SPW == 8 ? 320 : 256),
                                   (MmFmt<FMT>::KS / SPW == 16 || NP > 1) ? 1 : 2)
 skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
@@ -264,39 +265,59 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             }
         }
     }
-    // x -> digit planes: a warp takes whole super-blocks, two at a time (four loads in flight);
+    // x -> digit planes: a warp takes whole super-blocks, two at a time, and loads the next two
+    // before it digitises the current ones (eight loads in flight);
     // unit u = activation row u / nb, super-block u % nb
     {
         const int units = NA * nb;
-        for (int u = warp; u < units; u += 2 * W) {
+        auto fetch = [&](int u, float4 (&v)[4], int (&as)[2], int (&ss)[2]) {
             const int u2 = u + W;
-            const int a0 = u / nb, s0 = u - a0 * nb;
-            const int a1 = u2 < units ? u2 / nb : a0, s1 = u2 < units ? u2 - a1 * nb : s0;
-            skn_xform xf0{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a0 * K : nullptr, 1.f};
-            skn_xform xf1{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a1 * K : nullptr, 1.f};
 #pragma unroll
-            for (int a = 0; a < NAMAX; ++a) {
-                if (a == a0) xf0.scale = nscale[a];
-                if (a == a1) xf1.scale = nscale[a];
+            for (int h = 0; h < 2; ++h) {
+                const int uu = h ? u2 : u;
+                if (uu < units) {
+                    const int a = uu / nb, sbx = uu - a * nb;
+                    skn_xform xf{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f};
+#pragma unroll
+                    for (int k = 0; k < NAMAX; ++k)
+                        if (k == a) xf.scale = nscale[k];
+                    const float *xa = x + (size_t)a * K;
+                    v[2 * h] = skn_load_x4(xa, sbx * 64 + lane, xf);
+                    v[2 * h + 1] = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
+                    as[h] = a;
+                    ss[h] = sbx;
+                } else {
+                    as[h] = -1;
+                    ss[h] = 0;
+                }
             }
-            const float *x0 = x + (size_t)a0 * K, *x1 = x + (size_t)a1 * K;
-            const float4 p0 = skn_load_x4(x0, s0 * 64 + lane, xf0), p1 = skn_load_x4(x0, s0 * 64 + 32 + lane, xf0);
-            float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
-            if (u2 < units) {
-                q0 = skn_load_x4(x1, s1 * 64 + lane, xf1);
-                q1 = skn_load_x4(x1, s1 * 64 + 32 + lane, xf1);
+        };
+        float4 cur[4], nxt[4];
+        int ca[2], cs[2], na[2], ns2[2];
+        if (warp < units) fetch(warp, cur, ca, cs);
+        for (int u = warp; u < units; u += 2 * W) {
+            const bool more = u + 2 * W < units;
+            if (more) fetch(u + 2 * W, nxt, na, ns2);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (ca[h] >= 0)
+                    mm_digitize(cur[2 * h], cur[2 * h + 1], cs[h], lane, dig + (size_t)ca[h] * 3 * PL, PL, sgrp + (size_t)ca[h] * nbp,
+                                xsum + (size_t)ca[h] * nb * 8);
+            if (more) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
+                ca[0] = na[0]; ca[1] = na[1]; cs[0] = ns2[0]; cs[1] = ns2[1];
             }
-            mm_digitize(p0, p1, s0, lane, dig + (size_t)a0 * 3 * PL, PL, sgrp + (size_t)a0 * nbp, xsum + (size_t)a0 * nb * 8);
-            if (u2 < units)
-                mm_digitize(q0, q1, s1, lane, dig + (size_t)a1 * 3 * PL, PL, sgrp + (size_t)a1 * nbp, xsum + (size_t)a1 * nb * 8);
         }
     }
     mm_bar_sync(1, W * 32);
     MV_STAMP(3);
 
     // this lane's two B columns (2t, 2t + 1): column c of a row pair is digit c % 3 of its row c / 3
-    const int bcol_row = g / 3, bcol_dig = g - 3 * bcol_row;          // the column this lane LOADS (g < 6)
-    const int rowA = (t >= 2) ? 1 : 0, rowB = (t >= 1) ? 1 : 0;       // rows (within a pair) of the columns it READS BACK
+    // B column c of a row pair = digit c / 2 of its row c & 1 (c < 6): a lane LOADS column g and
+    // READS BACK columns 2t (first row of the pair) and 2t + 1 (second row), both of digit t
+    const int bcol_row = g & 1, bcol_dig = g >> 1;
+    constexpr int rowA = 0, rowB = 1;
     bool failed = false;
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
@@ -369,8 +390,12 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
                 for (int ap = 0; ap < NP; ++ap) {
                     const int *c = cl[p & 1][ap], *h = ch[p & 1][ap];
-                    lo[ap][0] += s0a * c[0]; lo[ap][1] += s0a * c[1]; lo[ap][2] += s0b * c[2]; lo[ap][3] += s0b * c[3];
-                    hi[ap][0] += s1a * h[0]; hi[ap][1] += s1a * h[1]; hi[ap][2] += s1b * h[2]; hi[ap][3] += s1b * h[3];
+                    lo[ap][0] += s0a * c[0]; lo[ap][2] += s0b * c[2];
+                    hi[ap][0] += s1a * h[0]; hi[ap][2] += s1b * h[2];
+                    if (!(ODD && ap == NP - 1)) {
+                        lo[ap][1] += s0a * c[1]; lo[ap][3] += s0b * c[3];
+                        hi[ap][1] += s1a * h[1]; hi[ap][3] += s1b * h[3];
+                    }
                 }
             }
             // 16 * sum_j sc_j dot_j per digit column (high-nibble results carry a factor 16), scaled
@@ -383,9 +408,11 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 const float sgA = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sbi)) * 0.0625f;
                 const float sgB = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sbi)) * 0.0625f;
                 accA[ap][0] = fmaf(da.x * sgA, (float)(lo[ap][0] * 16 + hi[ap][0]), accA[ap][0]);
-                accB[ap][0] = fmaf(da.x * sgB, (float)(lo[ap][1] * 16 + hi[ap][1]), accB[ap][0]);
                 accA[ap][1] = fmaf(db.x * sgA, (float)(lo[ap][2] * 16 + hi[ap][2]), accA[ap][1]);
-                accB[ap][1] = fmaf(db.x * sgB, (float)(lo[ap][3] * 16 + hi[ap][3]), accB[ap][1]);
+                if (!(ODD && ap == NP - 1)) {
+                    accB[ap][0] = fmaf(da.x * sgB, (float)(lo[ap][1] * 16 + hi[ap][1]), accB[ap][0]);
+                    accB[ap][1] = fmaf(db.x * sgB, (float)(lo[ap][3] * 16 + hi[ap][3]), accB[ap][1]);
+                }
             }
             // min term: this lane covers one weight row and four sub-blocks, every activation row
             const uint4 hm = (t & 1) ? hb : ha;
@@ -469,9 +496,11 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                     if constexpr (FMT == MM_FMT_Q80) skn_mma_s8s8(c, a0, a1, a2, a3, b0, b1);
                     else skn_mma_u8s8(c, a0, a1, a2, a3, b0, b1);
                     accA[ap][0] = fmaf(d_a * sgA[ap], (float)c[0], accA[ap][0]);
-                    accB[ap][0] = fmaf(d_a * sgB[ap], (float)c[1], accB[ap][0]);
                     accA[ap][1] = fmaf(d_b * sgA[ap], (float)c[2], accA[ap][1]);
-                    accB[ap][1] = fmaf(d_b * sgB[ap], (float)c[3], accB[ap][1]);
+                    if (!(ODD && ap == NP - 1)) {
+                        accB[ap][0] = fmaf(d_a * sgB[ap], (float)c[1], accB[ap][0]);
+                        accB[ap][1] = fmaf(d_b * sgB[ap], (float)c[3], accB[ap][1]);
+                    }
                 }
             }
             if constexpr (FMT == MM_FMT_Q40) {
@@ -496,15 +525,14 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
         }
         __syncwarp();      // every lane has read its share of the stage
         if (lane == 0) skn_mbar_arrive(&empty[stg]);
-        // ---- tile epilogue.  Columns of a pair: lane t = 0 holds (row 0 digit 0, row 0 digit 1),
-        // t = 1 (row 0 digit 2, row 1 digit 0), t = 2 (row 1 digit 1, row 1 digit 2), t = 3 nothing.
+        // ---- tile epilogue: lane t holds digit t of both rows of a pair (t = 3: nothing)
+        const float dw = (t == 0) ? 1.f : ((t == 1) ? 256.f : ((t == 2) ? 65536.f : 0.f));
 #pragma unroll
         for (int ap = 0; ap < NP; ++ap) {
 #pragma unroll
             for (int wr = 0; wr < 2; ++wr) {            // weight rows g, g + 8
-                const float A = accA[ap][wr], B = accB[ap][wr];
-                float e0 = (t == 0) ? fmaf(B, 256.f, A) : ((t == 1) ? A * 65536.f : 0.f);
-                float e1 = (t == 1) ? B : ((t == 2) ? fmaf(B, 65536.f, A * 256.f) : 0.f);
+                float e0 = (t < 3) ? accA[ap][wr] * dw : 0.f;
+                float e1 = (t < 3) ? accB[ap][wr] * dw : 0.f;
                 e0 += __shfl_xor_sync(0xffffffffu, e0, 1);
                 e1 += __shfl_xor_sync(0xffffffffu, e1, 1);
                 e0 += __shfl_xor_sync(0xffffffffu, e0, 2);
@@ -578,12 +606,21 @@ static int mm_fmt_of(int32_t type) {
     }
 }
 
+template <int FMT, int SPW>
+static mm_kernel_t mm_kernel_na(int n_act) {
+    switch (n_act) {
+    case 1: return skn_matvec_mma<FMT, SPW, 1, true>;
+    case 2: return skn_matvec_mma<FMT, SPW, 1, false>;
+    case 3: return skn_matvec_mma<FMT, SPW, 2, true>;
+    default: return skn_matvec_mma<FMT, SPW, 2, false>;
+    }
+}
+
 static mm_kernel_t mm_kernel(int fmt, int warps, int n_act) {
-    if (fmt == MM_FMT_Q80) return n_act > 2 ? skn_matvec_mma<MM_FMT_Q80, 1, 2> : skn_matvec_mma<MM_FMT_Q80, 1, 1>;
-    if (fmt == MM_FMT_Q40) return n_act > 2 ? skn_matvec_mma<MM_FMT_Q40, 2, 2> : skn_matvec_mma<MM_FMT_Q40, 2, 1>;
-    if (n_act > 2) return skn_matvec_mma<MM_FMT_Q4K, 2, 2>;
-    return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1>
-                       : (warps == 8 ? skn_matvec_mma<MM_FMT_Q4K, 2, 1> : skn_matvec_mma<MM_FMT_Q4K, 4, 1>);
+    if (fmt == MM_FMT_Q80) return mm_kernel_na<MM_FMT_Q80, 1>(n_act);
+    if (fmt == MM_FMT_Q40) return mm_kernel_na<MM_FMT_Q40, 2>(n_act);
+    if (n_act > 1 || warps == 8) return mm_kernel_na<MM_FMT_Q4K, 2>(n_act);
+    return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1, true> : skn_matvec_mma<MM_FMT_Q4K, 4, 1, true>;
 }
 
 static size_t mm_fixed_smem(int nb, int n_act, int64_t rows_max, int nks, int warps) {
@@ -619,7 +656,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols
     static const int budget_env = env_int("SKN_MM_SMEM_KB", 0);
     int warps = warps_env > 0 ? warps_env : 8;
     warps = warps >= 16 ? 16 : (warps >= 8 ? 8 : 4);
-    if (n_act > 2 || fmt != MM_FMT_Q4K) warps = 8;
+    if (n_act > 1 || fmt != MM_FMT_Q4K) warps = 8;
     (void)relaxed;
     // few tiles: half an SM, so that the next launch's CTA is resident early; many tiles: a deeper
     // ring matters more than the neighbour
