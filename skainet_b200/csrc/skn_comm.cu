@@ -70,7 +70,7 @@ __device__ __forceinline__ uint32_t *comm_flag(uint8_t *base, int buf, int src) 
 
 // out[i] = resid[i] + sum over ranks of partial_r[i]   (resid may be NULL, out may alias resid
 // or partial); n is a multiple of 4.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 skn_allreduce_push_kernel(comm_peers peers, int rank, int world, int64_t cap, uint32_t *__restrict__ state,
                           int32_t *__restrict__ status, const float *__restrict__ partial,
                           const float *__restrict__ resid, float *__restrict__ out, int64_t n) {
@@ -89,13 +89,17 @@ skn_allreduce_push_kernel(comm_peers peers, int rank, int world, int64_t cap, ui
         float4 *to = reinterpret_cast<float4 *>(comm_inbox(peers.base[dst], buf, world, rank, cap));
         for (int64_t i = tid; i < n4; i += nthr) to[i] = reinterpret_cast<const float4 *>(partial)[i];
     }
-    __threadfence_system();
+    // the CTA barrier orders every thread's peer stores before thread 0's system-wide fence
+    // (fences are cumulative), so one fence per CTA is enough
     __syncthreads();
     if (threadIdx.x == 0) {
-        s_last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
+        __threadfence_system();
+        s_last = gridDim.x == 1 || atomicAdd(&state[1], 1u) == gridDim.x - 1;
         if (s_last) {
-            state[1] = 0;
-            __threadfence_system();
+            if (gridDim.x > 1) {
+                state[1] = 0;
+                __threadfence_system();
+            }
             for (int p = 1; p < world; ++p) st_release_sys(comm_flag(peers.base[(rank + p) % world], buf, rank), q + 1);
         }
     }
@@ -130,10 +134,14 @@ skn_allreduce_push_kernel(comm_peers peers, int rank, int world, int64_t cap, ui
     __syncthreads();
     // the CTA that finishes last moves the counter on
     if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {
-            state[2] = 0;
+        if (gridDim.x == 1) {
             *reinterpret_cast<volatile uint32_t *>(state) = q + 1;
+        } else {
+            __threadfence();
+            if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {
+                state[2] = 0;
+                *reinterpret_cast<volatile uint32_t *>(state) = q + 1;
+            }
         }
     }
 }
@@ -281,9 +289,16 @@ int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *re
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     comm_peers peers;
     for (int i = 0; i < COMM_MAX_WORLD; ++i) peers.base[i] = c->peer[i];
+    // a decode-size vector: one CTA (no tickets, one fence); otherwise at most one CTA per SM, so
+    // that every CTA is resident while any of them waits
+    int threads = 256;
     int64_t blocks = (n / 4 + 255) / 256;
-    if (blocks > ctx->sm_count) blocks = ctx->sm_count;    // every CTA resident while any of them waits
-    skn_allreduce_push_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(peers, c->rank, c->world, c->capacity, c->d_state,
+    if (n <= 16384) {
+        blocks = 1;
+        threads = n / 4 >= 1024 ? 1024 : (int)((n / 4 + 31) / 32 * 32);
+    }
+    if (blocks > ctx->sm_count) blocks = ctx->sm_count;
+    skn_allreduce_push_kernel<<<(unsigned)blocks, threads, 0, ctx->stream>>>(peers, c->rank, c->world, c->capacity, c->d_state,
                                                                        ctx->d_status, partial_dev, resid_dev, out_dev, n);
     SKN_CUDA(ctx, cudaGetLastError());
     return SKN_OK;
