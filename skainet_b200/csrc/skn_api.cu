@@ -123,6 +123,7 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
         if (value < 0 || value > (1 << 30)) return skn_fail(ctx, SKN_ERR_ARG, "prefill threshold out of range");
         ctx->prefill_min_m = (int)value;
         return SKN_OK;
+    case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value ? 1 : 0; return SKN_OK;
     default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
     }
 }

@@ -30,9 +30,9 @@
 
 #define SKN_MAGIC_COMM 0x736b6e6du   // 'sknm'
 
-constexpr int COMM_NBUF = 2;
-constexpr int COMM_MAX_WORLD = 8;
-constexpr size_t COMM_FLAG_BYTES = 4096;
+constexpr int COMM_NBUF = SKN_COMM_NBUF;
+constexpr int COMM_MAX_WORLD = SKN_COMM_MAX_WORLD;
+constexpr size_t COMM_FLAG_BYTES = SKN_COMM_FLAG_BYTES;
 
 struct skn_comm {
     uint32_t magic;
@@ -51,6 +51,16 @@ struct comm_peers {
 };
 
 static bool comm_ok(const skn_comm *c) { return c && c->magic == SKN_MAGIC_COMM && skn_ctx_ok(c->ctx); }
+
+bool skn_comm_get_view(const skn_comm *c, skn_comm_view *v) {
+    if (!comm_ok(c) || !c->connected || !v) return false;
+    v->rank = c->rank;
+    v->world = c->world;
+    v->capacity = c->capacity;
+    for (int i = 0; i < COMM_MAX_WORLD; ++i) v->base[i] = c->peer[i];
+    v->state = c->d_state;
+    return true;
+}
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -36,6 +36,7 @@ struct skn_ctx {
     int sm_count;
     int relaxed_order;          // SKN_OPT_RELAXED_ORDER
     int prefill_min_m;          // SKN_OPT_PREFILL_MIN_M: batch size from which the tensor-core path runs
+    int fused_exchange;         // SKN_OPT_FUSED_EXCHANGE
     int32_t *d_status;          // device status word written by bounded waits
     int32_t *h_status;          // pinned mirror
     // staging for the host-pointer entry points (grown on demand)
@@ -94,7 +95,8 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 // integer tensor-core matvec (skn_matvec_mma.cu); false = shapes or type not covered
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err, bool swiglu = false, int n_act = 1, bool add_per_act = false);
+                       cudaStream_t stream, cudaError_t &err, bool swiglu = false, int n_act = 1, bool add_per_act = false,
+                       const struct skn_mv_exchange *xc = nullptr);
 // activation rows one tensor-core matvec launch can take for this tensor (0: not covered)
 int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols);
 // y[t][m] = W[t] . f(x[m]) (+ add) for M activation rows through the tensor-core matvec, in launches
@@ -102,7 +104,7 @@ int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int
 // x rows are K apart, outputs (and per-row add vectors) n_rows apart.
 cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
                                    const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
-                                   const float *silu_u, bool swiglu, cudaStream_t stream);
+                                   const float *silu_u, bool swiglu, cudaStream_t stream, const struct skn_mv_exchange *xc = nullptr);
 // h = silu(Wg . f(x)) * (Wu . f(x)) in one launch (f: optional RMSNorm); cudaErrorNotSupported when
 // the tensor-core matvec does not cover the tensors (nothing launched)
 cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,
@@ -140,3 +142,22 @@ int32_t skn_attn_causal_pending(skn_kvcache *kv, const float *q_dev, int32_t n_q
                                 float *out_dev);
 int32_t *skn_kv_len_dev(const skn_kvcache *kv);
 cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, cudaStream_t st);
+
+// inter-GPU exchange (skn_comm.cu): layout constants and the device-side view the matvec kernels
+// use to push partial products from their epilogue and to add them up while they prepare x
+constexpr int SKN_COMM_NBUF = 2;
+constexpr int SKN_COMM_MAX_WORLD = 8;
+constexpr size_t SKN_COMM_FLAG_BYTES = 4096;
+struct skn_comm_view {
+    int32_t rank, world;
+    int64_t capacity;                       // floats per (buffer, source rank)
+    uint8_t *base[SKN_COMM_MAX_WORLD];      // inbox of every rank as mapped on this device
+    uint32_t *state;                        // [0] exchanges completed, [1] push tickets, [2] finish tickets
+};
+bool skn_comm_get_view(const skn_comm *c, skn_comm_view *v);
+struct skn_mv_exchange {                    // optional argument of skn_launch_matvec_acts
+    skn_comm_view view;
+    bool push;                              // outputs are partial products: push them, y is not written
+    bool reduce;                            // x is the residual stream: add the partials pushed before
+    float *writeback;                       // reduce: the summed residual stream goes here (may be NULL)
+};

@@ -276,6 +276,20 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
         fell_back = (e == cudaErrorNotSupported);
         return fell_back ? cudaSuccess : e;
     };
+    // residual stream: m->x, or alternately m->x / m->h while exchanges are fused into the matvecs
+    float *xcur = m->x, *xalt = m->h;
+    bool pending = false;
+    skn_comm_view xview = {};
+    bool fusedx = tp && fold && ctx->fused_exchange && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
+    if (fusedx) {
+        // only when every layer takes the multi-row tensor-core path (a pending exchange is consumed
+        // by the next layer's first projection)
+        for (auto &l : m->layers)
+            fusedx = fusedx && small && skn_mma_max_acts(ctx, l.wq->type, 2 * kd + qd, d) > 0 && l.wk->type == l.wq->type &&
+                     l.wv->type == l.wq->type && l.wq->pitch == l.wk->pitch && l.wq->pitch == l.wv->pitch &&
+                     skn_mma_max_acts(ctx, l.wo->type, d, qd) > 0 && skn_mma_max_acts(ctx, l.wg->type, 2 * F, d) > 0 &&
+                     l.wu->type == l.wg->type && l.wu->pitch == l.wg->pitch && skn_mma_max_acts(ctx, l.wd->type, d, F) > 0;
+    }
     for (auto &l : m->layers) {
         // Decode-size batches whose projections the tensor-core matvec covers: every product takes
         // all M activation rows (a few rows per launch, the weights of the later launches come
@@ -286,44 +300,65 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
             skn_mma_max_acts(ctx, l.wg->type, 2 * F, d) > 0 && l.wu->type == l.wg->type && l.wu->pitch == l.wg->pitch &&
             skn_mma_max_acts(ctx, l.wd->type, d, F) > 0;
         if (rows_path) {
-            const float *src = m->x;
+            // Tensor parallelism with one or two rows: the K-sharded projections push their partial
+            // products into every rank's inbox from their epilogue, and the next projection adds
+            // them to the residual stream while it prepares x (no exchange launch); the summed
+            // stream alternates between two buffers (xcur is read, xalt written by CTA 0).
+            skn_mv_exchange xpush = {}, xred = {};
+            if (fusedx) {
+                xpush.view = xview; xpush.push = true;
+                xred.view = xview; xred.reduce = true;
+            }
+            const bool last_layer = (&l == &m->layers.back());
+            const float *src = xcur;
             if (!fold) {
-                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.attn_norm, m->h, M, d, m->rms_eps, st));
+                SKN_CUDA(ctx, skn_launch_rmsnorm(xcur, l.attn_norm, m->h, M, d, m->rms_eps, st));
                 src = m->h;
             }
             {
                 const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
                 float *ys[3] = {m->q, m->k, m->v};
+                xred.writeback = xalt;
                 SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 3, ws, src, M, ys, nullptr, false, fold ? l.attn_norm : nullptr, m->rms_eps,
-                                                     nullptr, false, st));
+                                                     nullptr, false, st, pending ? &xred : nullptr));
+                if (pending) { float *tmp = xcur; xcur = xalt; xalt = tmp; pending = false; }
             }
             if ((rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
             if ((rc = skn_attn_causal_pending(l.kv, m->q, Hq, T, scale, m->att))) return rc;
             {
                 const skn_tensor *ws[1] = {l.wo};
-                float *ys[1] = {tp ? m->proj : m->x};
-                const float *as[1] = {tp ? nullptr : m->x};
-                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->att, M, ys, as, true, nullptr, 0.f, nullptr, false, st));
+                float *ys[1] = {tp ? m->proj : xcur};
+                const float *as[1] = {tp ? nullptr : xcur};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->att, M, ys, as, true, nullptr, 0.f, nullptr, false, st,
+                                                     fusedx ? &xpush : nullptr));
+                if (fusedx) pending = true;
+                else if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, xcur, xcur, (int64_t)M * d))) return rc;
             }
-            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
-            src = m->x;
+            src = xcur;
             if (!fold) {
-                SKN_CUDA(ctx, skn_launch_rmsnorm(m->x, l.ffn_norm, m->h, M, d, m->rms_eps, st));
+                SKN_CUDA(ctx, skn_launch_rmsnorm(xcur, l.ffn_norm, m->h, M, d, m->rms_eps, st));
                 src = m->h;
             }
             {
                 const skn_tensor *ws[2] = {l.wg, l.wu};
                 float *ys[2] = {m->ffn_g, m->ffn_g};
+                xred.writeback = xalt;
                 SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 2, ws, src, M, ys, nullptr, false, fold ? l.ffn_norm : nullptr, m->rms_eps,
-                                                     nullptr, true, st));
+                                                     nullptr, true, st, pending ? &xred : nullptr));
+                if (pending) { float *tmp = xcur; xcur = xalt; xalt = tmp; pending = false; }
             }
             {
+                // the last layer's partial sums meet in the exchange kernel: the LM head that follows
+                // need not be a tensor-core matvec
+                const bool fuse_down = fusedx && !last_layer;
                 const skn_tensor *ws[1] = {l.wd};
-                float *ys[1] = {tp ? m->proj : m->x};
-                const float *as[1] = {tp ? nullptr : m->x};
-                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->ffn_g, M, ys, as, true, nullptr, 0.f, nullptr, false, st));
+                float *ys[1] = {tp ? m->proj : xcur};
+                const float *as[1] = {tp ? nullptr : xcur};
+                SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 1, ws, m->ffn_g, M, ys, as, true, nullptr, 0.f, nullptr, false, st,
+                                                     fuse_down ? &xpush : nullptr));
+                if (fuse_down) pending = true;
+                else if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, xcur, xcur, (int64_t)M * d))) return rc;
             }
-            if (tp && (rc = skn_allreduce_dev(m->comm, m->proj, m->x, m->x, (int64_t)M * d))) return rc;
             continue;
         }
         if (small) {
@@ -428,10 +463,10 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     for (int b = 0; b < B && !fb; ++b) {
         const skn_tensor *ws[1] = {m->output};
         float *ys[1] = {m->logits + (int64_t)b * m->vocab_l};
-        SKN_CUDA(ctx, fused(1, ws, m->x + ((int64_t)b * T + (T - 1)) * d, ys, nullptr, m->out_norm, nullptr, fb));
+        SKN_CUDA(ctx, fused(1, ws, xcur + ((int64_t)b * T + (T - 1)) * d, ys, nullptr, m->out_norm, nullptr, fb));
     }
     if (fb) {
-        SKN_CUDA(ctx, skn_launch_last_rows(m->x, m->last, B, T, d, st));
+        SKN_CUDA(ctx, skn_launch_last_rows(xcur, m->last, B, T, d, st));
         SKN_CUDA(ctx, skn_launch_rmsnorm(m->last, m->out_norm, m->h, B, d, m->rms_eps, st));
         if ((rc = skn_matmul_dev(ctx, m->output, m->h, B, d, nullptr, m->logits))) return rc;
     }

@@ -955,7 +955,7 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 
 cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
                                    const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
-                                   const float *silu_u, bool swiglu, cudaStream_t stream) {
+                                   const float *silu_u, bool swiglu, cudaStream_t stream, const skn_mv_exchange *xc) {
     if (n < 1 || n > 3 || M < 1) return cudaErrorNotSupported;
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
@@ -971,6 +971,7 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
     if (w[0]->type != SKN_TYPE_Q4_K && M < simple_min_m) return cudaErrorNotSupported;
     const int launches = (M + maxa - 1) / maxa;
     const int64_t K = w[0]->n_cols;
+    if (xc && launches != 1) return cudaErrorNotSupported;      // an exchange covers all rows of one launch
     for (int i = 0, m0 = 0; i < launches; ++i) {
         const int na = (M - m0 + (launches - i) - 1) / (launches - i);       // even shares
         float *ys[3] = {nullptr, nullptr, nullptr};
@@ -981,7 +982,7 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
         }
         cudaError_t err = cudaSuccess;
         if (!skn_mma_try_group(ctx, n, w, x + (int64_t)m0 * K, ys, add ? as : nullptr, norm_gain, norm_eps,
-                               silu_u ? silu_u + (int64_t)m0 * K : nullptr, stream, err, swiglu, na, add_per_act))
+                               silu_u ? silu_u + (int64_t)m0 * K : nullptr, stream, err, swiglu, na, add_per_act, xc))
             return cudaErrorNotSupported;
         if (err != cudaSuccess) return err;
         m0 += na;

@@ -236,35 +236,34 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     skn_pdl_launch_dependents();
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
-    float nscale[NAMAX];
-#pragma unroll
-    for (int a = 0; a < NAMAX; ++a) nscale[a] = 1.f;
-    if (grp.norm_gain) {
-        // RMSNorm scale of every activation row: each CTA reads all of x anyway
-        __shared__ float red[NAMAX][16];
-#pragma unroll
-        for (int a = 0; a < NAMAX; ++a) {
-            if (a < NA) {
-                float ss = 0.f;
-                for (int f = threadIdx.x; f < K / 4; f += W * 32) {
-                    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)a * K) + f);
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    // Tensor-parallel consumer: the previous launch of every rank pushed its partial products into
+    // this rank's inbox; wait for the peers' flags (bounded), then every load of x adds them up.
+    const float *redp = nullptr;
+    if (grp.xc_reduce && grp.xc_world > 1) {
+        const uint32_t q = *reinterpret_cast<volatile uint32_t *>(grp.xc_state) - 1u;    // the exchange this rank completed last
+        const int buf = (int)(q % SKN_COMM_NBUF);
+        if (warp == 0 && lane < grp.xc_world && lane != grp.xc_rank && *reinterpret_cast<volatile int32_t *>(status) == 0) {
+            const uint32_t *flag = reinterpret_cast<const uint32_t *>(grp.xc_base[grp.xc_rank]) + buf * SKN_COMM_MAX_WORLD + lane;
+            const uint64_t t0 = skn_globaltimer_ns();
+            uint32_t spins = 0, v;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if (v == q + 1u) break;
+                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > 2000000000ull) {
+                    atomicExch(status, SKN_ERR_TIMEOUT);
+                    break;
                 }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                if (lane == 0) red[a][warp] = ss;
             }
         }
         mm_bar_sync(1, W * 32);
-#pragma unroll
-        for (int a = 0; a < NAMAX; ++a) {
-            if (a < NA) {
-                float tot = 0.f;
-                for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
-                nscale[a] = rsqrtf(tot / (float)K + grp.norm_eps);
-            }
-        }
+        redp = reinterpret_cast<const float *>(grp.xc_base[grp.xc_rank] + SKN_COMM_FLAG_BYTES) + (size_t)buf * grp.xc_world * grp.xc_cap;
     }
+    // RMSNorm folded in without a pass of its own: the digits are taken of x * gain, the sum of
+    // squares of x is collected on the way, and the scalar 1 / rms multiplies the block scales and
+    // group sums afterwards.
+    float sq[NAMAX];
+#pragma unroll
+    for (int a = 0; a < NAMAX; ++a) sq[a] = 0.f;
     // x -> digit planes: a warp takes whole super-blocks, two at a time, and loads the next two
     // before it digitises the current ones (eight loads in flight);
     // unit u = activation row u / nb, super-block u % nb
@@ -277,13 +276,24 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 const int uu = h ? u2 : u;
                 if (uu < units) {
                     const int a = uu / nb, sbx = uu - a * nb;
-                    skn_xform xf{grp.norm_gain, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f};
-#pragma unroll
-                    for (int k = 0; k < NAMAX; ++k)
-                        if (k == a) xf.scale = nscale[k];
+                    skn_xform xf{nullptr, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f,
+                                 redp ? redp + (size_t)a * K : nullptr, redp ? grp.xc_world : 0, grp.xc_cap,
+                                 (redp && grp.xc_wb && blockIdx.x == 0) ? grp.xc_wb + (size_t)a * K : nullptr};
                     const float *xa = x + (size_t)a * K;
-                    v[2 * h] = skn_load_x4(xa, sbx * 64 + lane, xf);
-                    v[2 * h + 1] = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
+                    float4 r0 = skn_load_x4(xa, sbx * 64 + lane, xf), r1 = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
+                    if (grp.norm_gain) {
+                        const float e = (r0.x * r0.x + r0.y * r0.y) + (r0.z * r0.z + r0.w * r0.w) + (r1.x * r1.x + r1.y * r1.y) +
+                                        (r1.z * r1.z + r1.w * r1.w);
+#pragma unroll
+                        for (int k = 0; k < NAMAX; ++k)
+                            if (k == a) sq[k] += e;
+                        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(grp.norm_gain) + sbx * 64 + lane);
+                        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(grp.norm_gain) + sbx * 64 + 32 + lane);
+                        r0.x *= g0.x; r0.y *= g0.y; r0.z *= g0.z; r0.w *= g0.w;
+                        r1.x *= g1.x; r1.y *= g1.y; r1.z *= g1.z; r1.w *= g1.w;
+                    }
+                    v[2 * h] = r0;
+                    v[2 * h + 1] = r1;
                     as[h] = a;
                     ss[h] = sbx;
                 } else {
@@ -307,6 +317,26 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
                 for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
                 ca[0] = na[0]; ca[1] = na[1]; cs[0] = ns2[0]; cs[1] = ns2[1];
+            }
+        }
+    }
+    if (grp.norm_gain) {
+        __shared__ float red[NAMAX][16];
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) {
+            float ss = sq[a];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[a][warp] = ss;
+        }
+        mm_bar_sync(1, W * 32);                 // digit planes, scales and sums are complete, so are the partial squares
+        for (int a = 0; a < NA; ++a) {
+            float tot = 0.f;
+            for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
+            const float ns = rsqrtf(tot / (float)K + grp.norm_eps);
+            for (int i = threadIdx.x; i < nb * 9; i += W * 32) {
+                if (i < nb) sgrp[(size_t)a * nbp + i] *= ns;
+                else xsum[(size_t)a * nb * 8 + (i - nb)] *= ns;
             }
         }
     }
@@ -566,6 +596,10 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     // summation tree depends on the shape only
     const int lsh = (rows * 16 <= W * 32) ? 4 : ((rows * 4 <= W * 32) ? 2 : 0);
     const int L = 1 << lsh;
+    const bool push = grp.xc_push && grp.xc_world > 1;
+    uint32_t xq = 0;
+    if (push) xq = *reinterpret_cast<volatile uint32_t *>(grp.xc_state);        // number of this exchange
+    const size_t push_off = SKN_COMM_FLAG_BYTES / sizeof(float) + ((size_t)(xq % SKN_COMM_NBUF) * grp.xc_world + grp.xc_rank) * grp.xc_cap;
     for (int a = 0; a < NA; ++a) {
         const float *pa = part + (size_t)a * rows * pw;
         for (int lb = warp * (32 >> lsh); lb < rows; lb += W * (32 >> lsh)) {     // warp-uniform trip count
@@ -581,9 +615,31 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 const int tt = skn_group_row(grp, row_begin + lr, local);
                 if (grp.swiglu) {
                     if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = s / (1.f + expf(-s)) * up;
+                } else if (push) {
+                    // a partial product: slot `rank` of every rank's inbox (ordinary peer stores)
+                    const size_t o = push_off + (size_t)a * grp.ystride[tt] + local;
+                    for (int r = 0; r < grp.xc_world; ++r) reinterpret_cast<float *>(grp.xc_base[r])[o] = s;
                 } else {
                     if (grp.add[tt]) s += grp.add[tt][(size_t)a * grp.addstride[tt] + local];
                     grp.y[tt][(size_t)a * grp.ystride[tt] + local] = s;
+                }
+            }
+        }
+    }
+    if (push) {
+        // the CTA barrier orders every thread's peer stores before thread 0's system-wide fence; the
+        // CTA that draws the last ticket counts the exchange and releases the flag on every peer
+        mm_bar_sync(1, W * 32);
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            if (atomicAdd(&grp.xc_state[1], 1u) == gridDim.x - 1) {
+                grp.xc_state[1] = 0;
+                *reinterpret_cast<volatile uint32_t *>(grp.xc_state) = xq + 1u;
+                __threadfence_system();
+                for (int r = 0; r < grp.xc_world; ++r) {
+                    if (r == grp.xc_rank) continue;
+                    uint32_t *flag = reinterpret_cast<uint32_t *>(grp.xc_base[r]) + (xq % SKN_COMM_NBUF) * SKN_COMM_MAX_WORLD + grp.xc_rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(xq + 1u) : "memory");
                 }
             }
         }
@@ -689,7 +745,8 @@ static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols
 // otherwise one bias for all rows).  Returns false when the shapes are not covered (nothing launched).
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
-                       cudaStream_t stream, cudaError_t &err, bool swiglu, int n_act, bool add_per_act) {
+                       cudaStream_t stream, cudaError_t &err, bool swiglu, int n_act, bool add_per_act,
+                       const skn_mv_exchange *xc) {
     static const int enabled = env_int("SKN_MM", 1);
     err = cudaSuccess;
     const int fmt = mm_fmt_of(w[0]->type);
@@ -699,6 +756,17 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
     grp.swiglu = swiglu ? 1 : 0;
     grp.n_act = n_act;
+    if (xc && xc->view.world > 1) {
+        if (xc->push && (swiglu || n != 1)) return false;
+        grp.xc_world = xc->view.world; grp.xc_rank = xc->view.rank; grp.xc_cap = xc->view.capacity;
+        grp.xc_push = xc->push ? 1 : 0; grp.xc_reduce = xc->reduce ? 1 : 0;
+        for (int i = 0; i < SKN_COMM_MAX_WORLD; ++i) grp.xc_base[i] = xc->view.base[i];
+        grp.xc_state = xc->view.state;
+        grp.xc_wb = xc->writeback;
+        // a slot holds n_act outputs of n_rows each (push) or n_act inputs of n_cols each (reduce)
+        if (xc->push && (int64_t)n_act * w[0]->n_rows > xc->view.capacity) return false;
+        if (xc->reduce && (int64_t)n_act * w[0]->n_cols > xc->view.capacity) return false;
+    }
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
         tot += w[t]->n_rows;

@@ -33,10 +33,27 @@ struct skn_xform {
     const float *gain;
     const float *silu_u;
     float scale;
+    // tensor-parallel consumer: x <- x + sum over ranks of the partial products waiting in this
+    // rank's inbox (red_world slots red_stride floats apart, rank order); red_wb != NULL: the sum is
+    // also stored there (the new residual stream)
+    const float *red;
+    int red_world;
+    int64_t red_stride;
+    float *red_wb;
 };
 
 __device__ __forceinline__ float4 skn_load_x4(const float *__restrict__ x, int f, const skn_xform &xf) {
-    float4 v = __ldg(reinterpret_cast<const float4 *>(x) + f);
+    float4 v;
+    if (xf.red_world > 1) {
+        v = __ldcg(reinterpret_cast<const float4 *>(x) + f);
+        for (int src = 0; src < xf.red_world; ++src) {
+            const float4 p = __ldcg(reinterpret_cast<const float4 *>(xf.red + (size_t)src * xf.red_stride) + f);
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        if (xf.red_wb) reinterpret_cast<float4 *>(xf.red_wb)[f] = v;
+    } else {
+        v = __ldg(reinterpret_cast<const float4 *>(x) + f);
+    }
     if (xf.silu_u) {
         const float4 u = __ldg(reinterpret_cast<const float4 *>(xf.silu_u) + f);
         v.x = v.x / (1.f + expf(-v.x)) * u.x;
@@ -70,6 +87,16 @@ struct skn_mv_group {
     int n_act;              // tensor-core kernel only: activation rows per launch (x rows K apart, 0 means 1)
     int64_t ystride[3];     // ... distance between the outputs of consecutive activation rows
     int64_t addstride[3];   // ... and between their `add` vectors (0: one bias shared by all rows)
+    // tensor-core kernel only, tensor parallelism (both off when xc_world <= 1):
+    //   xc_push   : the outputs are partial products: they go to slot xc_rank of every rank's inbox
+    //               (y is not written) and the last CTA releases the peers' flags
+    //   xc_reduce : x is the residual stream; the partial products pushed by the previous launch of
+    //               every rank are added to it while x is prepared; CTA 0 stores the sum to xc_wb
+    int xc_world, xc_rank, xc_push, xc_reduce;
+    int64_t xc_cap;              // floats per (buffer, source rank) of an inbox
+    uint8_t *xc_base[8];         // inboxes of all ranks as mapped here (xc_base[xc_rank] is local)
+    uint32_t *xc_state;          // [0] exchanges completed, [1] push tickets
+    float *xc_wb;
     int swiglu;             // tensor-core kernel only: W[0] = gate, W[1] = up (equal shapes); rows are
                             // interleaved (virtual row v = tensor v & 1, row v >> 1) so that a CTA holds
                             // both products of a column and writes y[0][r] = silu(gate . x) * (up . x)
