@@ -324,7 +324,7 @@ def run_ours(args):
                        "launch_order": ("relaxed: the layers of a step are independent and declared so "
                                         "(SKN_OPT_RELAXED_ORDER)") if args.order == "relaxed" else
                        "stream order: every launch waits for the previous one",
-                       "parallelism": (f"tp{world}" + (", exchange fused into the matvecs" if args.fused_exchange else "")) if world > 1 else "none",
+                       "parallelism": (f"tp{world}" + (", exchange fused into the matvecs" if (args.fused_exchange == "on" or (args.fused_exchange == "auto" and world >= 4)) and B <= 2 else "")) if world > 1 else "none",
                    "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                        "l2_policy": f"inputs larger than L2: {layers} distinct weights = "
                                     f"{layers * W_BYTES / 1e6:.0f} MB streamed per step",
@@ -548,7 +548,7 @@ def run_decode(args):
         dist.init_process_group("nccl", device_id=dev)
     ctx = skn.Context(local)
     exchange = Exchange.connect_processes(ctx, B * T * cfg.d_model) if world > 1 else None
-    ctx.set_fused_exchange(args.fused_exchange)
+    ctx.set_fused_exchange({"auto": None, "on": True, "off": False}[args.fused_exchange])
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
@@ -635,7 +635,7 @@ def run_decode(args):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg5: Llama-style decoder, {cfg.n_layers} layers, Q4_K / Q6_K, batch {B}, "
                                f"{T}-token prefill then greedy decode",
-                   "parallelism": (f"tp{world}" + (", exchange fused into the matvecs" if args.fused_exchange else "")) if world > 1 else "none",
+                   "parallelism": (f"tp{world}" + (", exchange fused into the matvecs" if (args.fused_exchange == "on" or (args.fused_exchange == "auto" and world >= 4)) and B <= 2 else "")) if world > 1 else "none",
                    "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                    "prefill_ms": prefill_ms, "prefill_tok_s": B * T * 1e3 / prefill_ms,
                    "weight_bytes_per_step": wbytes},
@@ -661,8 +661,9 @@ def main():
                     help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
                          "may overlap; stream: each launch waits for the one before it")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences per step")
-    ap.add_argument("--fused-exchange", action="store_true",
-                    help="tensor-parallel decode: push partial sums from the matvec epilogue (SKN_OPT_FUSED_EXCHANGE)")
+    ap.add_argument("--fused-exchange", default="auto", choices=["auto", "on", "off"],
+                    help="tensor-parallel decode: push partial sums from the matvec epilogue (SKN_OPT_FUSED_EXCHANGE); "
+                         "auto = on from four ranks")
     ap.add_argument("--workload", default="matvec", choices=["matvec", "ffn", "attn", "sweep", "decode"],
                     help="matvec is the headline line; the others print one secondary JSON line (1 GPU)")
     args = ap.parse_args()

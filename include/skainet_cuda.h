@@ -84,12 +84,12 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
  * the fp64 oracle); below it, and always with value 0, products are fp32 fused dequant-dot
  * (1e-5). */
 #define SKN_OPT_PREFILL_MIN_M 2
-/* SKN_OPT_FUSED_EXCHANGE (default 0): tensor-parallel decoder with one or two rows per step: the
+/* SKN_OPT_FUSED_EXCHANGE (1 on, 0 off, -1 automatic = default): tensor-parallel decoder with one or two rows per step: the
  * K-sharded projections push their partial products into every rank's inbox from the matvec
  * epilogue and the next projection adds them to the residual stream while it prepares x,
  * instead of a separate exchange launch (skn_allreduce_dev) after each of them.  Same results
- * bit for bit.  Off by default: measured slightly slower on 2 GPUs (every CTA of the consuming
- * launch repeats the sum). */
+ * bit for bit.  Automatic means on from four ranks: measured slightly slower than the exchange
+ * launches on 2 GPUs (every CTA of the consuming launch repeats the sum), faster on 4. */
 #define SKN_OPT_FUSED_EXCHANGE 3
 int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value);
 

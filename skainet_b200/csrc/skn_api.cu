@@ -84,6 +84,7 @@ int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
     CTX_TRY(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
     ctx->stream = ctx->own_stream;
     ctx->prefill_min_m = 64;
+    ctx->fused_exchange = -1;
     CTX_TRY(cudaMalloc((void **)&ctx->d_status, 32768));
     CTX_TRY(cudaMemset(ctx->d_status, 0, 32768));
     CTX_TRY(cudaMallocHost((void **)&ctx->h_status, 256));
@@ -123,7 +124,7 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
         if (value < 0 || value > (1 << 30)) return skn_fail(ctx, SKN_ERR_ARG, "prefill threshold out of range");
         ctx->prefill_min_m = (int)value;
         return SKN_OK;
-    case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value ? 1 : 0; return SKN_OK;
+    case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value < 0 ? -1 : (value ? 1 : 0); return SKN_OK;
     default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
     }
 }

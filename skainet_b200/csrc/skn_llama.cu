@@ -280,7 +280,9 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     float *xcur = m->x, *xalt = m->h;
     bool pending = false;
     skn_comm_view xview = {};
-    bool fusedx = tp && fold && ctx->fused_exchange && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
+    // (automatic: from four ranks on, where it measured faster than the exchange launches)
+    const bool want_fused = ctx->fused_exchange > 0 || (ctx->fused_exchange < 0 && m->world >= 4);
+    bool fusedx = tp && fold && want_fused && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
     if (fusedx) {
         // only when every layer takes the multi-row tensor-core path (a pending exchange is consumed
         // by the next layer's first projection)

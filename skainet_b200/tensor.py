@@ -139,10 +139,11 @@ class Context:
         """Batch size from which matmuls use the tensor cores (bf16 operands); 0 = never."""
         _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 2, int(m)))
 
-    def set_fused_exchange(self, on: bool):
+    def set_fused_exchange(self, on):
         """Tensor-parallel decode steps of one or two rows: push partial products from the matvec
-        epilogue and sum them in the next projection's preparation of x (SKN_OPT_FUSED_EXCHANGE)."""
-        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 3, 1 if on else 0))
+        epilogue and sum them in the next projection's preparation of x (SKN_OPT_FUSED_EXCHANGE).
+        True / False, or None for the automatic choice (on from four ranks)."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 3, -1 if on is None else (1 if on else 0)))
 
     def sync(self):
         _check(self._h, _ffi.lib().skn_sync(self._h))
