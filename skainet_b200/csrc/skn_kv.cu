@@ -267,6 +267,21 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
         for (int e = 0; e < VEC; ++e) qv[g][e] *= scale;
     }
 
+    // short chunks (short contexts: latency matters, not bandwidth): the warp's first V tile is
+    // requested before the scores are computed, so that its latency overlaps pass 1
+    constexpr bool PREV = CHUNK <= 64;
+    float v0[PREV ? TT : 1][VEC];
+    if constexpr (PREV) {
+        const int tl = warp * TT;
+        if (tl < nt) {
+#pragma unroll
+            for (int j = 0; j < TT; ++j) {
+                const int t = min(tl + j, nt - 1);
+                VecLoad<VEC>::ld(vbase + (size_t)((s0 + t0 + t) % cap) * D, v0[j]);
+            }
+        }
+    }
+
     // ---- pass 1: scores ------------------------------------------------------------------
     float mrun = -INFINITY;   // this lane's head only (head = value index % G)
     const int vidx = lane / REP;          // value index held after the transposed reduce
@@ -352,11 +367,18 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
         const int tl = (ti * ATT_WARPS + warp) * TT;
         if (tl >= nt) break;
         float vr[TT][VEC];
+        if (PREV && ti == 0) {
 #pragma unroll
-        for (int j = 0; j < TT; ++j) {
-            const int t = min(tl + j, nt - 1);
-            const int slot = (s0 + t0 + t) % cap;
-            VecLoad<VEC>::ld(vbase + (size_t)slot * D, vr[j]);
+            for (int j = 0; j < TT; ++j)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) vr[j][e] = v0[j][e];
+        } else {
+#pragma unroll
+            for (int j = 0; j < TT; ++j) {
+                const int t = min(tl + j, nt - 1);
+                const int slot = (s0 + t0 + t) % cap;
+                VecLoad<VEC>::ld(vbase + (size_t)slot * D, vr[j]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < TT; ++j) {
