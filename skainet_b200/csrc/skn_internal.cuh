@@ -96,7 +96,7 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
                        cudaStream_t stream, cudaError_t &err, bool swiglu = false, int n_act = 1, bool add_per_act = false,
-                       const struct skn_mv_exchange *xc = nullptr);
+                       const struct skn_mv_exchange *xc = nullptr, const struct skn_mv_rope *rope = nullptr);
 // activation rows one tensor-core matvec launch can take for this tensor (0: not covered)
 int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols);
 // y[t][m] = W[t] . f(x[m]) (+ add) for M activation rows through the tensor-core matvec, in launches
@@ -104,7 +104,8 @@ int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int
 // x rows are K apart, outputs (and per-row add vectors) n_rows apart.
 cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
                                    const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
-                                   const float *silu_u, bool swiglu, cudaStream_t stream, const struct skn_mv_exchange *xc = nullptr);
+                                   const float *silu_u, bool swiglu, cudaStream_t stream, const struct skn_mv_exchange *xc = nullptr,
+                                   const struct skn_mv_rope *rope = nullptr);
 // h = silu(Wg . f(x)) * (Wu . f(x)) in one launch (f: optional RMSNorm); cudaErrorNotSupported when
 // the tensor-core matvec does not cover the tensors (nothing launched)
 cudaError_t skn_launch_gate_up_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const float *x, float *h,
@@ -155,6 +156,12 @@ struct skn_comm_view {
     uint32_t *state;                        // [0] exchanges completed, [1] push tickets, [2] finish tickets
 };
 bool skn_comm_get_view(const skn_comm *c, skn_comm_view *v);
+struct skn_mv_rope {                        // optional argument of skn_launch_matvec_acts: (wq, wk, wv) of a single-token step
+    int head_dim, n_kv_heads, capacity, seq0;   // seq0: sequence of the first activation row
+    const int32_t *len_dev, *start_dev;         // cache lengths (= positions of the new tokens) and ring starts
+    float *k_cache, *v_cache;
+    float theta;
+};
 struct skn_mv_exchange {                    // optional argument of skn_launch_matvec_acts
     skn_comm_view view;
     bool push;                              // outputs are partial products: push them, y is not written

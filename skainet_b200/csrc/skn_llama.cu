@@ -45,8 +45,8 @@ extern "C" int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q, int32_t 
                                        float *out, void *scratch);
 extern "C" int32_t skn_comm_info(const skn_comm *c, int32_t *rank, int32_t *world, int64_t *capacity_floats);
 extern "C" int32_t skn_allreduce_dev(skn_comm *c, const float *partial, const float *resid, float *out, int64_t n);
-extern "C" int32_t skn_kv_info(const skn_kvcache *kv, int32_t *, int32_t *, int32_t *, int32_t *, void **, void **,
-                               void **len_dev, void **);
+extern "C" int32_t skn_kv_info(const skn_kvcache *kv, int32_t *, int32_t *, int32_t *, int32_t *capacity, void **k_dev,
+                               void **v_dev, void **len_dev, void **start_dev);
 
 static bool llama_ok(const skn_llama *m) { return m && m->magic == SKN_MAGIC_LLAMA && skn_ctx_ok(m->ctx); }
 
@@ -317,15 +317,28 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
                 SKN_CUDA(ctx, skn_launch_rmsnorm(xcur, l.attn_norm, m->h, M, d, m->rms_eps, st));
                 src = m->h;
             }
+            // single-token steps: the Q/K/V launch rotates q and k in its epilogue and writes k and v
+            // straight into the cache (row a of the batch is sequence a, its position the cache length)
+            skn_mv_rope rope = {};
+            const bool rope_fused = (T == 1 && M <= 4);     // larger batches: the separate kernel spreads the sincos work better
+            if (rope_fused) {
+                void *kdev = nullptr, *vdev = nullptr, *ldev = nullptr, *sdev = nullptr;
+                int32_t cap = 0;
+                if ((rc = skn_kv_info(l.kv, nullptr, nullptr, nullptr, &cap, &kdev, &vdev, &ldev, &sdev))) return rc;
+                if (m->host_len + 1 > cap) return skn_fail(ctx, SKN_ERR_SHAPE, "context of %d tokens exceeded", cap);
+                rope.head_dim = D; rope.n_kv_heads = Hkv; rope.capacity = cap; rope.seq0 = 0;
+                rope.len_dev = (const int32_t *)ldev; rope.start_dev = (const int32_t *)sdev;
+                rope.k_cache = (float *)kdev; rope.v_cache = (float *)vdev; rope.theta = m->rope_theta;
+            }
             {
                 const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};
                 float *ys[3] = {m->q, m->k, m->v};
                 xred.writeback = xalt;
                 SKN_CUDA(ctx, skn_launch_matvec_acts(ctx, 3, ws, src, M, ys, nullptr, false, fold ? l.attn_norm : nullptr, m->rms_eps,
-                                                     nullptr, false, st, pending ? &xred : nullptr));
+                                                     nullptr, false, st, pending ? &xred : nullptr, rope_fused ? &rope : nullptr));
                 if (pending) { float *tmp = xcur; xcur = xalt; xalt = tmp; pending = false; }
             }
-            if ((rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
+            if (!rope_fused && (rc = skn_kv_rope_append_pending(l.kv, m->q, m->k, m->v, Hq, T, m->rope_theta, m->host_len))) return rc;
             if ((rc = skn_attn_causal_pending(l.kv, m->q, Hq, T, scale, m->att))) return rc;
             {
                 const skn_tensor *ws[1] = {l.wo};

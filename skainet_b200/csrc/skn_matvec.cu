@@ -955,7 +955,8 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
 
 cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
                                    const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps,
-                                   const float *silu_u, bool swiglu, cudaStream_t stream, const skn_mv_exchange *xc) {
+                                   const float *silu_u, bool swiglu, cudaStream_t stream, const skn_mv_exchange *xc,
+                                   const skn_mv_rope *rope) {
     if (n < 1 || n > 3 || M < 1) return cudaErrorNotSupported;
     int64_t tot = 0;
     for (int t = 0; t < n; ++t) {
@@ -981,8 +982,13 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
             if (add && add[t]) as[t] = add[t] + (add_per_act ? (int64_t)m0 * w[t]->n_rows : 0);
         }
         cudaError_t err = cudaSuccess;
+        skn_mv_rope rp;
+        if (rope) {
+            rp = *rope;
+            rp.seq0 = rope->seq0 + m0;
+        }
         if (!skn_mma_try_group(ctx, n, w, x + (int64_t)m0 * K, ys, add ? as : nullptr, norm_gain, norm_eps,
-                               silu_u ? silu_u + (int64_t)m0 * K : nullptr, stream, err, swiglu, na, add_per_act, xc))
+                               silu_u ? silu_u + (int64_t)m0 * K : nullptr, stream, err, swiglu, na, add_per_act, xc, rope ? &rp : nullptr))
             return cudaErrorNotSupported;
         if (err != cudaSuccess) return err;
         m0 += na;

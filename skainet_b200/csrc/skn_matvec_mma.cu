@@ -33,6 +33,8 @@
 // sums per (row, super-chunk, warp) meet in shared memory and are added in a fixed order.
 #include "skn_mv_common.cuh"
 
+#include <math.h>
+
 // Block formats of this kernel.  A "super-block" is 256 weights: one Q4_K block, or eight of the
 // 32-weight blocks of Q8_0 / Q4_0 (each with its own fp16 scale).  KS super-blocks (one bulk copy
 // per row) make a K super-chunk; rows are padded by 32 bytes in shared memory, which puts the
@@ -185,7 +187,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     float *part = reinterpret_cast<float *>(empty + nst);
 
     // with interleaved gate / up rows every CTA owns whole (gate, up) pairs: even boundaries
-    const int64_t even = grp.swiglu ? ~(int64_t)1 : ~(int64_t)0;
+    const int64_t even = (grp.swiglu || grp.rope_hd) ? ~(int64_t)1 : ~(int64_t)0;
     const int64_t row_begin = ((int64_t)blockIdx.x * N / gridDim.x) & even;
     const int64_t row_end = (blockIdx.x + 1 == gridDim.x) ? N : (((int64_t)(blockIdx.x + 1) * N / gridDim.x) & even);
     const int rows = (int)(row_end - row_begin);
@@ -615,6 +617,23 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 const int tt = skn_group_row(grp, row_begin + lr, local);
                 if (grp.swiglu) {
                     if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = s / (1.f + expf(-s)) * up;
+                } else if (grp.rope_hd) {
+                    // rotary embedding of the pair (2i, 2i+1) this row belongs to (`up` is the other
+                    // row of the pair), k and v straight into the cache
+                    const int hd = grp.rope_hd, seq = grp.rope_a0 + a;
+                    const int pos = grp.rope_len[seq];
+                    const int slot = (grp.rope_start[seq] + pos) % grp.rope_cap;
+                    const int h = (int)(local / hd), dd = (int)(local % hd);
+                    float o = s;
+                    if (tt < 2) {
+                        const double ang = (double)pos * exp2(-grp.rope_log2theta * (2.0 * (double)(dd >> 1) / (double)hd));
+                        double sd, cd;
+                        sincos(ang, &sd, &cd);
+                        const float sn = (float)sd, cs = (float)cd;
+                        o = (dd & 1) ? (up * sn + s * cs) : (s * cs - up * sn);
+                    }
+                    if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = o;
+                    else (tt == 1 ? grp.rope_kc : grp.rope_vc)[(((size_t)seq * grp.rope_nkv + h) * grp.rope_cap + slot) * hd + dd] = o;
                 } else if (push) {
                     // a partial product: slot `rank` of every rank's inbox (ordinary peer stores)
                     const size_t o = push_off + (size_t)a * grp.ystride[tt] + local;
@@ -746,7 +765,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols
 bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, float *const *y,
                        const float *const *add, const float *norm_gain, float norm_eps, const float *silu_u,
                        cudaStream_t stream, cudaError_t &err, bool swiglu, int n_act, bool add_per_act,
-                       const skn_mv_exchange *xc) {
+                       const skn_mv_exchange *xc, const skn_mv_rope *rope) {
     static const int enabled = env_int("SKN_MM", 1);
     err = cudaSuccess;
     const int fmt = mm_fmt_of(w[0]->type);
@@ -756,6 +775,14 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     grp.norm_gain = norm_gain; grp.norm_eps = norm_eps; grp.silu_u = silu_u;
     grp.swiglu = swiglu ? 1 : 0;
     grp.n_act = n_act;
+    if (rope) {
+        if (n != 3 || swiglu || (xc && xc->push) || rope->head_dim < 2 || (rope->head_dim & 1) || w[0]->n_rows % rope->head_dim ||
+            w[1]->n_rows != (int64_t)rope->n_kv_heads * rope->head_dim || w[2]->n_rows != w[1]->n_rows)
+            return false;
+        grp.rope_hd = rope->head_dim; grp.rope_cap = rope->capacity; grp.rope_nkv = rope->n_kv_heads; grp.rope_a0 = rope->seq0;
+        grp.rope_len = rope->len_dev; grp.rope_start = rope->start_dev; grp.rope_kc = rope->k_cache; grp.rope_vc = rope->v_cache;
+        grp.rope_log2theta = log2((double)rope->theta);
+    }
     if (xc && xc->view.world > 1) {
         if (xc->push && (swiglu || n != 1)) return false;
         grp.xc_world = xc->view.world; grp.xc_rank = xc->view.rank; grp.xc_cap = xc->view.capacity;

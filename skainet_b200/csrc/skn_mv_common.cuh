@@ -97,6 +97,14 @@ struct skn_mv_group {
     uint8_t *xc_base[8];         // inboxes of all ranks as mapped here (xc_base[xc_rank] is local)
     uint32_t *xc_state;          // [0] exchanges completed, [1] push tickets
     float *xc_wb;
+    // tensor-core kernel only, Q/K/V launch of a single-token decoder step (rope_hd > 0): tensors are
+    // (wq, wk, wv); activation row a belongs to sequence rope_a0 + a whose new token has position
+    // rope_len[seq]; q is rotated and written to y[0], k is rotated and written straight into the
+    // cache slot of that position, v is copied there (cache: [seq][kv head][capacity][head dim])
+    int rope_hd, rope_cap, rope_nkv, rope_a0;
+    const int32_t *rope_len, *rope_start;
+    float *rope_kc, *rope_vc;
+    double rope_log2theta;
     int swiglu;             // tensor-core kernel only: W[0] = gate, W[1] = up (equal shapes); rows are
                             // interleaved (virtual row v = tensor v & 1, row v >> 1) so that a CTA holds
                             // both products of a column and writes y[0][r] = silu(gate . x) * (up . x)
