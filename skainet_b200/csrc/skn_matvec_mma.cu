@@ -119,8 +119,8 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
         s0 += __shfl_xor_sync(0xffffffffu, s0, o);
         s1 += __shfl_xor_sync(0xffffffffu, s1, o);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // mx >= 0 (or NaN-free by fmaxf): its bit pattern orders like the value, one integer reduction
+    mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
     float tot = s0 + s1;
     tot += __shfl_xor_sync(0xffffffffu, tot, 8);
     tot += __shfl_xor_sync(0xffffffffu, tot, 16);
@@ -266,16 +266,20 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     float sq[NAMAX];
 #pragma unroll
     for (int a = 0; a < NAMAX; ++a) sq[a] = 0.f;
-    // x -> digit planes: a warp takes whole super-blocks, two at a time, and loads the next two
-    // before it digitises the current ones (eight loads in flight);
+    // x -> digit planes: a warp takes whole super-blocks, four per round (eight loads in flight, four
+    // independent digitisations for the scheduler to interleave);
     // unit u = activation row u / nb, super-block u % nb
     {
         const int units = NA * nb;
-        auto fetch = [&](int u, float4 (&v)[4], int (&as)[2], int (&ss)[2]) {
-            const int u2 = u + W;
+        constexpr int UR = 4;
+        for (int u0 = warp; u0 < units; u0 += UR * W) {
+            float4 v[UR][2];
+            int ua[UR], us[UR];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int uu = h ? u2 : u;
+            for (int h = 0; h < UR; ++h) {
+                const int uu = u0 + h * W;
+                ua[h] = -1;
+                us[h] = 0;
                 if (uu < units) {
                     const int a = uu / nb, sbx = uu - a * nb;
                     skn_xform xf{nullptr, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f,
@@ -294,32 +298,17 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                         r0.x *= g0.x; r0.y *= g0.y; r0.z *= g0.z; r0.w *= g0.w;
                         r1.x *= g1.x; r1.y *= g1.y; r1.z *= g1.z; r1.w *= g1.w;
                     }
-                    v[2 * h] = r0;
-                    v[2 * h + 1] = r1;
-                    as[h] = a;
-                    ss[h] = sbx;
-                } else {
-                    as[h] = -1;
-                    ss[h] = 0;
+                    v[h][0] = r0;
+                    v[h][1] = r1;
+                    ua[h] = a;
+                    us[h] = sbx;
                 }
             }
-        };
-        float4 cur[4], nxt[4];
-        int ca[2], cs[2], na[2], ns2[2];
-        if (warp < units) fetch(warp, cur, ca, cs);
-        for (int u = warp; u < units; u += 2 * W) {
-            const bool more = u + 2 * W < units;
-            if (more) fetch(u + 2 * W, nxt, na, ns2);
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-                if (ca[h] >= 0)
-                    mm_digitize(cur[2 * h], cur[2 * h + 1], cs[h], lane, dig + (size_t)ca[h] * 3 * PL, PL, sgrp + (size_t)ca[h] * nbp,
-                                xsum + (size_t)ca[h] * nb * 8);
-            if (more) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
-                ca[0] = na[0]; ca[1] = na[1]; cs[0] = ns2[0]; cs[1] = ns2[1];
-            }
+            for (int h = 0; h < UR; ++h)
+                if (ua[h] >= 0)
+                    mm_digitize(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * 3 * PL, PL, sgrp + (size_t)ua[h] * nbp,
+                                xsum + (size_t)ua[h] * nb * 8);
         }
     }
     if (grp.norm_gain) {
