@@ -173,16 +173,21 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     const int warp = threadIdx.x >> 5;          // 0..W-1 compute, W = producer
     const int g = lane >> 2, t = lane & 3;
     const int nb = K / 256;
-    const int nbp = (nb + 3) / 4 * 4;
+    // launches of three or four rows keep the digit planes of ONE K super-chunk at a time (their
+    // planes would not fit otherwise); one or two rows prepare all of x up front
+    constexpr bool CHUNKED = NP > 1;
+    const int nbp = ((CHUNKED ? MM_KS : nb) + 3) / 4 * 4;        // scale slots per activation row
+    const int nxs = CHUNKED ? MM_KS : nb;       // super-blocks of group sums per activation row
     const int nks = (nb + MM_KS - 1) / MM_KS;   // K super-chunks
-    const int PL = nb * 256 + 32;               // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
+    const int ksb = CHUNKED ? (nb < MM_KS ? nb : MM_KS) : nb;    // super-blocks whose digit planes are resident
+    const int PL = ksb * 256 + 32;              // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
 
     // shared memory: ring | digit planes [row][3] | block scales [row] | group sums [row] | barriers | partials [row]
     uint8_t *ring = smem;
     uint8_t *dig = smem + (size_t)nst * MM_STAGE;
     float *sgrp = reinterpret_cast<float *>(dig + ((size_t)NA * 3 * PL + 127) / 128 * 128);
     float *xsum = sgrp + (size_t)NA * nbp;
-    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nb * 8);
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nxs * 8);
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
@@ -261,17 +266,23 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
         redp = reinterpret_cast<const float *>(grp.xc_base[grp.xc_rank] + SKN_COMM_FLAG_BYTES) + (size_t)buf * grp.xc_world * grp.xc_cap;
     }
     // RMSNorm folded in without a pass of its own: the digits are taken of x * gain, the sum of
-    // squares of x is collected on the way, and the scalar 1 / rms multiplies the block scales and
-    // group sums afterwards.
-    float sq[NAMAX];
-#pragma unroll
-    for (int a = 0; a < NAMAX; ++a) sq[a] = 0.f;
-    // x -> digit planes: a warp takes whole super-blocks, four per round (eight loads in flight, four
-    // independent digitisations for the scheduler to interleave);
-    // unit u = activation row u / nb, super-block u % nb
-    {
-        const int units = NA * nb;
+    // squares of x is collected on the way (per warp, in shared memory), and the scalar 1 / rms
+    // multiplies the outputs at the end.
+    __shared__ float red[NAMAX][16];
+    if (lane < NAMAX) red[lane][warp] = 0.f;
+    __syncwarp();
+    // x -> digit planes of K super-chunk kc: a warp takes whole super-blocks, four per round (eight
+    // loads in flight, four independent digitisations for the scheduler to interleave);
+    // unit u = activation row u / nsb, super-block (of the chunk) u % nsb.  The planes of one chunk are
+    // resident at a time, so shared memory does not grow with K.
+    auto prep_chunk = [&](int kc) {
+        int nsbc = nb - kc * MM_KS;
+        nsbc = nsbc > MM_KS ? MM_KS : nsbc;
+        const int units = NA * nsbc;
         constexpr int UR = 4;
+        float sq[NAMAX];
+#pragma unroll
+        for (int a = 0; a < NAMAX; ++a) sq[a] = 0.f;
         for (int u0 = warp; u0 < units; u0 += UR * W) {
             float4 v[UR][2];
             int ua[UR], us[UR];
@@ -281,7 +292,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 ua[h] = -1;
                 us[h] = 0;
                 if (uu < units) {
-                    const int a = uu / nb, sbx = uu - a * nb;
+                    const int a = uu / nsbc, sbl = uu - a * nsbc, sbx = kc * MM_KS + sbl;      // sbx: index in x
                     skn_xform xf{nullptr, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f,
                                  redp ? redp + (size_t)a * K : nullptr, redp ? grp.xc_world : 0, grp.xc_cap,
                                  (redp && grp.xc_wb && blockIdx.x == 0) ? grp.xc_wb + (size_t)a * K : nullptr};
@@ -301,38 +312,25 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                     v[h][0] = r0;
                     v[h][1] = r1;
                     ua[h] = a;
-                    us[h] = sbx;
+                    us[h] = CHUNKED ? sbl : sbx;      // index among the resident planes
                 }
             }
 #pragma unroll
             for (int h = 0; h < UR; ++h)
                 if (ua[h] >= 0)
                     mm_digitize(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * 3 * PL, PL, sgrp + (size_t)ua[h] * nbp,
-                                xsum + (size_t)ua[h] * nb * 8);
+                                xsum + (size_t)ua[h] * nxs * 8);
         }
-    }
-    if (grp.norm_gain) {
-        __shared__ float red[NAMAX][16];
+        if (grp.norm_gain) {
 #pragma unroll
-        for (int a = 0; a < NAMAX; ++a) {
-            float ss = sq[a];
+            for (int a = 0; a < NAMAX; ++a) {
+                float ss = sq[a];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) red[a][warp] = ss;
-        }
-        mm_bar_sync(1, W * 32);                 // digit planes, scales and sums are complete, so are the partial squares
-        for (int a = 0; a < NA; ++a) {
-            float tot = 0.f;
-            for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
-            const float ns = rsqrtf(tot / (float)K + grp.norm_eps);
-            for (int i = threadIdx.x; i < nb * 9; i += W * 32) {
-                if (i < nb) sgrp[(size_t)a * nbp + i] *= ns;
-                else xsum[(size_t)a * nb * 8 + (i - nb)] *= ns;
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) red[a][warp] += ss;
             }
         }
-    }
-    mm_bar_sync(1, W * 32);
-    MV_STAMP(3);
+    };
 
     // this lane's two B columns (2t, 2t + 1): column c of a row pair is digit c % 3 of its row c / 3
     // B column c of a row pair = digit c / 2 of its row c & 1 (c < 6): a lane LOADS column g and
@@ -343,10 +341,25 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
     const uint32_t ring_s = skn_smem_u32(ring), dig_s = skn_smem_u32(dig), sgrp_s = skn_smem_u32(sgrp), xsum_s = skn_smem_u32(xsum);
+    int cur_ks = -1;
+    if (!CHUNKED) {
+        for (int kc = 0; kc < nks; ++kc) prep_chunk(kc);
+        mm_bar_sync(1, W * 32);
+    }
+    MV_STAMP(3);
     for (int i = 0; i < ntiles; ++i) {
         const uint32_t st = ring_s + (uint32_t)stg * MM_STAGE;
         int nsb = nb - ks * MM_KS;
         nsb = nsb > MM_KS ? MM_KS : nsb;
+        if (CHUNKED && ks != cur_ks) {
+            // every compute warp walks the same tile sequence, so all of them get here together:
+            // nobody reads the old planes any more, then everybody sees the new ones
+            if (cur_ks >= 0) mm_bar_sync(1, W * 32);
+            prep_chunk(ks);
+            mm_bar_sync(1, W * 32);
+            cur_ks = ks;
+        }
+        const int sb0 = CHUNKED ? 0 : ks * MM_KS;   // resident index of the tile's first super-block
         if (!failed && !skn_mbar_wait(&full[stg], par)) {
             failed = true;
             atomicExch(status, SKN_ERR_TIMEOUT);
@@ -366,7 +379,6 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             const uint32_t bb = ba + 8 * MM_ROW_STRIDE;
             if constexpr (FMT == MM_FMT_Q4K) {
             const uint4 ha = mm_lds128(ba), hb = mm_lds128(bb);
-            const int sbi = ks * MM_KS + sb;
             // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
             const uint32_t sa[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u)};
             const uint32_t sq[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u)};
@@ -381,7 +393,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
                 bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + sbi * 256 + 8 * t);
+                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256 + 8 * t);
             }
             // The MMAs of byte pair p + 1 are issued before the results of pair p are consumed, so
             // that their latency overlaps the integer multiply-adds.
@@ -426,8 +438,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
-                const float sgA = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sbi)) * 0.0625f;
-                const float sgB = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sbi)) * 0.0625f;
+                const float sgA = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sb0 + sb)) * 0.0625f;
+                const float sgB = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sb0 + sb)) * 0.0625f;
                 accA[ap][0] = fmaf(da.x * sgA, (float)(lo[ap][0] * 16 + hi[ap][0]), accA[ap][0]);
                 accA[ap][1] = fmaf(db.x * sgA, (float)(lo[ap][2] * 16 + hi[ap][2]), accA[ap][1]);
                 if (!(ODD && ap == NP - 1)) {
@@ -443,7 +455,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int a = 0; a < NAMAX; ++a) {
                 if (a < NA) {
-                    const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nb + sbi) * 8 + 4 * (t >> 1)));
+                    const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nxs + sb0 + sb) * 8 + 4 * (t >> 1)));
                     float m = m0 * xs.x;
                     m = fmaf(m1, xs.y, m);
                     m = fmaf(m2, xs.z, m);
@@ -452,22 +464,21 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 }
             }
             } else {
-            const int sbi = ks * MM_KS + sb;
             uint32_t bsrc[NP];
             bool bon[NP];
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
                 bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + sbi * 256) +
+                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256) +
                            (FMT == MM_FMT_Q80 ? 8 * t : 4 * t);
             }
             float sgA[NP], sgB[NP];
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
-                sgA[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sbi));
-                sgB[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sbi));
+                sgA[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sb0 + sb));
+                sgB[ap] = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sb0 + sb));
             }
             // eight 32-weight blocks, one MMA each; block j of a row starts 2-byte aligned, its
             // quants are word aligned for odd j and two bytes off for even j
@@ -533,7 +544,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
                 for (int a = 0; a < NAMAX; ++a) {
                     if (a < NA) {
-                        const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nb + sbi) * 8 + j0));
+                        const float4 xs = mm_lds128f(xsum_s + 4u * (uint32_t)((a * nxs + sb0 + sb) * 8 + j0));
                         float m = d0 * xs.x;
                         m = fmaf(d1, xs.y, m);
                         m = fmaf(d2, xs.z, m);
@@ -580,8 +591,20 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
         if (++stg == nst) { stg = 0; par ^= 1u; }
     }
     MV_STAMP(5);
+    // RMSNorm: the scalar 1 / rms of every activation row multiplies its outputs (the products above
+    // are linear in x, and the digits were taken of x * gain)
     mm_bar_sync(1, W * 32);
     MV_STAMP(6);
+    float nscale[NAMAX];
+#pragma unroll
+    for (int a = 0; a < NAMAX; ++a) {
+        nscale[a] = 1.f;
+        if (grp.norm_gain && a < NA) {
+            float tot = 0.f;
+            for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
+            nscale[a] = rsqrtf(tot / (float)K + grp.norm_eps);
+        }
+    }
     // L lanes per row (16, 4 or 1, the most that still covers the CTA's rows in about one pass):
     // each adds its share of the row's partials in index order, then a fixed butterfly, so the
     // summation tree depends on the shape only
@@ -600,6 +623,9 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             if (lr < rows)
                 for (int cc = sub; cc < pw; cc += L) s += pa[(size_t)lr * pw + cc];
             for (int o = L >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+            for (int k = 0; k < NAMAX; ++k)
+                if (k == a) s *= nscale[k];
             const float up = __shfl_xor_sync(0xffffffffu, s, L);      // the next row: the `up` product of a gate row
             if (sub == 0 && lr < rows) {
                 int64_t local;
@@ -687,9 +713,12 @@ static mm_kernel_t mm_kernel(int fmt, int warps, int n_act) {
     return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1, true> : skn_matvec_mma<MM_FMT_Q4K, 4, 1, true>;
 }
 
-static size_t mm_fixed_smem(int nb, int n_act, int64_t rows_max, int nks, int warps) {
-    return ((size_t)n_act * 3 * (nb * 256 + 32) + 127) / 128 * 128 + (size_t)n_act * ((nb + 3) / 4 * 4) * 4 +
-           (size_t)n_act * nb * 8 * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
+static size_t mm_fixed_smem(int fmt, int nb, int n_act, int64_t rows_max, int nks, int warps) {
+    // three or four rows: digit planes of one K super-chunk at a time; one or two: all of x
+    const bool chunked = n_act > 2;
+    const int ks = mm_ks(fmt), ksb = chunked ? (nb < ks ? nb : ks) : nb, nxs = chunked ? ks : nb;
+    return ((size_t)n_act * 3 * (ksb * 256 + 32) + 127) / 128 * 128 + (size_t)n_act * ((nxs + 3) / 4 * 4) * 4 +
+           (size_t)n_act * nxs * 8 * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
 }
 
 // most activation rows one launch can take for this shape (the digit planes and partial sums of
@@ -700,7 +729,7 @@ static int mm_max_acts(const skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_co
     if (grid > n_rows) grid = n_rows;
     const int64_t rows_max = (n_rows + grid - 1) / grid + 2;
     for (int a = 4; a > 1; --a)
-        if (mm_fixed_smem(nb, a, rows_max, (nb + mm_ks(fmt) - 1) / mm_ks(fmt), 8) + 2 * (size_t)(mm_stage_bytes(fmt) + 16) <= 200 * 1024)
+        if (mm_fixed_smem(fmt, nb, a, rows_max, (nb + mm_ks(fmt) - 1) / mm_ks(fmt), 8) + 2 * (size_t)(mm_stage_bytes(fmt) + 16) <= 200 * 1024)
             return a;
     return 1;
 }
@@ -725,7 +754,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols
     // few tiles: half an SM, so that the next launch's CTA is resident early; many tiles: a deeper
     // ring matters more than the neighbour
     const size_t budget = (size_t)(budget_env > 0 ? budget_env : (ntiles >= 6 ? 200 : 110)) * 1024;
-    const size_t fixed = mm_fixed_smem(nb, n_act, rows_max, nks, warps);
+    const size_t fixed = mm_fixed_smem(fmt, nb, n_act, rows_max, nks, warps);
     int nst = nst_env > 0 ? nst_env : (ntiles < 4 ? ntiles : 4);
     while (nst > 1 && fixed + (size_t)nst * stage > budget) --nst;
     if (nst < 2 && ntiles > 1 && budget_env <= 0) {
