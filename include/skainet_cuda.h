@@ -45,6 +45,12 @@ extern "C" {
 #define SKN_TYPE_Q8_0 8
 #define SKN_TYPE_Q4_K 12
 #define SKN_TYPE_Q6_K 14
+/* Further block types of the reference's table (Constants.kt:62-70), served by the dequantiser
+ * and the generic fused dequant-dot (any M, fp32); they have no streaming / tensor-core kernels. */
+#define SKN_TYPE_Q4_1 3   /* 32 weights, 20 bytes: d, m (fp16), 16 nibble bytes: q * d + m */
+#define SKN_TYPE_Q5_0 6   /* 32 weights, 22 bytes: d, 32 high bits, 16 nibble bytes: (q - 16) * d */
+#define SKN_TYPE_Q5_1 7   /* 32 weights, 24 bytes: d, m, 32 high bits, 16 nibble bytes: q * d + m */
+#define SKN_TYPE_Q5_K 13  /* 256 weights, 176 bytes: d, dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes */
 
 typedef struct skn_ctx skn_ctx;
 typedef struct skn_tensor skn_tensor;

@@ -27,7 +27,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14  # Constants.kt:14-52
-GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}  # Constants.kt:58-90
+Q4_1, Q5_0, Q5_1, Q5_K = 3, 6, 7, 13
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176)}  # Constants.kt:58-90
 
 _lib = None
 
@@ -238,7 +240,54 @@ def np_dequant_q6_k(raw: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
-NP_DEQUANT = {Q4_0: np_dequant_q4_0, Q8_0: np_dequant_q8_0, Q4_K: np_dequant_q4_k, Q6_K: np_dequant_q6_k}
+def _nib32(qs: np.ndarray) -> np.ndarray:
+    """16 bytes per block -> 32 nibbles (low nibbles first), uint8."""
+    return np.concatenate([qs & 15, qs >> 4], axis=1)
+
+
+def _bits32(qh4: np.ndarray) -> np.ndarray:
+    """4 little-endian bytes per block -> 32 bits (bit i = weight i), uint8."""
+    w = np.ascontiguousarray(qh4).view(np.uint32).reshape(-1, 1)
+    return ((w >> np.arange(32, dtype=np.uint32)[None, :]) & 1).astype(np.uint8)
+
+
+def np_dequant_q4_1(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 20)
+    d, m = _f16(b[:, 0:2])[:, None], _f16(b[:, 2:4])[:, None]
+    return (d * _nib32(b[:, 4:20]).astype(np.float32) + m).reshape(-1)
+
+
+def np_dequant_q5_0(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 22)
+    d = _f16(b[:, 0:2])[:, None]
+    q = (_nib32(b[:, 6:22]) | (_bits32(b[:, 2:6]) << 4)).astype(np.int8) - np.int8(16)
+    return (d * q.astype(np.float32)).reshape(-1)
+
+
+def np_dequant_q5_1(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 24)
+    d, m = _f16(b[:, 0:2])[:, None], _f16(b[:, 2:4])[:, None]
+    q = (_nib32(b[:, 8:24]) | (_bits32(b[:, 4:8]) << 4)).astype(np.float32)
+    return (d * q + m).reshape(-1)
+
+
+def np_dequant_q5_k(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 176)
+    n = b.shape[0]
+    d = _f16(b[:, 0:2])[:, None]
+    dmin = _f16(b[:, 2:4])[:, None]
+    sc, mn = np_q4k_scales(b[:, 4:16])
+    dl = (d * sc.astype(np.float32))[:, :, None]
+    ml = (dmin * mn.astype(np.float32))[:, :, None]
+    qs = b[:, 48:176].reshape(n, 4, 32)
+    nib = np.stack([qs & 15, qs >> 4], axis=2).reshape(n, 8, 32)
+    hi = (b[:, 16:48][:, None, :] >> np.arange(8, dtype=np.uint8)[None, :, None]) & 1
+    q = (nib | (hi << 4)).astype(np.float32)
+    return (dl * q - ml).reshape(-1)
+
+
+NP_DEQUANT = {Q4_0: np_dequant_q4_0, Q8_0: np_dequant_q8_0, Q4_K: np_dequant_q4_k, Q6_K: np_dequant_q6_k,
+              Q4_1: np_dequant_q4_1, Q5_0: np_dequant_q5_0, Q5_1: np_dequant_q5_1, Q5_K: np_dequant_q5_k}
 
 
 def np_dequant(qtype: int, blocks: np.ndarray) -> np.ndarray:

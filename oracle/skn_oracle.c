@@ -33,7 +33,7 @@
 #endif
 
 /* GGML type ids, Constants.kt:14-52 */
-enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14 };
+enum { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14 };
 
 /* (elements per block, bytes per block): Constants.kt:58-90 */
 int skn_oracle_geometry(int type, int *elems, int *bytes) {
@@ -42,6 +42,10 @@ int skn_oracle_geometry(int type, int *elems, int *bytes) {
     case T_Q8_0: *elems = 32;  *bytes = 2 + 32; return 0;                     /* Constants.kt:65 */
     case T_Q4_K: *elems = 256; *bytes = 2 + 2 + 256 / 2 + 12; return 0;       /* Constants.kt:69 */
     case T_Q6_K: *elems = 256; *bytes = 2 + 256 / 2 + 256 / 4 + 256 / 16; return 0; /* Constants.kt:71 */
+    case T_Q4_1: *elems = 32;  *bytes = 2 + 2 + 16; return 0;                 /* Constants.kt:62 */
+    case T_Q5_0: *elems = 32;  *bytes = 2 + 4 + 16; return 0;                 /* Constants.kt:63 */
+    case T_Q5_1: *elems = 32;  *bytes = 2 + 2 + 4 + 16; return 0;             /* Constants.kt:64 */
+    case T_Q5_K: *elems = 256; *bytes = 2 + 2 + 12 + 256 / 8 + 256 / 2; return 0; /* Constants.kt:70 */
     default: return -1;
     }
 }
@@ -147,11 +151,73 @@ static void dq_q6_k(const uint8_t *b, float *out) {
     }
 }
 
+/* q * d + m (two roundings, as gguf-py's `(d * qs) + m`). */
+static void dq_q4_1(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b)), m = half_to_float(rd16(b + 2));
+    const uint8_t *qs = b + 4;
+    for (int e = 0; e < 16; ++e) {
+        out[e]      = d * (float)(qs[e] & 15) + m;
+        out[e + 16] = d * (float)(qs[e] >> 4) + m;
+    }
+}
+
+/* The fifth bit of weight i is bit i of the little-endian 32-bit word that follows the scale(s). */
+static uint32_t rd32(const uint8_t *p) { return (uint32_t)rd16(p) | ((uint32_t)rd16(p + 2) << 16); }
+
+static void dq_q5_0(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b));
+    const uint32_t qh = rd32(b + 2);
+    const uint8_t *qs = b + 6;
+    for (int e = 0; e < 16; ++e) {
+        const int lo = (qs[e] & 15) | (int)(((qh >> e) & 1u) << 4);
+        const int hi = (qs[e] >> 4) | (int)(((qh >> (e + 16)) & 1u) << 4);
+        out[e]      = d * (float)(lo - 16);
+        out[e + 16] = d * (float)(hi - 16);
+    }
+}
+
+static void dq_q5_1(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b)), m = half_to_float(rd16(b + 2));
+    const uint32_t qh = rd32(b + 4);
+    const uint8_t *qs = b + 8;
+    for (int e = 0; e < 16; ++e) {
+        const int lo = (qs[e] & 15) | (int)(((qh >> e) & 1u) << 4);
+        const int hi = (qs[e] >> 4) | (int)(((qh >> (e + 16)) & 1u) << 4);
+        out[e]      = d * (float)lo + m;
+        out[e + 16] = d * (float)hi + m;
+    }
+}
+
+/* Q4_K's layout with a fifth bit per weight: bit j of byte qh[l] belongs to weight l of sub-block j. */
+static void dq_q5_k(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b));
+    const float dmin = half_to_float(rd16(b + 2));
+    const uint8_t *s = b + 4;
+    const uint8_t *qh = b + 16;
+    const uint8_t *qs = b + 48;
+    for (int j = 0; j < 8; ++j) {
+        int sc, mn;
+        q4k_scale_min(s, j, &sc, &mn);
+        const float dl = d * (float)sc;
+        const float ml = dmin * (float)mn;
+        const uint8_t *q = qs + 32 * (j >> 1);
+        for (int l = 0; l < 32; ++l) {
+            const int nib = (j & 1) ? (q[l] >> 4) : (q[l] & 15);
+            const int v = nib | (((qh[l] >> j) & 1) << 4);
+            out[32 * j + l] = dl * (float)v - ml;
+        }
+    }
+}
+
 static void dq_block(int type, const uint8_t *b, float *out) {
     switch (type) {
     case T_Q4_0: dq_q4_0(b, out); break;
     case T_Q8_0: dq_q8_0(b, out); break;
     case T_Q4_K: dq_q4_k(b, out); break;
+    case T_Q4_1: dq_q4_1(b, out); break;
+    case T_Q5_0: dq_q5_0(b, out); break;
+    case T_Q5_1: dq_q5_1(b, out); break;
+    case T_Q5_K: dq_q5_k(b, out); break;
     default:     dq_q6_k(b, out); break;
     }
 }

@@ -79,6 +79,10 @@ static inline bool skn_geometry(int32_t type, int32_t *elems, int32_t *bytes) {
     case SKN_TYPE_Q8_0: *elems = 32;  *bytes = 34;  return true;
     case SKN_TYPE_Q4_K: *elems = 256; *bytes = 144; return true;
     case SKN_TYPE_Q6_K: *elems = 256; *bytes = 210; return true;
+    case SKN_TYPE_Q4_1: *elems = 32;  *bytes = 20;  return true;
+    case SKN_TYPE_Q5_0: *elems = 32;  *bytes = 22;  return true;
+    case SKN_TYPE_Q5_1: *elems = 32;  *bytes = 24;  return true;
+    case SKN_TYPE_Q5_K: *elems = 256; *bytes = 176; return true;
     default: return false;
     }
 }

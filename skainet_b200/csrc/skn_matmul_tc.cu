@@ -608,7 +608,8 @@ static cudaError_t dispatch_tc(const __nv_bfloat16 *A, int M, int K, const skn_t
 }
 
 bool skn_tc_supported(const skn_tensor *w, int32_t M) {
-    return M >= 1 && (w->n_cols % TC_BK) == 0 && w->n_cols >= TC_BK && (w->n_rows % 8) == 0 && (w->pitch % 16) == 0 &&
+    const bool type_ok = w->type == SKN_TYPE_Q4_0 || w->type == SKN_TYPE_Q8_0 || w->type == SKN_TYPE_Q4_K || w->type == SKN_TYPE_Q6_K;
+    return type_ok && M >= 1 && (w->n_cols % TC_BK) == 0 && w->n_cols >= TC_BK && (w->n_rows % 8) == 0 && (w->pitch % 16) == 0 &&
            (reinterpret_cast<uintptr_t>(w->d_blocks) & 1) == 0;
 }
 

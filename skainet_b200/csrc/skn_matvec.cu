@@ -1057,6 +1057,10 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
     case SKN_TYPE_Q8_0: return launch_generic<SKN_TYPE_Q8_0>(w, x, M, bias, y, ctx->sm_count, stream);
     case SKN_TYPE_Q4_K: return launch_generic<SKN_TYPE_Q4_K>(w, x, M, bias, y, ctx->sm_count, stream);
     case SKN_TYPE_Q6_K: return launch_generic<SKN_TYPE_Q6_K>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q4_1: return launch_generic<SKN_TYPE_Q4_1>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q5_0: return launch_generic<SKN_TYPE_Q5_0>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q5_1: return launch_generic<SKN_TYPE_Q5_1>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q5_K: return launch_generic<SKN_TYPE_Q5_K>(w, x, M, bias, y, ctx->sm_count, stream);
     default: return cudaErrorInvalidValue;
     }
 }

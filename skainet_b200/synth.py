@@ -10,8 +10,14 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
-GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+Q4_1, Q5_0, Q5_1, Q5_K = 3, 6, 7, 13
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176)}
+# the four types of the benchmark configurations (streaming / tensor-core kernels) ...
 TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
+# ... and the further block types served by the dequantiser and the generic dequant-dot
+EXTRA_TYPE_NAMES = {Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K"}
+ALL_TYPE_NAMES = {**TYPE_NAMES, **EXTRA_TYPE_NAMES}
 
 
 def rng(seed: int) -> np.random.Generator:
@@ -44,6 +50,16 @@ def make_blocks(g: np.random.Generator, qtype: int, n_blocks: int) -> np.ndarray
         out[:, 0:192] = g.integers(0, 256, size=(n_blocks, 192), dtype=np.uint8)
         out[:, 192:208] = sc
         out[:, 208:210] = d
+    elif qtype in (Q4_1, Q5_0, Q5_1):
+        # fp16 scale (and min) as for Q4_0, every other byte uniform
+        out[:, :] = g.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+        out[:, 0:2] = _half_abs_normal(g, n_blocks, 0.01)
+        if qtype != Q5_0:
+            out[:, 2:4] = _half_abs_normal(g, n_blocks, 0.005)
+    elif qtype == Q5_K:
+        out[:, 0:2] = _half_abs_normal(g, n_blocks, 0.01)
+        out[:, 2:4] = _half_abs_normal(g, n_blocks, 0.005)
+        out[:, 4:176] = g.integers(0, 256, size=(n_blocks, 172), dtype=np.uint8)
     else:
         raise ValueError(f"unsupported type {qtype}")
     return out

@@ -5,7 +5,7 @@ import pytest
 from oracle import oracle
 from skainet_b200 import synth
 
-TYPES = list(synth.TYPE_NAMES.items())
+TYPES = list(synth.ALL_TYPE_NAMES.items())
 
 
 @pytest.mark.parametrize("qt,name", TYPES)
@@ -30,7 +30,8 @@ def test_two_restatements_agree_on_fresh_blocks(qt, name):
 
 def test_geometry_table():
     # Constants.kt:58-90
-    assert oracle.GEOMETRY == {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210)}
+    assert oracle.GEOMETRY == {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210),
+                               3: (32, 20), 6: (32, 22), 7: (32, 24), 13: (256, 176)}
     assert oracle.row_bytes(12, 4096) == 2304
     assert oracle.row_bytes(14, 14336) == 11760
     with pytest.raises(ValueError):
