@@ -45,12 +45,16 @@ extern "C" {
 #define SKN_TYPE_Q8_0 8
 #define SKN_TYPE_Q4_K 12
 #define SKN_TYPE_Q6_K 14
-/* Further block types of the reference's table (Constants.kt:62-70), served by the dequantiser
+/* Further block types of the reference's table (Constants.kt:62-80), served by the dequantiser
  * and the generic fused dequant-dot (any M, fp32); they have no streaming / tensor-core kernels. */
 #define SKN_TYPE_Q4_1 3   /* 32 weights, 20 bytes: d, m (fp16), 16 nibble bytes: q * d + m */
 #define SKN_TYPE_Q5_0 6   /* 32 weights, 22 bytes: d, 32 high bits, 16 nibble bytes: (q - 16) * d */
 #define SKN_TYPE_Q5_1 7   /* 32 weights, 24 bytes: d, m, 32 high bits, 16 nibble bytes: q * d + m */
 #define SKN_TYPE_Q5_K 13  /* 256 weights, 176 bytes: d, dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes */
+#define SKN_TYPE_Q2_K 10  /* 256 weights, 84 bytes: 16 scale/min nibble pairs, 64 bytes of 2-bit quants, d, dmin */
+#define SKN_TYPE_Q3_K 11  /* 256 weights, 110 bytes: 32 high-bit bytes, 64 bytes of 2-bit quants, 12 scale bytes, d */
+#define SKN_TYPE_IQ4_NL 20 /* 32 weights, 18 bytes: d, 16 nibble bytes indexing the 16-entry IQ4 codebook */
+#define SKN_TYPE_IQ4_XS 23 /* 256 weights, 136 bytes: d, 16 scale high bits, 4 scale nibble bytes, 128 codebook nibbles */
 
 typedef struct skn_ctx skn_ctx;
 typedef struct skn_tensor skn_tensor;

@@ -28,8 +28,10 @@ _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14  # Constants.kt:14-52
 Q4_1, Q5_0, Q5_1, Q5_K = 3, 6, 7, 13
+Q2_K, Q3_K, IQ4_NL, IQ4_XS = 10, 11, 20, 23
 GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
-            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176)}  # Constants.kt:58-90
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176),
+            Q2_K: (256, 84), Q3_K: (256, 110), IQ4_NL: (32, 18), IQ4_XS: (256, 136)}  # Constants.kt:58-90
 
 _lib = None
 
@@ -286,7 +288,65 @@ def np_dequant_q5_k(raw: np.ndarray) -> np.ndarray:
     return (dl * q - ml).reshape(-1)
 
 
-NP_DEQUANT = {Q4_0: np_dequant_q4_0, Q8_0: np_dequant_q8_0, Q4_K: np_dequant_q4_k, Q6_K: np_dequant_q6_k,
+def _crumbs256(qs: np.ndarray) -> np.ndarray:
+    """64 bytes per block -> 256 two-bit fields: weight 128h + 32s + l = (qs[32h + l] >> 2s) & 3."""
+    n = qs.shape[0]
+    q = qs.reshape(n, 2, 1, 32) >> (2 * np.arange(4, dtype=np.uint8))[None, None, :, None]
+    return (q & 3).reshape(n, 256)
+
+
+def np_dequant_q2_k(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 84)
+    n = b.shape[0]
+    d, dmin = _f16(b[:, 80:82])[:, None], _f16(b[:, 82:84])[:, None]
+    dl = (d * (b[:, 0:16] & 15).astype(np.float32))[:, :, None]
+    ml = (dmin * (b[:, 0:16] >> 4).astype(np.float32))[:, :, None]
+    q = _crumbs256(b[:, 16:80]).reshape(n, 16, 16).astype(np.float32)
+    return (dl * q - ml).reshape(-1)
+
+
+def np_dequant_q3_k(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 110)
+    n = b.shape[0]
+    d = _f16(b[:, 108:110])[:, None]
+    sp = b[:, 96:108]
+    i = np.arange(16)
+    lo = np.where(i < 8, sp[:, i & 7] & 15, sp[:, i & 7] >> 4)
+    hi = (sp[:, 8 + (i & 3)] >> (2 * (i >> 2)).astype(np.uint8)) & 3
+    sc = (lo | (hi << 4)).astype(np.int8) - np.int8(32)
+    dl = (d * sc.astype(np.float32))[:, :, None]
+    clear = ((b[:, None, 0:32] >> np.arange(8, dtype=np.uint8)[None, :, None]) & 1) ^ 1   # [n, g, l]
+    q = _crumbs256(b[:, 32:96]).astype(np.int8) - (clear.reshape(n, 256) << 2).astype(np.int8)
+    return (dl * q.reshape(n, 16, 16).astype(np.float32)).reshape(-1)
+
+
+# the 16-entry non-linear codebook of the IQ4 formats (part of the published format)
+IQ4_CODEBOOK = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int8)
+
+
+def np_dequant_iq4_nl(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 18)
+    d = _f16(b[:, 0:2])[:, None]
+    return (d * IQ4_CODEBOOK[_nib32(b[:, 2:18])].astype(np.float32)).reshape(-1)
+
+
+def np_dequant_iq4_xs(raw: np.ndarray) -> np.ndarray:
+    b = raw.reshape(-1, 136)
+    n = b.shape[0]
+    d = _f16(b[:, 0:2])[:, None]
+    sh = np.ascontiguousarray(b[:, 2:4]).view(np.uint16).reshape(n, 1)
+    i = np.arange(8)
+    lo = (b[:, 4:8][:, i >> 1] >> (4 * (i & 1)).astype(np.uint8)) & 15
+    hi = ((sh >> (2 * i).astype(np.uint16)) & 3).astype(np.uint8)
+    sc = (lo | (hi << 4)).astype(np.int8) - np.int8(32)
+    dl = (d * sc.astype(np.float32))[:, :, None]
+    qs = b[:, 8:136].reshape(n, 8, 16)
+    idx = np.concatenate([qs & 15, qs >> 4], axis=2)
+    return (dl * IQ4_CODEBOOK[idx].astype(np.float32)).reshape(-1)
+
+
+NP_DEQUANT = {Q2_K: np_dequant_q2_k, Q3_K: np_dequant_q3_k, IQ4_NL: np_dequant_iq4_nl, IQ4_XS: np_dequant_iq4_xs,
+              Q4_0: np_dequant_q4_0, Q8_0: np_dequant_q8_0, Q4_K: np_dequant_q4_k, Q6_K: np_dequant_q6_k,
               Q4_1: np_dequant_q4_1, Q5_0: np_dequant_q5_0, Q5_1: np_dequant_q5_1, Q5_K: np_dequant_q5_k}
 
 

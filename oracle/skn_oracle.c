@@ -33,7 +33,8 @@
 #endif
 
 /* GGML type ids, Constants.kt:14-52 */
-enum { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14 };
+enum { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13,
+       T_Q6_K = 14, T_IQ4_NL = 20, T_IQ4_XS = 23 };
 
 /* (elements per block, bytes per block): Constants.kt:58-90 */
 int skn_oracle_geometry(int type, int *elems, int *bytes) {
@@ -46,6 +47,10 @@ int skn_oracle_geometry(int type, int *elems, int *bytes) {
     case T_Q5_0: *elems = 32;  *bytes = 2 + 4 + 16; return 0;                 /* Constants.kt:63 */
     case T_Q5_1: *elems = 32;  *bytes = 2 + 2 + 4 + 16; return 0;             /* Constants.kt:64 */
     case T_Q5_K: *elems = 256; *bytes = 2 + 2 + 12 + 256 / 8 + 256 / 2; return 0; /* Constants.kt:70 */
+    case T_Q2_K: *elems = 256; *bytes = 2 + 2 + 256 / 16 + 256 / 4; return 0; /* Constants.kt:67 */
+    case T_Q3_K: *elems = 256; *bytes = 2 + 256 / 4 + 256 / 8 + 12; return 0; /* Constants.kt:68 */
+    case T_IQ4_NL: *elems = 32; *bytes = 2 + 16; return 0;                    /* Constants.kt:77 */
+    case T_IQ4_XS: *elems = 256; *bytes = 2 + 2 + 256 / 2 + 256 / 64; return 0; /* Constants.kt:80 */
     default: return -1;
     }
 }
@@ -209,6 +214,66 @@ static void dq_q5_k(const uint8_t *b, float *out) {
     }
 }
 
+/* Q2_K: 16 scale bytes (low nibble scale, high nibble min), 64 bytes of 2-bit quants, d, dmin.
+ * Weight 128h + 32s + l sits in byte qs[32h + l] at bit 2s; its scale byte is number (128h + 32s + l) / 16. */
+static void dq_q2_k(const uint8_t *b, float *out) {
+    const uint8_t *sc = b, *qs = b + 16;
+    const float d = half_to_float(rd16(b + 80)), dmin = half_to_float(rd16(b + 82));
+    for (int e = 0; e < 256; ++e) {
+        const int h = e >> 7, s = (e >> 5) & 3, l = e & 31;
+        const float dl = d * (float)(sc[e >> 4] & 15);
+        const float ml = dmin * (float)(sc[e >> 4] >> 4);
+        const int q = (qs[32 * h + l] >> (2 * s)) & 3;
+        out[e] = dl * (float)q - ml;
+    }
+}
+
+/* Q3_K: 32 bytes of high bits (bit g of hmask[l] belongs to weight 32g + l; a CLEAR bit subtracts 4),
+ * 64 bytes of 2-bit quants laid out as in Q2_K, 12 bytes holding sixteen 6-bit scales (offset 32), d.
+ * Scale i: low nibble from byte i & 7 (upper nibble when i >= 8), two high bits from byte 8 + (i & 3) at bit 2(i / 4). */
+static void dq_q3_k(const uint8_t *b, float *out) {
+    const uint8_t *hm = b, *qs = b + 32, *sp = b + 96;
+    const float d = half_to_float(rd16(b + 108));
+    for (int e = 0; e < 256; ++e) {
+        const int i = e >> 4, h = e >> 7, s = (e >> 5) & 3, l = e & 31, g = e >> 5;
+        const int lo = (i < 8) ? (sp[i] & 15) : (sp[i - 8] >> 4);
+        const int hi = (sp[8 + (i & 3)] >> (2 * (i >> 2))) & 3;
+        const float dl = d * (float)((lo | (hi << 4)) - 32);
+        const int q = ((qs[32 * h + l] >> (2 * s)) & 3) - ((((hm[l] >> g) & 1) ^ 1) << 2);
+        out[e] = dl * (float)q;
+    }
+}
+
+/* The 16-entry non-linear codebook of the IQ4 formats (part of the published format). */
+static const int8_t iq4_codebook[16] = { -127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113 };
+
+/* IQ4_NL: Q4_0's layout; the nibble indexes the codebook. */
+static void dq_iq4_nl(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b));
+    const uint8_t *qs = b + 2;
+    for (int e = 0; e < 16; ++e) {
+        out[e]      = d * (float)iq4_codebook[qs[e] & 15];
+        out[e + 16] = d * (float)iq4_codebook[qs[e] >> 4];
+    }
+}
+
+/* IQ4_XS: d, 16 bits of scale high parts (2 per sub-block), 4 bytes of scale low nibbles, 128 nibble bytes.
+ * Sub-block i (32 weights): bytes qs[16i .. 16i+15], low nibbles first; scale = (low | high << 4) - 32. */
+static void dq_iq4_xs(const uint8_t *b, float *out) {
+    const float d = half_to_float(rd16(b));
+    const uint32_t sh = rd16(b + 2);
+    const uint8_t *sl = b + 4, *qs = b + 8;
+    for (int i = 0; i < 8; ++i) {
+        const int lo = (sl[i >> 1] >> (4 * (i & 1))) & 15;
+        const int hi = (int)((sh >> (2 * i)) & 3u);
+        const float dl = d * (float)((lo | (hi << 4)) - 32);
+        for (int l = 0; l < 16; ++l) {
+            out[32 * i + l]      = dl * (float)iq4_codebook[qs[16 * i + l] & 15];
+            out[32 * i + l + 16] = dl * (float)iq4_codebook[qs[16 * i + l] >> 4];
+        }
+    }
+}
+
 static void dq_block(int type, const uint8_t *b, float *out) {
     switch (type) {
     case T_Q4_0: dq_q4_0(b, out); break;
@@ -218,6 +283,10 @@ static void dq_block(int type, const uint8_t *b, float *out) {
     case T_Q5_0: dq_q5_0(b, out); break;
     case T_Q5_1: dq_q5_1(b, out); break;
     case T_Q5_K: dq_q5_k(b, out); break;
+    case T_Q2_K: dq_q2_k(b, out); break;
+    case T_Q3_K: dq_q3_k(b, out); break;
+    case T_IQ4_NL: dq_iq4_nl(b, out); break;
+    case T_IQ4_XS: dq_iq4_xs(b, out); break;
     default:     dq_q6_k(b, out); break;
     }
 }

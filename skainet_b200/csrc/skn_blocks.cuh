@@ -6,6 +6,8 @@
 //   Q4_K        : group = sub-block j of a 144-byte super-block (8 per block)
 //   Q6_K        : group = (half h, quarter g) of a 210-byte super-block (8 per block)
 //   Q4_1 / Q5_0 / Q5_1 : group = block (20 / 22 / 24 bytes); Q5_K: sub-block of a 176-byte super-block
+//   Q2_K / Q3_K : group = (half h, bit pair s) of an 84- / 110-byte super-block (two 16-weight scale groups)
+//   IQ4_NL : group = block (18 bytes); IQ4_XS : sub-block of a 136-byte super-block
 // decode_group<T>() returns the 32 fp32 weights of one group, evaluated in the order that
 // makes them bit-identical to gguf-py: (d*sc)*q - dmin*m for Q4_K, (d*sc)*(q-32) for Q6_K,
 // q*d for Q8_0, (q-8)*d for Q4_0.  __fmul_rn / __fsub_rn keep the compiler from fusing or
@@ -22,6 +24,10 @@ template <> struct BlockTraits<SKN_TYPE_Q4_1> { static constexpr int ELEMS = 32,
 template <> struct BlockTraits<SKN_TYPE_Q5_0> { static constexpr int ELEMS = 32,  BYTES = 22;  };
 template <> struct BlockTraits<SKN_TYPE_Q5_1> { static constexpr int ELEMS = 32,  BYTES = 24;  };
 template <> struct BlockTraits<SKN_TYPE_Q5_K> { static constexpr int ELEMS = 256, BYTES = 176; };
+template <> struct BlockTraits<SKN_TYPE_Q2_K> { static constexpr int ELEMS = 256, BYTES = 84;  };
+template <> struct BlockTraits<SKN_TYPE_Q3_K> { static constexpr int ELEMS = 256, BYTES = 110; };
+template <> struct BlockTraits<SKN_TYPE_IQ4_NL> { static constexpr int ELEMS = 32,  BYTES = 18;  };
+template <> struct BlockTraits<SKN_TYPE_IQ4_XS> { static constexpr int ELEMS = 256, BYTES = 136; };
 
 __device__ __forceinline__ float skn_half_bits_to_float(uint32_t h) {
     return __half2float(__ushort_as_half((unsigned short)h));
@@ -167,5 +173,85 @@ __device__ __forceinline__ void decode_group<SKN_TYPE_Q5_K>(const uint8_t *row, 
     for (int l = 0; l < 32; ++l) {
         const int v = ((q[l] >> sh) & 15) | (((qh[l] >> j) & 1) << 4);
         w[l] = __fsub_rn(__fmul_rn(dl, (float)v), ml);
+    }
+}
+
+// Q2_K: weight 128h + 32s + l is bits 2s..2s+1 of byte qs[32h + l]; scale byte (128h + 32s + l) / 16 holds
+// the 4-bit scale (low nibble) and the 4-bit min (high nibble): (d*sc)*q - dmin*m
+template <>
+__device__ __forceinline__ void decode_group<SKN_TYPE_Q2_K>(const uint8_t *row, int64_t g, float (&w)[32]) {
+    const uint8_t *b = row + (g >> 3) * 84;
+    const int j = (int)(g & 7), h = j >> 2, sh = 2 * (j & 3);
+    const float d = skn_half_bits_to_float(skn_ld16(b + 80));
+    const float dmin = skn_half_bits_to_float(skn_ld16(b + 82));
+    const int s0 = b[2 * j], s1 = b[2 * j + 1];
+    const float dl0 = __fmul_rn(d, (float)(s0 & 15)), ml0 = __fmul_rn(dmin, (float)(s0 >> 4));
+    const float dl1 = __fmul_rn(d, (float)(s1 & 15)), ml1 = __fmul_rn(dmin, (float)(s1 >> 4));
+    const uint8_t *q = b + 16 + 32 * h;
+#pragma unroll
+    for (int l = 0; l < 32; ++l) {
+        const int v = (q[l] >> sh) & 3;
+        w[l] = __fsub_rn(__fmul_rn(l < 16 ? dl0 : dl1, (float)v), l < 16 ? ml0 : ml1);
+    }
+}
+
+// sixteen 6-bit scales (offset 32) of a Q3_K block from its 12 packed bytes
+__device__ __forceinline__ int skn_q3k_scale(const uint8_t *s, int i) {
+    const int lo = (i < 8) ? (s[i] & 15) : (s[i - 8] >> 4);
+    const int hi = (s[8 + (i & 3)] >> (2 * (i >> 2))) & 3;
+    return (lo | (hi << 4)) - 32;
+}
+
+// Q3_K: Q2_K's 2-bit layout; bit j of hmask[l] belongs to weight 32j + l and a CLEAR bit subtracts 4
+template <>
+__device__ __forceinline__ void decode_group<SKN_TYPE_Q3_K>(const uint8_t *row, int64_t g, float (&w)[32]) {
+    const uint8_t *b = row + (g >> 3) * 110;
+    const int j = (int)(g & 7), h = j >> 2, sh = 2 * (j & 3);
+    const float d = skn_half_bits_to_float(skn_ld16(b + 108));
+    const float dl0 = __fmul_rn(d, (float)skn_q3k_scale(b + 96, 2 * j));
+    const float dl1 = __fmul_rn(d, (float)skn_q3k_scale(b + 96, 2 * j + 1));
+    const uint8_t *hm = b, *q = b + 32 + 32 * h;
+#pragma unroll
+    for (int l = 0; l < 32; ++l) {
+        const int v = ((q[l] >> sh) & 3) - ((((hm[l] >> j) & 1) ^ 1) << 2);
+        w[l] = __fmul_rn(l < 16 ? dl0 : dl1, (float)v);
+    }
+}
+
+// entry i of the 16-entry non-linear IQ4 codebook (part of the published format), as two packed words
+__device__ __forceinline__ int skn_iq4_value(int i) {
+    const unsigned long long lo = 0xF6EADDCFBFAD9881ull;   // -127 -104 -83 -65 -49 -35 -22 -10
+    const unsigned long long hi = 0x7159453526190D01ull;   //    1   13  25  38  53  69  89 113
+    return (int)(signed char)(((i & 8) ? hi : lo) >> (8 * (i & 7)));
+}
+
+template <>
+__device__ __forceinline__ void decode_group<SKN_TYPE_IQ4_NL>(const uint8_t *row, int64_t g, float (&w)[32]) {
+    const uint8_t *b = row + g * 18;
+    const float d = skn_half_bits_to_float(skn_ld16(b));
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int v = b[2 + e];
+        w[e]      = __fmul_rn(d, (float)skn_iq4_value(v & 15));
+        w[e + 16] = __fmul_rn(d, (float)skn_iq4_value(v >> 4));
+    }
+}
+
+// IQ4_XS: sub-block j = bytes qs[16j .. 16j+15] (low nibbles first); 6-bit scale (offset 32) from
+// scales_l (nibble j) and scales_h (bits 2j, 2j+1)
+template <>
+__device__ __forceinline__ void decode_group<SKN_TYPE_IQ4_XS>(const uint8_t *row, int64_t g, float (&w)[32]) {
+    const uint8_t *b = row + (g >> 3) * 136;
+    const int j = (int)(g & 7);
+    const float d = skn_half_bits_to_float(skn_ld16(b));
+    const int lo = (b[4 + (j >> 1)] >> (4 * (j & 1))) & 15;
+    const int hi = (int)((skn_ld16(b + 2) >> (2 * j)) & 3u);
+    const float dl = __fmul_rn(d, (float)((lo | (hi << 4)) - 32));
+    const uint8_t *q = b + 8 + 16 * j;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int v = q[e];
+        w[e]      = __fmul_rn(dl, (float)skn_iq4_value(v & 15));
+        w[e + 16] = __fmul_rn(dl, (float)skn_iq4_value(v >> 4));
     }
 }

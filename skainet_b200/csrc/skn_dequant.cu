@@ -37,6 +37,10 @@ cudaError_t skn_launch_dequant(int32_t type, const uint8_t *blocks, int64_t pitc
     case SKN_TYPE_Q5_0: skn_dequant_kernel<SKN_TYPE_Q5_0><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
     case SKN_TYPE_Q5_1: skn_dequant_kernel<SKN_TYPE_Q5_1><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
     case SKN_TYPE_Q5_K: skn_dequant_kernel<SKN_TYPE_Q5_K><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_Q2_K: skn_dequant_kernel<SKN_TYPE_Q2_K><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_Q3_K: skn_dequant_kernel<SKN_TYPE_Q3_K><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_IQ4_NL: skn_dequant_kernel<SKN_TYPE_IQ4_NL><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
+    case SKN_TYPE_IQ4_XS: skn_dequant_kernel<SKN_TYPE_IQ4_XS><<<grid, block, 0, stream>>>(blocks, pitch, n_rows, gpr, out); break;
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
@@ -70,6 +74,10 @@ cudaError_t skn_launch_embed(const skn_tensor *emb, const int32_t *ids, int M, f
     case SKN_TYPE_Q5_0: skn_embed_kernel<SKN_TYPE_Q5_0><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
     case SKN_TYPE_Q5_1: skn_embed_kernel<SKN_TYPE_Q5_1><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
     case SKN_TYPE_Q5_K: skn_embed_kernel<SKN_TYPE_Q5_K><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_Q2_K: skn_embed_kernel<SKN_TYPE_Q2_K><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_Q3_K: skn_embed_kernel<SKN_TYPE_Q3_K><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_IQ4_NL: skn_embed_kernel<SKN_TYPE_IQ4_NL><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
+    case SKN_TYPE_IQ4_XS: skn_embed_kernel<SKN_TYPE_IQ4_XS><<<M, 128, 0, st>>>(emb->d_blocks, emb->pitch, emb->n_rows, gpr, ids, out); break;
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

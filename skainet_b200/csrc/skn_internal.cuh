@@ -83,6 +83,10 @@ static inline bool skn_geometry(int32_t type, int32_t *elems, int32_t *bytes) {
     case SKN_TYPE_Q5_0: *elems = 32;  *bytes = 22;  return true;
     case SKN_TYPE_Q5_1: *elems = 32;  *bytes = 24;  return true;
     case SKN_TYPE_Q5_K: *elems = 256; *bytes = 176; return true;
+    case SKN_TYPE_Q2_K: *elems = 256; *bytes = 84;  return true;
+    case SKN_TYPE_Q3_K: *elems = 256; *bytes = 110; return true;
+    case SKN_TYPE_IQ4_NL: *elems = 32;  *bytes = 18;  return true;
+    case SKN_TYPE_IQ4_XS: *elems = 256; *bytes = 136; return true;
     default: return false;
     }
 }

@@ -1061,6 +1061,10 @@ cudaError_t skn_launch_matvec(skn_ctx *ctx, const skn_tensor *w, const float *x,
     case SKN_TYPE_Q5_0: return launch_generic<SKN_TYPE_Q5_0>(w, x, M, bias, y, ctx->sm_count, stream);
     case SKN_TYPE_Q5_1: return launch_generic<SKN_TYPE_Q5_1>(w, x, M, bias, y, ctx->sm_count, stream);
     case SKN_TYPE_Q5_K: return launch_generic<SKN_TYPE_Q5_K>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q2_K: return launch_generic<SKN_TYPE_Q2_K>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_Q3_K: return launch_generic<SKN_TYPE_Q3_K>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_IQ4_NL: return launch_generic<SKN_TYPE_IQ4_NL>(w, x, M, bias, y, ctx->sm_count, stream);
+    case SKN_TYPE_IQ4_XS: return launch_generic<SKN_TYPE_IQ4_XS>(w, x, M, bias, y, ctx->sm_count, stream);
     default: return cudaErrorInvalidValue;
     }
 }

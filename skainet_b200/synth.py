@@ -11,12 +11,15 @@ import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
 Q4_1, Q5_0, Q5_1, Q5_K = 3, 6, 7, 13
+Q2_K, Q3_K, IQ4_NL, IQ4_XS = 10, 11, 20, 23
 GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
-            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176)}
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176),
+            Q2_K: (256, 84), Q3_K: (256, 110), IQ4_NL: (32, 18), IQ4_XS: (256, 136)}
 # the four types of the benchmark configurations (streaming / tensor-core kernels) ...
 TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
 # ... and the further block types served by the dequantiser and the generic dequant-dot
-EXTRA_TYPE_NAMES = {Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K"}
+EXTRA_TYPE_NAMES = {Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K",
+                    Q2_K: "Q2_K", Q3_K: "Q3_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS"}
 ALL_TYPE_NAMES = {**TYPE_NAMES, **EXTRA_TYPE_NAMES}
 
 
@@ -60,6 +63,16 @@ def make_blocks(g: np.random.Generator, qtype: int, n_blocks: int) -> np.ndarray
         out[:, 0:2] = _half_abs_normal(g, n_blocks, 0.01)
         out[:, 2:4] = _half_abs_normal(g, n_blocks, 0.005)
         out[:, 4:176] = g.integers(0, 256, size=(n_blocks, 172), dtype=np.uint8)
+    elif qtype in (Q2_K, Q3_K, IQ4_NL, IQ4_XS):
+        # fp16 super-block scale(s) where the format keeps them, every other byte uniform
+        out[:, :] = g.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+        if qtype == Q2_K:
+            out[:, 80:82] = _half_abs_normal(g, n_blocks, 0.01)
+            out[:, 82:84] = _half_abs_normal(g, n_blocks, 0.005)
+        elif qtype == Q3_K:
+            out[:, 108:110] = _half_abs_normal(g, n_blocks, 0.01)
+        else:
+            out[:, 0:2] = _half_abs_normal(g, n_blocks, 0.0003 if qtype == IQ4_XS else 0.001)
     else:
         raise ValueError(f"unsupported type {qtype}")
     return out

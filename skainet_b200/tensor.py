@@ -28,15 +28,20 @@ SKN_ERR_CUDA, SKN_ERR_TIMEOUT, SKN_ERR_BAD_HANDLE, SKN_ERR_ARG, SKN_ERR_COMM = 5
 
 class GGMLQuantizationType(enum.IntEnum):
     """Constants.kt:14-52 (the block types this backend runs: the four of the hot path with their
-    own kernels, and Q4_1 / Q5_0 / Q5_1 / Q5_K on the dequantiser and the generic dequant-dot)."""
+    own kernels, and Q4_1 / Q5_0 / Q5_1 / Q5_K / Q2_K / Q3_K / IQ4_NL / IQ4_XS on the dequantiser and
+    the generic dequant-dot)."""
     Q4_0 = 2
     Q4_1 = 3
     Q5_0 = 6
     Q5_1 = 7
     Q8_0 = 8
+    Q2_K = 10
+    Q3_K = 11
     Q4_K = 12
     Q5_K = 13
     Q6_K = 14
+    IQ4_NL = 20
+    IQ4_XS = 23
 
 
 QK_K = 256  # Constants.kt:55
@@ -49,6 +54,10 @@ GGML_QUANT_SIZES = {  # Constants.kt:58-90
     GGMLQuantizationType.Q5_0: (32, 2 + 4 + 16),
     GGMLQuantizationType.Q5_1: (32, 2 + 2 + 4 + 16),
     GGMLQuantizationType.Q5_K: (256, 2 + 2 + 12 + QK_K // 8 + QK_K // 2),
+    GGMLQuantizationType.Q2_K: (256, 2 + 2 + QK_K // 16 + QK_K // 4),
+    GGMLQuantizationType.Q3_K: (256, 2 + QK_K // 4 + QK_K // 8 + 12),
+    GGMLQuantizationType.IQ4_NL: (32, 2 + 16),
+    GGMLQuantizationType.IQ4_XS: (256, 2 + 2 + QK_K // 2 + QK_K // 64),
 }
 
 

@@ -3,7 +3,7 @@ reference's gguf module says it is transliterating: Constants.kt:3-6, Quants.kt:
 
 Run in a container that has `gguf` 0.19.0 importable:
     python tests/golden/make_golden.py
-For each of Q4_0 / Q8_0 / Q4_K / Q6_K and Q4_1 / Q5_0 / Q5_1 / Q5_K the file holds raw blocks (uint8) and the fp32
+For each of Q4_0 / Q8_0 / Q4_K / Q6_K and Q4_1 / Q5_0 / Q5_1 / Q5_K / Q2_K / Q3_K / IQ4_NL / IQ4_XS the file holds raw blocks (uint8) and the fp32
 values `gguf.quants.dequantize` returns for them: 48 seeded random blocks with the
 benchmark's value distributions, 8 blocks of uniformly random bytes with a finite
 fp16 scale, and hand-built edge blocks (all-zero, all-ones bits, subnormal / negative /
@@ -22,10 +22,12 @@ from gguf import quants  # noqa: E402
 from gguf.constants import GGMLQuantizationType as T  # noqa: E402
 
 GG = {synth.Q4_0: T.Q4_0, synth.Q8_0: T.Q8_0, synth.Q4_K: T.Q4_K, synth.Q6_K: T.Q6_K,
-      synth.Q4_1: T.Q4_1, synth.Q5_0: T.Q5_0, synth.Q5_1: T.Q5_1, synth.Q5_K: T.Q5_K}
+      synth.Q4_1: T.Q4_1, synth.Q5_0: T.Q5_0, synth.Q5_1: T.Q5_1, synth.Q5_K: T.Q5_K,
+      synth.Q2_K: T.Q2_K, synth.Q3_K: T.Q3_K, synth.IQ4_NL: T.IQ4_NL, synth.IQ4_XS: T.IQ4_XS}
 # byte offsets of the fp16 fields per type
 F16_FIELDS = {synth.Q4_0: [0], synth.Q8_0: [0], synth.Q4_K: [0, 2], synth.Q6_K: [208],
-              synth.Q4_1: [0, 2], synth.Q5_0: [0], synth.Q5_1: [0, 2], synth.Q5_K: [0, 2]}
+              synth.Q4_1: [0, 2], synth.Q5_0: [0], synth.Q5_1: [0, 2], synth.Q5_K: [0, 2],
+              synth.Q2_K: [80, 82], synth.Q3_K: [108], synth.IQ4_NL: [0], synth.IQ4_XS: [0]}
 EDGE_HALVES = [0x0000, 0x0001, 0x03FF, 0x0400, 0x7BFF, 0x8001, 0xBC00, 0x3C00]  # 0, subnormals, min normal, max, -sub, -1, 1
 
 

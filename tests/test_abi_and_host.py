@@ -39,7 +39,7 @@ def test_version_and_geometry():
     for t, (ee, bb) in skn.GGML_QUANT_SIZES.items():
         assert L.skn_quant_geometry(int(t), ctypes.byref(e), ctypes.byref(b)) == 0
         assert (e.value, b.value) == (ee, bb)
-    assert L.skn_quant_geometry(10, ctypes.byref(e), ctypes.byref(b)) == 2  # SKN_ERR_TYPE (Q2_K not built)
+    assert L.skn_quant_geometry(16, ctypes.byref(e), ctypes.byref(b)) == 2  # SKN_ERR_TYPE (IQ2_XXS not built)
     rb = ctypes.c_int64()
     assert L.skn_quant_row_bytes(12, 4096, ctypes.byref(rb)) == 0 and rb.value == 2304
     assert L.skn_quant_row_bytes(12, 4000, ctypes.byref(rb)) == 1           # SKN_ERR_SHAPE

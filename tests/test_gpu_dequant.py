@@ -67,5 +67,5 @@ def test_upload_errors(ctx):
     with pytest.raises(ValueError, match="byte length"):
         skn.QuantTensor(ctx, (3, 256), synth.Q4_K, w)
     with pytest.raises(skn.SknError) as ei:
-        skn.QuantTensor(ctx, (2, 256), 10, w)   # Q2_K: in the reference's table, not built here
+        skn.QuantTensor(ctx, (2, 256), 16, w)   # IQ2_XXS: in the reference's table, not built here
     assert ei.value.code == 2

@@ -220,7 +220,7 @@ def test_fused_norm_and_swiglu_preparation(ctx):
 @pytest.mark.parametrize("qt,name", list(synth.EXTRA_TYPE_NAMES.items()))
 @pytest.mark.parametrize("M", [1, 3, 16])
 def test_further_block_types_on_the_generic_kernel(ctx, qt, name, M):
-    """Q4_1 / Q5_0 / Q5_1 / Q5_K have no streaming or tensor-core kernel: every M runs the generic
+    """Q4_1 / Q5_0 / Q5_1 / Q5_K / Q2_K / Q3_K / IQ4_NL / IQ4_XS have no streaming or tensor-core kernel: every M runs the generic
     fused dequant-dot in fp32 (also from the prefill threshold on)."""
     run_case(ctx, qt, 96, 1024, M, seed=300 + qt, bias=(M == 3))
     run_case(ctx, qt, 40, 256, M, seed=400 + qt)

@@ -31,7 +31,8 @@ def test_two_restatements_agree_on_fresh_blocks(qt, name):
 def test_geometry_table():
     # Constants.kt:58-90
     assert oracle.GEOMETRY == {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210),
-                               3: (32, 20), 6: (32, 22), 7: (32, 24), 13: (256, 176)}
+                               3: (32, 20), 6: (32, 22), 7: (32, 24), 13: (256, 176),
+                               10: (256, 84), 11: (256, 110), 20: (32, 18), 23: (256, 136)}
     assert oracle.row_bytes(12, 4096) == 2304
     assert oracle.row_bytes(14, 14336) == 11760
     with pytest.raises(ValueError):
