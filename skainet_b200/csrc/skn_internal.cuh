@@ -46,6 +46,7 @@ struct skn_ctx {
     void *d_scratch2;  size_t d_scratch2_bytes;  // attention split partials
     skn_group_plan group_plans[32];
     int n_group_plans;
+    uint32_t attn_stream_cfg;   // bit per (head_dim, group size): the streamed attention kernel's attributes are set on this device
     char err[512];
 };
 

@@ -20,8 +20,10 @@
 //
 // HBM-bound: 2 * head_dim * 4 bytes per cached token per kv head, read exactly once.
 #include "skn_internal.cuh"
+#include "skn_ptx.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 #include <new>
 
 struct skn_kvcache {
@@ -221,6 +223,20 @@ template <> struct VecLoad<4> {
 template <> struct VecLoad<2> {
     static __device__ __forceinline__ void ld(const float *p, float (&r)[2]) {
         const float2 v = __ldg(reinterpret_cast<const float2 *>(p));
+        r[0] = v.x; r[1] = v.y;
+    }
+};
+// the same from shared memory (plain vector loads)
+template <int VEC> struct VecLds;
+template <> struct VecLds<4> {
+    static __device__ __forceinline__ void ld(const float *p, float (&r)[4]) {
+        const float4 v = *reinterpret_cast<const float4 *>(p);
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    }
+};
+template <> struct VecLds<2> {
+    static __device__ __forceinline__ void ld(const float *p, float (&r)[2]) {
+        const float2 v = *reinterpret_cast<const float2 *>(p);
         r[0] = v.x; r[1] = v.y;
     }
 };
@@ -445,24 +461,266 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
 
+// The same split attention for long contexts (256-token chunks, grids of several CTAs per SM: the
+// bandwidth-bound regime), fed by bulk async copies instead of per-lane global loads.  All tokens
+// of a (sequence, kv head) are contiguous in the ring, so a tile of ATT_WARPS * TT tokens is one
+// copy (two where the ring wraps).  A producer warp streams the chunk's K tiles and then its V tiles
+// through `nst` stages of shared memory (full / empty mbarriers); the four compute warps read their
+// tokens of a tile from shared memory.  V tiles are already on their way while the scores, the
+// chunk maximum and the probabilities are computed, so HBM stays busy across the two passes.
+// Writes the (max, sum, unnormalised output) record per (head, split); the merge kernel follows.
+template <int D, int G, int TT>
+__global__ void __launch_bounds__((ATT_WARPS + 1) * 32)
+skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
+                       const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
+                       float scale, float *__restrict__ part, int S, int tq, int len_extra, int nst,
+                       int32_t *__restrict__ status) {
+    constexpr int CHUNK = ATT_CHUNK;
+    constexpr int VEC = D / 32;
+    constexpr int NV = TT * G;
+    constexpr int REP = 32 / NV;
+    constexpr int TILE = ATT_WARPS * TT;             // tokens per stage
+    constexpr int TILE_BYTES = TILE * D * 4;
+    extern __shared__ __align__(128) uint8_t att_smem[];
+    __shared__ float s_sc[CHUNK][G];
+    __shared__ float s_red[ATT_WARPS][G];
+    __shared__ float s_m[G], s_l[G];
+    __shared__ float s_o[ATT_WARPS][G][D];
+    uint64_t *full = reinterpret_cast<uint64_t *>(att_smem + (size_t)nst * TILE_BYTES);
+    uint64_t *empty = full + nst;
+
+    const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int L = max(0, len[b] + len_extra - (tq - 1 - bq % tq));
+    const int t0 = sp * CHUNK;
+    if (t0 >= L) return;
+    const int nt = min(CHUNK, L - t0);
+    const int ntile = (nt + TILE - 1) / TILE;
+    const int s0 = start[b];
+    const int Hq = Hkv * G;
+    const size_t head = ((size_t)b * Hkv + kvh) * cap * D;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < nst; ++i) {
+            skn_mbar_init(&full[i], 1);
+            skn_mbar_init(&empty[i], ATT_WARPS);
+        }
+        skn_fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == ATT_WARPS) {
+        // ---- producer: K tiles 0 .. ntile-1, then V tiles 0 .. ntile-1 ----
+        if (lane == 0) {
+            bool failed = false;
+            for (int i = 0; i < 2 * ntile; ++i) {
+                const int stg = i % nst;
+                if (i >= nst && !failed && !skn_mbar_wait(&empty[stg], (uint32_t)(i / nst - 1) & 1u)) {
+                    failed = true;
+                    atomicExch(status, SKN_ERR_TIMEOUT);
+                }
+                const int tile = i < ntile ? i : i - ntile;
+                const float *src = (i < ntile ? kc : vc) + head;
+                const int ntok = min(TILE, nt - tile * TILE);
+                const int slot0 = (s0 + t0 + tile * TILE) % cap;
+                const int n1 = min(ntok, cap - slot0);          // tokens before the ring wraps
+                uint8_t *dst = att_smem + (size_t)stg * TILE_BYTES;
+                skn_fence_proxy_async();
+                skn_mbar_expect_tx(&full[stg], (uint32_t)ntok * D * 4);
+                skn_bulk_g2s(dst, src + (size_t)slot0 * D, (uint32_t)n1 * D * 4, &full[stg]);
+                if (ntok > n1) skn_bulk_g2s(dst + (size_t)n1 * D * 4, src, (uint32_t)(ntok - n1) * D * 4, &full[stg]);
+            }
+        }
+        return;
+    }
+
+    float qv[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        VecLoad<VEC>::ld(q + ((size_t)bq * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qv[g][e] *= scale;
+    }
+    bool failed = false;
+    auto wait_full = [&](int i) {
+        if (!failed && !skn_mbar_wait(&full[i % nst], (uint32_t)(i / nst) & 1u)) {
+            failed = true;
+            atomicExch(status, SKN_ERR_TIMEOUT);
+        }
+    };
+    auto tile_row = [&](int i, int local) -> const float * {
+        return reinterpret_cast<const float *>(att_smem + (size_t)(i % nst) * TILE_BYTES) + (size_t)local * D + lane * VEC;
+    };
+
+    // ---- pass 1: scores ------------------------------------------------------------------
+    float mrun = -INFINITY;
+    const int vidx = lane / REP;
+    const int my_j = vidx / G, my_g = vidx % G;
+    for (int ti = 0; ti < ntile; ++ti) {
+        wait_full(ti);
+        const int tl = ti * TILE + warp * TT;             // first token of this warp within the chunk
+        const int last = min(TILE, nt - ti * TILE) - 1;   // last valid token of the tile
+        if (tl < nt) {
+            float kr[TT][VEC];
+#pragma unroll
+            for (int j = 0; j < TT; ++j) {
+                VecLds<VEC>::ld(tile_row(ti, min(warp * TT + j, last)), kr[j]);
+            }
+            float pv[NV];
+#pragma unroll
+            for (int j = 0; j < TT; ++j)
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) a = fmaf(qv[g][e], kr[j][e], a);
+                    pv[j * G + g] = a;
+                }
+            const float sc = warp_transpose_reduce<NV>(pv, lane);
+            if (tl + my_j < nt) {
+                if ((lane % REP) == 0) s_sc[tl + my_j][my_g] = sc;
+                mrun = fmaxf(mrun, sc);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) skn_mbar_arrive(&empty[ti % nst]);
+    }
+    constexpr int NT = ATT_WARPS * 32;
+    auto bar = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory"); };
+#pragma unroll
+    for (int o = 16; o >= REP * G; o >>= 1) mrun = fmaxf(mrun, __shfl_xor_sync(0xffffffffu, mrun, o));
+    if (lane < REP * G && (lane % REP) == 0) s_red[warp][lane / REP] = mrun;
+    bar();
+    if (threadIdx.x < G) {
+        float m = s_red[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; ++w) m = fmaxf(m, s_red[w][threadIdx.x]);
+        s_m[threadIdx.x] = m;
+    }
+    bar();
+    float lsum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) lsum[g] = 0.f;
+    for (int t = threadIdx.x; t < nt; t += NT) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float p = expf(s_sc[t][g] - s_m[g]);
+            s_sc[t][g] = p;
+            lsum[g] += p;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum[g] += __shfl_xor_sync(0xffffffffu, lsum[g], o);
+    }
+    bar();                      // s_red is reused
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) s_red[warp][g] = lsum[g];
+    }
+    bar();
+    if (threadIdx.x < G) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) l += s_red[w][threadIdx.x];
+        s_l[threadIdx.x] = l;
+    }
+
+    // ---- pass 2: probabilities x V ---------------------------------------------------------
+    float o[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[g][e] = 0.f;
+    for (int ti = 0; ti < ntile; ++ti) {
+        const int i = ntile + ti;
+        wait_full(i);
+        const int tl = ti * TILE + warp * TT;
+        if (tl < nt) {
+#pragma unroll
+            for (int j = 0; j < TT; ++j) {
+                if (tl + j < nt) {
+                    float vr[VEC];
+                    VecLds<VEC>::ld(tile_row(i, warp * TT + j), vr);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float pr = s_sc[tl + j][g];
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) o[g][e] = fmaf(pr, vr[e], o[g][e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) skn_mbar_arrive(&empty[i % nst]);
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s_o[warp][g][lane * VEC + e] = o[g][e];
+    bar();
+    for (int i = threadIdx.x; i < G * D; i += NT) {
+        const int g = i / D, d = i % D;
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) a += s_o[w][g][d];
+        float *rec = part + (((size_t)bq * Hq + kvh * G + g) * S + sp) * (D + 2);
+        rec[2 + d] = a;
+        if (d == 0) { rec[0] = s_m[g]; rec[1] = s_l[g]; }
+    }
+}
+
+// Log-sum-exp merge of the splits of one (query, head): D threads.  The splits' maxima and sums are
+// reduced across the block first; every thread then adds up its output element with the loads of eight
+// splits in flight at a time (the records sit in L2: the loop is bound by their latency).
 template <int D>
-__global__ void skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
-                                      float *__restrict__ out, int tq, int chunk, int len_extra) {
+__global__ void __launch_bounds__(D)
+skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
+                      float *__restrict__ out, int tq, int chunk, int len_extra) {
     const int h = blockIdx.x, b = blockIdx.y;          // b = sequence * tq + t
     const int L = max(0, len[b / tq] + len_extra - (tq - 1 - b % tq));
     const int ns = (L + chunk - 1) / chunk;
+    const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    constexpr int NW = D / 32;
     const float *rec = part + ((size_t)b * Hq + h) * S * (D + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < ns; ++s) m = fmaxf(m, rec[(size_t)s * (D + 2)]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float l = 0.f, a = 0.f;
-        for (int s = 0; s < ns; ++s) {
-            const float w = expf(rec[(size_t)s * (D + 2)] - m);
-            l = fmaf(rec[(size_t)s * (D + 2) + 1], w, l);
-            a = fmaf(rec[(size_t)s * (D + 2) + 2 + d], w, a);
-        }
-        out[((size_t)b * Hq + h) * D + d] = ns > 0 ? a / l : 0.f;
+    __shared__ float s_red[2][NW];
+    if (ns == 0) {
+        out[((size_t)b * Hq + h) * D + d] = 0.f;
+        return;
     }
+    float m = -INFINITY;
+    for (int s = d; s < ns; s += D) m = fmaxf(m, rec[(size_t)s * (D + 2)]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) s_red[0][warp] = m;
+    __syncthreads();
+    m = s_red[0][0];
+#pragma unroll
+    for (int w = 1; w < NW; ++w) m = fmaxf(m, s_red[0][w]);
+    float l = 0.f;
+    for (int s = d; s < ns; s += D) l = fmaf(rec[(size_t)s * (D + 2) + 1], expf(rec[(size_t)s * (D + 2)] - m), l);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) s_red[1][warp] = l;
+    __syncthreads();
+    l = s_red[1][0];
+#pragma unroll
+    for (int w = 1; w < NW; ++w) l += s_red[1][w];
+    float a = 0.f;
+    for (int s0 = 0; s0 < ns; s0 += 8) {
+        float v[8], e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int ss = min(s0 + k, ns - 1);
+            v[k] = rec[(size_t)ss * (D + 2) + 2 + d];
+            e[k] = rec[(size_t)ss * (D + 2)];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (s0 + k < ns) a = fmaf(v[k], expf(e[k] - m), a);
+    }
+    out[((size_t)b * Hq + h) * D + d] = a / l;
 }
 
 template <int D, int G>
@@ -476,7 +734,25 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
     const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
     unsigned *tickets = (tq == 1 && small_grid && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
-    if (chunk == 32)
+    static const int stream_on = [] { const char *v = getenv("SKN_ATTN_STREAM"); return v ? atoi(v) : 1; }();
+    if (chunk == ATT_CHUNK && !tickets && stream_on) {
+        // long contexts: tiles by bulk async copy through a shared-memory ring
+        constexpr int TILE_BYTES = ATT_WARPS * TT * D * 4;
+        // two stages: measured, more resident CTAs per SM (five at 44 KB each for D = 128, G = 4) beat a deeper ring
+        static const int nst_env = [] { const char *v = getenv("SKN_ATTN_NST"); return v ? atoi(v) : 0; }();
+        const int nst = (nst_env >= 2 && nst_env <= 6) ? nst_env : 2;
+        const size_t smem = (size_t)nst * TILE_BYTES + 2 * (size_t)nst * sizeof(uint64_t);
+        auto kern = skn_attn_stream_kernel<D, G, TT>;
+        const uint32_t cfg_bit = 1u << ((D == 128 ? 4 : 0) + (G == 1 ? 0 : (G == 2 ? 1 : (G == 4 ? 2 : 3))));
+        if (!(kv->ctx->attn_stream_cfg & cfg_bit)) {
+            cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(100 * 1024));
+            if (e0 == cudaSuccess) e0 = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e0 != cudaSuccess) return e0;
+            kv->ctx->attn_stream_cfg |= cfg_bit;
+        }
+        kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
+                                                          scale, part, S, tq, len_extra, nst, kv->ctx->d_status);
+    } else if (chunk == 32)
         skn_attn_split_kernel<D, G, TT, 32><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
                                                                                 kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else if (chunk == 64)

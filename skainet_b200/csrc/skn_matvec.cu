@@ -941,7 +941,8 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
     // a single activation row: Q4_K on the tensor-core kernel, the 32-weight-block formats on
     // their CUDA-core streaming kernels (the same routes skn_launch_matvec takes, so grouped and
     // separate launches give identical bits)
-    if (w[0]->type == SKN_TYPE_Q4_K && skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
+    static const int q6k_mma = env_int("SKN_MM_Q6K", 1);
+    if ((w[0]->type == SKN_TYPE_Q4_K || (q6k_mma && w[0]->type == SKN_TYPE_Q6_K)) && skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
     bool took = false;
     switch (w[0]->type) {
     case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
@@ -969,7 +970,9 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
     // the 32-weight-block formats take this route from two activation rows on (a single row is as
     // fast or faster on their CUDA-core streaming kernels)
     static const int simple_min_m = env_int("SKN_MM_SIMPLE_MIN_M", 2);
-    if (w[0]->type != SKN_TYPE_Q4_K && M < simple_min_m) return cudaErrorNotSupported;
+    static const int q6k_mma = env_int("SKN_MM_Q6K", 1);
+    if (w[0]->type == SKN_TYPE_Q6_K && !q6k_mma) return cudaErrorNotSupported;
+    if (w[0]->type != SKN_TYPE_Q4_K && w[0]->type != SKN_TYPE_Q6_K && M < simple_min_m) return cudaErrorNotSupported;
     const int launches = (M + maxa - 1) / maxa;
     const int64_t K = w[0]->n_cols;
     if (xc && launches != 1) return cudaErrorNotSupported;      // an exchange covers all rows of one launch

@@ -39,14 +39,19 @@
 // 32-weight blocks of Q8_0 / Q4_0 (each with its own fp16 scale).  KS super-blocks (one bulk copy
 // per row) make a K super-chunk; rows are padded by 32 bytes in shared memory, which puts the
 // eight row groups of a fragment load on disjoint banks (row stride = 8 words mod 32).
-constexpr int MM_FMT_Q4K = 0, MM_FMT_Q80 = 1, MM_FMT_Q40 = 2;
+// Q6_K: one 210-byte block per super-block; eight of them are 1680 bytes = a multiple of 16 (a bulk
+// copy's granularity), padded by 16 to the same 8-words-mod-32 row stride.  Its scale groups are 16
+// weights, so the group sums of x are kept per 16 activations (XS per super-block).
+constexpr int MM_FMT_Q4K = 0, MM_FMT_Q80 = 1, MM_FMT_Q40 = 2, MM_FMT_Q6K = 3;
 template <int FMT> struct MmFmt;
-template <> struct MmFmt<MM_FMT_Q4K> { static constexpr int KS = 16, SB_BYTES = 144; };
-template <> struct MmFmt<MM_FMT_Q80> { static constexpr int KS = 8, SB_BYTES = 272; };
-template <> struct MmFmt<MM_FMT_Q40> { static constexpr int KS = 16, SB_BYTES = 144; };
-static constexpr int mm_ks(int fmt) { return fmt == MM_FMT_Q80 ? 8 : 16; }
-static constexpr int mm_sb_bytes(int fmt) { return fmt == MM_FMT_Q80 ? 272 : 144; }
-static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + 32); }
+template <> struct MmFmt<MM_FMT_Q4K> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 32, XS = 8; };
+template <> struct MmFmt<MM_FMT_Q80> { static constexpr int KS = 8, SB_BYTES = 272, PAD = 32, XS = 8; };
+template <> struct MmFmt<MM_FMT_Q40> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 32, XS = 8; };
+template <> struct MmFmt<MM_FMT_Q6K> { static constexpr int KS = 8, SB_BYTES = 210, PAD = 16, XS = 16; };
+static constexpr int mm_ks(int fmt) { return (fmt == MM_FMT_Q80 || fmt == MM_FMT_Q6K) ? 8 : 16; }
+static constexpr int mm_sb_bytes(int fmt) { return fmt == MM_FMT_Q80 ? 272 : (fmt == MM_FMT_Q6K ? 210 : 144); }
+static constexpr int mm_xs(int fmt) { return fmt == MM_FMT_Q6K ? 16 : 8; }
+static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + (fmt == MM_FMT_Q6K ? 16 : 32)); }
 
 __device__ __forceinline__ void skn_mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
@@ -67,6 +72,17 @@ __device__ __forceinline__ float mm_byte_f(uint32_t w, uint32_t i) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u + i)) - 8388608.f;
 }
 __device__ __forceinline__ int mm_byte_i(uint32_t w, uint32_t i) { return (int)__byte_perm(w, 0u, 0x4440u + i); }
+// signed byte i of w, sign-extended (selector values 8..15 replicate a byte's sign bit)
+// (the __byte_perm intrinsic only honours three bits per selector, so the instruction is spelled out)
+__device__ __forceinline__ int mm_sbyte_i(uint32_t w, uint32_t i) {
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"(0x8880u + 0x1111u * i));
+    return r;
+}
+// signed byte i of w as a float, w given with its bytes' sign bits flipped: (2^23 + 128 + b) - (2^23 + 128)
+__device__ __forceinline__ float mm_sbyte_f(uint32_t w_flipped, uint32_t i) {
+    return __uint_as_float(__byte_perm(w_flipped, 0x4B000000u, 0x7440u + i)) - 8388736.f;
+}
 
 // loads from a 32-bit shared-memory address (explicit state space: no generic addressing, no
 // 64-bit address arithmetic in the inner loops)
@@ -109,15 +125,31 @@ __device__ __forceinline__ void mm_bar_sync(int id, int nthreads) {
 // One super-block (256 activations, two float4 per lane: elements 4*lane.. and 128 + 4*lane..)
 // -> three digit planes (byte k of a plane = that digit of activation k), the scale 2^(e-21)
 // (NaN when the block holds a NaN or an infinity) and the eight 32-element sums.
+// XS16: sixteen 16-element sums instead of the eight 32-element ones.
+template <bool XS16>
 static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4 v1, int sbi, int lane, uint8_t *dig, int PL,
                                                    float *sgrp, float *xsum) {
     float mx = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                      fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
     float s0 = (v0.x + v0.y) + (v0.z + v0.w), s1 = (v1.x + v1.y) + (v1.z + v1.w);
+    if constexpr (XS16) {
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        for (int o = 2; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        }
+        if ((lane & 3) == 0) {
+            xsum[sbi * 16 + (lane >> 2)] = s0;
+            xsum[sbi * 16 + 8 + (lane >> 2)] = s1;
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
+    } else {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        }
     }
     // mx >= 0 (or NaN-free by fmaxf): its bit pattern orders like the value, one integer reduction
     mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
@@ -143,7 +175,7 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
         *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * f) = a;
         *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * (f + 32)) = b;
     }
-    if ((lane & 7) == 0) {
+    if (!XS16 && (lane & 7) == 0) {
         xsum[sbi * 8 + (lane >> 3)] = s0;
         xsum[sbi * 8 + 4 + (lane >> 3)] = s1;
     }
@@ -156,16 +188,28 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
 //
 // Several activation rows per launch: one MMA serves TWO rows (digit columns 0..2 and 3..5 of the
 // B operand), NP such pairs share the A fragments, block headers and scale decoding.
-template <int FMT, int SPW, int NP, bool ODD>   // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs;
+//
+// FEAT selects what is compiled in besides the product and the bias / residual add: 0 nothing, 1 the
+// fused preparations of x (RMSNorm gain, silu(x) * u) and the SwiGLU epilogue, 2 those and the
+// rotary-embedding / cache epilogue, 3 those and the tensor-parallel exchange.  The plain variant
+// is the fastest: the instruction footprint of the unused paths costs instruction-cache misses
+// (15 % on a 4096 x 4096 launch).
+template <int FMT, int SPW, int NP, bool ODD, int FEAT>   // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs;
                                                 // ODD: the last pair has one row only (its odd columns are skipped)
 __global__ void __launch_bounds__(MmFmt<FMT>::KS / SPW == 16 ? 544 : (MmFmt<FMT>::KS / SPW == 8 ? 320 : 256),
                                   (MmFmt<FMT>::KS / SPW == 16 || NP > 1) ? 1 : 2)
 skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const float *__restrict__ x,
                int32_t *__restrict__ status, int relaxed) {
     constexpr int MM_KS = MmFmt<FMT>::KS, MM_BLOCK_BYTES = MmFmt<FMT>::SB_BYTES;
-    constexpr int MM_ROW_STRIDE = MM_KS * MM_BLOCK_BYTES + 32, MM_STAGE = 16 * MM_ROW_STRIDE;
+    constexpr int MM_ROW_STRIDE = MM_KS * MM_BLOCK_BYTES + MmFmt<FMT>::PAD, MM_STAGE = 16 * MM_ROW_STRIDE;
+    constexpr int XS = MmFmt<FMT>::XS;
     constexpr int W = MM_KS / SPW;
     constexpr int NAMAX = 2 * NP;
+    constexpr bool F_PREP = FEAT >= 1, F_ROPE = FEAT >= 2, F_XC = FEAT == 3;
+    const float *const f_gain = F_PREP ? grp.norm_gain : nullptr;
+    const float *const f_silu = F_PREP ? grp.silu_u : nullptr;
+    const bool f_swiglu = F_PREP && grp.swiglu;
+    const int f_rope_hd = F_ROPE ? grp.rope_hd : 0;
     const int64_t N = grp.n_end[grp.count - 1];
     const int NA = grp.n_act;                   // 1 .. NAMAX activation rows
     extern __shared__ __align__(128) uint8_t smem[];
@@ -187,12 +231,12 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     uint8_t *dig = smem + (size_t)nst * MM_STAGE;
     float *sgrp = reinterpret_cast<float *>(dig + ((size_t)NA * 3 * PL + 127) / 128 * 128);
     float *xsum = sgrp + (size_t)NA * nbp;
-    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nxs * 8);
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nxs * XS);
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
     // with interleaved gate / up rows every CTA owns whole (gate, up) pairs: even boundaries
-    const int64_t even = (grp.swiglu || grp.rope_hd) ? ~(int64_t)1 : ~(int64_t)0;
+    const int64_t even = (f_swiglu || f_rope_hd) ? ~(int64_t)1 : ~(int64_t)0;
     const int64_t row_begin = ((int64_t)blockIdx.x * N / gridDim.x) & even;
     const int64_t row_end = (blockIdx.x + 1 == gridDim.x) ? N : (((int64_t)(blockIdx.x + 1) * N / gridDim.x) & even);
     const int rows = (int)(row_end - row_begin);
@@ -220,7 +264,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             }
             int nsb = nb - ks * MM_KS;
             nsb = nsb > MM_KS ? MM_KS : nsb;
-            const uint32_t bytes = (uint32_t)nsb * MM_BLOCK_BYTES;
+            // a short last chunk of 210-byte blocks ends off a 16-byte boundary: the copy runs on into the row's padding
+            const uint32_t bytes = ((uint32_t)nsb * MM_BLOCK_BYTES + 15u) & ~15u;
             int nvalid = rows - rt * 16;
             nvalid = nvalid > 16 ? 16 : nvalid;
             if (lane == 0) skn_mbar_expect_tx(&full[stg], bytes * (uint32_t)nvalid);
@@ -246,7 +291,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     // Tensor-parallel consumer: the previous launch of every rank pushed its partial products into
     // this rank's inbox; wait for the peers' flags (bounded), then every load of x adds them up.
     const float *redp = nullptr;
-    if (grp.xc_reduce && grp.xc_world > 1) {
+    if (F_XC && grp.xc_reduce && grp.xc_world > 1) {
         const uint32_t q = *reinterpret_cast<volatile uint32_t *>(grp.xc_state) - 1u;    // the exchange this rank completed last
         const int buf = (int)(q % SKN_COMM_NBUF);
         if (warp == 0 && lane < grp.xc_world && lane != grp.xc_rank && *reinterpret_cast<volatile int32_t *>(status) == 0) {
@@ -293,19 +338,19 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 us[h] = 0;
                 if (uu < units) {
                     const int a = uu / nsbc, sbl = uu - a * nsbc, sbx = kc * MM_KS + sbl;      // sbx: index in x
-                    skn_xform xf{nullptr, grp.silu_u ? grp.silu_u + (size_t)a * K : nullptr, 1.f,
+                    skn_xform xf{nullptr, f_silu ? f_silu + (size_t)a * K : nullptr, 1.f,
                                  redp ? redp + (size_t)a * K : nullptr, redp ? grp.xc_world : 0, grp.xc_cap,
                                  (redp && grp.xc_wb && blockIdx.x == 0) ? grp.xc_wb + (size_t)a * K : nullptr};
                     const float *xa = x + (size_t)a * K;
                     float4 r0 = skn_load_x4(xa, sbx * 64 + lane, xf), r1 = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
-                    if (grp.norm_gain) {
+                    if (f_gain) {
                         const float e = (r0.x * r0.x + r0.y * r0.y) + (r0.z * r0.z + r0.w * r0.w) + (r1.x * r1.x + r1.y * r1.y) +
                                         (r1.z * r1.z + r1.w * r1.w);
 #pragma unroll
                         for (int k = 0; k < NAMAX; ++k)
                             if (k == a) sq[k] += e;
-                        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(grp.norm_gain) + sbx * 64 + lane);
-                        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(grp.norm_gain) + sbx * 64 + 32 + lane);
+                        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(f_gain) + sbx * 64 + lane);
+                        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(f_gain) + sbx * 64 + 32 + lane);
                         r0.x *= g0.x; r0.y *= g0.y; r0.z *= g0.z; r0.w *= g0.w;
                         r1.x *= g1.x; r1.y *= g1.y; r1.z *= g1.z; r1.w *= g1.w;
                     }
@@ -318,10 +363,10 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int h = 0; h < UR; ++h)
                 if (ua[h] >= 0)
-                    mm_digitize(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * 3 * PL, PL, sgrp + (size_t)ua[h] * nbp,
-                                xsum + (size_t)ua[h] * nxs * 8);
+                    mm_digitize<XS == 16>(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * 3 * PL, PL, sgrp + (size_t)ua[h] * nbp,
+                                          xsum + (size_t)ua[h] * nxs * XS);
         }
-        if (grp.norm_gain) {
+        if (f_gain) {
 #pragma unroll
             for (int a = 0; a < NAMAX; ++a) {
                 float ss = sq[a];
@@ -463,6 +508,116 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                     ms[a] = fmaf(dmin, m, ms[a]);
                 }
             }
+            } else if constexpr (FMT == MM_FMT_Q6K) {
+            // A 210-byte block starts two bytes off a word boundary when its index in the row is odd:
+            // every word is taken from two aligned words with a funnel shift (by 0 or 16 bits).
+            const uint32_t sh = (ba & 2u) * 8u;
+            const uint32_t wa = ba & ~3u, wb = bb & ~3u;
+            auto ldw = [&](uint32_t base, int off) {
+                return __funnelshift_r(mm_lds32(base + off), mm_lds32(base + off + 4), sh);
+            };
+            uint32_t bsrc[NP];
+            bool bon[NP];
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int arow = 2 * ap + bcol_row;
+                bon[ap] = g < 6 && arow < NA;
+                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256) + 4 * t;
+            }
+            // sixteen int8 scales of each row: five aligned words -> four block words
+            uint32_t sa[4], sq[4];
+            {
+                uint32_t ua[5], ub[5];
+#pragma unroll
+                for (int j = 0; j < 5; ++j) { ua[j] = mm_lds32(wa + 192 + 4 * j); ub[j] = mm_lds32(wb + 192 + 4 * j); }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { sa[j] = __funnelshift_r(ua[j], ua[j + 1], sh); sq[j] = __funnelshift_r(ub[j], ub[j + 1], sh); }
+            }
+            int acc[NP][4];                 // [pair][row g col 2t, col 2t+1, row g+8 col 2t, col 2t+1]: sum of scale * dot
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[ap][c] = 0;
+            // Weight 128h + 32q + l (quarter q, l = 0..31) has its low four bits in ql[64h + 32(q & 1) + l]
+            // (low nibble for q < 2) and its top two in bits 2q, 2q+1 of qh[32h + l]; its scale is number
+            // 8h + 2q + l / 16.  Lane t holds bytes l = 4t..4t+3 (part 0) and 16 + 4t.. (part 1) of every
+            // 32-byte run; a 16-weight scale group is one MMA on the k slots 0..15 (slots 16..31 are zero).
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t Ha[2], Hb[2];
+#pragma unroll
+                for (int pt = 0; pt < 2; ++pt) {
+                    Ha[pt] = ldw(wa, 128 + 32 * h + 16 * pt + 4 * t);
+                    Hb[pt] = ldw(wb, 128 + 32 * h + 16 * pt + 4 * t);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    uint32_t La[2], Lb[2];
+#pragma unroll
+                    for (int pt = 0; pt < 2; ++pt) {
+                        La[pt] = ldw(wa, 64 * h + 32 * r + 16 * pt + 4 * t);
+                        Lb[pt] = ldw(wb, 64 * h + 32 * r + 16 * pt + 4 * t);
+                    }
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        const int q = r + 2 * hi;               // quarter of the half
+#pragma unroll
+                        for (int pt = 0; pt < 2; ++pt) {
+                            const uint32_t na = hi ? (La[pt] >> 4) : La[pt], nq = hi ? (Lb[pt] >> 4) : Lb[pt];
+                            const uint32_t ta = (q < 2) ? (Ha[pt] << (4 - 2 * q)) : (Ha[pt] >> (2 * q - 4));
+                            const uint32_t tq = (q < 2) ? (Hb[pt] << (4 - 2 * q)) : (Hb[pt] >> (2 * q - 4));
+                            const uint32_t a0 = (na & 0x0F0F0F0Fu) | (ta & 0x30303030u);
+                            const uint32_t a1 = (nq & 0x0F0F0F0Fu) | (tq & 0x30303030u);
+                            const int si = 8 * h + 2 * q + pt;  // scale index
+                            const int s_a = mm_sbyte_i(sa[si >> 2], si & 3), s_b = mm_sbyte_i(sq[si >> 2], si & 3);
+#pragma unroll
+                            for (int ap = 0; ap < NP; ++ap) {
+                                uint32_t b0 = 0u;
+                                if (bon[ap]) b0 = mm_lds32(bsrc[ap] + (4 * h + q) * 32 + 16 * pt);
+                                int c[4];
+                                skn_mma_u8s8(c, a0, a1, 0u, 0u, b0, 0u);
+                                acc[ap][0] += s_a * c[0]; acc[ap][2] += s_b * c[2];
+                                if (!(ODD && ap == NP - 1)) { acc[ap][1] += s_a * c[1]; acc[ap][3] += s_b * c[3]; }
+                            }
+                        }
+                    }
+                }
+            }
+            const float d_a = mm_lds_half(ba + 208), d_b = mm_lds_half(bb + 208);
+#pragma unroll
+            for (int ap = 0; ap < NP; ++ap) {
+                const int ra = min(2 * ap + rowA, NA - 1), rb = min(2 * ap + rowB, NA - 1);
+                const float sgA = mm_lds32f(sgrp_s + 4u * (uint32_t)(ra * nbp + sb0 + sb));
+                const float sgB = mm_lds32f(sgrp_s + 4u * (uint32_t)(rb * nbp + sb0 + sb));
+                accA[ap][0] = fmaf(d_a * sgA, (float)acc[ap][0], accA[ap][0]);
+                accA[ap][1] = fmaf(d_b * sgA, (float)acc[ap][2], accA[ap][1]);
+                if (!(ODD && ap == NP - 1)) {
+                    accB[ap][0] = fmaf(d_a * sgB, (float)acc[ap][1], accB[ap][0]);
+                    accB[ap][1] = fmaf(d_b * sgB, (float)acc[ap][3], accB[ap][1]);
+                }
+            }
+            // offset term 32 * d * sum_i scale_i * sum(x of group i): this lane covers one weight row and
+            // eight of the sixteen scale groups, every activation row
+            {
+                const uint32_t r0 = (t & 1) ? ((t & 2) ? sq[2] : sq[0]) : ((t & 2) ? sa[2] : sa[0]);
+                const uint32_t r1 = (t & 1) ? ((t & 2) ? sq[3] : sq[1]) : ((t & 2) ? sa[3] : sa[1]);
+                const uint32_t f0 = r0 ^ 0x80808080u, f1 = r1 ^ 0x80808080u;
+                const float dd = 32.f * ((t & 1) ? d_b : d_a);
+                float sf[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { sf[j] = mm_sbyte_f(f0, j); sf[4 + j] = mm_sbyte_f(f1, j); }
+#pragma unroll
+                for (int a = 0; a < NAMAX; ++a) {
+                    if (a < NA) {
+                        const uint32_t xa = xsum_s + 4u * (uint32_t)((a * nxs + sb0 + sb) * 16 + 8 * (t >> 1));
+                        const float4 x0 = mm_lds128f(xa), x1 = mm_lds128f(xa + 16);
+                        float m = sf[0] * x0.x;
+                        m = fmaf(sf[1], x0.y, m); m = fmaf(sf[2], x0.z, m); m = fmaf(sf[3], x0.w, m);
+                        m = fmaf(sf[4], x1.x, m); m = fmaf(sf[5], x1.y, m); m = fmaf(sf[6], x1.z, m); m = fmaf(sf[7], x1.w, m);
+                        ms[a] = fmaf(dd, m, ms[a]);
+                    }
+                }
+            }
             } else {
             uint32_t bsrc[NP];
             bool bon[NP];
@@ -599,7 +754,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
     for (int a = 0; a < NAMAX; ++a) {
         nscale[a] = 1.f;
-        if (grp.norm_gain && a < NA) {
+        if (f_gain && a < NA) {
             float tot = 0.f;
             for (int w2 = 0; w2 < W; ++w2) tot += red[a][w2];
             nscale[a] = rsqrtf(tot / (float)K + grp.norm_eps);
@@ -610,7 +765,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     // summation tree depends on the shape only
     const int lsh = (rows * 16 <= W * 32) ? 4 : ((rows * 4 <= W * 32) ? 2 : 0);
     const int L = 1 << lsh;
-    const bool push = grp.xc_push && grp.xc_world > 1;
+    const bool push = F_XC && grp.xc_push && grp.xc_world > 1;
     uint32_t xq = 0;
     if (push) xq = *reinterpret_cast<volatile uint32_t *>(grp.xc_state);        // number of this exchange
     const size_t push_off = SKN_COMM_FLAG_BYTES / sizeof(float) + ((size_t)(xq % SKN_COMM_NBUF) * grp.xc_world + grp.xc_rank) * grp.xc_cap;
@@ -630,12 +785,12 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             if (sub == 0 && lr < rows) {
                 int64_t local;
                 const int tt = skn_group_row(grp, row_begin + lr, local);
-                if (grp.swiglu) {
+                if (f_swiglu) {
                     if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = s / (1.f + expf(-s)) * up;
-                } else if (grp.rope_hd) {
+                } else if (f_rope_hd) {
                     // rotary embedding of the pair (2i, 2i+1) this row belongs to (`up` is the other
                     // row of the pair), k and v straight into the cache
-                    const int hd = grp.rope_hd, seq = grp.rope_a0 + a;
+                    const int hd = F_ROPE ? f_rope_hd : 2, seq = grp.rope_a0 + a;
                     const int pos = grp.rope_len[seq];
                     const int slot = (grp.rope_start[seq] + pos) % grp.rope_cap;
                     const int h = (int)(local / hd), dd = (int)(local % hd);
@@ -692,25 +847,38 @@ static int mm_fmt_of(int32_t type) {
     case SKN_TYPE_Q4_K: return MM_FMT_Q4K;
     case SKN_TYPE_Q8_0: return MM_FMT_Q80;
     case SKN_TYPE_Q4_0: return MM_FMT_Q40;
+    case SKN_TYPE_Q6_K: return MM_FMT_Q6K;
     default: return -1;
     }
 }
 
-template <int FMT, int SPW>
+template <int FMT, int SPW, int FEAT>
 static mm_kernel_t mm_kernel_na(int n_act) {
     switch (n_act) {
-    case 1: return skn_matvec_mma<FMT, SPW, 1, true>;
-    case 2: return skn_matvec_mma<FMT, SPW, 1, false>;
-    case 3: return skn_matvec_mma<FMT, SPW, 2, true>;
-    default: return skn_matvec_mma<FMT, SPW, 2, false>;
+    case 1: return skn_matvec_mma<FMT, SPW, 1, true, FEAT>;
+    case 2: return skn_matvec_mma<FMT, SPW, 1, false, FEAT>;
+    case 3: return skn_matvec_mma<FMT, SPW, 2, true, FEAT>;
+    default: return skn_matvec_mma<FMT, SPW, 2, false, FEAT>;
     }
 }
 
-static mm_kernel_t mm_kernel(int fmt, int warps, int n_act) {
-    if (fmt == MM_FMT_Q80) return mm_kernel_na<MM_FMT_Q80, 1>(n_act);
-    if (fmt == MM_FMT_Q40) return mm_kernel_na<MM_FMT_Q40, 2>(n_act);
-    if (n_act > 1 || warps == 8) return mm_kernel_na<MM_FMT_Q4K, 2>(n_act);
-    return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1, true> : skn_matvec_mma<MM_FMT_Q4K, 4, 1, true>;
+template <int FMT, int SPW>
+static mm_kernel_t mm_kernel_feat(int n_act, int feat) {
+    switch (feat) {
+    case 0: return mm_kernel_na<FMT, SPW, 0>(n_act);
+    case 1: return mm_kernel_na<FMT, SPW, 1>(n_act);
+    case 2: return mm_kernel_na<FMT, SPW, 2>(n_act);
+    default: return mm_kernel_na<FMT, SPW, 3>(n_act);
+    }
+}
+
+// feat: the smallest feature class (see the kernel) that covers the launch
+static mm_kernel_t mm_kernel(int fmt, int warps, int n_act, int feat) {
+    if (fmt == MM_FMT_Q80) return mm_kernel_feat<MM_FMT_Q80, 1>(n_act, feat);
+    if (fmt == MM_FMT_Q40) return mm_kernel_feat<MM_FMT_Q40, 2>(n_act, feat);
+    if (fmt == MM_FMT_Q6K) return mm_kernel_feat<MM_FMT_Q6K, 1>(n_act, feat);
+    if (n_act > 1 || warps == 8) return mm_kernel_feat<MM_FMT_Q4K, 2>(n_act, feat);
+    return warps == 16 ? skn_matvec_mma<MM_FMT_Q4K, 1, 1, true, 3> : skn_matvec_mma<MM_FMT_Q4K, 4, 1, true, 3>;
 }
 
 static size_t mm_fixed_smem(int fmt, int nb, int n_act, int64_t rows_max, int nks, int warps) {
@@ -718,7 +886,7 @@ static size_t mm_fixed_smem(int fmt, int nb, int n_act, int64_t rows_max, int nk
     const bool chunked = n_act > 2;
     const int ks = mm_ks(fmt), ksb = chunked ? (nb < ks ? nb : ks) : nb, nxs = chunked ? ks : nb;
     return ((size_t)n_act * 3 * (ksb * 256 + 32) + 127) / 128 * 128 + (size_t)n_act * ((nxs + 3) / 4 * 4) * 4 +
-           (size_t)n_act * nxs * 8 * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
+           (size_t)n_act * nxs * mm_xs(fmt) * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
 }
 
 // most activation rows one launch can take for this shape (the digit planes and partial sums of
@@ -734,7 +902,7 @@ static int mm_max_acts(const skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_co
     return 1;
 }
 
-static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols, int n_act, skn_mv_plan &pl, bool relaxed) {
+static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols, int n_act, int feat, skn_mv_plan &pl, bool relaxed) {
     pl = skn_mv_plan{-1, 0, 0, 0, 0, 0};
     if (n_cols % 256 || n_cols > (1 << 18) || n_rows < 1 || n_act < 1 || n_act > 4) return cudaSuccess;
     const int nb = (int)(n_cols / 256);
@@ -765,7 +933,7 @@ static cudaError_t mm_plan(skn_ctx *ctx, int fmt, int64_t n_rows, int64_t n_cols
     }
     const size_t smem = fixed + (size_t)nst * stage;
     if (smem > 220 * 1024) return cudaSuccess;
-    mm_kernel_t kern = mm_kernel(fmt, warps, n_act);
+    mm_kernel_t kern = mm_kernel(fmt, warps, n_act, feat);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return e;
     // all of the SM's L1 / shared memory as shared memory, so that two CTAs (consecutive launches) fit
@@ -823,13 +991,14 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     grp.count = n;
     if (n_act < 1 || n_act > mm_max_acts(ctx, fmt, tot, w[0]->n_cols)) return false;
     skn_mv_plan pl = skn_mv_plan{0, 0, 0, 0, 0, 0};
-    const int32_t key_type = 1000 + 16 * n_act + w[0]->type;       // distinct from the CUDA-core kernels' plans
+    const int feat = (xc && xc->view.world > 1) ? 3 : (rope ? 2 : ((norm_gain || silu_u || swiglu) ? 1 : 0));
+    const int32_t key_type = 1000 + 256 * feat + 32 * n_act + w[0]->type;       // distinct from the CUDA-core kernels' plans
     for (int i = 0; i < ctx->n_group_plans; ++i) {
         const skn_group_plan &c = ctx->group_plans[i];
         if (c.type == key_type && c.rows == tot && c.cols == w[0]->n_cols && c.relaxed == ctx->relaxed_order) { pl = c.pl; break; }
     }
     if (pl.state == 0) {
-        err = mm_plan(ctx, fmt, tot, w[0]->n_cols, n_act, pl, ctx->relaxed_order != 0);
+        err = mm_plan(ctx, fmt, tot, w[0]->n_cols, n_act, feat, pl, ctx->relaxed_order != 0);
         if (err != cudaSuccess) return true;
         if (ctx->n_group_plans < 32)
             ctx->group_plans[ctx->n_group_plans++] = skn_group_plan{key_type, ctx->relaxed_order, tot, w[0]->n_cols, pl};
@@ -846,7 +1015,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     static const int pdl = env_int("SKN_PDL", 1);
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    err = cudaLaunchKernelEx(&cfg, mm_kernel(fmt, pl.nch, n_act), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
+    err = cudaLaunchKernelEx(&cfg, mm_kernel(fmt, pl.nch, n_act, feat), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
                              ctx->relaxed_order);
     return true;
 }

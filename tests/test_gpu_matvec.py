@@ -68,6 +68,14 @@ def test_cfg2_shapes(ctx, qt, N, K, M):
     run_case(ctx, qt, N, K, M, seed=1)
 
 
+@pytest.mark.parametrize("N,K,M", [(32000, 4096, 1), (32000, 4096, 4), (4096, 14336, 1), (4096, 14336, 3), (1000, 2816, 2),
+                                   (37, 768, 4)])
+def test_q6k_at_lm_head_and_down_projection_sizes(ctx, N, K, M):
+    """Q6_K on the integer tensor-core path: 16-weight scale groups, blocks on 2-byte boundaries, short
+    last K chunks (11 and 3 blocks), 1 to 4 activation rows."""
+    run_case(ctx, synth.Q6_K, N, K, M, seed=5000 + N + K + M, bias=(M == 2))
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at cfg1's size: W(a x1 + b x2) = a W x1 + b W x2."""
     w, _ = synth.cfg1(0)
