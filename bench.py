@@ -336,7 +336,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": layers * 4 * N_COLS,
                     "d2h_bytes_per_step": layers * 4 * N_ROWS, "steps": e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "skn_matvec_mma<0, 2, 1, true>", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "skn_matvec_mma<0, 2, 1, true, 0>", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": UNIT, "frac": achieved / peak,
                          "us_per_launch": per_launch_us, "traffic": DRAM_TRAFFIC_PER_LAUNCH},
             "clocks": clocks,
