@@ -437,7 +437,8 @@ def run_attn(args):
     torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
     g = synth.rng(3)
-    kv = skn.KVCache(ctx, B, Hkv, D, cap)
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype=args.kv_dtype)
+    eb = 2 if args.kv_dtype == "f16" else 4             # bytes per cached element
     lens = g.integers(1024, 4097, size=B).astype(np.int32)
     kc = g.standard_normal((B, Hkv, T, D), dtype=np.float32)
     kv.load(kc, kc[:, ::-1].copy(), lens)
@@ -464,16 +465,18 @@ def run_attn(args):
     ms = e0.elapsed_time(e1) / steps
     # bytes: K and V of every cached token of every kv head, mean length over the timed steps
     mean_len = float(lens.mean()) + warm + (steps + 1) / 2.0
-    alg = B * mean_len * Hkv * D * 4 * 2 + B * Hkv * D * 4 * 2 + 2 * B * Hq * D * 4
+    alg = B * mean_len * Hkv * D * eb * 2 + B * Hkv * D * 4 * 2 + 2 * B * Hq * D * 4
     gbs = alg / (ms * 1e-3) / 1e9
     peak, kind = measured_peak()
     print(json.dumps({
         "metric": "attn_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "cfg4: GQA decode attention B=8, 32q/8kv heads, D=128, ctx 1024..4096 (+1 per step)",
+                   "kv_cache": args.kv_dtype + (" (the configuration's cache)" if args.kv_dtype == "f32" else
+                                                " (beyond the configuration: K and V rounded to fp16 once, arithmetic fp32)"),
                    "mean_len": mean_len, "steps_per_s": 1e3 / ms},
         "gpu_launches": 3 * steps,
-        "roofline": {"bound": "hbm", "kernel": "skn_attn_split_kernel", "achieved": gbs, "peak": peak, "peak_kind": kind,
+        "roofline": {"bound": "hbm", "kernel": "skn_attn_stream_kernel + merge + append", "achieved": gbs, "peak": peak, "peak_kind": kind,
                      "unit": "GB/s", "frac": gbs / peak, "traffic": None}}), flush=True)
 
 
@@ -558,7 +561,7 @@ def run_decode(args):
               "w_gate": (cfg.ffn_dim, cfg.d_model), "w_up": (cfg.ffn_dim, cfg.d_model), "w_down": (cfg.d_model, cfg.ffn_dim)}
     layer = {k: synth.make_weight(g, cfg.proj_type, *shp) for k, shp in shapes.items()}
     emb = synth.make_weight(g, cfg.head_type, cfg.vocab, cfg.d_model)
-    dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=T + 136, exchange=exchange)
+    dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=T + 136, exchange=exchange, kv_dtype=args.kv_dtype)
     ones = np.ones(cfg.d_model, dtype=np.float32)
     for i in range(cfg.n_layers):
         dec.set_layer(i, layer, ones, ones)
@@ -638,7 +641,7 @@ def run_decode(args):
                    "parallelism": (f"tp{world}" + (", exchange fused into the matvecs" if (args.fused_exchange == "on" or (args.fused_exchange == "auto" and world >= 4)) and B <= 2 else "")) if world > 1 else "none",
                    "launch": "CUDA graph replay of one step" if graph is not None else "eager launches",
                    "prefill_ms": prefill_ms, "prefill_tok_s": B * T * 1e3 / prefill_ms,
-                   "weight_bytes_per_step": wbytes},
+                   "kv_cache": args.kv_dtype, "weight_bytes_per_step": wbytes},
         "roofline": {"bound": "hbm", "kernel": "decode step (weight stream, all GPUs)", "achieved": gbs, "peak": peak * world,
                      "peak_kind": kind, "unit": "GB/s", "frac": gbs / (peak * world), "traffic": None},
         "clocks": clocks}), flush=True)
@@ -661,6 +664,8 @@ def main():
                     help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
                          "may overlap; stream: each launch waits for the one before it")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences per step")
+    ap.add_argument("--kv-dtype", default="f32", choices=["f32", "f16"],
+                    help="attn / decode workloads: element type of the KV cache (f32 is what the configurations specify)")
     ap.add_argument("--fused-exchange", default="auto", choices=["auto", "on", "off"],
                     help="tensor-parallel decode: push partial sums from the matvec epilogue (SKN_OPT_FUSED_EXCHANGE); "
                          "auto = on from four ranks")

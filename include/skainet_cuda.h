@@ -101,6 +101,9 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
  * bit for bit.  Automatic means on from four ranks: measured slightly slower than the exchange
  * launches on 2 GPUs (every CTA of the consuming launch repeats the sum), faster on 4. */
 #define SKN_OPT_FUSED_EXCHANGE 3
+/* SKN_OPT_KV_F16 (default 0): with value 1, decoders created afterwards (skn_llama_create, skn_llama_create_tp)
+ * keep their KV caches in fp16 (see skn_kv_create_typed). */
+#define SKN_OPT_KV_F16 4
 int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value);
 
 /* Wait for everything enqueued on the context's stream; reports a pending
@@ -203,6 +206,16 @@ int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor 
  * ring buffer, device resident).  head_dim is 64 or 128. */
 int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
                       skn_kvcache **out);
+/* The same cache with a chosen element type.  SKN_KV_F16 stores K and V as IEEE fp16 (rounded to nearest
+ * even on their way in, widened on their way out; every sum stays fp32), which halves the bytes attention
+ * reads per cached token.  Every entry point below keeps its fp32 interface: appends, loads, gathers, q
+ * and the attention output are fp32 whatever the cache holds.  SKN_ERR_TYPE for any other value. */
+#define SKN_KV_F32 0
+#define SKN_KV_F16 1
+int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
+                            int32_t kv_dtype, skn_kvcache **out);
+/* element type of the cache (what k_dev / v_dev of skn_kv_info point at) */
+int32_t skn_kv_dtype(const skn_kvcache *kv, int32_t *kv_dtype);
 int32_t skn_kv_destroy(skn_kvcache *kv);
 /* forget every cached token */
 int32_t skn_kv_reset(skn_kvcache *kv);

@@ -41,6 +41,8 @@ SIGNATURES = {
     "skn_ffn_swiglu": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "skn_ffn_swiglu_dev": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "skn_kv_create": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, P(c_vp)]),
+    "skn_kv_create_typed": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, P(c_vp)]),
+    "skn_kv_dtype": (c_i32, [c_vp, P(c_i32)]),
     "skn_kv_destroy": (c_i32, [c_vp]),
     "skn_kv_reset": (c_i32, [c_vp]),
     "skn_kv_load": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp]),

@@ -125,6 +125,7 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
         ctx->prefill_min_m = (int)value;
         return SKN_OK;
     case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value < 0 ? -1 : (value ? 1 : 0); return SKN_OK;
+    case SKN_OPT_KV_F16: ctx->kv_f16 = value ? 1 : 0; return SKN_OK;
     default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
     }
 }

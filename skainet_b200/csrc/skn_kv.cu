@@ -22,6 +22,7 @@
 #include "skn_internal.cuh"
 #include "skn_ptx.cuh"
 
+#include <cuda_fp16.h>
 #include <math.h>
 #include <stdlib.h>
 #include <new>
@@ -30,7 +31,8 @@ struct skn_kvcache {
     uint32_t magic;
     skn_ctx *ctx;
     int32_t batch, n_kv_heads, head_dim, capacity;
-    float *d_k, *d_v;
+    int32_t dtype;               // SKN_KV_F32 or SKN_KV_F16: element type of d_k / d_v
+    void *d_k, *d_v;
     int32_t *d_len, *d_start;
     unsigned *d_tickets;         // [batch][n_kv_heads], zero between launches: split-attention merge tickets
 };
@@ -41,8 +43,57 @@ constexpr int ATT_MERGE_MAX_SPLITS = 64;   // most splits the in-kernel merge ha
 
 static bool kv_ok(const skn_kvcache *kv) { return kv && kv->magic == SKN_MAGIC_KV && skn_ctx_ok(kv->ctx); }
 
+// Cache element types: fp32, or fp16 (half the attention traffic; values are rounded to nearest
+// even on their way in and widened to fp32 on their way out, all arithmetic stays fp32).
+template <class CT> struct KvElem;
+template <> struct KvElem<float> {
+    static __device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+    static __device__ __forceinline__ void st2(float *p, float2 v) { *reinterpret_cast<float2 *>(p) = v; }
+    static __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+    static __device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+    static __device__ __forceinline__ float2 ld2(const float *p) { return *reinterpret_cast<const float2 *>(p); }
+    static __device__ __forceinline__ float2 ldg2(const float *p) { return __ldg(reinterpret_cast<const float2 *>(p)); }
+};
+template <> struct KvElem<__half> {
+    static __device__ __forceinline__ void st4(__half *p, float4 v) {
+        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t *>(&a);
+        u.y = *reinterpret_cast<const uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(p) = u;
+    }
+    static __device__ __forceinline__ void st2(__half *p, float2 v) { *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(v.x, v.y); }
+    static __device__ __forceinline__ float4 widen4(uint2 u) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ float4 ld4(const __half *p) { return widen4(*reinterpret_cast<const uint2 *>(p)); }
+    static __device__ __forceinline__ float4 ldg4(const __half *p) { return widen4(__ldg(reinterpret_cast<const uint2 *>(p))); }
+    static __device__ __forceinline__ float2 ld2(const __half *p) { return __half22float2(*reinterpret_cast<const __half2 *>(p)); }
+    static __device__ __forceinline__ float2 ldg2(const __half *p) {
+        const uint32_t u = __ldg(reinterpret_cast<const uint32_t *>(p));
+        return __half22float2(*reinterpret_cast<const __half2 *>(&u));
+    }
+};
+// VEC (2 or 4) consecutive cache elements -> fp32 registers; GLOBAL: read-only global load, else a plain (shared-memory) load
+template <class CT, int VEC, bool GLOBAL> struct KvLoad;
+template <class CT, bool GLOBAL> struct KvLoad<CT, 4, GLOBAL> {
+    static __device__ __forceinline__ void ld(const CT *p, float (&r)[4]) {
+        const float4 v = GLOBAL ? KvElem<CT>::ldg4(p) : KvElem<CT>::ld4(p);
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    }
+};
+template <class CT, bool GLOBAL> struct KvLoad<CT, 2, GLOBAL> {
+    static __device__ __forceinline__ void ld(const CT *p, float (&r)[2]) {
+        const float2 v = GLOBAL ? KvElem<CT>::ldg2(p) : KvElem<CT>::ld2(p);
+        r[0] = v.x; r[1] = v.y;
+    }
+};
+
 // ----------------------------------------------------------------------------------------
-__global__ void skn_kv_append_kernel(float *__restrict__ kc, float *__restrict__ vc, int32_t *__restrict__ len,
+template <class CT>
+__global__ void skn_kv_append_kernel(CT *__restrict__ kc, CT *__restrict__ vc, int32_t *__restrict__ len,
                                      int32_t *__restrict__ start, const float *__restrict__ k_new,
                                      const float *__restrict__ v_new, int Hkv, int D, int cap) {
     const int b = blockIdx.x;
@@ -53,8 +104,8 @@ __global__ void skn_kv_append_kernel(float *__restrict__ kc, float *__restrict__
         const int h = (i * 4) / D, d = (i * 4) % D;
         const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
         const size_t src = ((size_t)b * Hkv + h) * D + d;
-        *reinterpret_cast<float4 *>(kc + dst) = *reinterpret_cast<const float4 *>(k_new + src);
-        *reinterpret_cast<float4 *>(vc + dst) = *reinterpret_cast<const float4 *>(v_new + src);
+        KvElem<CT>::st4(kc + dst, *reinterpret_cast<const float4 *>(k_new + src));
+        KvElem<CT>::st4(vc + dst, *reinterpret_cast<const float4 *>(v_new + src));
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -66,7 +117,8 @@ __global__ void skn_kv_append_kernel(float *__restrict__ kc, float *__restrict__
 // T new tokens per sequence: k_new, v_new are [batch][T][Hkv][D]; token t goes to ring slot
 // (start + len + t) % cap.  The lengths are advanced afterwards by skn_kv_advance_kernel, so
 // every CTA of this launch reads the same old length.  The caller guarantees len + T <= cap.
-__global__ void skn_kv_append_many_kernel(float *__restrict__ kc, float *__restrict__ vc, const int32_t *__restrict__ len,
+template <class CT>
+__global__ void skn_kv_append_many_kernel(CT *__restrict__ kc, CT *__restrict__ vc, const int32_t *__restrict__ len,
                                           const int32_t *__restrict__ start, const float *__restrict__ k_new,
                                           const float *__restrict__ v_new, int Hkv, int D, int cap, int T) {
     const int b = blockIdx.y, t = blockIdx.x;
@@ -76,8 +128,8 @@ __global__ void skn_kv_append_many_kernel(float *__restrict__ kc, float *__restr
         const int h = (i * 4) / D, d = (i * 4) % D;
         const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
         const size_t src = (((size_t)b * T + t) * Hkv + h) * D + d;
-        *reinterpret_cast<float4 *>(kc + dst) = *reinterpret_cast<const float4 *>(k_new + src);
-        *reinterpret_cast<float4 *>(vc + dst) = *reinterpret_cast<const float4 *>(v_new + src);
+        KvElem<CT>::st4(kc + dst, *reinterpret_cast<const float4 *>(k_new + src));
+        KvElem<CT>::st4(vc + dst, *reinterpret_cast<const float4 *>(v_new + src));
     }
 }
 
@@ -92,9 +144,10 @@ __global__ void skn_kv_advance_kernel(int32_t *__restrict__ len, int B, int T, i
 // at position 4096 an fp32 angle is already off by ~5e-4 rad); one pair per thread.  The
 // lengths are NOT advanced here: the decoder runs attention with `len_extra = T` and advances
 // every layer's lengths with one launch at the end of the step.
+template <class CT>
 __global__ void __launch_bounds__(128)
 skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, const float *__restrict__ v_new,
-                       float *__restrict__ kc, float *__restrict__ vc, const int32_t *__restrict__ len,
+                       CT *__restrict__ kc, CT *__restrict__ vc, const int32_t *__restrict__ len,
                        const int32_t *__restrict__ start, int Hq, int Hkv, int D, int cap, int T, double log2_theta) {
     const int b = blockIdx.z, t = blockIdx.y;
     const int pos = len[b] + t;
@@ -104,8 +157,8 @@ skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, c
     if (blockIdx.x == gridDim.x - 1) {
         for (int i = threadIdx.x; i < Hkv * D / 4; i += blockDim.x) {
             const int h = (i * 4) / D, d = (i * 4) % D;
-            *reinterpret_cast<float4 *>(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d) =
-                *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d);
+            KvElem<CT>::st4(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d,
+                            *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d));
         }
         return;
     }
@@ -123,8 +176,7 @@ skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, c
     } else {
         const int hk = h - Hq;
         const float2 a = reinterpret_cast<const float2 *>(k_new + (row * Hkv + hk) * D)[p];
-        reinterpret_cast<float2 *>(kc + (((size_t)b * Hkv + hk) * cap + slot) * D)[p] =
-            make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs);
+        KvElem<CT>::st2(kc + (((size_t)b * Hkv + hk) * cap + slot) * D + 2 * p, make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs));
     }
 }
 
@@ -137,7 +189,18 @@ __global__ void skn_kv_advance_all_kernel(int32_t *const *__restrict__ lens, int
     }
 }
 
-__global__ void skn_kv_gather_kernel(const float *__restrict__ kc, const float *__restrict__ vc,
+// dense fp32 [rows][tokens][D] -> the first `tokens` slots of every (sequence, kv head) of an fp16 cache
+__global__ void skn_kv_load_half_kernel(const float *__restrict__ src, __half *__restrict__ dst, int64_t rows, int tokens,
+                                        int D, int cap) {
+    const int64_t per_row = (int64_t)tokens * D / 4, total = rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row, e = (i % per_row) * 4;
+        KvElem<__half>::st4(dst + (size_t)r * cap * D + e, *reinterpret_cast<const float4 *>(src + (size_t)r * tokens * D + e));
+    }
+}
+
+template <class CT>
+__global__ void skn_kv_gather_kernel(const CT *__restrict__ kc, const CT *__restrict__ vc,
                                      const int32_t *__restrict__ start, int b, int Hkv, int D, int cap, int pos0,
                                      int count, float *__restrict__ k_out, float *__restrict__ v_out) {
     // out: [Hkv][count][D]
@@ -151,8 +214,8 @@ __global__ void skn_kv_gather_kernel(const float *__restrict__ kc, const float *
         const int slot = (s0 + pos0 + p) % cap;
         const size_t src = (((size_t)b * Hkv + h) * cap + slot) * D + d;
         const size_t dst = ((size_t)h * count + p) * D + d;
-        *reinterpret_cast<float4 *>(k_out + dst) = *reinterpret_cast<const float4 *>(kc + src);
-        *reinterpret_cast<float4 *>(v_out + dst) = *reinterpret_cast<const float4 *>(vc + src);
+        *reinterpret_cast<float4 *>(k_out + dst) = KvElem<CT>::ld4(kc + src);
+        *reinterpret_cast<float4 *>(v_out + dst) = KvElem<CT>::ld4(vc + src);
     }
 }
 
@@ -226,25 +289,11 @@ template <> struct VecLoad<2> {
         r[0] = v.x; r[1] = v.y;
     }
 };
-// the same from shared memory (plain vector loads)
-template <int VEC> struct VecLds;
-template <> struct VecLds<4> {
-    static __device__ __forceinline__ void ld(const float *p, float (&r)[4]) {
-        const float4 v = *reinterpret_cast<const float4 *>(p);
-        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-    }
-};
-template <> struct VecLds<2> {
-    static __device__ __forceinline__ void ld(const float *p, float (&r)[2]) {
-        const float2 v = *reinterpret_cast<const float2 *>(p);
-        r[0] = v.x; r[1] = v.y;
-    }
-};
 
 // D: head dim (64 or 128); G: query heads per kv head; TT: tokens per warp tile (TT*G <= 32)
-template <int D, int G, int TT, int CHUNK>
+template <int D, int G, int TT, int CHUNK, class CT>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
+skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, const CT *__restrict__ vc,
                       const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
                       float scale, float *__restrict__ part, int S, int tq, int len_extra, float *__restrict__ out,
                       unsigned *__restrict__ tickets) {
@@ -272,8 +321,8 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
     const int nt = min(CHUNK, L - t0);
     const int s0 = start[b];
     const int Hq = Hkv * G;
-    const float *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
-    const float *vbase = vc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
+    const CT *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
+    const CT *vbase = vc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
 
     float qv[G][VEC];
 #pragma unroll
@@ -293,7 +342,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
                 const int t = min(tl + j, nt - 1);
-                VecLoad<VEC>::ld(vbase + (size_t)((s0 + t0 + t) % cap) * D, v0[j]);
+                KvLoad<CT, VEC, true>::ld(vbase + (size_t)((s0 + t0 + t) % cap) * D, v0[j]);
             }
         }
     }
@@ -311,7 +360,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
         for (int j = 0; j < TT; ++j) {
             const int t = min(tl + j, nt - 1);            // clamp: the extra scores are discarded
             const int slot = (s0 + t0 + t) % cap;
-            VecLoad<VEC>::ld(kbase + (size_t)slot * D, kr[j]);
+            KvLoad<CT, VEC, true>::ld(kbase + (size_t)slot * D, kr[j]);
         }
         float pv[NV];
 #pragma unroll
@@ -393,7 +442,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
             for (int j = 0; j < TT; ++j) {
                 const int t = min(tl + j, nt - 1);
                 const int slot = (s0 + t0 + t) % cap;
-                VecLoad<VEC>::ld(vbase + (size_t)slot * D, vr[j]);
+                KvLoad<CT, VEC, true>::ld(vbase + (size_t)slot * D, vr[j]);
             }
         }
 #pragma unroll
@@ -469,9 +518,9 @@ skn_attn_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
 // tokens of a tile from shared memory.  V tiles are already on their way while the scores, the
 // chunk maximum and the probabilities are computed, so HBM stays busy across the two passes.
 // Writes the (max, sum, unnormalised output) record per (head, split); the merge kernel follows.
-template <int D, int G, int TT>
+template <int D, int G, int TT, class CT>
 __global__ void __launch_bounds__((ATT_WARPS + 1) * 32)
-skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
+skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, const CT *__restrict__ vc,
                        const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
                        float scale, float *__restrict__ part, int S, int tq, int len_extra, int nst,
                        int32_t *__restrict__ status) {
@@ -480,7 +529,7 @@ skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc
     constexpr int NV = TT * G;
     constexpr int REP = 32 / NV;
     constexpr int TILE = ATT_WARPS * TT;             // tokens per stage
-    constexpr int TILE_BYTES = TILE * D * 4;
+    constexpr int TILE_BYTES = TILE * D * (int)sizeof(CT);
     extern __shared__ __align__(128) uint8_t att_smem[];
     __shared__ float s_sc[CHUNK][G];
     __shared__ float s_red[ATT_WARPS][G];
@@ -520,15 +569,16 @@ skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc
                     atomicExch(status, SKN_ERR_TIMEOUT);
                 }
                 const int tile = i < ntile ? i : i - ntile;
-                const float *src = (i < ntile ? kc : vc) + head;
+                const CT *src = (i < ntile ? kc : vc) + head;
                 const int ntok = min(TILE, nt - tile * TILE);
                 const int slot0 = (s0 + t0 + tile * TILE) % cap;
                 const int n1 = min(ntok, cap - slot0);          // tokens before the ring wraps
                 uint8_t *dst = att_smem + (size_t)stg * TILE_BYTES;
                 skn_fence_proxy_async();
-                skn_mbar_expect_tx(&full[stg], (uint32_t)ntok * D * 4);
-                skn_bulk_g2s(dst, src + (size_t)slot0 * D, (uint32_t)n1 * D * 4, &full[stg]);
-                if (ntok > n1) skn_bulk_g2s(dst + (size_t)n1 * D * 4, src, (uint32_t)(ntok - n1) * D * 4, &full[stg]);
+                constexpr uint32_t ROW = D * (uint32_t)sizeof(CT);
+                skn_mbar_expect_tx(&full[stg], (uint32_t)ntok * ROW);
+                skn_bulk_g2s(dst, src + (size_t)slot0 * D, (uint32_t)n1 * ROW, &full[stg]);
+                if (ntok > n1) skn_bulk_g2s(dst + (size_t)n1 * ROW, src, (uint32_t)(ntok - n1) * ROW, &full[stg]);
             }
         }
         return;
@@ -548,8 +598,8 @@ skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc
             atomicExch(status, SKN_ERR_TIMEOUT);
         }
     };
-    auto tile_row = [&](int i, int local) -> const float * {
-        return reinterpret_cast<const float *>(att_smem + (size_t)(i % nst) * TILE_BYTES) + (size_t)local * D + lane * VEC;
+    auto tile_row = [&](int i, int local) -> const CT * {
+        return reinterpret_cast<const CT *>(att_smem + (size_t)(i % nst) * TILE_BYTES) + (size_t)local * D + lane * VEC;
     };
 
     // ---- pass 1: scores ------------------------------------------------------------------
@@ -564,7 +614,7 @@ skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc
             float kr[TT][VEC];
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
-                VecLds<VEC>::ld(tile_row(ti, min(warp * TT + j, last)), kr[j]);
+                KvLoad<CT, VEC, false>::ld(tile_row(ti, min(warp * TT + j, last)), kr[j]);
             }
             float pv[NV];
 #pragma unroll
@@ -642,7 +692,7 @@ skn_attn_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc
             for (int j = 0; j < TT; ++j) {
                 if (tl + j < nt) {
                     float vr[VEC];
-                    VecLds<VEC>::ld(tile_row(i, warp * TT + j), vr);
+                    KvLoad<CT, VEC, false>::ld(tile_row(i, warp * TT + j), vr);
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
                         const float pr = s_sc[tl + j][g];
@@ -723,10 +773,11 @@ skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict_
     out[((size_t)b * Hq + h) * D + d] = a / l;
 }
 
-template <int D, int G>
+template <int D, int G, class CT>
 static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scale, float *part, int chunk, float *out,
                                cudaStream_t stream, int tq, int len_extra) {
     constexpr int TT = (G >= 8) ? 4 : 8;
+    const CT *kc = static_cast<const CT *>(kv->d_k), *vc = static_cast<const CT *>(kv->d_v);
     const int S = (kv->capacity + chunk - 1) / chunk;
     const dim3 grid((unsigned)S, (unsigned)kv->n_kv_heads, (unsigned)(kv->batch * tq));
     // single-token decode: the last split of every (sequence, kv head) merges in the same launch;
@@ -737,29 +788,29 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     static const int stream_on = [] { const char *v = getenv("SKN_ATTN_STREAM"); return v ? atoi(v) : 1; }();
     if (chunk == ATT_CHUNK && !tickets && stream_on) {
         // long contexts: tiles by bulk async copy through a shared-memory ring
-        constexpr int TILE_BYTES = ATT_WARPS * TT * D * 4;
+        constexpr int TILE_BYTES = ATT_WARPS * TT * D * (int)sizeof(CT);
         // two stages: measured, more resident CTAs per SM (five at 44 KB each for D = 128, G = 4) beat a deeper ring
         static const int nst_env = [] { const char *v = getenv("SKN_ATTN_NST"); return v ? atoi(v) : 0; }();
         const int nst = (nst_env >= 2 && nst_env <= 6) ? nst_env : 2;
         const size_t smem = (size_t)nst * TILE_BYTES + 2 * (size_t)nst * sizeof(uint64_t);
-        auto kern = skn_attn_stream_kernel<D, G, TT>;
-        const uint32_t cfg_bit = 1u << ((D == 128 ? 4 : 0) + (G == 1 ? 0 : (G == 2 ? 1 : (G == 4 ? 2 : 3))));
+        auto kern = skn_attn_stream_kernel<D, G, TT, CT>;
+        const uint32_t cfg_bit = 1u << ((sizeof(CT) == 2 ? 8 : 0) + (D == 128 ? 4 : 0) + (G == 1 ? 0 : (G == 2 ? 1 : (G == 4 ? 2 : 3))));
         if (!(kv->ctx->attn_stream_cfg & cfg_bit)) {
             cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(100 * 1024));
             if (e0 == cudaSuccess) e0 = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             if (e0 != cudaSuccess) return e0;
             kv->ctx->attn_stream_cfg |= cfg_bit;
         }
-        kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
+        kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kc, vc, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
                                                           scale, part, S, tq, len_extra, nst, kv->ctx->d_status);
     } else if (chunk == 32)
-        skn_attn_split_kernel<D, G, TT, 32><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+        skn_attn_split_kernel<D, G, TT, 32, CT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kc, vc, kv->d_len, kv->d_start,
                                                                                 kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else if (chunk == 64)
-        skn_attn_split_kernel<D, G, TT, 64><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+        skn_attn_split_kernel<D, G, TT, 64, CT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kc, vc, kv->d_len, kv->d_start,
                                                                                 kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else
-        skn_attn_split_kernel<D, G, TT, ATT_CHUNK><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kv->d_k, kv->d_v, kv->d_len, kv->d_start,
+        skn_attn_split_kernel<D, G, TT, ATT_CHUNK, CT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kc, vc, kv->d_len, kv->d_start,
                                                                                        kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || tickets) return e;
@@ -786,24 +837,31 @@ static int attn_pick_chunk(const skn_kvcache *kv, int n_q_heads, int tq, size_t 
     return pick;
 }
 
-static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,
-                                 float *out, cudaStream_t st, int tq = 1, int len_extra = 0) {
+template <class CT>
+static cudaError_t dispatch_attn_t(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,
+                                   float *out, cudaStream_t st, int tq, int len_extra) {
     if (kv->head_dim == 128) {
         switch (G) {
-        case 1: return launch_attn<128, 1>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 2: return launch_attn<128, 2>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 4: return launch_attn<128, 4>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 8: return launch_attn<128, 8>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 1: return launch_attn<128, 1, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 2: return launch_attn<128, 2, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 4: return launch_attn<128, 4, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 8: return launch_attn<128, 8, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
         }
     } else if (kv->head_dim == 64) {
         switch (G) {
-        case 1: return launch_attn<64, 1>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 2: return launch_attn<64, 2>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 4: return launch_attn<64, 4>(kv, q, scale, part, chunk, out, st, tq, len_extra);
-        case 8: return launch_attn<64, 8>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 1: return launch_attn<64, 1, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 2: return launch_attn<64, 2, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 4: return launch_attn<64, 4, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
+        case 8: return launch_attn<64, 8, CT>(kv, q, scale, part, chunk, out, st, tq, len_extra);
         }
     }
     return cudaErrorInvalidValue;
+}
+
+static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,
+                                 float *out, cudaStream_t st, int tq = 1, int len_extra = 0) {
+    return kv->dtype == SKN_KV_F16 ? dispatch_attn_t<__half>(kv, G, q, scale, part, chunk, out, st, tq, len_extra)
+                                   : dispatch_attn_t<float>(kv, G, q, scale, part, chunk, out, st, tq, len_extra);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -811,9 +869,15 @@ extern "C" {
 
 int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
                       skn_kvcache **out) {
+    return skn_kv_create_typed(ctx, batch, n_kv_heads, head_dim, capacity, SKN_KV_F32, out);
+}
+
+int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
+                            int32_t kv_dtype, skn_kvcache **out) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
     if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     *out = nullptr;
+    if (kv_dtype != SKN_KV_F32 && kv_dtype != SKN_KV_F16) return skn_fail(ctx, SKN_ERR_TYPE, "cache element type %d is neither fp32 nor fp16", kv_dtype);
     if (batch < 1 || n_kv_heads < 1 || capacity < 1) return skn_fail(ctx, SKN_ERR_ARG, "batch, heads and capacity must be positive");
     if (head_dim != 64 && head_dim != 128) return skn_fail(ctx, SKN_ERR_SHAPE, "head_dim must be 64 or 128 (got %d)", head_dim);
     skn_kvcache *kv = new (std::nothrow) skn_kvcache();
@@ -822,7 +886,8 @@ int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t h
     kv->magic = SKN_MAGIC_KV;
     kv->ctx = ctx;
     kv->batch = batch; kv->n_kv_heads = n_kv_heads; kv->head_dim = head_dim; kv->capacity = capacity;
-    const size_t n = (size_t)batch * n_kv_heads * capacity * head_dim * sizeof(float);
+    kv->dtype = kv_dtype;
+    const size_t n = (size_t)batch * n_kv_heads * capacity * head_dim * (kv_dtype == SKN_KV_F16 ? 2 : sizeof(float));
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_k, n);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_v, n);
@@ -881,7 +946,20 @@ int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, i
     const size_t row = (size_t)tokens * kv->head_dim * sizeof(float);
     const size_t pitch = (size_t)kv->capacity * kv->head_dim * sizeof(float);
     const size_t nrows = (size_t)kv->batch * kv->n_kv_heads;
-    if (tokens > 0) {
+    if (tokens > 0 && kv->dtype == SKN_KV_F16) {
+        // fp32 rows to a staging buffer, one tensor at a time, then rounded into the cache
+        const int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, row * nrows);
+        if (rc) return rc;
+        const int64_t n4 = (int64_t)nrows * tokens * kv->head_dim / 4;
+        int blocks = (int)((n4 + 255) / 256 < (int64_t)ctx->sm_count * 16 ? (n4 + 255) / 256 : (int64_t)ctx->sm_count * 16);
+        for (int which = 0; which < 2; ++which) {
+            SKN_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, which ? v_host : k_host, row * nrows, cudaMemcpyHostToDevice, ctx->stream));
+            skn_kv_load_half_kernel<<<blocks, 256, 0, ctx->stream>>>((const float *)ctx->d_stage_in,
+                                                                     static_cast<__half *>(which ? kv->d_v : kv->d_k), (int64_t)nrows,
+                                                                     tokens, kv->head_dim, kv->capacity);
+            SKN_CUDA(ctx, cudaGetLastError());
+        }
+    } else if (tokens > 0) {
         SKN_CUDA(ctx, cudaMemcpy2DAsync(kv->d_k, pitch, k_host, row, row, nrows, cudaMemcpyHostToDevice, ctx->stream));
         SKN_CUDA(ctx, cudaMemcpy2DAsync(kv->d_v, pitch, v_host, row, row, nrows, cudaMemcpyHostToDevice, ctx->stream));
     }
@@ -907,8 +985,14 @@ int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *
     if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     if ((((uintptr_t)k_new_dev) | ((uintptr_t)v_new_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "k/v must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    skn_kv_append_kernel<<<kv->batch, 256, 0, ctx->stream>>>(kv->d_k, kv->d_v, kv->d_len, kv->d_start, k_new_dev, v_new_dev,
-                                                             kv->n_kv_heads, kv->head_dim, kv->capacity);
+    if (kv->dtype == SKN_KV_F16)
+        skn_kv_append_kernel<__half><<<kv->batch, 256, 0, ctx->stream>>>(static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v),
+                                                                         kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+                                                                         kv->n_kv_heads, kv->head_dim, kv->capacity);
+    else
+        skn_kv_append_kernel<float><<<kv->batch, 256, 0, ctx->stream>>>(static_cast<float *>(kv->d_k), static_cast<float *>(kv->d_v),
+                                                                        kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+                                                                        kv->n_kv_heads, kv->head_dim, kv->capacity);
     SKN_CUDA(ctx, cudaGetLastError());
     return SKN_OK;
 }
@@ -949,8 +1033,14 @@ int32_t skn_kv_gather(skn_kvcache *kv, int32_t b, int32_t pos_begin, int32_t cou
     const int64_t total = (int64_t)kv->n_kv_heads * count * kv->head_dim / 4;
     int blocks = (int)((total + 255) / 256);
     if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
-    skn_kv_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(kv->d_k, kv->d_v, kv->d_start, b, kv->n_kv_heads, kv->head_dim,
-                                                          kv->capacity, pos_begin, count, dk, dv);
+    if (kv->dtype == SKN_KV_F16)
+        skn_kv_gather_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(static_cast<const __half *>(kv->d_k), static_cast<const __half *>(kv->d_v),
+                                                                      kv->d_start, b, kv->n_kv_heads, kv->head_dim, kv->capacity,
+                                                                      pos_begin, count, dk, dv);
+    else
+        skn_kv_gather_kernel<float><<<blocks, 256, 0, ctx->stream>>>(static_cast<const float *>(kv->d_k), static_cast<const float *>(kv->d_v),
+                                                                     kv->d_start, b, kv->n_kv_heads, kv->head_dim, kv->capacity,
+                                                                     pos_begin, count, dk, dv);
     SKN_CUDA(ctx, cudaGetLastError());
     SKN_CUDA(ctx, cudaMemcpyAsync(k_out_host, dk, n, cudaMemcpyDeviceToHost, ctx->stream));
     SKN_CUDA(ctx, cudaMemcpyAsync(v_out_host, dv, n, cudaMemcpyDeviceToHost, ctx->stream));
@@ -1031,8 +1121,14 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
     if ((int64_t)host_len_upper + T > kv->capacity)
         return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    skn_kv_append_many_kernel<<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
-        kv->d_k, kv->d_v, kv->d_len, kv->d_start, k_new_dev, v_new_dev, kv->n_kv_heads, kv->head_dim, kv->capacity, T);
+    if (kv->dtype == SKN_KV_F16)
+        skn_kv_append_many_kernel<__half><<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
+            static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v), kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+            kv->n_kv_heads, kv->head_dim, kv->capacity, T);
+    else
+        skn_kv_append_many_kernel<float><<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
+            static_cast<float *>(kv->d_k), static_cast<float *>(kv->d_v), kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+            kv->n_kv_heads, kv->head_dim, kv->capacity, T);
     SKN_CUDA(ctx, cudaGetLastError());
     skn_kv_advance_kernel<<<(kv->batch + 127) / 128, 128, 0, ctx->stream>>>(kv->d_len, kv->batch, T, kv->capacity);
     SKN_CUDA(ctx, cudaGetLastError());
@@ -1084,9 +1180,15 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
         return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
     if ((int64_t)kv->batch > 65535 || T > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch or T exceeds 65535");
     const int pair_blocks = ((n_q_heads + kv->n_kv_heads) * (kv->head_dim / 2) + 127) / 128;
-    skn_rope_append_kernel<<<dim3((unsigned)pair_blocks + 1, (unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
-        q_dev, k_new_dev, v_new_dev, kv->d_k, kv->d_v, kv->d_len, kv->d_start, n_q_heads, kv->n_kv_heads, kv->head_dim,
-        kv->capacity, T, log2((double)theta));
+    const dim3 rgrid((unsigned)pair_blocks + 1, (unsigned)T, (unsigned)kv->batch);
+    if (kv->dtype == SKN_KV_F16)
+        skn_rope_append_kernel<__half><<<rgrid, 128, 0, ctx->stream>>>(
+            q_dev, k_new_dev, v_new_dev, static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v), kv->d_len, kv->d_start,
+            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta));
+    else
+        skn_rope_append_kernel<float><<<rgrid, 128, 0, ctx->stream>>>(
+            q_dev, k_new_dev, v_new_dev, static_cast<float *>(kv->d_k), static_cast<float *>(kv->d_v), kv->d_len, kv->d_start,
+            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta));
     SKN_CUDA(ctx, cudaGetLastError());
     return SKN_OK;
 }
@@ -1145,6 +1247,14 @@ int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t
     }
     SKN_CUDA(ctx, dispatch_attn(kv, G, q_dev, scale, part, attn_pick_chunk(kv, n_q_heads, 1, SKN_ATTN_STATIC_SCRATCH_BYTES),
                                 out_dev, ctx->stream));
+    return SKN_OK;
+}
+
+// element type of the cache buffers (SKN_KV_F32 / SKN_KV_F16): what the pointers of skn_kv_info point at
+int32_t skn_kv_dtype(const skn_kvcache *kv, int32_t *kv_dtype) {
+    if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
+    if (!kv_dtype) return skn_fail(kv->ctx, SKN_ERR_ARG, "kv_dtype is NULL");
+    *kv_dtype = kv->dtype;
     return SKN_OK;
 }
 

@@ -163,6 +163,10 @@ class Context:
         True / False, or None for the automatic choice (on from four ranks)."""
         _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 3, -1 if on is None else (1 if on else 0)))
 
+    def set_kv_f16(self, on: bool):
+        """Decoders created afterwards keep their KV caches in fp16 (SKN_OPT_KV_F16)."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 4, 1 if on else 0))
+
     def sync(self):
         _check(self._h, _ffi.lib().skn_sync(self._h))
 
@@ -305,13 +309,20 @@ def ffn_swiglu(ctx: Context, wg: QuantTensor, wu: QuantTensor, wd: QuantTensor, 
 
 
 class KVCache:
-    """Device-resident fp32 KV cache (head-major ring) with decode attention."""
+    """Device-resident KV cache (head-major ring) with decode attention.  `dtype` is "f32" (default) or
+    "f16": the element type K and V are kept in; every method takes and returns fp32 either way."""
 
-    def __init__(self, ctx: Context, batch: int, n_kv_heads: int, head_dim: int, capacity: int):
+    DTYPES = {"f32": 0, "f16": 1}
+
+    def __init__(self, ctx: Context, batch: int, n_kv_heads: int, head_dim: int, capacity: int, dtype: str = "f32"):
+        if dtype not in self.DTYPES:
+            raise ValueError("dtype must be 'f32' or 'f16'")
         self.ctx = ctx
         self.batch, self.n_kv_heads, self.head_dim, self.capacity = batch, n_kv_heads, head_dim, capacity
+        self.dtype = dtype
         self._h = ctypes.c_void_p()
-        rc = _ffi.lib().skn_kv_create(ctx.handle, batch, n_kv_heads, head_dim, capacity, ctypes.byref(self._h))
+        rc = _ffi.lib().skn_kv_create_typed(ctx.handle, batch, n_kv_heads, head_dim, capacity, self.DTYPES[dtype],
+                                            ctypes.byref(self._h))
         if rc != SKN_OK:
             self._h = ctypes.c_void_p()
             _raise(ctx.handle, rc)

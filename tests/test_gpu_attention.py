@@ -134,6 +134,55 @@ def test_cfg4_decode_steps(ctx):
     kv.close()
 
 
+def h16(a):
+    """What an fp16 cache keeps of fp32 values: round to nearest even, widened back."""
+    return a.astype(np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,cap", [(1, 1, 1, 64, 16), (2, 4, 2, 128, 300), (3, 8, 1, 64, 700),
+                                            (2, 32, 8, 128, 1100), (8, 32, 8, 128, 4224)])
+def test_fp16_cache_attention_matches_oracle_on_rounded_values(ctx, B, Hq, Hkv, D, cap):
+    """An fp16 cache rounds K and V once on their way in; attention over it equals the fp64 oracle over the
+    rounded values within the fp32 tolerance (short contexts: per-lane loads; the last case: bulk-copy tiles)."""
+    g = synth.rng(B * 1000 + Hq + cap + 7)
+    kc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    vc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    lens = g.integers(1, cap + 1, size=B).astype(np.int32)
+    lens[0] = cap
+    q = g.standard_normal((B, Hq, D), dtype=np.float32)
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype="f16")
+    kv.load(kc, vc, lens)
+    out = kv.attend(q)
+    kg, vg = kv.gather(0, 0, min(cap, 40))
+    kv.close()
+    assert np.array_equal(kg, h16(kc[0, :, :min(cap, 40)])) and np.array_equal(vg, h16(vc[0, :, :min(cap, 40)]))
+    check_attention(out, q, h16(kc), h16(vc), lens)
+
+
+def test_fp16_cache_append_gather_and_ring_wrap(ctx):
+    g = synth.rng(16)
+    B, Hq, Hkv, D, cap = 2, 8, 2, 128, 20
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype="f16")
+    ks, vs = [], []
+    for step in range(27):
+        k_new = g.standard_normal((B, Hkv, D), dtype=np.float32) * 50
+        v_new = g.standard_normal((B, Hkv, D), dtype=np.float32) * 1e-3
+        kv.append(k_new, v_new)
+        ks.append(k_new)
+        vs.append(v_new)
+    K = h16(np.stack(ks[-cap:], axis=2))
+    V = h16(np.stack(vs[-cap:], axis=2))
+    for b in range(B):
+        kg, vg = kv.gather(b, 0, cap)
+        assert np.array_equal(kg, K[b]) and np.array_equal(vg, V[b])
+    q = g.standard_normal((B, Hq, D), dtype=np.float32) * 0.02
+    out = kv.attend(q)
+    check_attention(out, q, K, V, np.full(B, cap, dtype=np.int32))
+    kv.close()
+    with pytest.raises(ValueError):
+        skn.KVCache(ctx, 1, 1, 64, 8, dtype="bf16")
+
+
 def test_attention_argument_errors(ctx):
     kv = skn.KVCache(ctx, 1, 2, 64, 8)
     with pytest.raises(ValueError, match="Shapes do not align."):
