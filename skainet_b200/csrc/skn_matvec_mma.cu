@@ -1,4 +1,5 @@
-// K2 (decode matvec), integer tensor-core form:  y[N] = W_q[N,K] . x[K]  for Q4_K weights.
+// K2 (decode matvec), integer tensor-core form:  y[N] = W_q[N,K] . x[K]  for Q4_K (described here), Q6_K, Q8_0 and
+// Q4_0 weights (further down).
 //
 // The CUDA-core kernels of skn_matvec.cu spend one logic operation and half a packed FMA per
 // weight and end up bound by instruction issue at about half of the HBM rate.  Here the dot
@@ -14,10 +15,11 @@
 //     activation is at most 2^-23 of the super-block's largest one.
 //   * the A operand is the quant bytes as they lie in the block.  For the byte pair p of a
 //     super-block (sub-block 2p in the low nibbles, 2p+1 in the high ones) two MMAs run: one on
-//     `word & 0x0F0F0F0F` (L = the low-nibble dot) and one on the raw bytes (L + 16 H).  With
-//     the integer scales s0, s1 of the two sub-blocks, 16 (s0 L + s1 H) = (16 s0 - s1) L +
-//     s1 (L + 16 H): two integer multiply-adds per result, accumulated over the super-block in
-//     s32 (at most 2^29 in magnitude).
+//     `word & 0x0F0F0F0F` against the digits of the activations of sub-block 2p, one on
+//     `word & 0xF0F0F0F0` (the high nibbles times 16) against those of sub-block 2p+1.  The integer
+//     scales of the two sub-blocks multiply the s32 results (two integer multiply-adds per result),
+//     accumulated over the super-block as lo and hi sums (at most 2^29 in magnitude); lo * 16 + hi
+//     is 16 times the scaled dot product.
 //   * once per (row, super-block) the digit columns are recombined in fp32 and scaled by
 //     d * 2^(e-21) / 16; the -dmin * m * sum(x) term is added per row and super-block.
 //
