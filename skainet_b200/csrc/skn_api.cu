@@ -67,8 +67,8 @@ int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
         if (e__ != cudaSuccess) {                                    \
             int32_t rc__ = skn_check_cuda(nullptr, e__, #call);      \
             if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream); \
-            if (ctx->d_status) cudaFree(ctx->d_status);              \
-            if (ctx->h_status) cudaFreeHost(ctx->h_status);          \
+            if (ctx->d_status_base) cudaFree(ctx->d_status_base);    \
+            if (ctx->h_status_base) cudaFreeHost(ctx->h_status_base); \
             ctx->magic = 0;                                          \
             delete ctx;                                              \
             return rc__;                                             \
@@ -85,9 +85,11 @@ int32_t skn_ctx_create(int32_t device, skn_ctx **out) {
     ctx->stream = ctx->own_stream;
     ctx->prefill_min_m = 64;
     ctx->fused_exchange = -1;
-    CTX_TRY(cudaMalloc((void **)&ctx->d_status, 32768));
+    CTX_TRY(cudaMalloc((void **)&ctx->d_status_base, SKN_SMALL_OUT_BYTES + 32768));
+    ctx->d_status = reinterpret_cast<int32_t *>(ctx->d_status_base + SKN_SMALL_OUT_BYTES);
     CTX_TRY(cudaMemset(ctx->d_status, 0, 32768));
-    CTX_TRY(cudaMallocHost((void **)&ctx->h_status, 256));
+    CTX_TRY(cudaMallocHost((void **)&ctx->h_status_base, SKN_SMALL_OUT_BYTES + 256));
+    ctx->h_status = reinterpret_cast<int32_t *>(ctx->h_status_base + SKN_SMALL_OUT_BYTES);
 #undef CTX_TRY
     *ctx->h_status = 0;
     *out = ctx;
@@ -102,8 +104,8 @@ int32_t skn_ctx_destroy(skn_ctx *ctx) {
     if (ctx->d_stage_out) cudaFree(ctx->d_stage_out);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_scratch2) cudaFree(ctx->d_scratch2);
-    if (ctx->d_status) cudaFree(ctx->d_status);
-    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->d_status_base) cudaFree(ctx->d_status_base);
+    if (ctx->h_status_base) cudaFreeHost(ctx->h_status_base);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     ctx->magic = 0;
     delete ctx;
@@ -135,6 +137,13 @@ int32_t skn_sync(skn_ctx *ctx) {
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     SKN_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return skn_status_check(ctx);
+}
+
+}  // extern "C"
+
+// the status word has just arrived in the pinned mirror: report it (and clear it on the device)
+int32_t skn_status_check(skn_ctx *ctx) {
     const int32_t st = *ctx->h_status;
     if (st != 0) {
         cudaMemsetAsync(ctx->d_status, 0, sizeof(int32_t), ctx->stream);
@@ -144,6 +153,8 @@ int32_t skn_sync(skn_ctx *ctx) {
     }
     return SKN_OK;
 }
+
+extern "C" {
 
 int32_t skn_quant_geometry(int32_t ggml_type, int32_t *block_elems, int32_t *block_bytes) {
     int32_t e, b;
@@ -428,6 +439,25 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
     const size_t yb = (size_t)M * (size_t)w->n_rows * sizeof(float);
     rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, xb_al + bb + 256);
     if (rc) return rc;
+    if (yb <= SKN_SMALL_OUT_BYTES) {
+        // decode-size result: it is written right below the status word and comes back with it in ONE copy
+        // (a separate copy of the status costs as much as the matvec itself)
+        const size_t yb_al = (yb + 255) / 256 * 256;
+        float *dxs = (float *)ctx->d_stage_in;
+        float *dbs = bias_host ? (float *)((uint8_t *)ctx->d_stage_in + xb_al) : nullptr;
+        float *dys = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_status) - yb_al);
+        uint8_t *hys = reinterpret_cast<uint8_t *>(ctx->h_status) - yb_al;
+        if (xb) SKN_CUDA(ctx, cudaMemcpyAsync(dxs, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+        if (dbs) SKN_CUDA(ctx, cudaMemcpyAsync(dbs, bias_host, bb, cudaMemcpyHostToDevice, ctx->stream));
+        rc = skn_matmul_dev(ctx, w, dxs, M, K, dbs, dys);
+        if (rc) return rc;
+        SKN_CUDA(ctx, cudaMemcpyAsync(hys, dys, yb_al + sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+        SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        rc = skn_status_check(ctx);
+        if (rc) return rc;
+        memcpy(y_host, hys, yb);
+        return SKN_OK;
+    }
     rc = skn_stage_reserve(ctx, &ctx->d_stage_out, &ctx->d_stage_out_bytes, yb);
     if (rc) return rc;
     float *dx = (float *)ctx->d_stage_in;

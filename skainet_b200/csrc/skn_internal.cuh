@@ -28,6 +28,8 @@ struct skn_group_plan {
     skn_mv_plan pl;
 };
 
+constexpr size_t SKN_SMALL_OUT_BYTES = 96 * 1024;
+
 struct skn_ctx {
     uint32_t magic;
     int device;
@@ -40,6 +42,10 @@ struct skn_ctx {
     int kv_f16;                 // SKN_OPT_KV_F16
     int32_t *d_status;          // device status word written by bounded waits
     int32_t *h_status;          // pinned mirror
+    // Small results of the host-pointer calls sit directly BELOW the status word, on the device and in the
+    // pinned mirror alike, so that one device-to-host copy brings a result and the status together.
+    uint8_t *d_status_base;     // allocation: [SKN_SMALL_OUT_BYTES of result area][status / trace area]
+    uint8_t *h_status_base;     // pinned:     [SKN_SMALL_OUT_BYTES of result area][status word]
     // staging for the host-pointer entry points (grown on demand)
     void *d_stage_in;  size_t d_stage_in_bytes;
     void *d_stage_out; size_t d_stage_out_bytes;
@@ -68,6 +74,7 @@ int32_t skn_check_cuda(skn_ctx *ctx, cudaError_t e, const char *what);
 bool skn_ctx_ok(const skn_ctx *ctx);
 bool skn_tensor_ok(const skn_tensor *t);
 int32_t skn_stage_reserve(skn_ctx *ctx, void **buf, size_t *cap, size_t need);
+int32_t skn_status_check(skn_ctx *ctx);
 
 #define SKN_CUDA(ctx, call)                                            \
     do {                                                               \
