@@ -824,8 +824,13 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
 static int attn_pick_chunk(const skn_kvcache *kv, int n_q_heads, int tq, size_t scratch_cap) {
     // finer splits while 256-token (then 64-token) chunks leave SMs idle (short contexts, small
     // batches) and the partials of the finer split fit `scratch_cap` bytes
+    static const int forced = [] { const char *v = getenv("SKN_ATTN_CHUNK"); return v ? atoi(v) : 0; }();   // tuning knob
     const int chunks[3] = {ATT_CHUNK, 64, 32};
     int pick = ATT_CHUNK;
+    if (forced == 32 || forced == 64 || forced == ATT_CHUNK) {
+        const int64_t S = (kv->capacity + forced - 1) / forced;
+        if ((size_t)((int64_t)kv->batch * tq * n_q_heads * S * (kv->head_dim + 2) * 4) <= scratch_cap) return forced;
+    }
     for (int i = 0; i < 3; ++i) {
         const int c = chunks[i];
         const int64_t S = (kv->capacity + c - 1) / c;

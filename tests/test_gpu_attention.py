@@ -183,6 +183,32 @@ def test_fp16_cache_append_gather_and_ring_wrap(ctx):
         skn.KVCache(ctx, 1, 1, 64, 8, dtype="bf16")
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+def test_wrapped_ring_in_the_bulk_copy_regime(ctx, dtype):
+    """A full cache that has wrapped (start = 37, not a tile boundary) at a size where the 256-token splits run
+    on bulk-copied tiles: the tile that straddles the end of the ring arrives as two copies."""
+    g = synth.rng(41)
+    B, Hq, Hkv, D, cap, extra = 8, 32, 8, 128, 1280, 37
+    kc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    vc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype=dtype)
+    kv.load(kc, vc, np.full(B, cap, dtype=np.int32))
+    for i in range(extra):
+        k_new = g.standard_normal((B, Hkv, D), dtype=np.float32)
+        v_new = g.standard_normal((B, Hkv, D), dtype=np.float32)
+        kc[:, :, i] = k_new                      # a full ring overwrites its oldest slot
+        vc[:, :, i] = v_new
+        kv.append(k_new, v_new)
+    lens, start = kv.lengths()
+    assert np.all(lens == cap) and np.all(start == extra)
+    q = g.standard_normal((B, Hq, D), dtype=np.float32)
+    out = kv.attend(q)
+    kv.close()
+    if dtype == "f16":
+        kc, vc = h16(kc), h16(vc)
+    check_attention(out, q, kc, vc, lens, start)
+
+
 def test_attention_argument_errors(ctx):
     kv = skn.KVCache(ctx, 1, 2, 64, 8)
     with pytest.raises(ValueError, match="Shapes do not align."):
