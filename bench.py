@@ -9,8 +9,10 @@ weights from HBM).  One step = one pass over the stack: LAYERS matvec launches b
 
   value     GB/s of algorithmic bytes (blocks + x + y per matvec), inputs resident in HBM,
             timed with CUDA events on the launching stream;
-  e2e       the same metric through the host-pointer C ABI call (skn_matmul): x copied from
-            pinned host memory and y copied back inside the timed region, weights resident;
+  e2e       the same metric through the host-pointer C ABI: a step is one skn_matmul_async per layer (x copied
+            from pinned host memory, y copied back to pinned host memory, every layer) and one skn_sync; the
+            figure of the blocking call (skn_matmul per layer, a synchronisation per layer) is reported beside
+            it as e2e.blocking_call;
   roofline  the streaming matvec kernel against the measured HBM copy bandwidth;
   cpu_baseline  the CPU oracle (a C restatement; the reference's Kotlin cannot run here)
             timed on this host's cores on a bounded sample of the same workload.
@@ -225,11 +227,24 @@ def run_ours(args):
     L = _ffi.lib()
     xh_ptr, yh_ptr = x_host.data_ptr(), y_host.data_ptr()
 
-    def step_e2e():
+    def step_e2e_blocking():
         for t in tensors:
             rc = L.skn_matmul(ctx.handle, t.handle, xh_ptr, 1, N_COLS, None, yh_ptr)
             if rc != 0:
                 raise RuntimeError(L.skn_last_error(ctx.handle).decode())
+
+    # every layer's result in its own pinned row: nothing is overwritten before the step's synchronisation
+    y_host_all = torch.empty((layers, N_ROWS), dtype=torch.float32).pin_memory()
+    yh_all_ptr = y_host_all.data_ptr()
+
+    def step_e2e():
+        for i, t in enumerate(tensors):
+            rc = L.skn_matmul_async(ctx.handle, t.handle, xh_ptr, 1, N_COLS, None, yh_all_ptr + i * 4 * N_ROWS)
+            if rc != 0:
+                raise RuntimeError(L.skn_last_error(ctx.handle).decode())
+        rc = L.skn_sync(ctx.handle)
+        if rc != 0:
+            raise RuntimeError(L.skn_last_error(ctx.handle).decode())
 
     def barrier():
         if world > 1:
@@ -297,16 +312,23 @@ def run_ours(args):
         step_e2e()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    step_e2e_blocking()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e_blocking()
+    torch.cuda.synchronize()
+    e2e_blocking_s = time.perf_counter() - t0
     if world > 1:
-        te = torch.tensor([e2e_s], device=dev)
+        te = torch.tensor([e2e_s, e2e_blocking_s], device=dev)
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_s = float(te.item())
+        e2e_s, e2e_blocking_s = float(te[0].item()), float(te[1].item())
     clocks = sampler.stop() if rank == 0 else None
 
     # sanity: results are finite and the same from both paths
     y_chk = y_dev[-1].cpu()
     assert torch.isfinite(y_chk).all()
     assert torch.equal(y_chk, y_host), "device-pointer and host-pointer paths disagree"
+    assert torch.equal(y_chk, y_host_all[-1]), "device-pointer and asynchronous host-pointer paths disagree"
 
     if rank == 0:
         launches_per_step = layers
@@ -334,7 +356,10 @@ def run_ours(args):
                        "other_order": None if ms_other is None else
                        {"order": other, "value": total_bytes * args.steps / (ms_other * 1e-3) / 1e9, "unit": UNIT}},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": layers * 4 * N_COLS,
-                    "d2h_bytes_per_step": layers * 4 * N_ROWS, "steps": e2e_steps},
+                    "d2h_bytes_per_step": layers * 4 * N_ROWS, "steps": e2e_steps,
+                    "api": "per step: skn_matmul_async for every layer (pinned host x in, pinned host y out), then skn_sync",
+                    "blocking_call": {"value": total_bytes * e2e_steps / e2e_blocking_s / 1e9, "unit": UNIT,
+                                      "api": "skn_matmul per layer (returns with y in host memory)"}},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "skn_matvec_mma<0, 2, 1, true, 0>", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": UNIT, "frac": achieved / peak,

@@ -166,6 +166,13 @@ int32_t skn_matmul(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32
                    const float *bias_host, float *y_host);
 int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, int32_t M, int64_t K,
                        const float *bias_dev, float *y_dev);
+/* skn_matmul for a loop over layers: returns as soon as the copy of x (and bias), the kernel and the copy of y
+ * are enqueued on the context's stream.  x_host and bias_host must stay unchanged and y_host must not be read
+ * until skn_sync(ctx) has returned (it also reports the kernels' status).  Calls on one context run in the order
+ * they were made, so a result may be the next call's x_host.  Page-locked host buffers keep the copies
+ * asynchronous; pageable ones work, with the copies staged by the driver. */
+int32_t skn_matmul_async(skn_ctx *ctx, const skn_tensor *w, const float *x_host, int32_t M, int64_t K,
+                         const float *bias_host, float *y_host);
 
 /* y[t] = W[t] . x (+ add[t]) for n <= 3 weights that multiply the same activation vector x (Q/K/V,
  * gate/up): one launch when the weights share type and K, separate launches otherwise.  add[t]

@@ -157,6 +157,20 @@ cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, i
     skn_rope_kernel<<<glue_blocks(pairs, sm_count), 256, 0, st>>>(x, len, T, H, D, log2((double)theta), pairs);
     return cudaGetLastError();
 }
+// dst[0..n) = src[0..n) in 16-byte words (n a multiple of 4, both 16-byte aligned).  `src` may be page-locked
+// host memory mapped into the device's address space: the copy then crosses PCIe inside a kernel, which costs
+// a kernel-to-kernel hand-over instead of a copy-engine operation between two kernels.
+__global__ void skn_fetch_kernel(const float4 *__restrict__ src, float4 *__restrict__ dst, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+cudaError_t skn_launch_fetch(const float *src, float *dst, int64_t n, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    const int64_t n4 = n / 4;
+    int blocks = (int)((n4 + 255) / 256);
+    if (blocks > 32) blocks = 32;
+    skn_fetch_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(dst), n4);
+    return cudaGetLastError();
+}
 cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     skn_add_kernel<<<glue_blocks(n / 4, sm_count), 256, 0, st>>>(a, b, out, n / 4);

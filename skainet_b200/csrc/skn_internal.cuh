@@ -46,6 +46,7 @@ struct skn_ctx {
     // pinned mirror alike, so that one device-to-host copy brings a result and the status together.
     uint8_t *d_status_base;     // allocation: [SKN_SMALL_OUT_BYTES of result area][status / trace area]
     uint8_t *h_status_base;     // pinned:     [SKN_SMALL_OUT_BYTES of result area][status word]
+    int32_t *h_status_dev;      // device-side address of h_status (page-locked memory is mapped)
     // staging for the host-pointer entry points (grown on demand)
     void *d_stage_in;  size_t d_stage_in_bytes;
     void *d_stage_out; size_t d_stage_out_bytes;
@@ -143,6 +144,7 @@ cudaError_t skn_launch_silu_mul(const float *g, const float *u, float *h, int64_
 cudaError_t skn_launch_rmsnorm(const float *x, const float *gain, float *y, int M, int D, float eps, cudaStream_t st);
 cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, int D, float theta, int sm_count, cudaStream_t st);
 cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st);
+cudaError_t skn_launch_fetch(const float *src, float *dst, int64_t n, cudaStream_t st);
 cudaError_t skn_launch_last_rows(const float *in, float *out, int B, int T, int D, cudaStream_t st);
 size_t skn_argmax_scratch_bytes(int M);
 cudaError_t skn_launch_argmax(const float *logits, int M, int V, int32_t *ids, void *scratch, cudaStream_t st);

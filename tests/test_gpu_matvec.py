@@ -76,6 +76,41 @@ def test_q6k_at_lm_head_and_down_projection_sizes(ctx, N, K, M):
     run_case(ctx, synth.Q6_K, N, K, M, seed=5000 + N + K + M, bias=(M == 2))
 
 
+@pytest.mark.parametrize("pinned", [False, True])
+def test_asynchronous_host_calls_run_in_order(ctx, pinned):
+    """skn_matmul_async: two dependent products enqueued back to back (the first result is the second call's
+    x_host), one skn_sync; results equal the blocking calls bit for bit.  Pageable buffers go through staged
+    copies, page-locked ones are read and written by the kernels themselves."""
+    import ctypes
+    from skainet_b200 import _ffi
+    L = _ffi.lib()
+    g = synth.rng(61)
+    N1, K, N2 = 512, 1024, 96
+    w1, w2 = synth.make_weight(g, synth.Q4_K, N1, K), synth.make_weight(g, synth.Q6_K, N2, N1)
+    x = synth.make_activations(g, 1, K)[0]
+    t1, t2 = skn.QuantTensor(ctx, (N1, K), synth.Q4_K, w1), skn.QuantTensor(ctx, (N2, N1), synth.Q6_K, w2)
+    if pinned:
+        torch = pytest.importorskip("torch")
+        keep = [torch.zeros(n, dtype=torch.float32).pin_memory() for n in (K, N1, N2)]
+        xp, y1, y2 = (t.numpy() for t in keep)
+        xp[:] = x
+        x = xp
+    else:
+        y1 = np.zeros(N1, dtype=np.float32)
+        y2 = np.zeros(N2, dtype=np.float32)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    assert L.skn_matmul_async(ctx.handle, t1.handle, ptr(x), 1, K, None, ptr(y1)) == 0
+    assert L.skn_matmul_async(ctx.handle, t2.handle, ptr(y1), 1, N1, None, ptr(y2)) == 0
+    assert L.skn_sync(ctx.handle) == 0
+    b1 = t1.matmul_t(x)
+    b2 = t2.matmul_t(b1)
+    t1.close()
+    t2.close()
+    assert np.array_equal(y1, b1) and np.array_equal(y2, b2)
+    ref1, ad1 = oracle.matmul(synth.Q4_K, w1, N1, K, x[None, :])
+    assert_close_dot(y1[None, :], ref1, ad1, FP32_TOL, "first product")
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at cfg1's size: W(a x1 + b x2) = a W x1 + b W x2."""
     w, _ = synth.cfg1(0)
