@@ -263,6 +263,20 @@ class QuantTensor:
                                                      y.ctypes.data))
         return y[0] if vec else y
 
+    def matmul_t_async(self, x: np.ndarray, out: np.ndarray, bias: Optional[np.ndarray] = None):
+        """Host-pointer form that only enqueues (skn_matmul_async): x [K] or [M, K] and out [N] or [M, N] are
+        C-contiguous fp32 host arrays that the caller keeps alive and untouched until Context.sync() returns
+        (page-locked arrays keep the call free of staged copies)."""
+        for a in (x, out) + (() if bias is None else (bias,)):
+            if a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
+                raise ValueError("fp32 C-contiguous host arrays are required")
+        m = 1 if x.ndim == 1 else x.shape[0]
+        n = self.shape.dimensions[0]
+        if x.ndim not in (1, 2) or out.size != m * n or (bias is not None and bias.shape != (n,)):
+            raise ValueError("Shapes do not align.")
+        _check(self.ctx.handle, _ffi.lib().skn_matmul_async(self.ctx.handle, self._h, x.ctypes.data, m, x.shape[-1],
+                                                           _ptr(bias), out.ctypes.data))
+
     def matmul_t_dev(self, x_dev, m: int, y_dev, bias_dev=None, k: Optional[int] = None):
         """Device-pointer form: enqueue only (x_dev, y_dev: torch CUDA tensors or addresses)."""
         kk = self.shape.dimensions[1] if k is None else k
