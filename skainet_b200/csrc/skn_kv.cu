@@ -1,6 +1,6 @@
 // K5-K7: device-resident KV cache and decode attention.
 //
-// Layout (fp32, head-major ring):  K, V : [batch][n_kv_heads][capacity][head_dim].
+// Layout (head-major ring of fp32 or, on request, fp16 elements):  K, V : [batch][n_kv_heads][capacity][head_dim].
 // Sequence b holds len[b] tokens; logical position p (0 = oldest) lives at ring slot
 // (start[b] + p) % capacity.  All tokens of one (sequence, kv head) are contiguous, so the
 // attention kernel streams them with fully coalesced 512-byte rows.
@@ -9,16 +9,19 @@
 //                         advances len (or start, once the ring is full)
 //  skn_kv_gather_kernel   ring -> dense, oldest first (export / verification)
 //  skn_attn_split_kernel  grid (splits, kv heads, batch): one CTA attends G = Hq/Hkv query
-//                         heads to a chunk of 256 cached tokens.  Pass 1 reads K once and
+//                         heads to a chunk of 256 (64, 32 for short contexts) cached tokens.  Pass 1 reads K once and
 //                         leaves the chunk's scores in shared memory (lane = 4 head dims;
 //                         32 (token, head) partial dots are summed with one transposed
 //                         butterfly of 31 shuffles); pass 2 reads V once and accumulates
 //                         exp(s - max) * v with the probabilities broadcast from shared
 //                         memory.  Writes (max, sum, unnormalised output) per (head, split)
 //                         to scratch.
-//  skn_attn_merge_kernel  log-sum-exp merge of the splits -> out[b][h][:]
+//  skn_attn_stream_kernel the same split for long contexts with the K and V tiles brought into a
+//                         shared-memory ring by bulk async copies (a producer warp, mbarriers)
+//  skn_attn_merge_kernel  log-sum-exp merge of the splits -> out[b][h][:] (small grids merge in
+//                         the split kernel: the CTA that draws the last ticket)
 //
-// HBM-bound: 2 * head_dim * 4 bytes per cached token per kv head, read exactly once.
+// HBM-bound: 2 * head_dim * element size bytes per cached token per kv head, read exactly once.
 #include "skn_internal.cuh"
 #include "skn_ptx.cuh"
 
