@@ -53,6 +53,10 @@ def test_bad_handles_are_rejected_without_a_gpu():
     assert L.skn_sync(None) == 7
     out = ctypes.c_void_p()
     assert L.skn_tensor_upload_quant(None, 12, 1, 256, None, 144, ctypes.byref(out)) == 7
+    assert L.skn_kv_create_typed(None, 1, 1, 64, 8, 1, ctypes.byref(out)) == 7
+    assert L.skn_matmul_async(None, None, None, 1, 256, None, None) == 7
+    dt = ctypes.c_int32()
+    assert L.skn_kv_dtype(None, ctypes.byref(dt)) == 7
 
 
 def test_quant_shape_to_byte_shape():
