@@ -1015,8 +1015,9 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     static const int pdl = env_int("SKN_PDL", 1);
+    static const int pdl_max_mb = env_int("SKN_PDL_MAX_MB", 1 << 20);   // tuning knob: largest launch (weight bytes) that may start early
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = (pdl && tot * w[0]->pitch <= (int64_t)pdl_max_mb * (1 << 20)) ? 1 : 0;
     err = cudaLaunchKernelEx(&cfg, mm_kernel(fmt, pl.nch, n_act, feat), grp, w[0]->pitch, (int)w[0]->n_cols, pl.wg, x, ctx->d_status,
                              ctx->relaxed_order);
     return true;
