@@ -42,18 +42,21 @@
 // per row) make a K super-chunk; rows are padded by 32 bytes in shared memory, which puts the
 // eight row groups of a fragment load on disjoint banks (row stride = 8 words mod 32).
 // Q6_K: one 210-byte block per super-block; eight of them are 1680 bytes = a multiple of 16 (a bulk
-// copy's granularity), padded by 16 to the same 8-words-mod-32 row stride.  Its scale groups are 16
-// weights, so the group sums of x are kept per 16 activations (XS per super-block).
+// copy's granularity) and 420 words = 4 mod 32: its fragments are read with 32-bit loads (lane (g, t) reads
+// word t of row g), which that stride spreads over all 32 banks without padding (a stride of 8 words mod 32,
+// right for the 64-bit loads of the other formats, made rows g and g + 4 collide: 2.5 M bank conflicts per
+// 32000 x 4096 launch).  Its scale groups are 16 weights, so the group sums of x are kept per 16
+// activations (XS per super-block).
 constexpr int MM_FMT_Q4K = 0, MM_FMT_Q80 = 1, MM_FMT_Q40 = 2, MM_FMT_Q6K = 3;
 template <int FMT> struct MmFmt;
 template <> struct MmFmt<MM_FMT_Q4K> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 32, XS = 8; };
 template <> struct MmFmt<MM_FMT_Q80> { static constexpr int KS = 8, SB_BYTES = 272, PAD = 32, XS = 8; };
 template <> struct MmFmt<MM_FMT_Q40> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 32, XS = 8; };
-template <> struct MmFmt<MM_FMT_Q6K> { static constexpr int KS = 8, SB_BYTES = 210, PAD = 16, XS = 16; };
+template <> struct MmFmt<MM_FMT_Q6K> { static constexpr int KS = 8, SB_BYTES = 210, PAD = 0, XS = 16; };
 static constexpr int mm_ks(int fmt) { return (fmt == MM_FMT_Q80 || fmt == MM_FMT_Q6K) ? 8 : 16; }
 static constexpr int mm_sb_bytes(int fmt) { return fmt == MM_FMT_Q80 ? 272 : (fmt == MM_FMT_Q6K ? 210 : 144); }
 static constexpr int mm_xs(int fmt) { return fmt == MM_FMT_Q6K ? 16 : 8; }
-static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + (fmt == MM_FMT_Q6K ? 16 : 32)); }
+static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + (fmt == MM_FMT_Q6K ? 0 : 32)); }
 
 __device__ __forceinline__ void skn_mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
