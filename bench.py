@@ -45,9 +45,9 @@ N_ROWS, N_COLS = 4096, 4096
 Q4_K = 12
 W_BYTES = N_ROWS * (N_COLS // 256) * 144
 ALG_BYTES = W_BYTES + 4 * N_COLS + 4 * N_ROWS      # 9 469 952 per matvec
-# dram__bytes_read.sum + dram__bytes_write.sum of one skn_matvec_stream<Q4KStream> launch on this
+# dram__bytes_read.sum + dram__bytes_write.sum of one skn_matvec_mma<0, 2, 1, true, 0> launch on this
 # workload, from the ncu capture summarised in profiles/q4k_matvec_cfg1.md
-DRAM_TRAFFIC_PER_LAUNCH = 9507328
+DRAM_TRAFFIC_PER_LAUNCH = 9489408
 METRIC = "q4k_matvec_gbs"
 UNIT = "GB/s"
 
