@@ -111,6 +111,32 @@ def test_asynchronous_host_calls_run_in_order(ctx, pinned):
     assert_close_dot(y1[None, :], ref1, ad1, FP32_TOL, "first product")
 
 
+def test_blocking_call_on_page_locked_buffers(ctx):
+    """skn_matmul with page-locked x, bias and y (no copy-engine transfer: x is fetched by a kernel, y and the
+    status word are written to the mapped buffers) returns the bits of the pageable route, for 1 and 3 rows."""
+    import ctypes
+    torch = pytest.importorskip("torch")
+    from skainet_b200 import _ffi
+    L = _ffi.lib()
+    g = synth.rng(62)
+    N, K = 328, 768
+    w = synth.make_weight(g, synth.Q4_K, N, K)
+    t = skn.QuantTensor(ctx, (N, K), synth.Q4_K, w)
+    for M in (1, 3):
+        x = synth.make_activations(g, M, K)
+        b = g.standard_normal(N).astype(np.float32)
+        want = t.matmul_t(x if M > 1 else x[0], b)
+        keep = [torch.zeros(n, dtype=torch.float32).pin_memory() for n in (M * K, N, M * N)]
+        xp, bp, yp = (a.numpy() for a in keep)
+        xp[:] = x.reshape(-1)
+        bp[:] = b
+        rc = L.skn_matmul(ctx.handle, t.handle, xp.ctypes.data_as(ctypes.c_void_p), M, K, bp.ctypes.data_as(ctypes.c_void_p),
+                          yp.ctypes.data_as(ctypes.c_void_p))
+        assert rc == 0
+        assert np.array_equal(yp.reshape(np.shape(want)), want)
+    t.close()
+
+
 def test_linearity_at_full_size(ctx):
     """Size-independent property at cfg1's size: W(a x1 + b x2) = a W x1 + b W x2."""
     w, _ = synth.cfg1(0)
