@@ -14,8 +14,12 @@
  * reference's repository root.
  *
  * A context is bound to one CUDA device and must be used by one host thread at a
- * time.  There is no CPU fallback: without a usable CUDA device every compute entry
- * point fails with SKN_ERR_CUDA.
+ * time: an entry point called while another thread is inside a call on the same context
+ * (directly, or through one of its tensors, caches, exchanges or decoders) returns
+ * SKN_ERR_BUSY without touching the context; its message is read with skn_last_error(NULL)
+ * on the refused thread.  The reference is single-threaded (no counterpart).  There is no
+ * CPU fallback: without a usable CUDA device every compute entry point fails with
+ * SKN_ERR_CUDA.
  */
 #ifndef SKAINET_CUDA_H
 #define SKAINET_CUDA_H
@@ -39,6 +43,7 @@ extern "C" {
 #define SKN_ERR_BAD_HANDLE 7
 #define SKN_ERR_ARG 8        /* null pointer, negative size, ... */
 #define SKN_ERR_COMM 9
+#define SKN_ERR_BUSY 10      /* the context is inside a call made by another host thread */
 
 /* GGML type ids: gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:14-52 */
 #define SKN_TYPE_Q4_0 2
@@ -104,10 +109,14 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
 /* SKN_OPT_KV_F16 (default 0): with value 1, decoders created afterwards (skn_llama_create, skn_llama_create_tp)
  * keep their KV caches in fp16 (see skn_kv_create_typed). */
 #define SKN_OPT_KV_F16 4
+/* SKN_OPT_WAIT_LIMIT_MS (default 0 = 2000): how long a kernel of the inter-GPU exchange waits for its
+ * peers' flags before it gives up, records SKN_ERR_TIMEOUT and returns (1 .. 600000 milliseconds). */
+#define SKN_OPT_WAIT_LIMIT_MS 5
 int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value);
 
-/* Wait for everything enqueued on the context's stream; reports a pending
- * device-side status (e.g. SKN_ERR_TIMEOUT) if a kernel recorded one. */
+/* Wait for everything enqueued on the context's stream; reports a pending device-side status if a
+ * kernel recorded one, and clears it: SKN_ERR_TIMEOUT (a bounded wait ran out) or SKN_ERR_SHAPE (a
+ * decoder step found its KV cache full: nothing was overwritten, the step's results are invalid). */
 int32_t skn_sync(skn_ctx *ctx);
 
 /* ---- block geometry ---------------------------------------------------------------- */
@@ -352,8 +361,13 @@ int32_t skn_llama_reset(skn_llama *m);
  * next (greedy token per sequence) and logits ([max_batch][vocab], last position) may be NULL. */
 int32_t skn_llama_forward(skn_llama *m, const int32_t *tokens_host, int32_t T, int32_t *next_host,
                           float *logits_host);
+/* The device form only enqueues.  A single-token step (tokens_dev == NULL) is a fixed launch sequence and may
+ * be captured into a CUDA graph once an uncaptured call has sized the scratch buffers; REPLAYING the graph
+ * advances the caches on the device but not skn_llama_position, so the host must count its replays against
+ * max_ctx itself.  A step that finds a cache full appends nothing, leaves the lengths at the capacity and
+ * makes the next skn_sync return SKN_ERR_SHAPE; skn_llama_reset starts over. */
 int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T);
-/* tokens cached per sequence so far (-1 on a bad handle) */
+/* tokens cached per sequence so far as counted by the host-side calls (-1 on a bad handle) */
 int32_t skn_llama_position(const skn_llama *m);
 
 /* ---- GGUF container --------------------------------------------------------------------------

@@ -24,6 +24,15 @@ int32_t skn_check_cuda(skn_ctx *ctx, cudaError_t e, const char *what) {
     return skn_fail(ctx, code, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
 }
 
+uint64_t skn_thread_token() {
+    static thread_local char anchor;        // its address is unique among live threads and never 0
+    return (uint64_t)(uintptr_t)&anchor;
+}
+
+int32_t skn_busy_fail() {
+    return skn_fail(nullptr, SKN_ERR_BUSY, "the context is in use by another host thread (one thread at a time)");
+}
+
 bool skn_ctx_ok(const skn_ctx *ctx) { return ctx && ctx->magic == SKN_MAGIC_CTX; }
 bool skn_tensor_ok(const skn_tensor *t) { return t && t->magic == SKN_MAGIC_TENSOR && skn_ctx_ok(t->ctx); }
 
@@ -119,12 +128,14 @@ int32_t skn_ctx_destroy(skn_ctx *ctx) {
 
 int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
     return SKN_OK;
 }
 
 int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     switch (option) {
     case SKN_OPT_RELAXED_ORDER: ctx->relaxed_order = value ? 1 : 0; return SKN_OK;
     case SKN_OPT_PREFILL_MIN_M:
@@ -133,12 +144,21 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
         return SKN_OK;
     case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value < 0 ? -1 : (value ? 1 : 0); return SKN_OK;
     case SKN_OPT_KV_F16: ctx->kv_f16 = value ? 1 : 0; return SKN_OK;
+    case SKN_OPT_WAIT_LIMIT_MS: {
+        if (value < 0 || value > 600000) return skn_fail(ctx, SKN_ERR_ARG, "wait limit outside [0, 600000] ms");
+        const int32_t ms = (int32_t)value;
+        SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+        SKN_CUDA(ctx, cudaMemcpyAsync(ctx->d_status + SKN_STATUS_WAIT_MS, &ms, sizeof(ms), cudaMemcpyHostToDevice, ctx->stream));
+        SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        return SKN_OK;
+    }
     default: return skn_fail(ctx, SKN_ERR_ARG, "unknown option %d", option);
     }
 }
 
 int32_t skn_sync(skn_ctx *ctx) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     SKN_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -154,7 +174,9 @@ int32_t skn_status_check(skn_ctx *ctx) {
         cudaMemsetAsync(ctx->d_status, 0, sizeof(int32_t), ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         return skn_fail(ctx, st, "a kernel reported device-side status %d (%s)", st,
-                        st == SKN_ERR_TIMEOUT ? "a bounded wait ran out" : "see status codes");
+                        st == SKN_ERR_TIMEOUT ? "a bounded wait ran out"
+                        : st == SKN_ERR_SHAPE ? "a KV cache was asked to hold more tokens than its capacity; nothing was overwritten"
+                                              : "see status codes");
     }
     return SKN_OK;
 }
@@ -183,6 +205,7 @@ int32_t skn_tensor_upload_quant_shard(skn_ctx *ctx, int32_t ggml_type, int64_t n
                                       const void *host_blocks, int64_t n_bytes, int64_t row_begin, int64_t row_count,
                                       int64_t col_begin, int64_t col_count, skn_tensor **out) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     *out = nullptr;
     int32_t e, b;
@@ -241,6 +264,7 @@ int32_t skn_tensor_upload_quant(skn_ctx *ctx, int32_t ggml_type, int64_t n_rows,
 int32_t skn_tensor_destroy(skn_tensor *t) {
     if (!t || t->magic != SKN_MAGIC_TENSOR) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad tensor handle");
     if (skn_ctx_ok(t->ctx)) {
+        SKN_ENTER(t->ctx);
         cudaSetDevice(t->ctx->device);
         cudaStreamSynchronize(t->ctx->stream);
     }
@@ -264,6 +288,7 @@ int32_t skn_tensor_info(const skn_tensor *t, int32_t *ggml_type, int64_t *n_rows
 
 int32_t skn_dequantize_dev(skn_ctx *ctx, const skn_tensor *t, float *out_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!skn_tensor_ok(t) || t->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
     if (!out_dev) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     if (((uintptr_t)out_dev) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "output must be 16-byte aligned");
@@ -274,6 +299,7 @@ int32_t skn_dequantize_dev(skn_ctx *ctx, const skn_tensor *t, float *out_dev) {
 
 int32_t skn_dequantize(skn_ctx *ctx, const skn_tensor *t, float *out_host) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!skn_tensor_ok(t) || t->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
     if (!out_host) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     const size_t bytes = (size_t)t->n_rows * (size_t)t->n_cols * sizeof(float);
@@ -300,6 +326,7 @@ int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, in
                        const float *bias_dev, float *y_dev) {
     int32_t rc = check_matmul_args(ctx, w, x_dev, M, K, y_dev);
     if (rc) return rc;
+    SKN_ENTER(ctx);
     if (M == 0 || w->n_rows == 0) return SKN_OK;
     if ((((uintptr_t)x_dev) & 15) || (((uintptr_t)y_dev) & 15))
         return skn_fail(ctx, SKN_ERR_ALIGN, "x and y must be 16-byte aligned device pointers");
@@ -330,6 +357,7 @@ int32_t skn_matmul_dev(skn_ctx *ctx, const skn_tensor *w, const float *x_dev, in
 int32_t skn_matvec_group_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w, const float *x_dev,
                              float *const *y_dev, const float *const *add_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (n < 1 || n > 3 || !w || !y_dev || !x_dev) return skn_fail(ctx, SKN_ERR_ARG, "1 to 3 tensors, non-NULL arrays");
     for (int32_t t = 0; t < n; ++t) {
         if (!skn_tensor_ok(w[t]) || w[t]->ctx != ctx) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
@@ -346,6 +374,7 @@ int32_t skn_matvec_fused_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w
                              float *const *y_dev, const float *const *add_dev, const float *norm_gain_dev,
                              float norm_eps, const float *silu_u_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (n < 1 || n > 3 || !w || !y_dev || !x_dev) return skn_fail(ctx, SKN_ERR_ARG, "1 to 3 tensors, non-NULL arrays");
     if (norm_gain_dev && silu_u_dev) return skn_fail(ctx, SKN_ERR_ARG, "either a norm gain or a SwiGLU partner, not both");
     for (int32_t t = 0; t < n; ++t) {
@@ -379,6 +408,7 @@ int32_t skn_matvec_fused_dev(skn_ctx *ctx, int32_t n, const skn_tensor *const *w
 int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
                            const float *x_dev, int32_t M, float *y_dev) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!skn_tensor_ok(wg) || !skn_tensor_ok(wu) || !skn_tensor_ok(wd) || wg->ctx != ctx || wu->ctx != ctx || wd->ctx != ctx)
         return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
     if (M < 0) return skn_fail(ctx, SKN_ERR_ARG, "M is negative");
@@ -415,6 +445,7 @@ int32_t skn_ffn_swiglu_dev(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor 
 int32_t skn_ffn_swiglu(skn_ctx *ctx, const skn_tensor *wg, const skn_tensor *wu, const skn_tensor *wd,
                        const float *x_host, int32_t M, float *y_host) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!skn_tensor_ok(wg) || !skn_tensor_ok(wd)) return skn_fail(ctx, SKN_ERR_BAD_HANDLE, "bad tensor handle");
     if (M < 0) return skn_fail(ctx, SKN_ERR_ARG, "M is negative");
     if (M == 0) return SKN_OK;
@@ -449,8 +480,12 @@ static int32_t matmul_host(skn_ctx *ctx, const skn_tensor *w, const float *x_hos
                            float *y_host, bool sync) {
     int32_t rc = check_matmul_args(ctx, w, x_host, M, K, y_host);
     if (rc) return rc;
+    SKN_ENTER(ctx);
     if (M == 0 || w->n_rows == 0) return SKN_OK;
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
+    // The product reads what the fetch kernel (or the staged copy) of this very call wrote: that chain keeps
+    // stream order whatever SKN_OPT_RELAXED_ORDER says about the caller's consecutive calls.
+    skn_order_guard guard(ctx);
     const size_t xb = (size_t)M * (size_t)K * sizeof(float);
     const size_t bb = bias_host ? (size_t)w->n_rows * sizeof(float) : 0;
     const size_t xb_al = (xb + 255) / 256 * 256;

@@ -27,6 +27,7 @@
 #include "skn_ptx.cuh"
 
 #include <new>
+#include <stdlib.h>
 
 #define SKN_MAGIC_COMM 0x736b6e6du   // 'sknm'
 
@@ -118,10 +119,10 @@ skn_allreduce_push_kernel(comm_peers peers, int rank, int world, int64_t cap, ui
     if (threadIdx.x < world && threadIdx.x != rank) {
         const uint32_t *flag = comm_flag(peers.base[rank], buf, threadIdx.x);
         if (*reinterpret_cast<volatile int32_t *>(status) == 0) {
-            const uint64_t t0 = skn_globaltimer_ns();
+            const uint64_t t0 = skn_globaltimer_ns(), limit = skn_wait_limit_ns(status);
             uint32_t spins = 0;
             while (ld_acquire_sys(flag) != q + 1) {
-                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > 2000000000ull) {
+                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > limit) {
                     atomicExch(status, SKN_ERR_TIMEOUT);
                     break;
                 }
@@ -260,6 +261,8 @@ int32_t skn_comm_connect_local(skn_comm *const *comms, int32_t n) {
         SKN_CUDA(ctx, cudaSetDevice(ctx->device));
         for (int j = 0; j < n; ++j) {
             if (j == i) continue;
+            if (getenv("SKN_FAKE_NO_PEER_ACCESS"))
+                return skn_fail(ctx, SKN_ERR_COMM, "device %d cannot access device %d", ctx->device, comms[j]->ctx->device);
             if (comms[j]->ctx->device != ctx->device) {
                 int can = 0;
                 SKN_CUDA(ctx, cudaDeviceCanAccessPeer(&can, ctx->device, comms[j]->ctx->device));
@@ -289,6 +292,7 @@ int32_t skn_comm_info(const skn_comm *c, int32_t *rank, int32_t *world, int64_t 
 int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *resid_dev, float *out_dev, int64_t n) {
     if (!comm_ok(c)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad exchange handle");
     skn_ctx *ctx = c->ctx;
+    SKN_ENTER(ctx);
     if (!c->connected) return skn_fail(ctx, SKN_ERR_COMM, "exchange not connected");
     if (n < 0 || n % 4) return skn_fail(ctx, SKN_ERR_SHAPE, "element count must be a non-negative multiple of 4");
     if (n > c->capacity) return skn_fail(ctx, SKN_ERR_SHAPE, "%lld floats exceed the exchange capacity %lld", (long long)n, (long long)c->capacity);

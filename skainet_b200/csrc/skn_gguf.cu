@@ -134,7 +134,12 @@ int32_t skn_gguf_open(const char *path, skn_gguf **out) {
     const uint64_t n_tensors = c.u64(), n_kv = c.u64();
     if (magic != 0x46554747u) rc = skn_fail(nullptr, SKN_ERR_ARG, "GGUF magic invalid");               // Constants.kt:10
     else if (g->version != 2 && g->version != 3) rc = skn_fail(nullptr, SKN_ERR_ARG, "Sorry, file appears to be version %u that we cannot handle", g->version);
-    else if (n_tensors > g->size || n_kv > g->size) rc = skn_fail(nullptr, SKN_ERR_ARG, "corrupt header counts");
+    // a metadata entry is at least 13 bytes (key length, type, one value byte), a tensor record at least 24
+    // (name length, rank, type, offset): counts the rest of the file cannot hold are corrupt, and nothing
+    // is reserved for them
+    else if (n_kv > (g->size - 24) / 13 || n_tensors > (g->size - 24) / 24 || n_kv * 13 + n_tensors * 24 > g->size - 24)
+        rc = skn_fail(nullptr, SKN_ERR_ARG, "corrupt header counts (%llu tensors, %llu metadata entries in %llu bytes)",
+                      (unsigned long long)n_tensors, (unsigned long long)n_kv, (unsigned long long)g->size);
     try {
         if (rc == SKN_OK) {
             g->kvs.reserve((size_t)n_kv);
@@ -183,11 +188,17 @@ int32_t skn_gguf_open(const char *path, skn_gguf **out) {
     if (rc == SKN_OK) {
         const uint64_t pos = (uint64_t)(c.p - g->base);
         g->data_start = (pos + g->alignment - 1) / g->alignment * g->alignment;
-        for (const auto &t : g->tensors)
+        for (const auto &t : g->tensors) {
+            if (t.offset % g->alignment) {
+                rc = skn_fail(nullptr, SKN_ERR_ARG, "%s: a tensor's data offset %llu is not a multiple of the alignment %llu", path,
+                              (unsigned long long)t.offset, (unsigned long long)g->alignment);
+                break;
+            }
             if (t.offset > g->size || g->data_start > g->size - t.offset || t.n_bytes > g->size - g->data_start - t.offset) {
                 rc = skn_fail(nullptr, SKN_ERR_ARG, "%s is truncated: a tensor's data lies outside the file", path);
                 break;
             }
+        }
     }
     if (rc != SKN_OK) {
         skn_gguf_close(g);

@@ -1,5 +1,6 @@
 // Small element-wise kernels around the matmuls (no counterpart in the reference).
 #include "skn_internal.cuh"
+#include "skn_ptx.cuh"
 
 // h = silu(g) * u, fp32 (the decode-size SwiGLU; the prefill path fuses this into the
 // tensor-core epilogue)
@@ -160,7 +161,12 @@ cudaError_t skn_launch_rope(float *x, const int32_t *len, int M, int T, int H, i
 // dst[0..n) = src[0..n) in 16-byte words (n a multiple of 4, both 16-byte aligned).  `src` may be page-locked
 // host memory mapped into the device's address space: the copy then crosses PCIe inside a kernel, which costs
 // a kernel-to-kernel hand-over instead of a copy-engine operation between two kernels.
+// Launched with programmatic stream serialisation: the kernel that follows (the product) may become resident
+// and prefetch its weights at once; this one waits for everything before it in the stream (the previous
+// product may still be reading `dst`) before it copies, and the product waits for this one before it reads.
 __global__ void skn_fetch_kernel(const float4 *__restrict__ src, float4 *__restrict__ dst, int64_t n4) {
+    skn_pdl_launch_dependents();
+    skn_pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 cudaError_t skn_launch_fetch(const float *src, float *dst, int64_t n, cudaStream_t st) {
@@ -168,8 +174,16 @@ cudaError_t skn_launch_fetch(const float *src, float *dst, int64_t n, cudaStream
     const int64_t n4 = n / 4;
     int blocks = (int)((n4 + 255) / 256);
     if (blocks > 32) blocks = 32;
-    skn_fetch_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(dst), n4);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, skn_fetch_kernel, reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(dst), n4);
 }
 cudaError_t skn_launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t st) {
     if (n == 0) return cudaSuccess;

@@ -55,8 +55,48 @@ struct skn_ctx {
     skn_group_plan group_plans[32];
     int n_group_plans;
     uint32_t attn_stream_cfg;   // bit per (head_dim, group size): the streamed attention kernel's attributes are set on this device
+    // one host thread at a time: the thread inside an entry point (0: none) and its nesting depth
+    // (entry points call one another); a second thread gets SKN_ERR_BUSY
+    uint64_t owner;
+    int owner_depth;
     char err[512];
 };
+
+// Entry-point guard of the one-thread-at-a-time rule.  Re-entrant for the owning thread.
+uint64_t skn_thread_token();
+struct skn_busy_guard {
+    skn_ctx *c;
+    bool ok;
+    explicit skn_busy_guard(skn_ctx *cx) : c(cx), ok(false) {
+        const uint64_t me = skn_thread_token();
+        uint64_t expected = 0;
+        if (__atomic_compare_exchange_n(&c->owner, &expected, me, false, __ATOMIC_ACQUIRE, __ATOMIC_RELAXED)) {
+            ok = true;
+            c->owner_depth = 1;
+        } else if (expected == me) {
+            ok = true;
+            ++c->owner_depth;
+        }
+    }
+    ~skn_busy_guard() {
+        if (ok && --c->owner_depth == 0) __atomic_store_n(&c->owner, (uint64_t)0, __ATOMIC_RELEASE);
+    }
+    skn_busy_guard(const skn_busy_guard &) = delete;
+    skn_busy_guard &operator=(const skn_busy_guard &) = delete;
+};
+int32_t skn_busy_fail();
+// after the handle checks of an entry point: claim the context for this thread or answer SKN_ERR_BUSY
+#define SKN_ENTER(ctx)                 \
+    skn_busy_guard busy_guard__(ctx);  \
+    if (!busy_guard__.ok) return skn_busy_fail()
+
+// the status area on the device: word 0 = status of bounded waits and capacity checks, word 1 = limit of the
+// flag waits of the inter-GPU exchange in milliseconds (0: the default of two seconds)
+constexpr int SKN_STATUS_WAIT_MS = 1;
+__device__ __forceinline__ uint64_t skn_wait_limit_ns(const int32_t *status) {
+    const int32_t ms = reinterpret_cast<const volatile int32_t *>(status)[SKN_STATUS_WAIT_MS];
+    return ms > 0 ? (uint64_t)ms * 1000000ull : 2000000000ull;
+}
 
 struct skn_tensor {
     uint32_t magic;
@@ -67,6 +107,18 @@ struct skn_tensor {
     int64_t pitch;       // device row pitch in bytes (multiple of 16)
     uint8_t *d_blocks;
     skn_mv_plan mv_plan[2];      // [0] stream order, [1] relaxed order
+};
+
+// Forces stream order on the context for the lifetime of the guard: call sequences whose launches depend on
+// one another (a decoder step; the fetch -> product chain inside a host-pointer call) must not inherit
+// SKN_OPT_RELAXED_ORDER, which only describes the caller's consecutive calls.
+struct skn_order_guard {
+    skn_ctx *c;
+    int saved;
+    explicit skn_order_guard(skn_ctx *cx) : c(cx), saved(cx->relaxed_order) { c->relaxed_order = 0; }
+    ~skn_order_guard() { c->relaxed_order = saved; }
+    skn_order_guard(const skn_order_guard &) = delete;
+    skn_order_guard &operator=(const skn_order_guard &) = delete;
 };
 
 // error plumbing (skn_api.cu)
@@ -161,7 +213,8 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
 int32_t skn_attn_causal_pending(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
                                 float *out_dev);
 int32_t *skn_kv_len_dev(const skn_kvcache *kv);
-cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, cudaStream_t st);
+cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, int32_t *status_dev,
+                               cudaStream_t st);
 
 // inter-GPU exchange (skn_comm.cu): layout constants and the device-side view the matvec kernels
 // use to push partial products from their epilogue and to add them up while they prepare x

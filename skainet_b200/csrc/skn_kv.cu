@@ -151,9 +151,15 @@ template <class CT>
 __global__ void __launch_bounds__(128)
 skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, const float *__restrict__ v_new,
                        CT *__restrict__ kc, CT *__restrict__ vc, const int32_t *__restrict__ len,
-                       const int32_t *__restrict__ start, int Hq, int Hkv, int D, int cap, int T, double log2_theta) {
+                       const int32_t *__restrict__ start, int Hq, int Hkv, int D, int cap, int T, double log2_theta,
+                       int32_t *__restrict__ status) {
     const int b = blockIdx.z, t = blockIdx.y;
     const int pos = len[b] + t;
+    if (pos >= cap) {
+        // the cache is full (a replayed step the host did not count): nothing is overwritten, the status word says so
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, SKN_ERR_SHAPE);
+        return;
+    }
     const int slot = (start[b] + pos) % cap;
     const int half = D / 2;
     const size_t row = (size_t)b * T + t;
@@ -184,10 +190,13 @@ skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, c
 }
 
 // len[l][b] += T for every layer's cache of a decoder (lens: device array of n_layers pointers)
-__global__ void skn_kv_advance_all_kernel(int32_t *const *__restrict__ lens, int n_layers, int B, int T, int cap) {
+// (a length that would pass the capacity stays at the capacity and SKN_ERR_SHAPE lands in the status word)
+__global__ void skn_kv_advance_all_kernel(int32_t *const *__restrict__ lens, int n_layers, int B, int T, int cap,
+                                          int32_t *__restrict__ status) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n_layers * B) {
         int32_t *len = lens[i / B] + (i % B);
+        if (*len + T > cap) atomicExch(status, SKN_ERR_SHAPE);
         *len = min(cap, *len + T);
     }
 }
@@ -313,7 +322,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
     // sees the cache up to and including its own token (tq = 1: plain decode)
     const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = max(0, len[b] + len_extra - (tq - 1 - bq % tq));
+    const int L = min(cap, max(0, len[b] + len_extra - (tq - 1 - bq % tq)));     // never past the ring: ns <= S
     const int t0 = sp * CHUNK;
     if (t0 >= L) {
         // an empty sequence has no split to merge: its output is zero
@@ -543,7 +552,7 @@ skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, c
 
     const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = max(0, len[b] + len_extra - (tq - 1 - bq % tq));
+    const int L = min(cap, max(0, len[b] + len_extra - (tq - 1 - bq % tq)));     // never past the ring: ns <= S
     const int t0 = sp * CHUNK;
     if (t0 >= L) return;
     const int nt = min(CHUNK, L - t0);
@@ -730,9 +739,9 @@ skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, c
 template <int D>
 __global__ void __launch_bounds__(D)
 skn_attn_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ len, int Hq, int S,
-                      float *__restrict__ out, int tq, int chunk, int len_extra) {
+                      float *__restrict__ out, int tq, int chunk, int len_extra, int cap) {
     const int h = blockIdx.x, b = blockIdx.y;          // b = sequence * tq + t
-    const int L = max(0, len[b / tq] + len_extra - (tq - 1 - b % tq));
+    const int L = min(cap, max(0, len[b / tq] + len_extra - (tq - 1 - b % tq)));
     const int ns = (L + chunk - 1) / chunk;
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
     constexpr int NW = D / 32;
@@ -818,7 +827,7 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || tickets) return e;
     const dim3 g2((unsigned)(kv->n_kv_heads * G), (unsigned)(kv->batch * tq));
-    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq, chunk, len_extra);
+    skn_attn_merge_kernel<D><<<g2, D, 0, stream>>>(part, kv->d_len, kv->n_kv_heads * G, S, out, tq, chunk, len_extra, kv->capacity);
     return cudaGetLastError();
 }
 
@@ -883,6 +892,7 @@ int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t h
 int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
                             int32_t kv_dtype, skn_kvcache **out) {
     if (!skn_ctx_ok(ctx)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad context handle");
+    SKN_ENTER(ctx);
     if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     *out = nullptr;
     if (kv_dtype != SKN_KV_F32 && kv_dtype != SKN_KV_F16) return skn_fail(ctx, SKN_ERR_TYPE, "cache element type %d is neither fp32 nor fp16", kv_dtype);
@@ -936,6 +946,7 @@ int32_t skn_kv_destroy(skn_kvcache *kv) {
 int32_t skn_kv_reset(skn_kvcache *kv) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     SKN_CUDA(ctx, cudaMemsetAsync(kv->d_len, 0, 2 * sizeof(int32_t) * kv->batch, ctx->stream));
     return SKN_OK;
@@ -945,6 +956,7 @@ int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, i
                     const int32_t *lens_host) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (tokens < 0 || tokens > kv->capacity) return skn_fail(ctx, SKN_ERR_SHAPE, "tokens (%d) exceeds the capacity (%d)", tokens, kv->capacity);
     if (!lens_host || (tokens > 0 && (!k_host || !v_host))) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     for (int b = 0; b < kv->batch; ++b)
@@ -980,6 +992,7 @@ int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, i
 int32_t skn_kv_lengths(skn_kvcache *kv, int32_t *lens_host, int32_t *start_host) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     SKN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (lens_host) SKN_CUDA(ctx, cudaMemcpy(lens_host, kv->d_len, sizeof(int32_t) * kv->batch, cudaMemcpyDeviceToHost));
@@ -990,6 +1003,7 @@ int32_t skn_kv_lengths(skn_kvcache *kv, int32_t *lens_host, int32_t *start_host)
 int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *v_new_dev) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     if ((((uintptr_t)k_new_dev) | ((uintptr_t)v_new_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "k/v must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1008,6 +1022,7 @@ int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *
 int32_t skn_kv_append(skn_kvcache *kv, const float *k_new_host, const float *v_new_host) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (!k_new_host || !v_new_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     const size_t n = (size_t)kv->batch * kv->n_kv_heads * kv->head_dim * sizeof(float);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1025,6 +1040,7 @@ int32_t skn_kv_gather(skn_kvcache *kv, int32_t b, int32_t pos_begin, int32_t cou
                       float *v_out_host) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (b < 0 || b >= kv->batch) return skn_fail(ctx, SKN_ERR_ARG, "sequence index out of range");
     if (pos_begin < 0 || count < 0) return skn_fail(ctx, SKN_ERR_ARG, "negative range");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1064,6 +1080,7 @@ int64_t skn_attn_scratch_bytes(const skn_kvcache *kv, int32_t n_q_heads) {
 static int32_t attn_check(skn_kvcache *kv, int32_t n_q_heads, const void *q, const void *out, int *G) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (!q || !out) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     if (n_q_heads < 1 || n_q_heads % kv->n_kv_heads) return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
     *G = n_q_heads / kv->n_kv_heads;
@@ -1080,6 +1097,7 @@ int32_t skn_attn_decode_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
     int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
     if (rc) return rc;
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
         return skn_fail(ctx, SKN_ERR_ALIGN, "q, out and scratch must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1102,6 +1120,7 @@ int32_t skn_attn_decode(skn_kvcache *kv, const float *q_host, int32_t n_q_heads,
     int32_t rc = attn_check(kv, n_q_heads, q_host, out_host, &G);
     if (rc) return rc;
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t n = (size_t)kv->batch * n_q_heads * kv->head_dim * sizeof(float);
     rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, n);
@@ -1122,6 +1141,7 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
                                int32_t host_len_upper) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (T < 0 || host_len_upper < 0) return skn_fail(ctx, SKN_ERR_ARG, "negative argument");
     if (T == 0) return SKN_OK;
     if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
@@ -1152,6 +1172,7 @@ static int32_t attn_causal_impl(skn_kvcache *kv, const float *q_dev, int32_t n_q
     int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
     if (rc) return rc;
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if (T < 1) return skn_fail(ctx, SKN_ERR_ARG, "T must be positive");
     if ((int64_t)T * kv->batch > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch * T exceeds 65535");
     if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev) | ((uintptr_t)scratch_dev)) & 15)
@@ -1184,6 +1205,7 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
                                    int32_t n_q_heads, int32_t T, float theta, int32_t host_len_upper) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if ((int64_t)host_len_upper + T > kv->capacity)
         return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
     if ((int64_t)kv->batch > 65535 || T > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch or T exceeds 65535");
@@ -1192,11 +1214,11 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
     if (kv->dtype == SKN_KV_F16)
         skn_rope_append_kernel<__half><<<rgrid, 128, 0, ctx->stream>>>(
             q_dev, k_new_dev, v_new_dev, static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v), kv->d_len, kv->d_start,
-            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta));
+            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta), ctx->d_status);
     else
         skn_rope_append_kernel<float><<<rgrid, 128, 0, ctx->stream>>>(
             q_dev, k_new_dev, v_new_dev, static_cast<float *>(kv->d_k), static_cast<float *>(kv->d_v), kv->d_len, kv->d_start,
-            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta));
+            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta), ctx->d_status);
     SKN_CUDA(ctx, cudaGetLastError());
     return SKN_OK;
 }
@@ -1208,10 +1230,11 @@ int32_t skn_attn_causal_pending(skn_kvcache *kv, const float *q_dev, int32_t n_q
 
 int32_t *skn_kv_len_dev(const skn_kvcache *kv) { return kv_ok(kv) ? kv->d_len : nullptr; }
 
-cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, cudaStream_t st) {
+cudaError_t skn_kv_advance_all(int32_t *const *lens_dev, int n_layers, int B, int T, int cap, int32_t *status_dev,
+                               cudaStream_t st) {
     const int n = n_layers * B;
     if (n == 0) return cudaSuccess;
-    skn_kv_advance_all_kernel<<<(n + 127) / 128, 128, 0, st>>>(lens_dev, n_layers, B, T, cap);
+    skn_kv_advance_all_kernel<<<(n + 127) / 128, 128, 0, st>>>(lens_dev, n_layers, B, T, cap, status_dev);
     return cudaGetLastError();
 }
 
@@ -1235,6 +1258,7 @@ int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t
     int32_t rc = attn_check(kv, n_q_heads, q_dev, out_dev, &G);
     if (rc) return rc;
     skn_ctx *ctx = kv->ctx;
+    SKN_ENTER(ctx);
     if ((((uintptr_t)q_dev) | ((uintptr_t)out_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "q and out must be 16-byte aligned");
     const int64_t need = skn_attn_scratch_bytes(kv, n_q_heads);
     if (need > SKN_ATTN_STATIC_SCRATCH_BYTES)

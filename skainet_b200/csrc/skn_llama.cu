@@ -196,6 +196,7 @@ int32_t skn_llama_set_layer(skn_llama *m, int32_t layer, const skn_tensor *wq, c
                             const float *ffn_norm_host) {
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
     skn_ctx *ctx = m->ctx;
+    SKN_ENTER(ctx);
     if (layer < 0 || layer >= m->n_layers) return skn_fail(ctx, SKN_ERR_ARG, "layer index out of range");
     if (!attn_norm_host || !ffn_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
     const int64_t d = m->d_model, qd = (int64_t)m->heads_l * m->head_dim, kd = (int64_t)m->kv_heads_l * m->head_dim;
@@ -215,6 +216,7 @@ int32_t skn_llama_set_head(skn_llama *m, const skn_tensor *tok_embd, const float
                            const skn_tensor *output) {
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
     skn_ctx *ctx = m->ctx;
+    SKN_ENTER(ctx);
     if (!out_norm_host) return skn_fail(ctx, SKN_ERR_ARG, "NULL norm gain");
     if (!shape_is(tok_embd, ctx, m->vocab, m->d_model) || !shape_is(output, ctx, m->vocab_l, m->d_model))
         return skn_fail(ctx, SKN_ERR_SHAPE, "Shapes do not align.");
@@ -227,6 +229,7 @@ int32_t skn_llama_set_head(skn_llama *m, const skn_tensor *tok_embd, const float
 // Forget all cached tokens.
 int32_t skn_llama_reset(skn_llama *m) {
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
+    SKN_ENTER(m->ctx);
     for (auto &l : m->layers) {
         int32_t rc = skn_kv_reset(l.kv);
         if (rc) return rc;
@@ -241,6 +244,7 @@ int32_t skn_llama_reset(skn_llama *m) {
 int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T) {
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
     skn_ctx *ctx = m->ctx;
+    SKN_ENTER(ctx);
     const int B = m->max_batch;
     if (T < 1 || (int64_t)B * T > m->max_rows) return skn_fail(ctx, SKN_ERR_SHAPE, "T outside [1, max_tokens]");
     if (!tokens_dev && T != 1) return skn_fail(ctx, SKN_ERR_ARG, "tokens may be NULL only for single-token steps");
@@ -258,11 +262,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     const bool small = M <= 64 && !(ctx->prefill_min_m > 0 && M >= ctx->prefill_min_m);
     // the step is a dependent chain: every launch keeps stream order whatever the context's
     // launch-order option says
-    struct OrderGuard {
-        skn_ctx *c; int saved;
-        explicit OrderGuard(skn_ctx *cx) : c(cx), saved(cx->relaxed_order) { c->relaxed_order = 0; }
-        ~OrderGuard() { c->relaxed_order = saved; }
-    } guard(ctx);
+    skn_order_guard guard(ctx);
     SKN_CUDA(ctx, skn_launch_embed(m->tok_embd, ids, M, m->x, st));
     int32_t rc;
     const int64_t qd = (int64_t)Hq * D, kd = (int64_t)Hkv * D, F = m->ffn_l;
@@ -474,7 +474,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
             else SKN_CUDA(ctx, skn_launch_add(m->x, m->proj, m->x, (int64_t)M * d, ctx->sm_count, st));
         }
     }
-    SKN_CUDA(ctx, skn_kv_advance_all(m->len_ptrs, m->n_layers, B, T, m->max_ctx, st));
+    SKN_CUDA(ctx, skn_kv_advance_all(m->len_ptrs, m->n_layers, B, T, m->max_ctx, ctx->d_status, st));
     m->host_len += T;
     // final norm + LM head on the last position of every sequence
     bool fb = !(B <= 64 && !(ctx->prefill_min_m > 0 && B >= ctx->prefill_min_m));
@@ -506,6 +506,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
 int32_t skn_llama_forward(skn_llama *m, const int32_t *tokens_host, int32_t T, int32_t *next_host, float *logits_host) {
     if (!llama_ok(m)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad decoder handle");
     skn_ctx *ctx = m->ctx;
+    SKN_ENTER(ctx);
     const int B = m->max_batch;
     if (T < 1 || (int64_t)B * T > m->max_rows) return skn_fail(ctx, SKN_ERR_SHAPE, "T outside [1, max_tokens]");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));

@@ -301,12 +301,12 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
         const int buf = (int)(q % SKN_COMM_NBUF);
         if (warp == 0 && lane < grp.xc_world && lane != grp.xc_rank && *reinterpret_cast<volatile int32_t *>(status) == 0) {
             const uint32_t *flag = reinterpret_cast<const uint32_t *>(grp.xc_base[grp.xc_rank]) + buf * SKN_COMM_MAX_WORLD + lane;
-            const uint64_t t0 = skn_globaltimer_ns();
+            const uint64_t t0 = skn_globaltimer_ns(), limit = skn_wait_limit_ns(status);
             uint32_t spins = 0, v;
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
                 if (v == q + 1u) break;
-                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > 2000000000ull) {
+                if ((++spins & 1023u) == 0 && skn_globaltimer_ns() - t0 > limit) {
                     atomicExch(status, SKN_ERR_TIMEOUT);
                     break;
                 }
@@ -797,6 +797,9 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                     // row of the pair), k and v straight into the cache
                     const int hd = F_ROPE ? f_rope_hd : 2, seq = grp.rope_a0 + a;
                     const int pos = grp.rope_len[seq];
+                    // a full cache (a replayed step the host did not count): nothing is overwritten
+                    const bool room = pos < grp.rope_cap;
+                    if (!room) atomicExch(status, SKN_ERR_SHAPE);
                     const int slot = (grp.rope_start[seq] + pos) % grp.rope_cap;
                     const int h = (int)(local / hd), dd = (int)(local % hd);
                     float o = s;
@@ -808,7 +811,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                         o = (dd & 1) ? (up * sn + s * cs) : (s * cs - up * sn);
                     }
                     if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = o;
-                    else (tt == 1 ? grp.rope_kc : grp.rope_vc)[(((size_t)seq * grp.rope_nkv + h) * grp.rope_cap + slot) * hd + dd] = o;
+                    else if (room) (tt == 1 ? grp.rope_kc : grp.rope_vc)[(((size_t)seq * grp.rope_nkv + h) * grp.rope_cap + slot) * hd + dd] = o;
                 } else if (push) {
                     // a partial product: slot `rank` of every rank's inbox (ordinary peer stores)
                     const size_t o = push_off + (size_t)a * grp.ystride[tt] + local;

@@ -81,7 +81,12 @@ class Exchange:
         from .tensor import _check
         exs = [cls(c, r, len(ctxs), capacity_floats) for r, c in enumerate(ctxs)]
         arr = (ctypes.c_void_p * len(exs))(*[e._h.value for e in exs])
-        _check(ctxs[0].handle, _ffi.lib().skn_comm_connect_local(arr, len(exs)))
+        try:
+            _check(ctxs[0].handle, _ffi.lib().skn_comm_connect_local(arr, len(exs)))
+        except Exception:
+            for e in exs:
+                e.close()
+            raise
         return exs
 
     def all_reduce(self, partial_dev, resid_dev, out_dev, n: int):

@@ -5,7 +5,7 @@ Kotlin originals so that tests read like the reference's own:
   Shape            core/src/commonMain/kotlin/sk/ai/net/Shape.kt
   QuantTensor      a Tensor (core/src/commonMain/kotlin/sk/ai/net/Tensor.kt:6-92) whose
                    elements are raw GGUF blocks resident in HBM
-  QuantLinear      core/src/commonMain/kotlin/sk/ai/net/nn/Linear.kt:43-49  (x . W^T + b)
+  (QuantLinear, Module and the parameter classes live in nn.py)
   GGMLQuantizationType / GGML_QUANT_SIZES / quant_shape_to_byte_shape
                    gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:14-90, Quants.kt:10-20
 
@@ -23,7 +23,7 @@ import numpy as np
 from . import _ffi
 
 SKN_OK, SKN_ERR_SHAPE, SKN_ERR_TYPE, SKN_ERR_ALIGN, SKN_ERR_OOM = 0, 1, 2, 3, 4
-SKN_ERR_CUDA, SKN_ERR_TIMEOUT, SKN_ERR_BAD_HANDLE, SKN_ERR_ARG, SKN_ERR_COMM = 5, 6, 7, 8, 9
+SKN_ERR_CUDA, SKN_ERR_TIMEOUT, SKN_ERR_BAD_HANDLE, SKN_ERR_ARG, SKN_ERR_COMM, SKN_ERR_BUSY = 5, 6, 7, 8, 9, 10
 
 
 class GGMLQuantizationType(enum.IntEnum):
@@ -106,7 +106,8 @@ class Shape:
 
 
 def _raise(ctx_handle, code: int):
-    msg = _ffi.lib().skn_last_error(ctx_handle).decode("utf-8", "replace")
+    # a refused (busy) call leaves its message with the refused thread, not in the context
+    msg = _ffi.lib().skn_last_error(None if code == SKN_ERR_BUSY else ctx_handle).decode("utf-8", "replace")
     if code == SKN_ERR_SHAPE:
         raise ValueError(msg)
     raise SknError(code, msg)
@@ -166,6 +167,11 @@ class Context:
     def set_kv_f16(self, on: bool):
         """Decoders created afterwards keep their KV caches in fp16 (SKN_OPT_KV_F16)."""
         _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 4, 1 if on else 0))
+
+    def set_wait_limit_ms(self, ms: int):
+        """How long a kernel of the inter-GPU exchange waits for its peers before it reports
+        SKN_ERR_TIMEOUT (SKN_OPT_WAIT_LIMIT_MS; 0 restores the default of two seconds)."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 5, int(ms)))
 
     def sync(self):
         _check(self._h, _ffi.lib().skn_sync(self._h))
@@ -293,20 +299,6 @@ class QuantTensor:
             self.close()
         except Exception:
             pass
-
-
-class QuantLinear:
-    """Linear.kt:43-49 with a quantized weight: forward(x) = x . W^T + b."""
-
-    def __init__(self, weight: QuantTensor, bias: Optional[np.ndarray] = None, name: str = "linear"):
-        self.name = name
-        self.weight = weight
-        self.bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
-
-    def forward(self, x: np.ndarray) -> np.ndarray:
-        return self.weight.matmul_t(x, self.bias)
-
-    __call__ = forward
 
 
 def ffn_swiglu(ctx: Context, wg: QuantTensor, wu: QuantTensor, wd: QuantTensor, x: np.ndarray) -> np.ndarray:

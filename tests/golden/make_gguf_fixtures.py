@@ -7,6 +7,8 @@ toy_f32.gguf       the layout of the reference's own fixture (3 string keys, thr
                    tensors x, y, result = x + y), re-created from a seed
 mixed_quant.gguf   scalar / string / array metadata of every value type, custom alignment 64,
                    and Q4_0, Q8_0, Q4_K, Q6_K, F16, F32 tensors (seeded blocks)
+quant_mlp.gguf     a 512-256-256-10 MLP in the naming of the reference's sample loader ("model.<layer>.weight" /
+                   "model.<layer>.bias"): Q4_K, Q6_K and Q8_0 weights, F32 and F16 biases (seeded blocks)
 """
 import json
 import os
@@ -70,6 +72,24 @@ def mixed(path):
     w.close()
 
 
+MLP_LAYERS = (("fc1", synth.Q4_K, 256, 512, np.float32), ("fc2", synth.Q6_K, 256, 256, np.float16),
+              ("fc3", synth.Q8_0, 10, 256, np.float32))
+
+
+def quant_mlp(path):
+    g = synth.rng(3)
+    w = gguf.GGUFWriter(path, "mlp")
+    w.add_string("general.name", "quantized MLP fixture")
+    for name, qt, n, k, bias_dtype in MLP_LAYERS:
+        raw = synth.make_weight(g, qt, n, k)
+        w.add_tensor(f"model.{name}.weight", raw, raw_dtype=T(qt))
+        w.add_tensor(f"model.{name}.bias", g.standard_normal(n).astype(bias_dtype))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
 def describe(path):
     r = gguf.GGUFReader(path)
     out = {"alignment": int(r.alignment), "data_offset": int(r.data_offset), "tensors": [], "fields": {}}
@@ -88,7 +108,7 @@ def describe(path):
 
 def main():
     exp = {}
-    for name, fn in (("toy_f32.gguf", toy), ("mixed_quant.gguf", mixed)):
+    for name, fn in (("toy_f32.gguf", toy), ("mixed_quant.gguf", mixed), ("quant_mlp.gguf", quant_mlp)):
         p = os.path.join(HERE, name)
         fn(p)
         exp[name] = describe(p)

@@ -16,7 +16,7 @@ GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 EXPECTED = json.load(open(os.path.join(GOLD, "gguf_expected.json")))
 
 
-@pytest.mark.parametrize("name", ["toy_f32.gguf", "mixed_quant.gguf"])
+@pytest.mark.parametrize("name", ["toy_f32.gguf", "mixed_quant.gguf", "quant_mlp.gguf"])
 def test_matches_gguf_py(name):
     exp = EXPECTED[name]
     with GGUFFile(os.path.join(GOLD, name)) as f:
@@ -76,6 +76,19 @@ def test_errors(tmp_path):
     v9.write_bytes(good[:4] + (9).to_bytes(4, "little") + good[8:])
     with pytest.raises(skn.SknError, match="version 9"):
         GGUFFile(str(v9))
+    # header counts the file cannot hold are refused before anything is reserved for them
+    huge = tmp_path / "huge.gguf"
+    huge.write_bytes(good[:8] + (len(good)).to_bytes(8, "little") + good[16:])
+    with pytest.raises(skn.SknError, match="corrupt header counts"):
+        GGUFFile(str(huge))
+    # a tensor whose data offset is off the file's alignment (64 here): the offset field of the first tensor record
+    first = good.index(b"blk.q4_0")
+    off_pos = first + len(b"blk.q4_0") + 4 + 2 * 8 + 4          # name, rank, two dims, type -> offset
+    assert int.from_bytes(good[off_pos:off_pos + 8], "little") == 0
+    mis = tmp_path / "misaligned.gguf"
+    mis.write_bytes(good[:off_pos] + (8).to_bytes(8, "little") + good[off_pos + 8:])
+    with pytest.raises(skn.SknError, match="not a multiple of the alignment"):
+        GGUFFile(str(mis))
     for cut in (30, 200, len(good) - 100):          # truncated metadata / truncated tensor data
         tr = tmp_path / f"cut{cut}.gguf"
         tr.write_bytes(good[:cut])

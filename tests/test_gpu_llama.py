@@ -177,3 +177,63 @@ def test_decoder_argument_errors(ctx):
     with pytest.raises(ValueError):
         dec.set_layer(0, bad, np.ones(256, np.float32), np.ones(256, np.float32))
     dec.close()
+
+
+def test_replayed_steps_stop_at_the_cache_capacity(ctx):
+    """A single-token step captured into a CUDA graph advances the caches on the device but not the host's
+    position.  Replaying it up to the capacity (a multiple of the attention chunk) works and equals eager
+    stepping bit for bit; one replay more appends nothing, reports SKN_ERR_SHAPE through skn_sync and
+    leaves the decoder usable after a reset."""
+    import torch
+    cfg = LlamaConfig(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=512)
+    layers, head = random_model_blocks(cfg, seed=4)
+    B, T, cap = 2, 8, 64
+    ones = np.ones(cfg.d_model, dtype=np.float32)
+    prompt = synth.rng(79).integers(0, cfg.vocab, size=(B, T)).astype(np.int32)
+
+    def make():
+        d = LlamaDecoder(ctx, cfg, batch=B, max_tokens=T, max_ctx=cap)
+        for i, l in enumerate(layers):
+            d.set_layer(i, l, ones, ones)
+        d.set_head(head[0], ones, head[1])
+        return d
+
+    eager = make()
+    first_ids, first_logits = eager.forward(prompt, want_logits=True)
+    for _ in range(cap - T - 1):
+        eager.forward(None)
+    want_ids, want_logits = eager.forward(None, want_logits=True)        # the step that fills the cache
+    assert eager.position == cap
+    with pytest.raises(ValueError, match="exceeded"):                      # the host-side count refuses the next one
+        eager.forward(None)
+    eager.close()
+
+    dec = make()
+    dec.forward(prompt)
+    dec.forward(None)                                                      # uncaptured step: sizes the scratch buffers
+    stream, cap_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.stream(cap_stream):
+            ctx.set_stream(cap_stream.cuda_stream)
+            with torch.cuda.graph(graph, stream=cap_stream):
+                dec.forward_dev(None, 1)
+        ctx.set_stream(stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            for _ in range(cap - T - 2):                                   # device length: T + 1 -> cap - 1
+                graph.replay()
+        ctx.sync()
+        got_ids, got_logits = dec.forward(None, want_logits=True)          # eager step to exactly cap
+        assert np.array_equal(got_ids, want_ids) and np.array_equal(got_logits, want_logits)
+        with torch.cuda.stream(stream):
+            graph.replay()                                                 # one past the capacity
+        with pytest.raises(ValueError, match="more tokens than its capacity"):
+            ctx.sync()
+        ctx.sync()                                                         # reported once, then cleared
+        dec.reset()
+        again_ids, again_logits = dec.forward(prompt, want_logits=True)
+        assert np.array_equal(again_ids, first_ids) and np.array_equal(again_logits, first_logits)
+    finally:
+        ctx.set_stream(None)
+        torch.cuda.synchronize()
+        dec.close()

@@ -111,6 +111,40 @@ def test_asynchronous_host_calls_run_in_order(ctx, pinned):
     assert_close_dot(y1[None, :], ref1, ad1, FP32_TOL, "first product")
 
 
+def test_host_pointer_calls_keep_their_own_order_under_relaxed_order(ctx):
+    """SKN_OPT_RELAXED_ORDER describes the caller's consecutive calls, not the fetch -> product chain inside
+    one host-pointer call: with the option on, page-locked buffers, a different x for every call and a
+    second call that consumes the first call's result, every result still equals the stream-order bits."""
+    import ctypes
+    torch = pytest.importorskip("torch")
+    from skainet_b200 import _ffi
+    L = _ffi.lib()
+    g = synth.rng(63)
+    N1, K, N2 = 512, 4096, 256
+    w1, w2 = synth.make_weight(g, synth.Q4_K, N1, K), synth.make_weight(g, synth.Q4_K, N2, N1)
+    t1, t2 = skn.QuantTensor(ctx, (N1, K), synth.Q4_K, w1), skn.QuantTensor(ctx, (N2, N1), synth.Q4_K, w2)
+    reps = 24
+    xs = synth.make_activations(g, reps, K)
+    want1 = np.stack([t1.matmul_t(xs[i]) for i in range(reps)])
+    want2 = np.stack([t2.matmul_t(want1[i]) for i in range(reps)])
+    keep = [torch.zeros(n, dtype=torch.float32).pin_memory() for n in (reps * K, reps * N1, reps * N2)]
+    xp, y1, y2 = (a.numpy() for a in keep)
+    xp[:] = xs.reshape(-1)
+    at = lambda a, off: ctypes.c_void_p(a.ctypes.data + 4 * off)
+    ctx.set_relaxed_order(True)
+    try:
+        for i in range(reps):
+            assert L.skn_matmul_async(ctx.handle, t1.handle, at(xp, i * K), 1, K, None, at(y1, i * N1)) == 0
+            assert L.skn_matmul_async(ctx.handle, t2.handle, at(y1, i * N1), 1, N1, None, at(y2, i * N2)) == 0
+        assert L.skn_sync(ctx.handle) == 0
+    finally:
+        ctx.set_relaxed_order(False)
+    t1.close()
+    t2.close()
+    assert np.array_equal(y1.reshape(reps, N1), want1)
+    assert np.array_equal(y2.reshape(reps, N2), want2)
+
+
 def test_blocking_call_on_page_locked_buffers(ctx):
     """skn_matmul with page-locked x, bias and y (no copy-engine transfer: x is fetched by a kernel, y and the
     status word are written to the mapped buffers) returns the bits of the pageable route, for 1 and 3 rows."""
