@@ -118,6 +118,7 @@ int32_t skn_ctx_destroy(skn_ctx *ctx) {
     if (ctx->d_stage_out) cudaFree(ctx->d_stage_out);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_scratch2) cudaFree(ctx->d_scratch2);
+    if (ctx->d_xq) cudaFree(ctx->d_xq);
     if (ctx->d_status_base) cudaFree(ctx->d_status_base);
     if (ctx->h_status_base) cudaFreeHost(ctx->h_status_base);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);

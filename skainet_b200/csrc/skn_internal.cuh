@@ -52,6 +52,8 @@ struct skn_ctx {
     void *d_stage_out; size_t d_stage_out_bytes;
     void *d_scratch;   size_t d_scratch_bytes;   // kernel scratch (bf16 operands, FFN intermediates)
     void *d_scratch2;  size_t d_scratch2_bytes;  // attention split partials
+    void *d_xq;        size_t d_xq_bytes;        // prepared activations of the many-row matvec (digit planes, block records)
+    uint32_t rows_cfg;                           // many-row matvec variants whose attributes are set on this device
     skn_group_plan group_plans[32];
     int n_group_plans;
     uint32_t attn_stream_cfg;   // bit per (head_dim, group size): the streamed attention kernel's attributes are set on this device
@@ -107,6 +109,9 @@ struct skn_tensor {
     int64_t pitch;       // device row pitch in bytes (multiple of 16)
     uint8_t *d_blocks;
     skn_mv_plan mv_plan[2];      // [0] stream order, [1] relaxed order
+    // tensor maps of the raw blocks for the many-row matvec (opaque CUtensorMap images), by box width in bytes (0: unset)
+    alignas(64) unsigned char rows_tmap[2][128];
+    int rows_tmap_wrow[2];
 };
 
 // Forces stream order on the context for the lifetime of the guard: call sequences whose launches depend on
@@ -169,6 +174,11 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
                        const struct skn_mv_exchange *xc = nullptr, const struct skn_mv_rope *rope = nullptr);
 // activation rows one tensor-core matvec launch can take for this tensor (0: not covered)
 int skn_mma_max_acts(const skn_ctx *ctx, int32_t type, int64_t n_rows_total, int64_t n_cols);
+// many-row tensor-core matvec (skn_matvec_rows.cu): x prepared once per launch by its own kernel, 3 to 16 rows
+int skn_rows_max_acts(const skn_ctx *ctx, int n, const skn_tensor *const *w);
+bool skn_rows_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const float *x, int M, float *const *y,
+                        const float *const *add, bool add_per_act, const float *norm_gain, float norm_eps, const float *silu_u,
+                        bool swiglu, cudaStream_t stream, cudaError_t &err);
 // y[t][m] = W[t] . f(x[m]) (+ add) for M activation rows through the tensor-core matvec, in launches
 // of as many rows as fit; cudaErrorNotSupported (nothing launched) when it does not cover the tensors.
 // x rows are K apart, outputs (and per-row add vectors) n_rows apart.

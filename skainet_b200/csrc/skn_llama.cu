@@ -270,7 +270,18 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     // cover.  Folding the norm / SwiGLU into the preparation of x saves a launch per layer but
     // adds a few microseconds to every row's launch: it pays for one or two rows, beyond that
     // one batched element-wise launch is cheaper.
-    const bool fold = M <= 2;
+    // (from three rows on, the many-row kernel's preparation pass applies the norm / SwiGLU product for all rows at
+    // once, when it covers the layer's projections)
+    bool fold = M <= 2;
+    if (M >= 3 && small) {
+        fold = true;
+        for (auto &l : m->layers) {
+            const skn_tensor *qkv[3] = {l.wq, l.wk, l.wv}, *gu[2] = {l.wg, l.wu};
+            fold = fold && l.wk->type == l.wq->type && l.wv->type == l.wq->type && l.wq->pitch == l.wk->pitch &&
+                   l.wq->pitch == l.wv->pitch && skn_rows_max_acts(ctx, 3, qkv) >= 4 && l.wu->type == l.wg->type &&
+                   l.wu->pitch == l.wg->pitch && skn_rows_max_acts(ctx, 2, gu) >= 4;
+        }
+    }
     auto fused = [&](int n, const skn_tensor *const *ws, const float *x, float *const *ys, const float *const *add,
                      const float *gain, const float *silu_u, bool &fell_back) -> cudaError_t {
         if (!fold) { fell_back = true; return cudaSuccess; }

@@ -938,11 +938,10 @@ cudaError_t skn_launch_matvec_fused(skn_ctx *ctx, int n, const skn_tensor *const
         same = w[t]->type == w[0]->type && w[t]->n_cols == w[0]->n_cols && w[t]->pitch == w[0]->pitch;
     if (!same || (w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
     cudaError_t err = cudaSuccess;
-    // a single activation row: Q4_K on the tensor-core kernel, the 32-weight-block formats on
-    // their CUDA-core streaming kernels (the same routes skn_launch_matvec takes, so grouped and
-    // separate launches give identical bits)
-    static const int q6k_mma = env_int("SKN_MM_Q6K", 1);
-    if ((w[0]->type == SKN_TYPE_Q4_K || (q6k_mma && w[0]->type == SKN_TYPE_Q6_K)) && skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
+    // a single activation row: the four formats of the tensor-core kernel run there (the same route
+    // skn_launch_matvec takes, so grouped and separate launches give identical bits); the CUDA-core
+    // streaming kernels remain for shapes that kernel does not cover
+    if (skn_mma_try_group(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err)) return err;
     bool took = false;
     switch (w[0]->type) {
     case SKN_TYPE_Q4_K: took = try_stream_group<Q4KStream>(ctx, n, w, x, y, add, norm_gain, norm_eps, silu_u, stream, err); break;
@@ -965,16 +964,38 @@ cudaError_t skn_launch_matvec_acts(skn_ctx *ctx, int n, const skn_tensor *const 
         tot += w[t]->n_rows;
     }
     if ((w[0]->pitch % 16) != 0) return cudaErrorNotSupported;
+    const int64_t K = w[0]->n_cols;
+    // three rows or more: the many-row kernel (x prepared once per launch by its own kernel, up to sixteen rows
+    // per pass over the weights); it has no rotary epilogue and no exchange
+    if (M >= 3 && !xc && !rope) {
+        const int maxr = skn_rows_max_acts(ctx, n, w);
+        if (maxr >= 4) {
+            const int launches = (M + maxr - 1) / maxr;
+            for (int i = 0, m0 = 0; i < launches; ++i) {
+                int na = (M - m0 + (launches - i) - 1) / (launches - i);     // even shares, at least three rows each
+                if (M - m0 - na > 0 && M - m0 - na < 3) na = M - m0;
+                if (na > maxr || na < 3) break;                               // (cannot happen for M >= 3: kept as a guard)
+                float *ys[3] = {nullptr, nullptr, nullptr};
+                const float *as[3] = {nullptr, nullptr, nullptr};
+                for (int t = 0; t < n; ++t) {
+                    ys[t] = y[t] + (int64_t)m0 * w[swiglu ? 0 : t]->n_rows;
+                    if (add && add[t]) as[t] = add[t] + (add_per_act ? (int64_t)m0 * w[t]->n_rows : 0);
+                }
+                cudaError_t err = cudaSuccess;
+                if (!skn_rows_try_group(ctx, n, w, x + (int64_t)m0 * K, na, ys, add ? as : nullptr, add_per_act, norm_gain, norm_eps,
+                                        silu_u ? silu_u + (int64_t)m0 * K : nullptr, swiglu, stream, err)) {
+                    if (i == 0) break;                                        // not covered after all: the route below
+                    return cudaErrorUnknown;
+                }
+                if (err != cudaSuccess) return err;
+                m0 += na;
+                if (m0 == M) return cudaSuccess;
+            }
+        }
+    }
     const int maxa = skn_mma_max_acts(ctx, w[0]->type, tot, w[0]->n_cols);
     if (maxa < 1) return cudaErrorNotSupported;
-    // the 32-weight-block formats take this route from two activation rows on (a single row is as
-    // fast or faster on their CUDA-core streaming kernels)
-    static const int simple_min_m = env_int("SKN_MM_SIMPLE_MIN_M", 2);
-    static const int q6k_mma = env_int("SKN_MM_Q6K", 1);
-    if (w[0]->type == SKN_TYPE_Q6_K && !q6k_mma) return cudaErrorNotSupported;
-    if (w[0]->type != SKN_TYPE_Q4_K && w[0]->type != SKN_TYPE_Q6_K && M < simple_min_m) return cudaErrorNotSupported;
     const int launches = (M + maxa - 1) / maxa;
-    const int64_t K = w[0]->n_cols;
     if (xc && launches != 1) return cudaErrorNotSupported;      // an exchange covers all rows of one launch
     for (int i = 0, m0 = 0; i < launches; ++i) {
         const int na = (M - m0 + (launches - i) - 1) / (launches - i);       // even shares

@@ -7,12 +7,13 @@
 // on the tensor cores (mma.sync m16n8k32, u8 x s8 -> s32), and the 6-bit sub-block scales are
 // applied in integers as well, so the per-weight work shrinks to a fraction of an instruction:
 //
-//   * x, per super-block of 256 activations, becomes a 23-bit fixed-point number with a
-//     power-of-two scale: X = rint(x * 2^(21-e)), e = exponent of the super-block's largest |x|,
-//     split into three balanced signed byte digits X = d0 + 256 d1 + 65536 d2 (the bytes of
-//     (X + 0x808080) ^ 0x808080).  The digit planes are columns 0..2 of the B operand (columns
-//     3..7 are zero), prepared once per CTA in shared memory.  The rounding error per
-//     activation is at most 2^-23 of the super-block's largest one.
+//   * x, per super-block of 256 activations, becomes a 32-bit fixed-point number with a
+//     power-of-two scale: X = rint(x * 2^(29-e)), e = exponent of the super-block's largest |x|,
+//     split into four balanced signed byte digits X = d0 + 2^8 d1 + 2^16 d2 + 2^24 d3.  The digit
+//     planes are B columns 0, 2, 4, 6 (a second activation row takes 1, 3, 5, 7), prepared once per
+//     CTA in shared memory.  Activations within 2^6 of the block's largest are exact, the others
+//     are rounded to 2^-30 of it; a few outliers that tower over their block are taken out of the
+//     planes and multiplied in fp32 (see mm_digitize).
 //   * the A operand is the quant bytes as they lie in the block.  For the byte pair p of a
 //     super-block (sub-block 2p in the low nibbles, 2p+1 in the high ones) two MMAs run: one on
 //     `word & 0x0F0F0F0F` against the digits of the activations of sub-block 2p, one on
@@ -21,7 +22,7 @@
 //     accumulated over the super-block as lo and hi sums (at most 2^29 in magnitude); lo * 16 + hi
 //     is 16 times the scaled dot product.
 //   * once per (row, super-block) the digit columns are recombined in fp32 and scaled by
-//     d * 2^(e-21) / 16; the -dmin * m * sum(x) term is added per row and super-block.
+//     d * 2^(e-29) / 16; the -dmin * m * sum(x) term is added per row and super-block.
 //
 // Work split: CTA b owns rows [b*N/grid, (b+1)*N/grid).  A tile is 16 rows x one K super-chunk
 // (up to 16 super-blocks, i.e. one bulk async copy of at most 2304 bytes per row: few, large
@@ -33,159 +34,7 @@
 // memory, which makes the 64-bit fragment loads of the eight row groups conflict-free.  Weights
 // are prefetched before the programmatic dependent-launch wait, x is read after it.  Partial
 // sums per (row, super-chunk, warp) meet in shared memory and are added in a fixed order.
-#include "skn_mv_common.cuh"
-
-#include <math.h>
-
-// Block formats of this kernel.  A "super-block" is 256 weights: one Q4_K block, or eight of the
-// 32-weight blocks of Q8_0 / Q4_0 (each with its own fp16 scale).  KS super-blocks (one bulk copy
-// per row) make a K super-chunk; rows are padded by 32 bytes in shared memory, which puts the
-// eight row groups of a fragment load on disjoint banks (row stride = 8 words mod 32).
-// Q6_K: one 210-byte block per super-block; eight of them are 1680 bytes = a multiple of 16 (a bulk
-// copy's granularity) and 420 words = 4 mod 32: its fragments are read with 32-bit loads (lane (g, t) reads
-// word t of row g), which that stride spreads over all 32 banks without padding (a stride of 8 words mod 32,
-// right for the 64-bit loads of the other formats, made rows g and g + 4 collide: 2.5 M bank conflicts per
-// 32000 x 4096 launch).  Its scale groups are 16 weights, so the group sums of x are kept per 16
-// activations (XS per super-block).
-constexpr int MM_FMT_Q4K = 0, MM_FMT_Q80 = 1, MM_FMT_Q40 = 2, MM_FMT_Q6K = 3;
-template <int FMT> struct MmFmt;
-template <> struct MmFmt<MM_FMT_Q4K> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 32, XS = 8; };
-template <> struct MmFmt<MM_FMT_Q80> { static constexpr int KS = 8, SB_BYTES = 272, PAD = 32, XS = 8; };
-template <> struct MmFmt<MM_FMT_Q40> { static constexpr int KS = 16, SB_BYTES = 144, PAD = 16, XS = 8; };   // 32-bit fragment loads: 4 words mod 32
-template <> struct MmFmt<MM_FMT_Q6K> { static constexpr int KS = 8, SB_BYTES = 210, PAD = 0, XS = 16; };
-static constexpr int mm_ks(int fmt) { return (fmt == MM_FMT_Q80 || fmt == MM_FMT_Q6K) ? 8 : 16; }
-static constexpr int mm_sb_bytes(int fmt) { return fmt == MM_FMT_Q80 ? 272 : (fmt == MM_FMT_Q6K ? 210 : 144); }
-static constexpr int mm_xs(int fmt) { return fmt == MM_FMT_Q6K ? 16 : 8; }
-static constexpr int mm_stage_bytes(int fmt) { return 16 * (mm_ks(fmt) * mm_sb_bytes(fmt) + (fmt == MM_FMT_Q6K ? 0 : (fmt == MM_FMT_Q40 ? 16 : 32))); }
-
-__device__ __forceinline__ void skn_mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                             uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-__device__ __forceinline__ void skn_mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                             uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-
-
-// byte i (0..3) of w as a float without the conversion pipe: (2^23 + b) - 2^23
-__device__ __forceinline__ float mm_byte_f(uint32_t w, uint32_t i) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u + i)) - 8388608.f;
-}
-__device__ __forceinline__ int mm_byte_i(uint32_t w, uint32_t i) { return (int)__byte_perm(w, 0u, 0x4440u + i); }
-// signed byte i of w, sign-extended (selector values 8..15 replicate a byte's sign bit)
-// (the __byte_perm intrinsic only honours three bits per selector, so the instruction is spelled out)
-__device__ __forceinline__ int mm_sbyte_i(uint32_t w, uint32_t i) {
-    int r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"(0x8880u + 0x1111u * i));
-    return r;
-}
-// signed byte i of w as a float, w given with its bytes' sign bits flipped: (2^23 + 128 + b) - (2^23 + 128)
-__device__ __forceinline__ float mm_sbyte_f(uint32_t w_flipped, uint32_t i) {
-    return __uint_as_float(__byte_perm(w_flipped, 0x4B000000u, 0x7440u + i)) - 8388736.f;
-}
-
-// loads from a 32-bit shared-memory address (explicit state space: no generic addressing, no
-// 64-bit address arithmetic in the inner loops)
-__device__ __forceinline__ uint2 mm_lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint4 mm_lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t mm_lds32(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-// fp16 at a 2-byte aligned shared address, widened
-__device__ __forceinline__ float mm_lds_half(uint32_t a) {
-    unsigned short v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-    return __half2float(__ushort_as_half(v));
-}
-__device__ __forceinline__ float mm_lds32f(uint32_t a) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ float4 mm_lds128f(uint32_t a) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-    return v;
-}
-
-__device__ __forceinline__ void mm_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// One super-block (256 activations, two float4 per lane: elements 4*lane.. and 128 + 4*lane..)
-// -> three digit planes (byte k of a plane = that digit of activation k), the scale 2^(e-21)
-// (NaN when the block holds a NaN or an infinity) and the eight 32-element sums.
-// XS16: sixteen 16-element sums instead of the eight 32-element ones.
-template <bool XS16>
-static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4 v1, int sbi, int lane, uint8_t *dig, int PL,
-                                                   float *sgrp, float *xsum) {
-    float mx = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
-                     fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-    float s0 = (v0.x + v0.y) + (v0.z + v0.w), s1 = (v1.x + v1.y) + (v1.z + v1.w);
-    if constexpr (XS16) {
-#pragma unroll
-        for (int o = 2; o > 0; o >>= 1) {
-            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        }
-        if ((lane & 3) == 0) {
-            xsum[sbi * 16 + (lane >> 2)] = s0;
-            xsum[sbi * 16 + 8 + (lane >> 2)] = s1;
-        }
-        s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
-    } else {
-#pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        }
-    }
-    // mx >= 0 (or NaN-free by fmaxf): its bit pattern orders like the value, one integer reduction
-    mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
-    float tot = s0 + s1;
-    tot += __shfl_xor_sync(0xffffffffu, tot, 8);
-    tot += __shfl_xor_sync(0xffffffffu, tot, 16);
-    int E = (int)(__float_as_uint(mx) >> 23);
-    E = E < 22 ? 22 : (E > 254 ? 254 : E);
-    const float mul = __int_as_float((275 - E) << 23);          // 2^(21-e)
-    // rint(v * mul) sits in the mantissa of v * mul + 1.5 * 2^23; adding 0x808080 and flipping
-    // the three sign bits leaves the three balanced digits in bytes 0..2
-    constexpr int C = 0x808080 - 0x4B400000;
-    const float in[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    uint32_t D[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) D[i] = (uint32_t)(__float_as_int(fmaf(in[i], mul, 12582912.f)) + C) ^ 0x808080u;
-    const int f = sbi * 64 + lane;
-#pragma unroll
-    for (int n = 0; n < 3; ++n) {
-        const uint32_t sel = 0x0040u + 0x11u * n;               // byte n of both operands
-        const uint32_t a = __byte_perm(__byte_perm(D[0], D[1], sel), __byte_perm(D[2], D[3], sel), 0x5410u);
-        const uint32_t b = __byte_perm(__byte_perm(D[4], D[5], sel), __byte_perm(D[6], D[7], sel), 0x5410u);
-        *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * f) = a;
-        *reinterpret_cast<uint32_t *>(dig + (size_t)n * PL + 4 * (f + 32)) = b;
-    }
-    if (!XS16 && (lane & 7) == 0) {
-        xsum[sbi * 8 + (lane >> 3)] = s0;
-        xsum[sbi * 8 + 4 + (lane >> 3)] = s1;
-    }
-    if (lane == 0) sgrp[sbi] = (fabsf(tot) <= 3.4028234e38f) ? __int_as_float((E - 21) << 23) : __int_as_float(0x7FC00000);
-}
+#include "skn_mma_common.cuh"
 
 // Register caps: the register file is split over the SM's four schedulers (16K registers each), so
 // two resident CTAs of 9 warps need five warps per scheduler, i.e. at most 102 registers per
@@ -229,14 +78,19 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     const int nxs = CHUNKED ? MM_KS : nb;       // super-blocks of group sums per activation row
     const int nks = (nb + MM_KS - 1) / MM_KS;   // K super-chunks
     const int ksb = CHUNKED ? (nb < MM_KS ? nb : MM_KS) : nb;    // super-blocks whose digit planes are resident
-    const int PL = ksb * 256 + 32;              // plane stride: 8 words mod 32, planes 0..2 on disjoint banks
+    const int PL = ksb * 256 + 32;              // plane stride: 8 words mod 32, the four planes on disjoint banks
+    const int RS = MM_ND * PL + 64;             // activation-row stride: 16 words mod 32, the two rows of a pair apart
 
-    // shared memory: ring | digit planes [row][3] | block scales [row] | group sums [row] | barriers | partials [row]
+    // shared memory: ring | digit planes [row][4] | block scales [row] | group sums [row] | outlier values, positions,
+    //                counts [row][block] | barriers | partials [row]
     uint8_t *ring = smem;
     uint8_t *dig = smem + (size_t)nst * MM_STAGE;
-    float *sgrp = reinterpret_cast<float *>(dig + ((size_t)NA * 3 * PL + 127) / 128 * 128);
+    float *sgrp = reinterpret_cast<float *>(dig + ((size_t)NA * RS + 127) / 128 * 128);
     float *xsum = sgrp + (size_t)NA * nbp;
-    uint64_t *full = reinterpret_cast<uint64_t *>(xsum + (size_t)NA * nxs * XS);
+    float *oval = xsum + (size_t)NA * nxs * XS;
+    uint32_t *oidx = reinterpret_cast<uint32_t *>(oval + (size_t)NA * nbp * MM_MAX_OUT);
+    uint8_t *ocnt = reinterpret_cast<uint8_t *>(oidx + (size_t)NA * nbp);
+    uint64_t *full = reinterpret_cast<uint64_t *>(ocnt + ((size_t)NA * nbp + 15) / 16 * 16);
     uint64_t *empty = full + nst;
     float *part = reinterpret_cast<float *>(empty + nst);
 
@@ -249,6 +103,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     const int ntiles = nrt * nks;               // tile i -> super-chunk i / nrt, row tile i % nrt
     const int pw = nks * W;                     // partial slots per (activation row, weight row)
 
+    __shared__ int s_anyout;                    // some prepared block of x has outliers (rare): the tile loop looks only then
+    if (threadIdx.x == 0) s_anyout = 0;
     MV_STAMP(0);
     if (warp == W && lane < nst) {
         skn_mbar_init(&full[lane], 1);
@@ -368,8 +224,9 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int h = 0; h < UR; ++h)
                 if (ua[h] >= 0)
-                    mm_digitize<XS == 16>(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * 3 * PL, PL, sgrp + (size_t)ua[h] * nbp,
-                                          xsum + (size_t)ua[h] * nxs * XS);
+                    mm_digitize<XS == 16>(v[h][0], v[h][1], us[h], lane, dig + (size_t)ua[h] * RS, PL, sgrp + (size_t)ua[h] * nbp,
+                                          xsum + (size_t)ua[h] * nxs * XS, oval + (size_t)ua[h] * nbp * MM_MAX_OUT,
+                                          oidx + (size_t)ua[h] * nbp, ocnt + (size_t)ua[h] * nbp, &s_anyout);
         }
         if (f_gain) {
 #pragma unroll
@@ -382,15 +239,16 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
         }
     };
 
-    // this lane's two B columns (2t, 2t + 1): column c of a row pair is digit c % 3 of its row c / 3
-    // B column c of a row pair = digit c / 2 of its row c & 1 (c < 6): a lane LOADS column g and
-    // READS BACK columns 2t (first row of the pair) and 2t + 1 (second row), both of digit t
+    // B column c of a row pair = digit c / 2 of its row c & 1: a lane LOADS column g and READS BACK
+    // columns 2t (first row of the pair) and 2t + 1 (second row), both of digit t
     const int bcol_row = g & 1, bcol_dig = g >> 1;
+    const float inv_dw = (t == 0) ? 1.f : ((t == 1) ? (1.f / 256.f) : ((t == 2) ? (1.f / 65536.f) : (1.f / 16777216.f)));
     constexpr int rowA = 0, rowB = 1;
     bool failed = false;
     int ks = 0, rt = 0, stg = 0;
     uint32_t par = 0;
     const uint32_t ring_s = skn_smem_u32(ring), dig_s = skn_smem_u32(dig), sgrp_s = skn_smem_u32(sgrp), xsum_s = skn_smem_u32(xsum);
+    const uint32_t oval_s = skn_smem_u32(oval), oidx_s = skn_smem_u32(oidx), ocnt_s = skn_smem_u32(ocnt);
     int cur_ks = -1;
     if (!CHUNKED) {
         for (int kc = 0; kc < nks; ++kc) prep_chunk(kc);
@@ -415,6 +273,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             atomicExch(status, SKN_ERR_TIMEOUT);
         }
         if (i == 0) MV_STAMP(4);
+        const bool anyout = *reinterpret_cast<volatile int *>(&s_anyout) != 0;     // (after this tile's planes were prepared)
         float accA[NP][2], accB[NP][2];         // [pair][weight row g / g + 8]: columns 2t and 2t + 1, all own super-blocks
         float ms[NAMAX];                        // min term of weight row g + 8 * (t & 1), sub-blocks 4 * (t >> 1) .. + 3
 #pragma unroll
@@ -427,6 +286,10 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             if (sb >= nsb) break;
             const uint32_t ba = st + g * MM_ROW_STRIDE + sb * MM_BLOCK_BYTES;
             const uint32_t bb = ba + 8 * MM_ROW_STRIDE;
+            // outlier counts of this block per activation row (almost always zero): loaded now, looked at after the MMAs
+            int ocn[NAMAX];
+#pragma unroll
+            for (int a = 0; a < NAMAX; ++a) ocn[a] = (anyout && a < NA) ? (int)mm_lds8(ocnt_s + (uint32_t)(a * nbp + sb0 + sb)) : 0;
             if constexpr (FMT == MM_FMT_Q4K) {
             const uint4 ha = mm_lds128(ba), hb = mm_lds128(bb);
             // 6-bit scales as bytes: word 0 = sub-blocks 0..3, word 1 = sub-blocks 4..7
@@ -442,8 +305,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
-                bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256 + 8 * t);
+                bon[ap] = arow < NA;
+                bsrc[ap] = dig_s + (uint32_t)((bon[ap] ? arow : 0) * RS + bcol_dig * PL + (sb0 + sb) * 256 + 8 * t);
             }
             // The MMAs of byte pair p + 1 are issued before the results of pair p are consumed, so
             // that their latency overlaps the integer multiply-adds.
@@ -455,11 +318,9 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 const uint32_t ah0 = wa.x & 0xF0F0F0F0u, ah1 = wb.x & 0xF0F0F0F0u, ah2 = wa.y & 0xF0F0F0F0u, ah3 = wb.y & 0xF0F0F0F0u;
 #pragma unroll
                 for (int ap = 0; ap < NP; ++ap) {
-                    uint2 b0 = make_uint2(0u, 0u), b1 = make_uint2(0u, 0u);
-                    if (bon[ap]) {
-                        b0 = mm_lds64(bsrc[ap] + (2 * p) * 32);
-                        b1 = mm_lds64(bsrc[ap] + (2 * p + 1) * 32);
-                    }
+                    // (unconditional: lanes whose column has no activation row read row 0 again; those columns are never used)
+                    const uint2 b0 = mm_lds64(bsrc[ap] + (2 * p) * 32);
+                    const uint2 b1 = mm_lds64(bsrc[ap] + (2 * p + 1) * 32);
                     skn_mma_u8s8(cl[buf][ap], al0, al1, al2, al3, b0.x, b0.y);
                     skn_mma_u8s8(ch[buf][ap], ah0, ah1, ah2, ah3, b1.x, b1.y);
                 }
@@ -526,8 +387,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
-                bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256) + 4 * t;
+                bon[ap] = arow < NA;
+                bsrc[ap] = dig_s + (uint32_t)((bon[ap] ? arow : 0) * RS + bcol_dig * PL + (sb0 + sb) * 256) + 4 * t;
             }
             // sixteen int8 scales of each row: five aligned words -> four block words
             uint32_t sa[4], sq[4];
@@ -577,8 +438,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                             const int s_a = mm_sbyte_i(sa[si >> 2], si & 3), s_b = mm_sbyte_i(sq[si >> 2], si & 3);
 #pragma unroll
                             for (int ap = 0; ap < NP; ++ap) {
-                                uint32_t b0 = 0u;
-                                if (bon[ap]) b0 = mm_lds32(bsrc[ap] + (4 * h + q) * 32 + 16 * pt);
+                                const uint32_t b0 = mm_lds32(bsrc[ap] + (4 * h + q) * 32 + 16 * pt);
                                 int c[4];
                                 skn_mma_u8s8(c, a0, a1, 0u, 0u, b0, 0u);
                                 acc[ap][0] += s_a * c[0]; acc[ap][2] += s_b * c[2];
@@ -629,8 +489,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 #pragma unroll
             for (int ap = 0; ap < NP; ++ap) {
                 const int arow = 2 * ap + bcol_row;
-                bon[ap] = g < 6 && arow < NA;
-                bsrc[ap] = dig_s + (uint32_t)(((bon[ap] ? arow : 0) * 3 + bcol_dig % 3) * PL + (sb0 + sb) * 256) +
+                bon[ap] = arow < NA;
+                bsrc[ap] = dig_s + (uint32_t)((bon[ap] ? arow : 0) * RS + bcol_dig * PL + (sb0 + sb) * 256) +
                            (FMT == MM_FMT_Q80 ? 8 * t : 4 * t);
             }
             float sgA[NP], sgB[NP];
@@ -674,15 +534,13 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 }
 #pragma unroll
                 for (int ap = 0; ap < NP; ++ap) {
-                    uint32_t b0 = 0u, b1 = 0u;
-                    if (bon[ap]) {
-                        if constexpr (FMT == MM_FMT_Q80) {
-                            const uint2 b = mm_lds64(bsrc[ap] + j * 32);
-                            b0 = b.x; b1 = b.y;
-                        } else {
-                            b0 = mm_lds32(bsrc[ap] + j * 32);
-                            b1 = mm_lds32(bsrc[ap] + j * 32 + 16);
-                        }
+                    uint32_t b0, b1;
+                    if constexpr (FMT == MM_FMT_Q80) {
+                        const uint2 b = mm_lds64(bsrc[ap] + j * 32);
+                        b0 = b.x; b1 = b.y;
+                    } else {
+                        b0 = mm_lds32(bsrc[ap] + j * 32);
+                        b1 = mm_lds32(bsrc[ap] + j * 32 + 16);
                     }
                     int c[4];
                     if constexpr (FMT == MM_FMT_Q80) skn_mma_s8s8(c, a0, a1, a2, a3, b0, b1);
@@ -714,17 +572,32 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                 }
             }
             }
+            // outliers (rare): lane t multiplies outlier t with the weights of rows g and g + 8; the product joins
+            // this lane's digit accumulator with the digit's power of two divided out
+#pragma unroll
+            for (int a = 0; a < NAMAX; ++a) {
+                if (ocn[a] != 0) {                                       // warp-uniform
+                    if (t < ocn[a]) {
+                        const uint32_t e = (uint32_t)(a * nbp + sb0 + sb);
+                        const int k = (int)mm_lds8(oidx_s + 4u * e + (uint32_t)t);
+                        const float xv = mm_lds32f(oval_s + 4u * (MM_MAX_OUT * e + (uint32_t)t)) * inv_dw;
+                        const float wa = mm_weight_at<FMT>(ba, k) * xv, wb = mm_weight_at<FMT>(bb, k) * xv;
+                        if (a & 1) { accB[a >> 1][0] += wa; accB[a >> 1][1] += wb; }
+                        else { accA[a >> 1][0] += wa; accA[a >> 1][1] += wb; }
+                    }
+                }
+            }
         }
         __syncwarp();      // every lane has read its share of the stage
         if (lane == 0) skn_mbar_arrive(&empty[stg]);
-        // ---- tile epilogue: lane t holds digit t of both rows of a pair (t = 3: nothing)
-        const float dw = (t == 0) ? 1.f : ((t == 1) ? 256.f : ((t == 2) ? 65536.f : 0.f));
+        // ---- tile epilogue: lane t holds digit t of both rows of a pair, and the products of their outliers number t
+        const float dw = (t == 0) ? 1.f : ((t == 1) ? 256.f : ((t == 2) ? 65536.f : 16777216.f));
 #pragma unroll
         for (int ap = 0; ap < NP; ++ap) {
 #pragma unroll
             for (int wr = 0; wr < 2; ++wr) {            // weight rows g, g + 8
-                float e0 = (t < 3) ? accA[ap][wr] * dw : 0.f;
-                float e1 = (t < 3) ? accB[ap][wr] * dw : 0.f;
+                float e0 = accA[ap][wr] * dw;
+                float e1 = accB[ap][wr] * dw;
                 e0 += __shfl_xor_sync(0xffffffffu, e0, 1);
                 e1 += __shfl_xor_sync(0xffffffffu, e1, 1);
                 e0 += __shfl_xor_sync(0xffffffffu, e0, 2);
@@ -893,8 +766,10 @@ static size_t mm_fixed_smem(int fmt, int nb, int n_act, int64_t rows_max, int nk
     // three or four rows: digit planes of one K super-chunk at a time; one or two: all of x
     const bool chunked = n_act > 2;
     const int ks = mm_ks(fmt), ksb = chunked ? (nb < ks ? nb : ks) : nb, nxs = chunked ? ks : nb;
-    return ((size_t)n_act * 3 * (ksb * 256 + 32) + 127) / 128 * 128 + (size_t)n_act * ((nxs + 3) / 4 * 4) * 4 +
-           (size_t)n_act * nxs * mm_xs(fmt) * 4 + (size_t)n_act * rows_max * nks * warps * 4 + 64;
+    const size_t nbp = (size_t)(nxs + 3) / 4 * 4;
+    return ((size_t)n_act * (MM_ND * (ksb * 256 + 32) + 64) + 127) / 128 * 128 + (size_t)n_act * nbp * 4 +
+           (size_t)n_act * nxs * mm_xs(fmt) * 4 + (size_t)n_act * nbp * (MM_MAX_OUT * 4 + 4) + ((size_t)n_act * nbp + 15) / 16 * 16 +
+           (size_t)n_act * rows_max * nks * warps * 4 + 64;
 }
 
 // most activation rows one launch can take for this shape (the digit planes and partial sums of

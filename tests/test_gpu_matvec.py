@@ -68,6 +68,44 @@ def test_cfg2_shapes(ctx, qt, N, K, M):
     run_case(ctx, qt, N, K, M, seed=1)
 
 
+def _sampled_rows_case(ctx, qt, N, K, M, seed, tol, n_sample=96, bias=False):
+    """The product at full size on the GPU, the oracle on `n_sample` sampled output rows (all M activation rows)."""
+    g = synth.rng(seed)
+    w = synth.make_weight(g, qt, N, K)
+    x = synth.make_activations(g, M, K)
+    b = g.standard_normal(N).astype(np.float32) if bias else None
+    t = skn.QuantTensor(ctx, (N, K), qt, w)
+    y = np.asarray(t.matmul_t(x if M > 1 else x[0], b)).reshape(M, N)
+    t.close()
+    assert np.isfinite(y).all()
+    rows = np.unique(np.concatenate([g.choice(N, size=min(N, n_sample - 4), replace=False), [0, 1, N - 2, N - 1]]))
+    y_ref, absdot = oracle.matmul(qt, np.ascontiguousarray(w[rows]), rows.size, K, x)
+    if bias:
+        y_ref = y_ref + b[rows].astype(np.float64)[None, :]
+        absdot = absdot + np.abs(b[rows].astype(np.float64))[None, :]
+    assert_close_dot(y[:, rows], y_ref, absdot, tol, f"type {qt} {N}x{K} M={M}")
+
+
+@pytest.mark.parametrize("qt", [synth.Q4_0, synth.Q8_0])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [16, 64])
+def test_cfg2_full_shapes_at_batch_16_and_64(ctx, qt, N, K, M):
+    """Config 2 at its own shapes: M = 16 is the many-row fp32 path (1e-5), M = 64 the bf16 tensor-core path (1e-2);
+    the oracle runs on sampled output rows."""
+    from conftest import BF16_TOL
+    _sampled_rows_case(ctx, qt, N, K, M, seed=1, tol=FP32_TOL if M < 64 else BF16_TOL)
+
+
+@pytest.mark.parametrize("qt,name", TYPES)
+@pytest.mark.parametrize("N,K,M", [(28672, 4096, 16), (4096, 14336, 16), (6144, 4096, 8), (4096, 4096, 5), (32000, 4096, 16),
+                                   (300, 2304, 7), (33, 256, 3), (1000, 5120, 12)])
+def test_many_rows_in_one_pass(ctx, qt, name, N, K, M):
+    """3 to 16 activation rows: every weight is read once (the many-row kernel for Q4_K / Q8_0 / Q4_0; Q6_K keeps four
+    rows per pass), decoder-size shapes and odd ones (short rows, a row count that does not fill a tile, a short
+    last K chunk), with a bias."""
+    _sampled_rows_case(ctx, qt, N, K, M, seed=6000 + N + K + M, tol=FP32_TOL, n_sample=64, bias=(M % 2 == 1))
+
+
 @pytest.mark.parametrize("N,K,M", [(32000, 4096, 1), (32000, 4096, 4), (4096, 14336, 1), (4096, 14336, 3), (1000, 2816, 2),
                                    (37, 768, 4)])
 def test_q6k_at_lm_head_and_down_projection_sizes(ctx, N, K, M):
@@ -244,6 +282,86 @@ def test_extreme_activations(ctx):
         y_ref, absdot = oracle.matmul(synth.Q4_K, w, N, K, x)
         assert_close_dot(y[None, :], y_ref, absdot, FP32_TOL, f"x scale {scale}")
     t.close()
+
+
+def _zero_weight_at(qt, w, N, K, pos):
+    """Raw blocks with the weight at column block * blk + pos[block] of every row made an exact zero (the
+    value a quantiser produces for a zero weight): Q4_0 q = 8, Q8_0 q = 0, Q4_K scale and min of the weight's
+    sub-block 0, Q6_K scale of its 16-weight group 0."""
+    e, bb = synth.GEOMETRY[qt]
+    nb = K // e
+    blk = w.reshape(N, nb, bb).copy()
+    for b in range(nb):
+        k = int(pos[b])
+        if qt == synth.Q4_0:
+            i = 2 + (k % 16)
+            blk[:, b, i] = (blk[:, b, i] & 0xF0) | 8 if k < 16 else (blk[:, b, i] & 0x0F) | 0x80
+        elif qt == synth.Q8_0:
+            blk[:, b, 2 + k] = 0
+        elif qt == synth.Q4_K:
+            j, sc = k // 32, blk[:, b, 4:16]
+            if j < 4:
+                sc[:, j] &= 0xC0
+                sc[:, j + 4] &= 0xC0
+            else:
+                sc[:, j + 4] = 0
+                sc[:, j - 4] &= 0x3F
+                sc[:, j] &= 0x3F
+        else:
+            h, l = k // 128, k % 128
+            blk[:, b, 192 + 8 * h + 2 * (l // 32) + (l % 32) // 16] = 0
+    return blk.reshape(N, nb * bb)
+
+
+@pytest.mark.parametrize("qt,name", TYPES)
+@pytest.mark.parametrize("M", [1, 3])
+@pytest.mark.parametrize("ratio", [1e2, 1e3, 1e4, 1e6])
+@pytest.mark.parametrize("zero_weight", [False, True])
+def test_in_block_outliers(ctx, qt, name, M, ratio, zero_weight):
+    """One activation per 256-block `ratio` times the rest (the channel outliers of a residual stream), met by
+    ordinary weights or by an exactly zero weight (then only its neighbours contribute, and they must not have
+    lost their precision to the outlier): the stated fp32 tolerance holds unchanged."""
+    g = synth.rng(8000 + int(np.log10(ratio)) * 10 + M)
+    N, K = 64, 2048
+    e, _ = synth.GEOMETRY[qt]
+    w = synth.make_weight(g, qt, N, K)
+    x = synth.make_activations(g, M, K)
+    big = g.integers(0, 256, size=K // 256)                       # position of the outlier inside every 256-block
+    cols = np.arange(K // 256) * 256 + big
+    x[:, cols] *= np.float32(ratio) * np.where(g.random((M, cols.size)) < 0.5, -1, 1).astype(np.float32)
+    if zero_weight:
+        pos = np.full(K // e, -1)
+        pos[cols // e] = cols % e
+        w0 = w.reshape(N, K // e, -1).copy()
+        keep = pos < 0
+        w = _zero_weight_at(qt, w, N, K, np.where(keep, 0, pos))
+        w.reshape(N, K // e, -1)[:, keep] = w0[:, keep]             # blocks without an outlier stay as drawn
+        deq = oracle.dequant(qt, w).reshape(N, K)
+        assert np.all(deq[:, cols] == 0.0)
+    t = skn.QuantTensor(ctx, (N, K), qt, w)
+    y = t.matmul_t(x if M > 1 else x[0])
+    t.close()
+    y_ref, absdot = oracle.matmul(qt, w, N, K, x)
+    assert_close_dot(np.asarray(y).reshape(M, N), y_ref, absdot, FP32_TOL, f"{name} M={M} outlier x{ratio:g} zero={zero_weight}")
+
+
+def test_many_outlier_blocks_and_mixed_scales(ctx):
+    """Every block of a row carries an outlier (more blocks than the kernel has second-tier slots for), and one
+    block mixes three scales (1e6, 1e3, 1): the result stays within the bound of one tier, 2^-30 of a block's
+    largest activation per activation, far inside the tolerance for ordinary weights."""
+    g = synth.rng(8100)
+    N, K = 48, 14336
+    for qt in (synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q4_0):
+        w = synth.make_weight(g, qt, N, K)
+        x = synth.make_activations(g, 2, K)
+        x[:, ::256] *= np.float32(3e4)
+        x[:, 7] *= np.float32(1e6)
+        x[:, 9] *= np.float32(1e3)
+        t = skn.QuantTensor(ctx, (N, K), qt, w)
+        y = t.matmul_t(x)
+        t.close()
+        y_ref, absdot = oracle.matmul(qt, w, N, K, x)
+        assert_close_dot(y, y_ref, absdot, FP32_TOL, f"type {qt}")
 
 
 def test_grouped_matvec_equals_separate_products(ctx):
