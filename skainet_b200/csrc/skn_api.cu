@@ -554,7 +554,7 @@ int32_t skn_matmul_async(skn_ctx *ctx, const skn_tensor *w, const float *x_host,
 
 }  // extern "C"
 
-#ifdef SKN_MV_TRACE
+#ifdef SKN_TUNING
 // Profiling builds only (never in the shipped library): copies the raw status/trace area.
 extern "C" int32_t skn_debug_read_status(skn_ctx *ctx, void *out_host, int64_t bytes) {
     if (!skn_ctx_ok(ctx) || bytes > 32768) return SKN_ERR_ARG;

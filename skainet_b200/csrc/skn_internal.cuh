@@ -238,11 +238,23 @@ struct skn_comm_view {
     uint32_t *state;                        // [0] exchanges completed, [1] push tickets, [2] finish tickets
 };
 bool skn_comm_get_view(const skn_comm *c, skn_comm_view *v);
+// Sweep knobs exist only in SKN_TUNING builds; the shipped library compiles every one down to its default.
+#ifdef SKN_TUNING
+#include <stdlib.h>
+static inline int skn_tune_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+#else
+static inline int skn_tune_int(const char *, int dflt) { return dflt; }
+#endif
+
 struct skn_mv_rope {                        // optional argument of skn_launch_matvec_acts: (wq, wk, wv) of a single-token step
     int head_dim, n_kv_heads, capacity, seq0;   // seq0: sequence of the first activation row
     const int32_t *len_dev, *start_dev;         // cache lengths (= positions of the new tokens) and ring starts
     float *k_cache, *v_cache;
     float theta;
+    const double *inv_freq;                     // optional device table theta^(-2i / head_dim), i < head_dim / 2 (NULL: computed per element)
 };
 struct skn_mv_exchange {                    // optional argument of skn_launch_matvec_acts
     skn_comm_view view;

@@ -322,7 +322,13 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
     // sees the cache up to and including its own token (tq = 1: plain decode)
     const int sp = blockIdx.x, kvh = blockIdx.y, bq = blockIdx.z, b = bq / tq;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int L = min(cap, max(0, len[b] + len_extra - (tq - 1 - bq % tq)));     // never past the ring: ns <= S
+    // the length, the ring start and q are requested together: one trip to L2 instead of three in a row
+    const int len_b = __ldg(len + b), s0 = __ldg(start + b);
+    const int Hq = Hkv * G;
+    float qv[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g) VecLoad<VEC>::ld(q + ((size_t)bq * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
+    const int L = min(cap, max(0, len_b + len_extra - (tq - 1 - bq % tq)));     // never past the ring: ns <= S
     const int t0 = sp * CHUNK;
     if (t0 >= L) {
         // an empty sequence has no split to merge: its output is zero
@@ -331,18 +337,12 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
         return;
     }
     const int nt = min(CHUNK, L - t0);
-    const int s0 = start[b];
-    const int Hq = Hkv * G;
     const CT *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
     const CT *vbase = vc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
-
-    float qv[G][VEC];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        VecLoad<VEC>::ld(q + ((size_t)bq * Hq + kvh * G + g) * D + lane * VEC, qv[g]);
+    for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int e = 0; e < VEC; ++e) qv[g][e] *= scale;
-    }
 
     // short chunks (short contexts: latency matters, not bandwidth): the warp's first V tile is
     // requested before the scores are computed, so that its latency overlaps pass 1
@@ -495,29 +495,62 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // weights of the splits once per (head, split), reusing the score buffer: w = exp(max_s - max) / sum
-    float *s_w = &s_sc[0][0];                       // CHUNK * G floats >= G * ns (the launcher admits ns <= min(CHUNK, ATT_MERGE_MAX_SPLITS))
-    if (threadIdx.x < G) {
-        const int g = threadIdx.x;
-        const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2);
-        float m = -INFINITY;
-        for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(rec + (size_t)s * (D + 2)));
-        float l = 0.f;
-        for (int s = 0; s < ns; ++s) {
-            const float w = expf(__ldcg(rec + (size_t)s * (D + 2)) - m);
-            s_w[g * ns + s] = w;
-            l = fmaf(__ldcg(rec + (size_t)s * (D + 2) + 1), w, l);
-        }
-        const float inv = 1.f / l;
-        for (int s = 0; s < ns; ++s) s_w[g * ns + s] *= inv;
+    // The tail is latency, not bandwidth: every load below is issued before the first one is consumed (a loop
+    // of load -> use over the splits would pay one trip to L2 per split).
+    // (max, sum) of every (head, split) in one round of loads, into the output staging buffer (free by now)
+    float *s_ms = &s_o[0][0][0];                    // [G][ns] maxima, then [G][ns] sums, then [G][ns] weights
+    float *s_ls = s_ms + G * ns;
+    float *s_w = s_ls + G * ns;                     // 3 G ns <= ATT_WARPS G D floats (ns <= 64 <= 4 D / 3)
+    for (int i = threadIdx.x; i < G * ns; i += ATT_WARPS * 32) {
+        const int g = i / ns, sidx = i - g * ns;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(part + (((size_t)bq * Hq + kvh * G + g) * S + sidx) * (D + 2)));
+        s_ms[i] = ml.x;
+        s_ls[i] = ml.y;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += ATT_WARPS * 32) {
-        const int g = i / D, d = i % D;
-        const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2) + 2 + d;
-        float a = 0.f;
-        for (int s = 0; s < ns; ++s) a = fmaf(__ldcg(rec + (size_t)s * (D + 2)), s_w[g * ns + s], a);
-        out[((size_t)bq * Hq + kvh * G + g) * D + d] = a;
+    // weights w = exp(max_s - max) / sum: one warp per head, lanes over the splits
+    for (int g = warp; g < G; g += ATT_WARPS) {
+        float m = -INFINITY;
+        for (int sidx = lane; sidx < ns; sidx += 32) m = fmaxf(m, s_ms[g * ns + sidx]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int sidx = lane; sidx < ns; sidx += 32) {
+            const float w = expf(s_ms[g * ns + sidx] - m);
+            s_w[g * ns + sidx] = w;
+            l = fmaf(s_ls[g * ns + sidx], w, l);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        const float inv = 1.f / l;
+        for (int sidx = lane; sidx < ns; sidx += 32) s_w[g * ns + sidx] *= inv;
+    }
+    __syncthreads();
+    constexpr int MB = 16;                          // splits loaded per batch
+    constexpr int NO = (G * D + ATT_WARPS * 32 - 1) / (ATT_WARPS * 32);    // outputs per thread
+    float acc[NO];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) acc[j] = 0.f;
+    for (int sb = 0; sb < ns; sb += MB) {
+        float r[NO][MB];
+#pragma unroll
+        for (int j = 0; j < NO; ++j) {
+            const int i = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1), g = i / D, d = i % D;
+            const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2) + 2 + d;
+#pragma unroll
+            for (int u = 0; u < MB; ++u) r[j][u] = (sb + u < ns) ? __ldcg(rec + (size_t)(sb + u) * (D + 2)) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NO; ++j) {
+            const int g = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1) / D;
+#pragma unroll
+            for (int u = 0; u < MB; ++u) acc[j] = fmaf(r[j][u], (sb + u < ns) ? s_w[g * ns + sb + u] : 0.f, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NO; ++j) {
+        const int i = threadIdx.x + j * ATT_WARPS * 32;
+        if (i < G * D) out[((size_t)bq * Hq + kvh * G) * D + i] = acc[j];
     }
     if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
@@ -797,13 +830,11 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
     const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
     unsigned *tickets = (tq == 1 && small_grid && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
-    static const int stream_on = [] { const char *v = getenv("SKN_ATTN_STREAM"); return v ? atoi(v) : 1; }();
-    if (chunk == ATT_CHUNK && !tickets && stream_on) {
+    if (chunk == ATT_CHUNK && !tickets) {
         // long contexts: tiles by bulk async copy through a shared-memory ring
         constexpr int TILE_BYTES = ATT_WARPS * TT * D * (int)sizeof(CT);
         // two stages: measured, more resident CTAs per SM (five at 44 KB each for D = 128, G = 4) beat a deeper ring
-        static const int nst_env = [] { const char *v = getenv("SKN_ATTN_NST"); return v ? atoi(v) : 0; }();
-        const int nst = (nst_env >= 2 && nst_env <= 6) ? nst_env : 2;
+        constexpr int nst = 2;
         const size_t smem = (size_t)nst * TILE_BYTES + 2 * (size_t)nst * sizeof(uint64_t);
         auto kern = skn_attn_stream_kernel<D, G, TT, CT>;
         const uint32_t cfg_bit = 1u << ((sizeof(CT) == 2 ? 8 : 0) + (D == 128 ? 4 : 0) + (G == 1 ? 0 : (G == 2 ? 1 : (G == 4 ? 2 : 3))));
@@ -816,6 +847,8 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
         kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kc, vc, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
                                                           scale, part, S, tq, len_extra, nst, kv->ctx->d_status);
     } else if (chunk == 32)
+        // (launched in plain stream order: started early by programmatic dependent launch, these CTAs and those of the
+        // projection behind them sat on the SMs while the Q/K/V projection still ran; measured 3.7 us per layer slower)
         skn_attn_split_kernel<D, G, TT, 32, CT><<<grid, ATT_WARPS * 32, 0, stream>>>(q, kc, vc, kv->d_len, kv->d_start,
                                                                                 kv->n_kv_heads, kv->capacity, scale, part, S, tq, len_extra, out, tickets);
     else if (chunk == 64)
@@ -831,14 +864,12 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     return cudaGetLastError();
 }
 
-// 64-token chunks when 256-token chunks would give fewer CTAs than two per SM (short contexts,
-// small batches) and the partials of the finer split fit `scratch_cap` bytes
 static int attn_pick_chunk(const skn_kvcache *kv, int n_q_heads, int tq, size_t scratch_cap) {
     // finer splits while 256-token (then 64-token) chunks leave SMs idle (short contexts, small
     // batches) and the partials of the finer split fit `scratch_cap` bytes
-    static const int forced = [] { const char *v = getenv("SKN_ATTN_CHUNK"); return v ? atoi(v) : 0; }();   // tuning knob
     const int chunks[3] = {ATT_CHUNK, 64, 32};
     int pick = ATT_CHUNK;
+    static const int forced = skn_tune_int("SKN_ATTN_CHUNK", 0);
     if (forced == 32 || forced == 64 || forced == ATT_CHUNK) {
         const int64_t S = (kv->capacity + forced - 1) / forced;
         if ((size_t)((int64_t)kv->batch * tq * n_q_heads * S * (kv->head_dim + 2) * 4) <= scratch_cap) return forced;

@@ -38,6 +38,7 @@ struct skn_llama {
     skn_comm *comm;
     int32_t world, rank, heads_l, kv_heads_l, ffn_l, vocab_l;
     float *cand;                      // [world][max_batch][2] (value, global id) of the cross-rank argmax
+    double *inv_freq;                 // rope_theta^(-2i / head_dim), i < head_dim / 2, for the fused rotary epilogue
 };
 
 // from skn_kv.cu
@@ -129,6 +130,12 @@ int32_t skn_llama_create_tp(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int
     if (e == cudaSuccess) e = cudaMalloc((void **)&m->len_ptrs, sizeof(int32_t *) * n_layers);
     if (e == cudaSuccess) e = cudaMalloc(&m->argmax_scratch, skn_argmax_scratch_bytes(max_batch));
     if (e == cudaSuccess) e = cudaMemset(m->argmax_scratch, 0, skn_argmax_scratch_bytes(max_batch));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&m->inv_freq, sizeof(double) * (size_t)(head_dim / 2 + 1));
+    if (e == cudaSuccess) {
+        std::vector<double> fr((size_t)head_dim / 2 + 1);
+        for (int i = 0; i < head_dim / 2; ++i) fr[i] = pow((double)rope_theta, -2.0 * (double)i / (double)head_dim);
+        e = cudaMemcpy(m->inv_freq, fr.data(), sizeof(double) * fr.size(), cudaMemcpyHostToDevice);
+    }
     int32_t rc = SKN_OK;
     if (e != cudaSuccess) rc = skn_check_cuda(ctx, e, "decoder activation buffers");
     for (int l = 0; l < n_layers && rc == SKN_OK; ++l) {
@@ -163,6 +170,7 @@ int32_t skn_llama_destroy(skn_llama *m) {
     if (m->ids_out) cudaFree(m->ids_out);
     if (m->len_ptrs) cudaFree(m->len_ptrs);
     if (m->argmax_scratch) cudaFree(m->argmax_scratch);
+    if (m->inv_freq) cudaFree(m->inv_freq);
     for (auto &l : m->layers) {
         if (l.attn_norm) cudaFree(l.attn_norm);
         if (l.ffn_norm) cudaFree(l.ffn_norm);
@@ -343,6 +351,7 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
                 rope.head_dim = D; rope.n_kv_heads = Hkv; rope.capacity = cap; rope.seq0 = 0;
                 rope.len_dev = (const int32_t *)ldev; rope.start_dev = (const int32_t *)sdev;
                 rope.k_cache = (float *)kdev; rope.v_cache = (float *)vdev; rope.theta = m->rope_theta;
+                rope.inv_freq = m->inv_freq;
             }
             {
                 const skn_tensor *ws[3] = {l.wq, l.wk, l.wv};

@@ -704,6 +704,7 @@ skn_matvec_stream(const skn_mv_group grp, int64_t pitch, int K, int nch, int wg,
         return grp.W[t] + local * pitch + (size_t)c * S::CHUNK_BYTES;
     };
 
+    MV_TRACE_VARS;
     MV_STAMP(0);
     // weights never depend on the previous kernel: start streaming them right away, one
     // stage per lane

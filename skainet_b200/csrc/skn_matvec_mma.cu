@@ -44,10 +44,11 @@
 // B operand), NP such pairs share the A fragments, block headers and scale decoding.
 //
 // FEAT selects what is compiled in besides the product and the bias / residual add: 0 nothing, 1 the
-// fused preparations of x (RMSNorm gain, silu(x) * u) and the SwiGLU epilogue, 2 those and the
-// rotary-embedding / cache epilogue, 3 those and the tensor-parallel exchange.  The plain variant
-// is the fastest: the instruction footprint of the unused paths costs instruction-cache misses
-// (15 % on a 4096 x 4096 launch).
+// RMSNorm folded into the preparation of x and the SwiGLU epilogue, 2 the RMSNorm and the
+// rotary-embedding / cache epilogue, 3 all of those, the silu(x) * u preparation and the tensor-parallel
+// exchange.  Code size matters: the kernels of a decoder layer take turns, so every launch starts from a cold
+// instruction cache and fetches its preparation code (run once) from L2; the rare paths (outliers) are out of
+// line for the same reason.  Single-row Q4_K variants: 38 / 50 / 56 / 82 KB.
 template <int FMT, int SPW, int NP, bool ODD, int FEAT>   // format; super-blocks of a tile per compute warp (W = KS / SPW warps); row pairs;
                                                 // ODD: the last pair has one row only (its odd columns are skipped)
 __global__ void __launch_bounds__(MmFmt<FMT>::KS / SPW == 16 ? 544 : (MmFmt<FMT>::KS / SPW == 8 ? 320 : 256),
@@ -61,8 +62,8 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     constexpr int NAMAX = 2 * NP;
     constexpr bool F_PREP = FEAT >= 1, F_ROPE = FEAT >= 2, F_XC = FEAT == 3;
     const float *const f_gain = F_PREP ? grp.norm_gain : nullptr;
-    const float *const f_silu = F_PREP ? grp.silu_u : nullptr;
-    const bool f_swiglu = F_PREP && grp.swiglu;
+    const float *const f_silu = F_XC ? grp.silu_u : nullptr;       // (the rare silu(x) * u preparation rides with the largest variant)
+    const bool f_swiglu = (FEAT == 1 || FEAT == 3) && grp.swiglu;
     const int f_rope_hd = F_ROPE ? grp.rope_hd : 0;
     const int64_t N = grp.n_end[grp.count - 1];
     const int NA = grp.n_act;                   // 1 .. NAMAX activation rows
@@ -105,6 +106,7 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 
     __shared__ int s_anyout;                    // some prepared block of x has outliers (rare): the tile loop looks only then
     if (threadIdx.x == 0) s_anyout = 0;
+    MV_TRACE_VARS;
     MV_STAMP(0);
     if (warp == W && lane < nst) {
         skn_mbar_init(&full[lane], 1);
@@ -149,6 +151,16 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     skn_pdl_launch_dependents();
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
+    // rotary epilogue: positions and ring starts are requested now and used at the very end
+    int rp_pos[NAMAX], rp_start[NAMAX];
+#pragma unroll
+    for (int a = 0; a < NAMAX; ++a) {
+        rp_pos[a] = rp_start[a] = 0;
+        if (f_rope_hd && a < NA) {
+            rp_pos[a] = grp.rope_len[grp.rope_a0 + a];
+            rp_start[a] = grp.rope_start[grp.rope_a0 + a];
+        }
+    }
     // Tensor-parallel consumer: the previous launch of every rank pushed its partial products into
     // this rank's inbox; wait for the peers' flags (bounded), then every load of x adds them up.
     const float *redp = nullptr;
@@ -177,48 +189,62 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
     __shared__ float red[NAMAX][16];
     if (lane < NAMAX) red[lane][warp] = 0.f;
     __syncwarp();
-    // x -> digit planes of K super-chunk kc: a warp takes whole super-blocks, four per round (eight
-    // loads in flight, four independent digitisations for the scheduler to interleave);
+    // x -> digit planes of K super-chunk kc: a warp takes whole super-blocks, two per round (four loads in
+    // flight, two independent digitisations for the scheduler to interleave; four per round made the code 11 KB
+    // longer, and a launch runs this once from a cold instruction cache);
     // unit u = activation row u / nsb, super-block (of the chunk) u % nsb.  The planes of one chunk are
     // resident at a time, so shared memory does not grow with K.
     auto prep_chunk = [&](int kc) {
         int nsbc = nb - kc * MM_KS;
         nsbc = nsbc > MM_KS ? MM_KS : nsbc;
         const int units = NA * nsbc;
-        constexpr int UR = 4;
+        constexpr int UR = 2;
         float sq[NAMAX];
 #pragma unroll
         for (int a = 0; a < NAMAX; ++a) sq[a] = 0.f;
         for (int u0 = warp; u0 < units; u0 += UR * W) {
             float4 v[UR][2];
-            int ua[UR], us[UR];
+            int ua[UR], us[UR], ux[UR];
+            // every load of the round is issued before anything waits for one (the norm's gain included: a load
+            // behind a use of the previous one would cost a trip to L2 per unit)
 #pragma unroll
             for (int h = 0; h < UR; ++h) {
                 const int uu = u0 + h * W;
                 ua[h] = -1;
-                us[h] = 0;
+                us[h] = ux[h] = 0;
                 if (uu < units) {
                     const int a = uu / nsbc, sbl = uu - a * nsbc, sbx = kc * MM_KS + sbl;      // sbx: index in x
                     skn_xform xf{nullptr, f_silu ? f_silu + (size_t)a * K : nullptr, 1.f,
                                  redp ? redp + (size_t)a * K : nullptr, redp ? grp.xc_world : 0, grp.xc_cap,
                                  (redp && grp.xc_wb && blockIdx.x == 0) ? grp.xc_wb + (size_t)a * K : nullptr};
                     const float *xa = x + (size_t)a * K;
-                    float4 r0 = skn_load_x4(xa, sbx * 64 + lane, xf), r1 = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
-                    if (f_gain) {
+                    v[h][0] = skn_load_x4(xa, sbx * 64 + lane, xf);
+                    v[h][1] = skn_load_x4(xa, sbx * 64 + 32 + lane, xf);
+                    ua[h] = a;
+                    us[h] = CHUNKED ? sbl : sbx;      // index among the resident planes
+                    ux[h] = sbx;
+                }
+            }
+            if (f_gain) {
+                float4 gq[UR][2];
+#pragma unroll
+                for (int h = 0; h < UR; ++h) {
+                    gq[h][0] = __ldg(reinterpret_cast<const float4 *>(f_gain) + ux[h] * 64 + lane);
+                    gq[h][1] = __ldg(reinterpret_cast<const float4 *>(f_gain) + ux[h] * 64 + 32 + lane);
+                }
+#pragma unroll
+                for (int h = 0; h < UR; ++h) {
+                    if (ua[h] >= 0) {
+                        float4 &r0 = v[h][0], &r1 = v[h][1];
                         const float e = (r0.x * r0.x + r0.y * r0.y) + (r0.z * r0.z + r0.w * r0.w) + (r1.x * r1.x + r1.y * r1.y) +
                                         (r1.z * r1.z + r1.w * r1.w);
 #pragma unroll
                         for (int k = 0; k < NAMAX; ++k)
-                            if (k == a) sq[k] += e;
-                        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(f_gain) + sbx * 64 + lane);
-                        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(f_gain) + sbx * 64 + 32 + lane);
+                            if (k == ua[h]) sq[k] += e;
+                        const float4 g0 = gq[h][0], g1 = gq[h][1];
                         r0.x *= g0.x; r0.y *= g0.y; r0.z *= g0.z; r0.w *= g0.w;
                         r1.x *= g1.x; r1.y *= g1.y; r1.z *= g1.z; r1.w *= g1.w;
                     }
-                    v[h][0] = r0;
-                    v[h][1] = r1;
-                    ua[h] = a;
-                    us[h] = CHUNKED ? sbl : sbx;      // index among the resident planes
                 }
             }
 #pragma unroll
@@ -578,12 +604,9 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
             for (int a = 0; a < NAMAX; ++a) {
                 if (ocn[a] != 0) {                                       // warp-uniform
                     if (t < ocn[a]) {
-                        const uint32_t e = (uint32_t)(a * nbp + sb0 + sb);
-                        const int k = (int)mm_lds8(oidx_s + 4u * e + (uint32_t)t);
-                        const float xv = mm_lds32f(oval_s + 4u * (MM_MAX_OUT * e + (uint32_t)t)) * inv_dw;
-                        const float wa = mm_weight_at<FMT>(ba, k) * xv, wb = mm_weight_at<FMT>(bb, k) * xv;
-                        if (a & 1) { accB[a >> 1][0] += wa; accB[a >> 1][1] += wb; }
-                        else { accA[a >> 1][0] += wa; accA[a >> 1][1] += wb; }
+                        const float2 wp = mm_outlier_products<FMT>(ba, bb, oidx_s, oval_s, (uint32_t)(a * nbp + sb0 + sb), t, inv_dw);
+                        if (a & 1) { accB[a >> 1][0] += wp.x; accB[a >> 1][1] += wp.y; }
+                        else { accA[a >> 1][0] += wp.x; accA[a >> 1][1] += wp.y; }
                     }
                 }
             }
@@ -669,18 +692,27 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
                     // rotary embedding of the pair (2i, 2i+1) this row belongs to (`up` is the other
                     // row of the pair), k and v straight into the cache
                     const int hd = F_ROPE ? f_rope_hd : 2, seq = grp.rope_a0 + a;
-                    const int pos = grp.rope_len[seq];
+                    int pos = 0, ring0 = 0;
+#pragma unroll
+                    for (int k = 0; k < NAMAX; ++k)
+                        if (k == a) { pos = rp_pos[k]; ring0 = rp_start[k]; }
                     // a full cache (a replayed step the host did not count): nothing is overwritten
                     const bool room = pos < grp.rope_cap;
                     if (!room) atomicExch(status, SKN_ERR_SHAPE);
-                    const int slot = (grp.rope_start[seq] + pos) % grp.rope_cap;
+                    const int slot = (ring0 + pos) % grp.rope_cap;
                     const int h = (int)(local / hd), dd = (int)(local % hd);
                     float o = s;
                     if (tt < 2) {
-                        const double ang = (double)pos * exp2(-grp.rope_log2theta * (2.0 * (double)(dd >> 1) / (double)hd));
-                        double sd, cd;
-                        sincos(ang, &sd, &cd);
-                        const float sn = (float)sd, cs = (float)cd;
+                        // the angle in double (positions reach thousands of radians), reduced to [-pi, pi] with a
+                        // two-term 2 pi, then the fp32 functions: a handful of fp64 instructions instead of a
+                        // double-precision sincos
+                        const double f = grp.rope_inv_freq ? grp.rope_inv_freq[dd >> 1]
+                                                           : exp2(-grp.rope_log2theta * (2.0 * (double)(dd >> 1) / (double)hd));
+                        const double ang = (double)pos * f;
+                        const double turns = rint(ang * 0.15915494309189535);
+                        const float red_ang = (float)fma(-turns, 2.4492935982947064e-16, fma(-turns, 6.283185307179586, ang));
+                        float sn, cs;
+                        sincosf(red_ang, &sn, &cs);
                         o = (dd & 1) ? (up * sn + s * cs) : (s * cs - up * sn);
                     }
                     if (tt == 0) grp.y[0][(size_t)a * grp.ystride[0] + local] = o;
@@ -851,6 +883,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
         grp.rope_hd = rope->head_dim; grp.rope_cap = rope->capacity; grp.rope_nkv = rope->n_kv_heads; grp.rope_a0 = rope->seq0;
         grp.rope_len = rope->len_dev; grp.rope_start = rope->start_dev; grp.rope_kc = rope->k_cache; grp.rope_vc = rope->v_cache;
         grp.rope_log2theta = log2((double)rope->theta);
+        grp.rope_inv_freq = rope->inv_freq;
     }
     if (xc && xc->view.world > 1) {
         if (xc->push && (swiglu || n != 1)) return false;
@@ -874,7 +907,7 @@ bool skn_mma_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const fl
     grp.count = n;
     if (n_act < 1 || n_act > mm_max_acts(ctx, fmt, tot, w[0]->n_cols)) return false;
     skn_mv_plan pl = skn_mv_plan{0, 0, 0, 0, 0, 0};
-    const int feat = (xc && xc->view.world > 1) ? 3 : (rope ? 2 : ((norm_gain || silu_u || swiglu) ? 1 : 0));
+    const int feat = ((xc && xc->view.world > 1) || silu_u) ? 3 : (rope ? 2 : ((norm_gain || swiglu) ? 1 : 0));
     const int32_t key_type = 1000 + 256 * feat + 32 * n_act + w[0]->type;       // distinct from the CUDA-core kernels' plans
     for (int i = 0; i < ctx->n_group_plans; ++i) {
         const skn_group_plan &c = ctx->group_plans[i];

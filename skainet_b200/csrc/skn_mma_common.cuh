@@ -128,6 +128,89 @@ __device__ __forceinline__ void mm_store_planes(const uint32_t (&D)[8], uint8_t 
     }
 }
 
+// Group sums of one super-block (lane: elements 4*lane.. and 128 + 4*lane..) into xsum, their total returned in every
+// lane.  XS16: sixteen 16-element sums instead of the eight 32-element ones.
+template <bool XS16>
+static __device__ __forceinline__ float mm_group_sums(const float (&in)[8], int sbi, int lane, float *xsum) {
+    float s0 = (in[0] + in[1]) + (in[2] + in[3]), s1 = (in[4] + in[5]) + (in[6] + in[7]);
+    if constexpr (XS16) {
+#pragma unroll
+        for (int o = 2; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        }
+        if ((lane & 3) == 0) {
+            xsum[sbi * 16 + (lane >> 2)] = s0;
+            xsum[sbi * 16 + 8 + (lane >> 2)] = s1;
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
+    } else {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        }
+        if ((lane & 7) == 0) {
+            xsum[sbi * 8 + (lane >> 3)] = s0;
+            xsum[sbi * 8 + 4 + (lane >> 3)] = s1;
+        }
+    }
+    float tot = s0 + s1;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 8);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 16);
+    return tot;
+}
+
+// The rare half of mm_digitize, kept out of line (the preparation is unrolled four super-blocks deep, and a launch
+// runs it once from a cold instruction cache: its size is paid in instruction fetches).  Called when at most four
+// lanes hold anything within 2^-MM_OUT_BAND of the block's largest: the exact test on the elements; if it passes,
+// the outliers go to the block's record, leave `in`, and the group sums are formed again without them.
+struct mm_outlier_result {
+    float in[8];
+    float tot;
+    int n_out, ES;
+};
+template <bool XS16>
+static __device__ __noinline__ mm_outlier_result mm_take_outliers(float i0, float i1, float i2, float i3, float i4, float i5, float i6,
+                                                                  float i7, float tot, int E, int sbi, int lane, float *xsum,
+                                                                  float *oval, uint32_t *oidx, int *any_out) {
+    mm_outlier_result r;
+    r.in[0] = i0; r.in[1] = i1; r.in[2] = i2; r.in[3] = i3; r.in[4] = i4; r.in[5] = i5; r.in[6] = i6; r.in[7] = i7;
+    r.tot = tot; r.n_out = 0; r.ES = E;
+    const uint32_t thr = (uint32_t)(E - MM_OUT_BAND) << 23;
+    uint32_t big[8], mb = 0;
+    int total = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t a = __float_as_uint(r.in[i]) & 0x7FFFFFFFu;
+        big[i] = __ballot_sync(0xffffffffu, a >= thr);
+        total += __popc(big[i]);
+        mb = max(mb, a < thr ? a : 0u);
+    }
+    mb = __reduce_max_sync(0xffffffffu, mb);    // the largest of the small ones
+    int EB = (int)(mb >> 23);
+    EB = EB < 30 ? 30 : EB;
+    if (total <= MM_MAX_OUT && mb != 0u && E - EB >= MM_OUT_GAP) {      // warp-uniform
+        int before = 0;                     // large ones in lower (element, lane) order
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((big[i] >> lane) & 1u) {
+                const int pos = before + __popc(big[i] & ((1u << lane) - 1u));
+                oval[4 * sbi + pos] = r.in[i];
+                reinterpret_cast<uint8_t *>(oidx + sbi)[pos] = (uint8_t)(i < 4 ? 4 * lane + i : 128 + 4 * lane + (i - 4));
+                r.in[i] = 0.f;              // out of the planes and of the sums
+            }
+            before += __popc(big[i]);
+        }
+        r.n_out = total;
+        r.ES = EB;
+        if (any_out && lane == 0) *any_out = 1;
+        r.tot = mm_group_sums<XS16>(r.in, sbi, lane, xsum);
+    }
+    return r;
+}
+
 // One super-block (256 activations, two float4 per lane: elements 4*lane.. and 128 + 4*lane..)
 // -> four digit planes (byte k of a plane = that digit of activation k), the scale 2^(e-29)
 // (NaN when the block holds a NaN or an infinity), the eight 32-element sums (outliers excluded: their whole
@@ -142,39 +225,8 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
     float in[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     const float mx = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                            fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-    // group sums and their total (the group sums go to xsum); run once up front, so that their shuffles overlap the
-    // maximum's reduction, and once more in the rare case that outliers are taken out
-    float tot;
-    auto sums = [&]() {
-        float s0 = (in[0] + in[1]) + (in[2] + in[3]), s1 = (in[4] + in[5]) + (in[6] + in[7]);
-        if constexpr (XS16) {
-#pragma unroll
-            for (int o = 2; o > 0; o >>= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            if ((lane & 3) == 0) {
-                xsum[sbi * 16 + (lane >> 2)] = s0;
-                xsum[sbi * 16 + 8 + (lane >> 2)] = s1;
-            }
-            s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
-        } else {
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            if ((lane & 7) == 0) {
-                xsum[sbi * 8 + (lane >> 3)] = s0;
-                xsum[sbi * 8 + 4 + (lane >> 3)] = s1;
-            }
-        }
-        tot = s0 + s1;
-        tot += __shfl_xor_sync(0xffffffffu, tot, 8);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 16);
-    };
-    sums();
+    // the group sums first, so that their shuffles overlap the maximum's reduction
+    float tot = mm_group_sums<XS16>(in, sbi, lane, xsum);
     // mx >= 0 (or NaN-free by fmaxf): its bit pattern orders like the value, one integer reduction
     const uint32_t mxb = __reduce_max_sync(0xffffffffu, __float_as_uint(mx));
     int E = (int)(mxb >> 23);
@@ -182,38 +234,14 @@ static __device__ __forceinline__ void mm_digitize(const float4 v0, const float4
     int ES = E;                                 // exponent the planes are scaled by
     int n_out = 0;
     // Outliers?  Only when at most four lanes hold anything within 2^-6 of the block's largest (ordinary data
-    // fails this at once: one comparison and a vote); then the exact test on the elements.
+    // fails this at once: one comparison and a vote).
     const uint32_t thr = (uint32_t)(E - MM_OUT_BAND) << 23;
     if (__popc(__ballot_sync(0xffffffffu, __float_as_uint(mx) >= thr)) <= MM_MAX_OUT && mxb < 0x7F800000u) {
-        uint32_t big[8], mb = 0;
-        int total = 0;
+        const mm_outlier_result r = mm_take_outliers<XS16>(in[0], in[1], in[2], in[3], in[4], in[5], in[6], in[7], tot, E, sbi, lane,
+                                                           xsum, oval, oidx, any_out);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t a = __float_as_uint(in[i]) & 0x7FFFFFFFu;
-            big[i] = __ballot_sync(0xffffffffu, a >= thr);
-            total += __popc(big[i]);
-            mb = max(mb, a < thr ? a : 0u);
-        }
-        mb = __reduce_max_sync(0xffffffffu, mb);    // the largest of the small ones
-        int EB = (int)(mb >> 23);
-        EB = EB < 30 ? 30 : EB;
-        if (total <= MM_MAX_OUT && mb != 0u && E - EB >= MM_OUT_GAP) {      // warp-uniform
-            int before = 0;                     // large ones in lower (element, lane) order
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if ((big[i] >> lane) & 1u) {
-                    const int pos = before + __popc(big[i] & ((1u << lane) - 1u));
-                    oval[4 * sbi + pos] = in[i];
-                    reinterpret_cast<uint8_t *>(oidx + sbi)[pos] = (uint8_t)(i < 4 ? 4 * lane + i : 128 + 4 * lane + (i - 4));
-                    in[i] = 0.f;                // out of the planes and of the sums
-                }
-                before += __popc(big[i]);
-            }
-            n_out = total;
-            ES = EB;
-            if (any_out && lane == 0) *any_out = 1;
-            sums();
-        }
+        for (int i = 0; i < 8; ++i) in[i] = r.in[i];
+        tot = r.tot; n_out = r.n_out; ES = r.ES;
     }
     const float mul = __int_as_float((283 - ES) << 23);           // 2^(29-e)
     uint32_t D[8];
@@ -273,3 +301,12 @@ __device__ __forceinline__ float mm_weight_at<3>(uint32_t blk, int k) {       //
     return (mm_lds_half(blk + 208) * (float)sc) * (float)(q - 32);
 }
 
+// Outlier number t of block e times the weights of rows g (block at `ba`) and g + 8 (`bb`), scaled by inv_dw; out of
+// line: rare, and the tile loop is better off without its code.
+template <int FMT>
+static __device__ __noinline__ float2 mm_outlier_products(uint32_t ba, uint32_t bb, uint32_t oidx_s, uint32_t oval_s, uint32_t e, int t,
+                                                          float inv_dw) {
+    const int k = (int)mm_lds8(oidx_s + 4u * e + (uint32_t)t);
+    const float xv = mm_lds32f(oval_s + 4u * (MM_MAX_OUT * e + (uint32_t)t)) * inv_dw;
+    return make_float2(mm_weight_at<FMT>(ba, k) * xv, mm_weight_at<FMT>(bb, k) * xv);
+}

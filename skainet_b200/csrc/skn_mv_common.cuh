@@ -5,18 +5,35 @@
 
 #include <stdlib.h>
 
-// SKN_MV_TRACE builds record per-CTA phase timestamps (SM clock and global timer) after the
+// SKN_TUNING builds record per-CTA phase timestamps (SM clock and global timer) after the
 // status word; used only for profiling experiments, never in the shipped library.
-#ifdef SKN_MV_TRACE
+#ifdef SKN_TUNING
+#define MV_TRACE_VARS unsigned mv_seq = 0
+// (and, for CTA 0, a timeline entry per launch: {launch number, start, dependency wait done, end} in global-timer ns)
 #define MV_STAMP(k)                                                                        \
     do {                                                                                   \
         if (threadIdx.x == 0) {                                                            \
             long long *tr = reinterpret_cast<long long *>(status) + 16 + blockIdx.x * 16;  \
-            tr[2 * (k)] = clock64();                                                       \
-            tr[2 * (k) + 1] = (long long)skn_globaltimer_ns();                             \
+            const long long now_ns = (long long)skn_globaltimer_ns();                      \
+            if (blockIdx.x == 0) {                                                         \
+                long long *tl = reinterpret_cast<long long *>(status) + 2560;              \
+                if ((k) == 0) {                                                            \
+                    const unsigned sq = atomicAdd(reinterpret_cast<unsigned *>(status) + 2, 1u); \
+                    mv_seq = sq;                                                           \
+                    tl[(sq % 192u) * 8 + 0] = (long long)sq;                               \
+                    tl[(sq % 192u) * 8 + 1] = now_ns;                                      \
+                } else if ((k) >= 2) {                                                     \
+                    tl[(mv_seq % 192u) * 8 + (k)] = now_ns;                              \
+                }                                                                          \
+            }                                                                              \
+            if ((k) != 1) {                                                                \
+                tr[2 * (k)] = clock64();                                                   \
+                tr[2 * (k) + 1] = now_ns;                                                  \
+            }                                                                              \
         }                                                                                  \
     } while (0)
 #else
+#define MV_TRACE_VARS
 #define MV_STAMP(k) do {} while (0)
 #endif
 
@@ -105,6 +122,7 @@ struct skn_mv_group {
     const int32_t *rope_len, *rope_start;
     float *rope_kc, *rope_vc;
     double rope_log2theta;
+    const double *rope_inv_freq;
     int swiglu;             // tensor-core kernel only: W[0] = gate, W[1] = up (equal shapes); rows are
                             // interleaved (virtual row v = tensor v & 1, row v >> 1) so that a CTA holds
                             // both products of a column and writes y[0][r] = silu(gate . x) * (up . x)
@@ -125,8 +143,5 @@ __device__ __forceinline__ int skn_group_row(const skn_mv_group &grp, int64_t v,
     return skn_group_find(grp, v, local);
 }
 
-static inline int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
-}
+static inline int env_int(const char *name, int dflt) { return skn_tune_int(name, dflt); }
 
