@@ -149,6 +149,10 @@ skn_matvec_mma(const skn_mv_group grp, int64_t pitch, int K, int nst, const floa
 
     // ---- compute warps ----
     skn_pdl_launch_dependents();
+    // the norm's gain is a parameter, not a product of the launch before: asked into L2 ahead of the wait (last used
+    // a whole step ago, it comes from HBM, behind this launch's own weight stream if requested any later)
+    if (F_PREP && f_gain)
+        for (int i = (int)threadIdx.x * 32; i < K; i += W * 32 * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(f_gain + i));
     if (!relaxed) skn_pdl_wait();
     MV_STAMP(2);
     // rotary epilogue: positions and ring starts are requested now and used at the very end
