@@ -572,7 +572,7 @@ def run_attn(args):
     ctx.set_stream(stream.cuda_stream)
     g = synth.rng(3)
     kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype=args.kv_dtype)
-    eb = 2 if args.kv_dtype == "f16" else 4             # bytes per cached element
+    eb = {"f32": 4, "f16": 2, "q8_0": 1.0625}[args.kv_dtype]             # bytes per cached element
     lens = g.integers(1024, 4097, size=B).astype(np.int32)
     kc = g.standard_normal((B, Hkv, T, D), dtype=np.float32)
     kv.load(kc, kc[:, ::-1].copy(), lens)
@@ -606,8 +606,9 @@ def run_attn(args):
         "metric": "attn_decode_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "cfg4: GQA decode attention B=8, 32q/8kv heads, D=128, ctx 1024..4096 (+1 per step)",
-                   "kv_cache": args.kv_dtype + (" (the configuration's cache)" if args.kv_dtype == "f32" else
-                                                " (beyond the configuration: K and V rounded to fp16 once, arithmetic fp32)"),
+                   "kv_cache": args.kv_dtype + {"f32": " (the configuration's cache)",
+                                                "f16": " (beyond the configuration: K and V rounded to fp16 once, arithmetic fp32)",
+                                                "q8_0": " (beyond the configuration: K and V in Q8_0-style blocks, arithmetic fp32)"}[args.kv_dtype],
                    "mean_len": mean_len, "steps_per_s": 1e3 / ms},
         "gpu_launches": 3 * steps,
         "roofline": {"bound": "hbm", "kernel": "skn_attn_stream_kernel + merge + append", "achieved": gbs, "peak": peak, "peak_kind": kind,
@@ -815,7 +816,7 @@ def main():
                     help="relaxed: the layers of a step are declared independent (SKN_OPT_RELAXED_ORDER) and "
                          "may overlap; stream: each launch waits for the one before it")
     ap.add_argument("--batch", type=int, default=1, help="decode workload: sequences per step")
-    ap.add_argument("--kv-dtype", default="f32", choices=["f32", "f16"],
+    ap.add_argument("--kv-dtype", default="f32", choices=["f32", "f16", "q8_0"],
                     help="attn / decode workloads: element type of the KV cache (f32 is what the configurations specify)")
     ap.add_argument("--fused-exchange", default="auto", choices=["auto", "on", "off"],
                     help="tensor-parallel decode: push partial sums from the matvec epilogue (SKN_OPT_FUSED_EXCHANGE); "

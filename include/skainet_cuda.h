@@ -107,8 +107,10 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
  * launches on 2 GPUs (every CTA of the consuming launch repeats the sum), faster on 4. */
 #define SKN_OPT_FUSED_EXCHANGE 3
 /* SKN_OPT_KV_F16 (default 0): with value 1, decoders created afterwards (skn_llama_create, skn_llama_create_tp)
- * keep their KV caches in fp16 (see skn_kv_create_typed). */
+ * keep their KV caches in fp16 (see skn_kv_create_typed).  SKN_OPT_KV_DTYPE is the general form: its value is
+ * the SKN_KV_* element type of the caches of decoders created afterwards. */
 #define SKN_OPT_KV_F16 4
+#define SKN_OPT_KV_DTYPE 6
 /* SKN_OPT_WAIT_LIMIT_MS (default 0 = 2000): how long a kernel of the inter-GPU exchange waits for its
  * peers' flags before it gives up, records SKN_ERR_TIMEOUT and returns (1 .. 600000 milliseconds). */
 #define SKN_OPT_WAIT_LIMIT_MS 5
@@ -224,10 +226,16 @@ int32_t skn_kv_create(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t h
                       skn_kvcache **out);
 /* The same cache with a chosen element type.  SKN_KV_F16 stores K and V as IEEE fp16 (rounded to nearest
  * even on their way in, widened on their way out; every sum stays fp32), which halves the bytes attention
- * reads per cached token.  Every entry point below keeps its fp32 interface: appends, loads, gathers, q
- * and the attention output are fp32 whatever the cache holds.  SKN_ERR_TYPE for any other value. */
+ * reads per cached token.  SKN_KV_Q8_0 stores them the way GGUF's Q8_0 stores weights
+ * (gguf/src/commonMain/kotlin/sk/ai/net/gguf/Constants.kt:60: 32 values per block, one fp16 scale): per 32 head
+ * dims d = max|x| / 127 and int8 q = round(x / d), read back as q * fp16(d) -- 1.0625 bytes per value instead of
+ * four.  In memory the quants and the scales are two planes of one allocation ([rows][head_dim] int8, then
+ * [rows][head_dim / 32] fp16, rows = batch * n_kv_heads * capacity), not interleaved 34-byte blocks.
+ * Every entry point below keeps its fp32 interface: appends, loads, gathers, q and the attention output are
+ * fp32 whatever the cache holds.  SKN_ERR_TYPE for any other value. */
 #define SKN_KV_F32 0
 #define SKN_KV_F16 1
+#define SKN_KV_Q8_0 2
 int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int32_t head_dim, int32_t capacity,
                             int32_t kv_dtype, skn_kvcache **out);
 /* element type of the cache (what k_dev / v_dev of skn_kv_info point at) */

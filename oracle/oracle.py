@@ -201,6 +201,30 @@ def np_dequant_q8_0(raw: np.ndarray) -> np.ndarray:
     return (q * d).reshape(-1)
 
 
+def np_quantize_q8_0(x: np.ndarray):
+    """Q8_0 quantisation of fp32 values in blocks of 32 along the last axis, as the KV cache of type SKN_KV_Q8_0
+    stores them.  The reference has no quantiser (its gguf module only reads: gguf/src/commonMain/kotlin/sk/ai/net/
+    gguf/Quants.kt); this restates gguf-py 0.19.0 `quants.py`, Q8_0.quantize_blocks (itself bit-exact with ggml's
+    quantize_row_q8_0_ref): d = max|x| / 127 in fp32, id = 1 / d (0 for an all-zero block), q = x * id rounded
+    half away from zero, d kept as fp16.  Returns (q int8 [..., n], d float16 [..., n / 32])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.shape[-1] % 32 == 0
+    blocks = x.reshape(-1, 32)
+    d = (np.abs(blocks).max(axis=1, keepdims=True) / np.float32(127)).astype(np.float32)
+    with np.errstate(all="ignore"):         # (a subnormal scale has an infinite inverse, as in the original)
+        inv = np.where(d == 0, np.float32(0), np.float32(1) / d).astype(np.float32)
+        t = (blocks * inv).astype(np.float32)
+        q = (np.sign(t) * np.floor(np.abs(t) + np.float32(0.5))).astype(np.int8)      # roundf: half away from zero
+        dh = d.astype(np.float16)
+    return q.reshape(x.shape), dh.reshape(x.shape[:-1] + (x.shape[-1] // 32,))
+
+
+def np_q8_0_roundtrip(x: np.ndarray) -> np.ndarray:
+    """What a Q8_0 cache hands back for x: q * fp16(d), in fp32 (gguf-py Q8_0.dequantize_blocks)."""
+    q, dh = np_quantize_q8_0(x)
+    return (q.reshape(-1, 32).astype(np.float32) * dh.reshape(-1, 1).astype(np.float32)).reshape(q.shape)
+
+
 def np_q4k_scales(s: np.ndarray):
     """s: [n,12] uint8 -> (sc[n,8], mn[n,8]) uint8."""
     sc = np.empty((s.shape[0], 8), dtype=np.uint8)

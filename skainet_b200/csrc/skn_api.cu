@@ -144,7 +144,11 @@ int32_t skn_ctx_set_option(skn_ctx *ctx, int32_t option, int64_t value) {
         ctx->prefill_min_m = (int)value;
         return SKN_OK;
     case SKN_OPT_FUSED_EXCHANGE: ctx->fused_exchange = value < 0 ? -1 : (value ? 1 : 0); return SKN_OK;
-    case SKN_OPT_KV_F16: ctx->kv_f16 = value ? 1 : 0; return SKN_OK;
+    case SKN_OPT_KV_F16: ctx->kv_f16 = value ? SKN_KV_F16 : SKN_KV_F32; return SKN_OK;
+    case SKN_OPT_KV_DTYPE:
+        if (value != SKN_KV_F32 && value != SKN_KV_F16 && value != SKN_KV_Q8_0) return skn_fail(ctx, SKN_ERR_TYPE, "cache element type %lld is none of fp32, fp16, Q8_0", (long long)value);
+        ctx->kv_f16 = (int)value;
+        return SKN_OK;
     case SKN_OPT_WAIT_LIMIT_MS: {
         if (value < 0 || value > 600000) return skn_fail(ctx, SKN_ERR_ARG, "wait limit outside [0, 600000] ms");
         const int32_t ms = (int32_t)value;

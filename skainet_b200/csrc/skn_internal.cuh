@@ -39,7 +39,7 @@ struct skn_ctx {
     int relaxed_order;          // SKN_OPT_RELAXED_ORDER
     int prefill_min_m;          // SKN_OPT_PREFILL_MIN_M: batch size from which the tensor-core path runs
     int fused_exchange;         // SKN_OPT_FUSED_EXCHANGE
-    int kv_f16;                 // SKN_OPT_KV_F16
+    int kv_f16;                 // SKN_OPT_KV_F16 / SKN_OPT_KV_DTYPE: SKN_KV_* element type of the caches of new decoders
     int32_t *d_status;          // device status word written by bounded waits
     int32_t *h_status;          // pinned mirror
     // Small results of the host-pointer calls sit directly BELOW the status word, on the device and in the

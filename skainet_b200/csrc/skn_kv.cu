@@ -34,7 +34,7 @@ struct skn_kvcache {
     uint32_t magic;
     skn_ctx *ctx;
     int32_t batch, n_kv_heads, head_dim, capacity;
-    int32_t dtype;               // SKN_KV_F32 or SKN_KV_F16: element type of d_k / d_v
+    int32_t dtype;               // SKN_KV_F32, SKN_KV_F16 or SKN_KV_Q8_0: element type of d_k / d_v
     void *d_k, *d_v;
     int32_t *d_len, *d_start;
     unsigned *d_tickets;         // [batch][n_kv_heads], zero between launches: split-attention merge tickets
@@ -94,6 +94,99 @@ template <class CT, bool GLOBAL> struct KvLoad<CT, 2, GLOBAL> {
     }
 };
 
+// Q8_0-style cache: every 32 consecutive head dims of a cached row share one fp16 scale d = max|x| / 127 and are
+// kept as int8 q = round(x / d) (ggml's quantize_row_q8_0: the division by the fp32 d, rounding half away from
+// zero; the value read back is q * fp16(d)).  Unlike the 34-byte GGUF block the two parts live in two planes of
+// the same allocation -- [rows][D] int8, then [rows][D / 32] fp16, rows = batch * kv heads * capacity -- so a
+// row's quants stay 16-byte aligned and a lane's four dims are one 32-bit load.
+struct skn_q8 { int8_t q; };
+template <class CT> struct KvIsQ8 { static constexpr bool value = false; };
+template <> struct KvIsQ8<skn_q8> { static constexpr bool value = true; };
+
+// scale plane of a cache tensor with `rows` rows (NULL for the unquantised element types)
+template <class CT>
+__device__ __forceinline__ __half *kv_scale_plane(CT *plane, size_t rows, int D) {
+    if constexpr (KvIsQ8<CT>::value) return reinterpret_cast<__half *>(reinterpret_cast<int8_t *>(plane) + rows * (size_t)D);
+    else return nullptr;
+}
+template <class CT>
+__device__ __forceinline__ const __half *kv_scale_plane(const CT *plane, size_t rows, int D) {
+    return kv_scale_plane(const_cast<CT *>(plane), rows, D);
+}
+__device__ __forceinline__ int kv_q8_quant(float x, float id) { return (int)roundf(x * id); }
+
+// Four consecutive dims d .. d + 3 of cache row `row`.  Quantised caches: the eight lanes (lane & ~7) .. + 7 of the
+// warp hold the eight quads of one 32-dim block and must call this together.
+template <class CT>
+__device__ __forceinline__ void kv_store4(CT *plane, __half *scales, size_t row, int D, int d, float4 v) {
+    if constexpr (KvIsQ8<CT>::value) {
+        const unsigned lane = threadIdx.x & 31u, mask = 0xFFu << (lane & 24u);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, o));
+        const float dq = amax / 127.f, id = dq != 0.f ? 1.f / dq : 0.f;
+        const uint32_t pk = (uint32_t)(kv_q8_quant(v.x, id) & 255) | ((uint32_t)(kv_q8_quant(v.y, id) & 255) << 8) |
+                            ((uint32_t)(kv_q8_quant(v.z, id) & 255) << 16) | ((uint32_t)(kv_q8_quant(v.w, id) & 255) << 24);
+        *reinterpret_cast<uint32_t *>(reinterpret_cast<int8_t *>(plane) + row * (size_t)D + d) = pk;
+        if ((lane & 7u) == 0) scales[row * (size_t)(D / 32) + (d >> 5)] = __float2half_rn(dq);
+    } else {
+        KvElem<CT>::st4(plane + row * (size_t)D + d, v);
+    }
+}
+// Two consecutive dims (a rotated pair).  Quantised caches: the sixteen lanes (lane & ~15) .. + 15 hold one block.
+template <class CT>
+__device__ __forceinline__ void kv_store2(CT *plane, __half *scales, size_t row, int D, int d, float2 v) {
+    if constexpr (KvIsQ8<CT>::value) {
+        const unsigned lane = threadIdx.x & 31u, mask = 0xFFFFu << (lane & 16u);
+        float amax = fmaxf(fabsf(v.x), fabsf(v.y));
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, o));
+        const float dq = amax / 127.f, id = dq != 0.f ? 1.f / dq : 0.f;
+        const unsigned short pk = (unsigned short)((kv_q8_quant(v.x, id) & 255) | ((kv_q8_quant(v.y, id) & 255) << 8));
+        *reinterpret_cast<unsigned short *>(reinterpret_cast<int8_t *>(plane) + row * (size_t)D + d) = pk;
+        if ((lane & 15u) == 0) scales[row * (size_t)(D / 32) + (d >> 5)] = __float2half_rn(dq);
+    } else {
+        KvElem<CT>::st2(plane + row * (size_t)D + d, v);
+    }
+}
+template <class CT>
+__device__ __forceinline__ float4 kv_load4(const CT *plane, const __half *scales, size_t row, int D, int d) {
+    if constexpr (KvIsQ8<CT>::value) {
+        const uint32_t pk = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const int8_t *>(plane) + row * (size_t)D + d);
+        const float sc = __half2float(scales[row * (size_t)(D / 32) + (d >> 5)]);
+        return make_float4((float)(int8_t)(pk & 255u) * sc, (float)(int8_t)((pk >> 8) & 255u) * sc,
+                           (float)(int8_t)((pk >> 16) & 255u) * sc, (float)(int8_t)(pk >> 24) * sc);
+    } else {
+        return KvElem<CT>::ld4(plane + row * (size_t)D + d);
+    }
+}
+
+// The attention kernels' view of one (sequence, kv head): VEC dims per lane of the row in ring slot `slot`.
+template <class CT, int D, int VEC> struct KvHeadReader {
+    const CT *base;
+    const __half *sc;
+    __device__ __forceinline__ KvHeadReader(const CT *plane, size_t rows, size_t head_row0, int lane)
+        : base(plane + head_row0 * D + lane * VEC), sc(nullptr) {
+        if constexpr (KvIsQ8<CT>::value) sc = kv_scale_plane(plane, rows, D) + head_row0 * (D / 32) + ((lane * VEC) >> 5);
+    }
+    __device__ __forceinline__ void ld(int slot, float (&r)[VEC]) const {
+        if constexpr (KvIsQ8<CT>::value) {
+            const float s = __half2float(__ldg(sc + (size_t)slot * (D / 32)));
+            const int8_t *p = reinterpret_cast<const int8_t *>(base) + (size_t)slot * D;
+            if constexpr (VEC == 4) {
+                const uint32_t pk = __ldg(reinterpret_cast<const uint32_t *>(p));
+                r[0] = (float)(int8_t)(pk & 255u) * s; r[1] = (float)(int8_t)((pk >> 8) & 255u) * s;
+                r[2] = (float)(int8_t)((pk >> 16) & 255u) * s; r[3] = (float)(int8_t)(pk >> 24) * s;
+            } else {
+                const unsigned short pk = __ldg(reinterpret_cast<const unsigned short *>(p));
+                r[0] = (float)(int8_t)(pk & 255u) * s; r[1] = (float)(int8_t)(pk >> 8) * s;
+            }
+        } else {
+            KvLoad<CT, VEC, true>::ld(base + (size_t)slot * D, r);
+        }
+    }
+};
+
 // ----------------------------------------------------------------------------------------
 template <class CT>
 __global__ void skn_kv_append_kernel(CT *__restrict__ kc, CT *__restrict__ vc, int32_t *__restrict__ len,
@@ -103,12 +196,14 @@ __global__ void skn_kv_append_kernel(CT *__restrict__ kc, CT *__restrict__ vc, i
     const int L = len[b], s0 = start[b];
     const int slot = (L < cap) ? (s0 + L) % cap : s0;   // full ring: overwrite the oldest token
     const int n4 = Hkv * D / 4;
+    const size_t rows = (size_t)gridDim.x * Hkv * cap;
+    __half *ks = kv_scale_plane(kc, rows, D), *vs = kv_scale_plane(vc, rows, D);
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
         const int h = (i * 4) / D, d = (i * 4) % D;
-        const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t dst = ((size_t)b * Hkv + h) * cap + slot;
         const size_t src = ((size_t)b * Hkv + h) * D + d;
-        KvElem<CT>::st4(kc + dst, *reinterpret_cast<const float4 *>(k_new + src));
-        KvElem<CT>::st4(vc + dst, *reinterpret_cast<const float4 *>(v_new + src));
+        kv_store4(kc, ks, dst, D, d, *reinterpret_cast<const float4 *>(k_new + src));
+        kv_store4(vc, vs, dst, D, d, *reinterpret_cast<const float4 *>(v_new + src));
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -127,12 +222,14 @@ __global__ void skn_kv_append_many_kernel(CT *__restrict__ kc, CT *__restrict__ 
     const int b = blockIdx.y, t = blockIdx.x;
     const int slot = (start[b] + len[b] + t) % cap;
     const int n4 = Hkv * D / 4;
+    const size_t rows = (size_t)gridDim.y * Hkv * cap;
+    __half *ks = kv_scale_plane(kc, rows, D), *vs = kv_scale_plane(vc, rows, D);
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
         const int h = (i * 4) / D, d = (i * 4) % D;
-        const size_t dst = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t dst = ((size_t)b * Hkv + h) * cap + slot;
         const size_t src = (((size_t)b * T + t) * Hkv + h) * D + d;
-        KvElem<CT>::st4(kc + dst, *reinterpret_cast<const float4 *>(k_new + src));
-        KvElem<CT>::st4(vc + dst, *reinterpret_cast<const float4 *>(v_new + src));
+        kv_store4(kc, ks, dst, D, d, *reinterpret_cast<const float4 *>(k_new + src));
+        kv_store4(vc, vs, dst, D, d, *reinterpret_cast<const float4 *>(v_new + src));
     }
 }
 
@@ -163,11 +260,12 @@ skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, c
     const int slot = (start[b] + pos) % cap;
     const int half = D / 2;
     const size_t row = (size_t)b * T + t;
+    const size_t rows = (size_t)gridDim.z * Hkv * cap;
     if (blockIdx.x == gridDim.x - 1) {
+        __half *vs = kv_scale_plane(vc, rows, D);
         for (int i = threadIdx.x; i < Hkv * D / 4; i += blockDim.x) {
             const int h = (i * 4) / D, d = (i * 4) % D;
-            KvElem<CT>::st4(vc + (((size_t)b * Hkv + h) * cap + slot) * D + d,
-                            *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d));
+            kv_store4(vc, vs, ((size_t)b * Hkv + h) * cap + slot, D, d, *reinterpret_cast<const float4 *>(v_new + (row * Hkv + h) * D + d));
         }
         return;
     }
@@ -185,7 +283,9 @@ skn_rope_append_kernel(float *__restrict__ q, const float *__restrict__ k_new, c
     } else {
         const int hk = h - Hq;
         const float2 a = reinterpret_cast<const float2 *>(k_new + (row * Hkv + hk) * D)[p];
-        KvElem<CT>::st2(kc + (((size_t)b * Hkv + hk) * cap + slot) * D + 2 * p, make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs));
+        // (a block's sixteen pairs sit in sixteen consecutive threads: D / 2 is a multiple of 16 and so is the early exit above)
+        kv_store2(kc, kv_scale_plane(kc, rows, D), ((size_t)b * Hkv + hk) * cap + slot, D, 2 * p,
+                  make_float2(a.x * cs - a.y * sn, a.x * sn + a.y * cs));
     }
 }
 
@@ -201,22 +301,27 @@ __global__ void skn_kv_advance_all_kernel(int32_t *const *__restrict__ lens, int
     }
 }
 
-// dense fp32 [rows][tokens][D] -> the first `tokens` slots of every (sequence, kv head) of an fp16 cache
-__global__ void skn_kv_load_half_kernel(const float *__restrict__ src, __half *__restrict__ dst, int64_t rows, int tokens,
+// dense fp32 [rows][tokens][D] -> the first `tokens` slots of every (sequence, kv head) of an fp16 or quantised cache
+// (total is a multiple of 8 and the stride of 32: the lanes of a block stay together)
+template <class CT>
+__global__ void skn_kv_load_conv_kernel(const float *__restrict__ src, CT *__restrict__ dst, int64_t rows, int tokens,
                                         int D, int cap) {
     const int64_t per_row = (int64_t)tokens * D / 4, total = rows * per_row;
+    __half *sc = kv_scale_plane(dst, (size_t)rows * cap, D);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / per_row, e = (i % per_row) * 4;
-        KvElem<__half>::st4(dst + (size_t)r * cap * D + e, *reinterpret_cast<const float4 *>(src + (size_t)r * tokens * D + e));
+        kv_store4(dst, sc, (size_t)r * cap + (size_t)(e / D), D, (int)(e % D), *reinterpret_cast<const float4 *>(src + (size_t)r * tokens * D + e));
     }
 }
 
 template <class CT>
 __global__ void skn_kv_gather_kernel(const CT *__restrict__ kc, const CT *__restrict__ vc,
                                      const int32_t *__restrict__ start, int b, int Hkv, int D, int cap, int pos0,
-                                     int count, float *__restrict__ k_out, float *__restrict__ v_out) {
+                                     int count, float *__restrict__ k_out, float *__restrict__ v_out, int batch) {
     // out: [Hkv][count][D]
     const int s0 = start[b];
+    const size_t rows = (size_t)batch * Hkv * cap;
+    const __half *ks = kv_scale_plane(kc, rows, D), *vs = kv_scale_plane(vc, rows, D);
     const int d4 = D / 4;
     const int64_t total = (int64_t)Hkv * count * d4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -224,10 +329,10 @@ __global__ void skn_kv_gather_kernel(const CT *__restrict__ kc, const CT *__rest
         const int p = (int)((i / d4) % count);
         const int h = (int)(i / ((int64_t)d4 * count));
         const int slot = (s0 + pos0 + p) % cap;
-        const size_t src = (((size_t)b * Hkv + h) * cap + slot) * D + d;
+        const size_t src = ((size_t)b * Hkv + h) * cap + slot;
         const size_t dst = ((size_t)h * count + p) * D + d;
-        *reinterpret_cast<float4 *>(k_out + dst) = KvElem<CT>::ld4(kc + src);
-        *reinterpret_cast<float4 *>(v_out + dst) = KvElem<CT>::ld4(vc + src);
+        *reinterpret_cast<float4 *>(k_out + dst) = kv_load4(kc, ks, src, D, d);
+        *reinterpret_cast<float4 *>(v_out + dst) = kv_load4(vc, vs, src, D, d);
     }
 }
 
@@ -337,8 +442,8 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
         return;
     }
     const int nt = min(CHUNK, L - t0);
-    const CT *kbase = kc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
-    const CT *vbase = vc + ((size_t)b * Hkv + kvh) * cap * D + lane * VEC;
+    const size_t cache_rows = (size_t)(gridDim.z / tq) * Hkv * cap, head_row0 = ((size_t)b * Hkv + kvh) * cap;
+    const KvHeadReader<CT, D, VEC> krd(kc, cache_rows, head_row0, lane), vrd(vc, cache_rows, head_row0, lane);
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -354,7 +459,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
                 const int t = min(tl + j, nt - 1);
-                KvLoad<CT, VEC, true>::ld(vbase + (size_t)((s0 + t0 + t) % cap) * D, v0[j]);
+                vrd.ld((s0 + t0 + t) % cap, v0[j]);
             }
         }
     }
@@ -372,7 +477,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
         for (int j = 0; j < TT; ++j) {
             const int t = min(tl + j, nt - 1);            // clamp: the extra scores are discarded
             const int slot = (s0 + t0 + t) % cap;
-            KvLoad<CT, VEC, true>::ld(kbase + (size_t)slot * D, kr[j]);
+            krd.ld(slot, kr[j]);
         }
         float pv[NV];
 #pragma unroll
@@ -454,7 +559,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
             for (int j = 0; j < TT; ++j) {
                 const int t = min(tl + j, nt - 1);
                 const int slot = (s0 + t0 + t) % cap;
-                KvLoad<CT, VEC, true>::ld(vbase + (size_t)slot * D, vr[j]);
+                vrd.ld(slot, vr[j]);
             }
         }
 #pragma unroll
@@ -830,8 +935,9 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
     const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
     unsigned *tickets = (tq == 1 && small_grid && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
-    if (chunk == ATT_CHUNK && !tickets) {
-        // long contexts: tiles by bulk async copy through a shared-memory ring
+    // long contexts: tiles by bulk async copy through a shared-memory ring (quantised caches: per-lane loads at every length)
+    const bool streamed = !KvIsQ8<CT>::value && chunk == ATT_CHUNK && !tickets;
+    if constexpr (!KvIsQ8<CT>::value) if (streamed) {
         constexpr int TILE_BYTES = ATT_WARPS * TT * D * (int)sizeof(CT);
         // two stages: measured, more resident CTAs per SM (five at 44 KB each for D = 128, G = 4) beat a deeper ring
         constexpr int nst = 2;
@@ -846,6 +952,9 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
         }
         kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kc, vc, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
                                                           scale, part, S, tq, len_extra, nst, kv->ctx->d_status);
+    }
+    if (streamed) {
+        // (launched above)
     } else if (chunk == 32)
         // (plain stream order: with a programmatic dependent launch, early or late release of its own dependents, a
         // decode step measured 0.4 to 1.8 % slower)
@@ -908,6 +1017,7 @@ static cudaError_t dispatch_attn_t(const skn_kvcache *kv, int G, const float *q,
 
 static cudaError_t dispatch_attn(const skn_kvcache *kv, int G, const float *q, float scale, float *part, int chunk,
                                  float *out, cudaStream_t st, int tq = 1, int len_extra = 0) {
+    if (kv->dtype == SKN_KV_Q8_0) return dispatch_attn_t<skn_q8>(kv, G, q, scale, part, chunk, out, st, tq, len_extra);
     return kv->dtype == SKN_KV_F16 ? dispatch_attn_t<__half>(kv, G, q, scale, part, chunk, out, st, tq, len_extra)
                                    : dispatch_attn_t<float>(kv, G, q, scale, part, chunk, out, st, tq, len_extra);
 }
@@ -926,7 +1036,8 @@ int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int
     SKN_ENTER(ctx);
     if (!out) return skn_fail(ctx, SKN_ERR_ARG, "out is NULL");
     *out = nullptr;
-    if (kv_dtype != SKN_KV_F32 && kv_dtype != SKN_KV_F16) return skn_fail(ctx, SKN_ERR_TYPE, "cache element type %d is neither fp32 nor fp16", kv_dtype);
+    if (kv_dtype != SKN_KV_F32 && kv_dtype != SKN_KV_F16 && kv_dtype != SKN_KV_Q8_0)
+        return skn_fail(ctx, SKN_ERR_TYPE, "cache element type %d is none of fp32, fp16, Q8_0", kv_dtype);
     if (batch < 1 || n_kv_heads < 1 || capacity < 1) return skn_fail(ctx, SKN_ERR_ARG, "batch, heads and capacity must be positive");
     if (head_dim != 64 && head_dim != 128) return skn_fail(ctx, SKN_ERR_SHAPE, "head_dim must be 64 or 128 (got %d)", head_dim);
     skn_kvcache *kv = new (std::nothrow) skn_kvcache();
@@ -936,7 +1047,9 @@ int32_t skn_kv_create_typed(skn_ctx *ctx, int32_t batch, int32_t n_kv_heads, int
     kv->ctx = ctx;
     kv->batch = batch; kv->n_kv_heads = n_kv_heads; kv->head_dim = head_dim; kv->capacity = capacity;
     kv->dtype = kv_dtype;
-    const size_t n = (size_t)batch * n_kv_heads * capacity * head_dim * (kv_dtype == SKN_KV_F16 ? 2 : sizeof(float));
+    // Q8_0: an int8 plane, then the fp16 scales of its 32-dim blocks
+    const size_t elems = (size_t)batch * n_kv_heads * capacity * head_dim;
+    const size_t n = kv_dtype == SKN_KV_Q8_0 ? elems + elems / 32 * 2 : elems * (kv_dtype == SKN_KV_F16 ? 2 : sizeof(float));
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_k, n);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->d_v, n);
@@ -997,17 +1110,22 @@ int32_t skn_kv_load(skn_kvcache *kv, const float *k_host, const float *v_host, i
     const size_t row = (size_t)tokens * kv->head_dim * sizeof(float);
     const size_t pitch = (size_t)kv->capacity * kv->head_dim * sizeof(float);
     const size_t nrows = (size_t)kv->batch * kv->n_kv_heads;
-    if (tokens > 0 && kv->dtype == SKN_KV_F16) {
-        // fp32 rows to a staging buffer, one tensor at a time, then rounded into the cache
+    if (tokens > 0 && kv->dtype != SKN_KV_F32) {
+        // fp32 rows to a staging buffer, one tensor at a time, then rounded / quantised into the cache
         const int32_t rc = skn_stage_reserve(ctx, &ctx->d_stage_in, &ctx->d_stage_in_bytes, row * nrows);
         if (rc) return rc;
         const int64_t n4 = (int64_t)nrows * tokens * kv->head_dim / 4;
         int blocks = (int)((n4 + 255) / 256 < (int64_t)ctx->sm_count * 16 ? (n4 + 255) / 256 : (int64_t)ctx->sm_count * 16);
         for (int which = 0; which < 2; ++which) {
             SKN_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, which ? v_host : k_host, row * nrows, cudaMemcpyHostToDevice, ctx->stream));
-            skn_kv_load_half_kernel<<<blocks, 256, 0, ctx->stream>>>((const float *)ctx->d_stage_in,
-                                                                     static_cast<__half *>(which ? kv->d_v : kv->d_k), (int64_t)nrows,
-                                                                     tokens, kv->head_dim, kv->capacity);
+            if (kv->dtype == SKN_KV_F16)
+                skn_kv_load_conv_kernel<__half><<<blocks, 256, 0, ctx->stream>>>((const float *)ctx->d_stage_in,
+                                                                                 static_cast<__half *>(which ? kv->d_v : kv->d_k),
+                                                                                 (int64_t)nrows, tokens, kv->head_dim, kv->capacity);
+            else
+                skn_kv_load_conv_kernel<skn_q8><<<blocks, 256, 0, ctx->stream>>>((const float *)ctx->d_stage_in,
+                                                                                 static_cast<skn_q8 *>(which ? kv->d_v : kv->d_k),
+                                                                                 (int64_t)nrows, tokens, kv->head_dim, kv->capacity);
             SKN_CUDA(ctx, cudaGetLastError());
         }
     } else if (tokens > 0) {
@@ -1038,7 +1156,11 @@ int32_t skn_kv_append_dev(skn_kvcache *kv, const float *k_new_dev, const float *
     if (!k_new_dev || !v_new_dev) return skn_fail(ctx, SKN_ERR_ARG, "NULL argument");
     if ((((uintptr_t)k_new_dev) | ((uintptr_t)v_new_dev)) & 15) return skn_fail(ctx, SKN_ERR_ALIGN, "k/v must be 16-byte aligned");
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (kv->dtype == SKN_KV_F16)
+    if (kv->dtype == SKN_KV_Q8_0)
+        skn_kv_append_kernel<skn_q8><<<kv->batch, 256, 0, ctx->stream>>>(static_cast<skn_q8 *>(kv->d_k), static_cast<skn_q8 *>(kv->d_v),
+                                                                         kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+                                                                         kv->n_kv_heads, kv->head_dim, kv->capacity);
+    else if (kv->dtype == SKN_KV_F16)
         skn_kv_append_kernel<__half><<<kv->batch, 256, 0, ctx->stream>>>(static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v),
                                                                          kv->d_len, kv->d_start, k_new_dev, v_new_dev,
                                                                          kv->n_kv_heads, kv->head_dim, kv->capacity);
@@ -1088,14 +1210,18 @@ int32_t skn_kv_gather(skn_kvcache *kv, int32_t b, int32_t pos_begin, int32_t cou
     const int64_t total = (int64_t)kv->n_kv_heads * count * kv->head_dim / 4;
     int blocks = (int)((total + 255) / 256);
     if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
-    if (kv->dtype == SKN_KV_F16)
+    if (kv->dtype == SKN_KV_Q8_0)
+        skn_kv_gather_kernel<skn_q8><<<blocks, 256, 0, ctx->stream>>>(static_cast<const skn_q8 *>(kv->d_k), static_cast<const skn_q8 *>(kv->d_v),
+                                                                      kv->d_start, b, kv->n_kv_heads, kv->head_dim, kv->capacity,
+                                                                      pos_begin, count, dk, dv, kv->batch);
+    else if (kv->dtype == SKN_KV_F16)
         skn_kv_gather_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(static_cast<const __half *>(kv->d_k), static_cast<const __half *>(kv->d_v),
                                                                       kv->d_start, b, kv->n_kv_heads, kv->head_dim, kv->capacity,
-                                                                      pos_begin, count, dk, dv);
+                                                                      pos_begin, count, dk, dv, kv->batch);
     else
         skn_kv_gather_kernel<float><<<blocks, 256, 0, ctx->stream>>>(static_cast<const float *>(kv->d_k), static_cast<const float *>(kv->d_v),
                                                                      kv->d_start, b, kv->n_kv_heads, kv->head_dim, kv->capacity,
-                                                                     pos_begin, count, dk, dv);
+                                                                     pos_begin, count, dk, dv, kv->batch);
     SKN_CUDA(ctx, cudaGetLastError());
     SKN_CUDA(ctx, cudaMemcpyAsync(k_out_host, dk, n, cudaMemcpyDeviceToHost, ctx->stream));
     SKN_CUDA(ctx, cudaMemcpyAsync(v_out_host, dv, n, cudaMemcpyDeviceToHost, ctx->stream));
@@ -1180,7 +1306,11 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
     if ((int64_t)host_len_upper + T > kv->capacity)
         return skn_fail(ctx, SKN_ERR_SHAPE, "%d cached + %d new tokens exceed the capacity %d", host_len_upper, T, kv->capacity);
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (kv->dtype == SKN_KV_F16)
+    if (kv->dtype == SKN_KV_Q8_0)
+        skn_kv_append_many_kernel<skn_q8><<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
+            static_cast<skn_q8 *>(kv->d_k), static_cast<skn_q8 *>(kv->d_v), kv->d_len, kv->d_start, k_new_dev, v_new_dev,
+            kv->n_kv_heads, kv->head_dim, kv->capacity, T);
+    else if (kv->dtype == SKN_KV_F16)
         skn_kv_append_many_kernel<__half><<<dim3((unsigned)T, (unsigned)kv->batch), 128, 0, ctx->stream>>>(
             static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v), kv->d_len, kv->d_start, k_new_dev, v_new_dev,
             kv->n_kv_heads, kv->head_dim, kv->capacity, T);
@@ -1242,7 +1372,11 @@ int32_t skn_kv_rope_append_pending(skn_kvcache *kv, float *q_dev, const float *k
     if ((int64_t)kv->batch > 65535 || T > 65535) return skn_fail(ctx, SKN_ERR_SHAPE, "batch or T exceeds 65535");
     const int pair_blocks = ((n_q_heads + kv->n_kv_heads) * (kv->head_dim / 2) + 127) / 128;
     const dim3 rgrid((unsigned)pair_blocks + 1, (unsigned)T, (unsigned)kv->batch);
-    if (kv->dtype == SKN_KV_F16)
+    if (kv->dtype == SKN_KV_Q8_0)
+        skn_rope_append_kernel<skn_q8><<<rgrid, 128, 0, ctx->stream>>>(
+            q_dev, k_new_dev, v_new_dev, static_cast<skn_q8 *>(kv->d_k), static_cast<skn_q8 *>(kv->d_v), kv->d_len, kv->d_start,
+            n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta), ctx->d_status);
+    else if (kv->dtype == SKN_KV_F16)
         skn_rope_append_kernel<__half><<<rgrid, 128, 0, ctx->stream>>>(
             q_dev, k_new_dev, v_new_dev, static_cast<__half *>(kv->d_k), static_cast<__half *>(kv->d_v), kv->d_len, kv->d_start,
             n_q_heads, kv->n_kv_heads, kv->head_dim, kv->capacity, T, log2((double)theta), ctx->d_status);
@@ -1313,7 +1447,7 @@ int32_t skn_attn_decode_noalloc_dev(skn_kvcache *kv, const float *q_dev, int32_t
     return SKN_OK;
 }
 
-// element type of the cache buffers (SKN_KV_F32 / SKN_KV_F16): what the pointers of skn_kv_info point at
+// element type of the cache buffers (SKN_KV_F32 / SKN_KV_F16 / SKN_KV_Q8_0): what the pointers of skn_kv_info point at
 int32_t skn_kv_dtype(const skn_kvcache *kv, int32_t *kv_dtype) {
     if (!kv_ok(kv)) return skn_fail(nullptr, SKN_ERR_BAD_HANDLE, "bad kv cache handle");
     if (!kv_dtype) return skn_fail(kv->ctx, SKN_ERR_ARG, "kv_dtype is NULL");

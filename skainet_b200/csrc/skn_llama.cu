@@ -33,7 +33,7 @@ struct skn_llama {
     int32_t **len_ptrs;               // device array: the length vector of every layer's cache
     void *argmax_scratch;             // candidates and tickets of the two-level argmax
     int32_t host_len;                 // tokens cached so far (the same for every sequence)
-    int32_t kv_f16;                   // the layers' caches hold fp16 (SKN_OPT_KV_F16 at creation)
+    int32_t kv_f16;                   // SKN_KV_* element type of the layers' caches (SKN_OPT_KV_F16 / SKN_OPT_KV_DTYPE at creation)
     // tensor parallelism: this rank's share of heads, FFN columns and vocabulary rows
     skn_comm *comm;
     int32_t world, rank, heads_l, kv_heads_l, ffn_l, vocab_l;
@@ -93,7 +93,7 @@ int32_t skn_llama_create_tp(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int
     m->ctx = ctx;
     m->n_layers = n_layers; m->d_model = d_model; m->n_heads = n_heads; m->n_kv_heads = n_kv_heads;
     m->head_dim = head_dim; m->ffn_dim = ffn_dim; m->vocab = vocab; m->max_batch = max_batch; m->max_ctx = max_ctx;
-    m->kv_f16 = ctx->kv_f16 ? 1 : 0;
+    m->kv_f16 = ctx->kv_f16;
     m->rope_theta = rope_theta; m->rms_eps = rms_eps;
     m->comm = comm; m->world = world; m->rank = rank;
     m->heads_l = n_heads / world; m->kv_heads_l = n_kv_heads / world; m->ffn_l = ffn_dim / world; m->vocab_l = vocab / world;
@@ -142,7 +142,7 @@ int32_t skn_llama_create_tp(skn_ctx *ctx, int32_t n_layers, int32_t d_model, int
         e = dev_alloc(&m->layers[l].attn_norm, d_model);
         if (e == cudaSuccess) e = dev_alloc(&m->layers[l].ffn_norm, d_model);
         if (e != cudaSuccess) { rc = skn_check_cuda(ctx, e, "decoder norm gains"); break; }
-        rc = skn_kv_create_typed(ctx, max_batch, m->kv_heads_l, head_dim, max_ctx, ctx->kv_f16 ? SKN_KV_F16 : SKN_KV_F32, &m->layers[l].kv);
+        rc = skn_kv_create_typed(ctx, max_batch, m->kv_heads_l, head_dim, max_ctx, ctx->kv_f16, &m->layers[l].kv);
     }
     if (rc == SKN_OK) {
         std::vector<int32_t *> lens(n_layers);

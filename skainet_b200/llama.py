@@ -36,12 +36,12 @@ class LlamaDecoder:
                  kv_dtype: str = "f32"):
         """exchange (parallel.Exchange): tensor-parallel decoder; this rank then keeps only its
         share of every weight (set_layer / set_head still take the WHOLE tensors' raw blocks and
-        upload the rank's shard).  kv_dtype "f16" keeps the layers' KV caches in fp16."""
-        if kv_dtype not in ("f32", "f16"):
-            raise ValueError("kv_dtype must be 'f32' or 'f16'")
+        upload the rank's shard).  kv_dtype "f16" / "q8_0" keeps the layers' KV caches in fp16 / Q8_0-style blocks."""
+        if kv_dtype not in ("f32", "f16", "q8_0"):
+            raise ValueError("kv_dtype must be 'f32', 'f16' or 'q8_0'")
         self.ctx, self.cfg, self.batch = ctx, cfg, batch
         self.kv_dtype = kv_dtype
-        ctx.set_kv_f16(kv_dtype == "f16")
+        ctx.set_kv_dtype(kv_dtype)
         self._h = ctypes.c_void_p()
         self._tensors = []
         self.exchange = exchange
@@ -51,7 +51,7 @@ class LlamaDecoder:
                                             cfg.head_dim, cfg.ffn_dim, cfg.vocab, cfg.rope_theta, cfg.rms_eps, batch,
                                             max_tokens, max_ctx, None if exchange is None else exchange.handle,
                                             ctypes.byref(self._h))
-        ctx.set_kv_f16(False)
+        ctx.set_kv_dtype("f32")
         if rc != SKN_OK:
             self._h = ctypes.c_void_p()
             _raise(ctx.handle, rc)

@@ -168,6 +168,10 @@ class Context:
         """Decoders created afterwards keep their KV caches in fp16 (SKN_OPT_KV_F16)."""
         _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 4, 1 if on else 0))
 
+    def set_kv_dtype(self, dtype: str):
+        """Element type of the KV caches of decoders created afterwards: "f32", "f16" or "q8_0" (SKN_OPT_KV_DTYPE)."""
+        _check(self._h, _ffi.lib().skn_ctx_set_option(self._h, 6, KVCache.DTYPES[dtype]))
+
     def set_wait_limit_ms(self, ms: int):
         """How long a kernel of the inter-GPU exchange waits for its peers before it reports
         SKN_ERR_TIMEOUT (SKN_OPT_WAIT_LIMIT_MS; 0 restores the default of two seconds)."""
@@ -315,14 +319,15 @@ def ffn_swiglu(ctx: Context, wg: QuantTensor, wu: QuantTensor, wd: QuantTensor, 
 
 
 class KVCache:
-    """Device-resident KV cache (head-major ring) with decode attention.  `dtype` is "f32" (default) or
-    "f16": the element type K and V are kept in; every method takes and returns fp32 either way."""
+    """Device-resident KV cache (head-major ring) with decode attention.  `dtype` is "f32" (default), "f16" or
+    "q8_0" (int8 with one fp16 scale per 32 head dims): the element type K and V are kept in; every method
+    takes and returns fp32 either way."""
 
-    DTYPES = {"f32": 0, "f16": 1}
+    DTYPES = {"f32": 0, "f16": 1, "q8_0": 2}
 
     def __init__(self, ctx: Context, batch: int, n_kv_heads: int, head_dim: int, capacity: int, dtype: str = "f32"):
         if dtype not in self.DTYPES:
-            raise ValueError("dtype must be 'f32' or 'f16'")
+            raise ValueError("dtype must be 'f32', 'f16' or 'q8_0'")
         self.ctx = ctx
         self.batch, self.n_kv_heads, self.head_dim, self.capacity = batch, n_kv_heads, head_dim, capacity
         self.dtype = dtype

@@ -3,13 +3,15 @@ against the fp64 textbook oracle, through the C ABI.
 
 Tolerance: fp32 softmax-weighted sums -- |out - ref| <= 1e-5 * sum_t p_t |v_t| per element
 (p the oracle's probabilities) and relative L2 <= 1e-5."""
+import ctypes
+
 import numpy as np
 import pytest
 
 import skainet_b200 as skn
 from conftest import FP32_TOL
 from oracle import oracle
-from skainet_b200 import synth
+from skainet_b200 import _ffi, synth
 
 pytestmark = pytest.mark.gpu
 
@@ -181,6 +183,70 @@ def test_fp16_cache_append_gather_and_ring_wrap(ctx):
     kv.close()
     with pytest.raises(ValueError):
         skn.KVCache(ctx, 1, 1, 64, 8, dtype="bf16")
+    assert _ffi.lib().skn_kv_create_typed(ctx.handle, 1, 1, 64, 8, 3, ctypes.byref(ctypes.c_void_p())) == 2   # SKN_ERR_TYPE
+
+
+def q8(a):
+    """What a Q8_0-style cache keeps of fp32 values: per 32 head dims d = max|x| / 127 (kept as fp16) and
+    int8 q = round(x / d); read back as q * d (oracle.np_quantize_q8_0, pinned to gguf-py)."""
+    return oracle.np_q8_0_roundtrip(a)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_q8_0_cache_load_append_gather_and_ring_wrap(ctx, D):
+    """Every way into a Q8_0 cache (pre-fill, single-token append, the ring's overwrite) quantises with the pinned
+    rule bit for bit: what gather returns equals the oracle's round trip of what went in, magnitudes from 1e-3
+    to 50, an all-zero block and exact ties included; attention over it equals the fp64 oracle over those values."""
+    g = synth.rng(61 + D)
+    B, Hq, Hkv, cap = 2, 8, 2, 20
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype="q8_0")
+    k0 = g.standard_normal((B, Hkv, 5, D), dtype=np.float32) * 3
+    v0 = g.standard_normal((B, Hkv, 5, D), dtype=np.float32) * 1e-3
+    k0[0, 0, 1, :32] = 0.0                                         # an all-zero block: scale 0, quants 0
+    k0[1, 1, 2, 32:64] = (np.arange(32) - 16) * 0.5                # ties: x / d ends in .5 for odd multiples
+    k0[1, 1, 2, 63] = 63.5
+    kv.load(k0, v0, np.full(B, 5, dtype=np.int32))
+    ks = [k0[:, :, i] for i in range(5)]
+    vs = [v0[:, :, i] for i in range(5)]
+    for step in range(22):
+        k_new = g.standard_normal((B, Hkv, D), dtype=np.float32) * 50
+        v_new = g.standard_normal((B, Hkv, D), dtype=np.float32) * (1e-3 if step % 2 else 7.0)
+        kv.append(k_new, v_new)
+        ks.append(k_new)
+        vs.append(v_new)
+    K = q8(np.stack(ks[-cap:], axis=2))
+    V = q8(np.stack(vs[-cap:], axis=2))
+    lens, start = kv.lengths()
+    assert np.all(lens == cap) and np.all(start == (5 + 22 - cap))
+    for b in range(B):
+        kg, vg = kv.gather(b, 0, cap)
+        assert np.array_equal(kg.view(np.uint32), K[b].view(np.uint32)) and np.array_equal(vg.view(np.uint32), V[b].view(np.uint32))
+    qv = g.standard_normal((B, Hq, D), dtype=np.float32) * 0.02
+    out = kv.attend(qv)
+    check_attention(out, qv, K, V, np.full(B, cap, dtype=np.int32))
+    kv.close()
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,cap", [(1, 1, 1, 64, 16), (2, 4, 2, 128, 300), (3, 8, 1, 64, 700),
+                                            (2, 32, 8, 128, 1100), (8, 32, 8, 128, 4224)])
+def test_q8_0_cache_attention_matches_oracle_on_quantised_values(ctx, B, Hq, Hkv, D, cap):
+    """Attention over a Q8_0 cache equals the fp64 oracle over the quantised-and-restored K and V within the fp32
+    tolerance, from a 16-token context to 4224 tokens (every split size, the in-kernel merge and the merge launch)."""
+    g = synth.rng(B * 1000 + Hq + cap + 11)
+    kc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    vc = g.standard_normal((B, Hkv, cap, D), dtype=np.float32)
+    lens = g.integers(1, cap + 1, size=B).astype(np.int32)
+    lens[0] = cap
+    qv = g.standard_normal((B, Hq, D), dtype=np.float32)
+    kv = skn.KVCache(ctx, B, Hkv, D, cap, dtype="q8_0")
+    kv.load(kc, vc, lens)
+    out = kv.attend(qv)
+    kv.close()
+    check_attention(out, qv, q8(kc), q8(vc), lens)
+    # and the quantisation itself costs what Q8_0 costs: about half a percent of the exact result
+    exact = oracle.attn_decode(qv, kc, vc, lens)
+    rel = np.linalg.norm(out.astype(np.float64) - exact) / np.linalg.norm(exact)
+    assert rel < 2e-2, rel
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16"])

@@ -119,15 +119,17 @@ def test_toy_decoder_matches_fp64_restatement(ctx):
     dec.close()
 
 
-def test_toy_decoder_with_fp16_kv_cache(ctx):
-    """The same decoder with its caches in fp16: K and V carry 11 significant bits, the logits follow
-    the fp64 restatement to 2e-3 (relative L2) and the fp32-cache decoder's greedy tokens on this model."""
+@pytest.mark.parametrize("kv_dtype,tol", [("f16", 2e-3), ("q8_0", 3e-2)])
+def test_toy_decoder_with_fp16_or_q8_0_kv_cache(ctx, kv_dtype, tol):
+    """The same decoder with its caches in fp16 (K and V carry 11 significant bits: the logits follow the fp64
+    restatement to 2e-3, relative L2) or in Q8_0-style blocks (8 bits against the block's largest: 3e-2), through
+    the prompt (many-token append) and single-token steps (rotary kernel writing the cache)."""
     cfg = LlamaConfig(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=512)
     layers, head = random_model_blocks(cfg, seed=4)
     B, T = 2, 5
     ones = np.ones(cfg.d_model, dtype=np.float32)
     decs = []
-    for kvd in ("f32", "f16"):
+    for kvd in ("f32", kv_dtype):
         dec = LlamaDecoder(ctx, cfg, batch=B, max_tokens=8, max_ctx=32, kv_dtype=kvd)
         for i, l in enumerate(layers):
             dec.set_layer(i, l, ones, ones)
@@ -139,12 +141,12 @@ def test_toy_decoder_with_fp16_kv_cache(ctx):
     ref_logits = ref.forward(prompt)
     outs = [d.forward(prompt, want_logits=True) for d in decs]
     assert rel(outs[0][1], ref_logits) <= 1e-4
-    assert rel(outs[1][1], ref_logits) <= 2e-3
+    assert rel(outs[1][1], ref_logits) <= tol
     for step in range(3):
         tok = g.integers(0, cfg.vocab, size=(B, 1)).astype(np.int32)
         ref_logits = ref.forward(tok)
         outs = [d.forward(tok, want_logits=True) for d in decs]
-        assert rel(outs[1][1], ref_logits) <= 2e-3, step
+        assert rel(outs[1][1], ref_logits) <= tol, step
         assert np.array_equal(outs[1][0], outs[1][1].argmax(-1))
     for d in decs:
         d.close()

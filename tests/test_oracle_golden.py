@@ -98,3 +98,20 @@ def test_ffn_oracle_against_numpy():
     a = x.astype(np.float64) @ Wg.T
     h = a / (1 + np.exp(-a)) * (x.astype(np.float64) @ Wu.T)
     assert np.allclose(y, h @ Wd.T, rtol=1e-10, atol=1e-10)
+
+
+def test_q8_0_quantiser_matches_gguf_py_bit_exact():
+    """oracle.np_quantize_q8_0 (the rule of the Q8_0-style KV cache) against blocks gguf-py 0.19.0 made of the
+    same rows (tests/golden/make_q8_quant_golden.py): scales and quants bit for bit, ties, an all-zero block, a
+    towering value, subnormals and an fp16-overflowing scale included; and the round trip equals the
+    pinned Q8_0 dequantiser on those blocks."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "q8_0_quant_golden.npz"))
+    x, blocks = z["x"], z["blocks"].reshape(z["x"].shape[0], -1, 34)
+    q, dh = oracle.np_quantize_q8_0(x)
+    assert np.array_equal(dh.view(np.uint16), np.ascontiguousarray(blocks[:, :, :2]).view(np.uint16).reshape(dh.shape))
+    assert np.array_equal(q.reshape(x.shape[0], -1, 32).view(np.uint8), blocks[:, :, 2:])
+    finite = np.isfinite(dh.astype(np.float32)).repeat(32, axis=-1).reshape(x.shape)
+    rt = oracle.np_q8_0_roundtrip(x)
+    want = oracle.dequant(synth.Q8_0, np.ascontiguousarray(z["blocks"]).reshape(-1)).reshape(x.shape)
+    assert np.array_equal(rt[finite].view(np.uint32), want[finite].view(np.uint32))
