@@ -303,7 +303,8 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     skn_comm_view xview = {};
     // (automatic: from four ranks on, where it measured faster than the exchange launches)
     const bool want_fused = ctx->fused_exchange > 0 || (ctx->fused_exchange < 0 && m->world >= 4);
-    bool fusedx = tp && fold && want_fused && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
+    // (the fused exchange rides on the single-launch tensor-core matvec: one or two rows)
+    bool fusedx = tp && fold && M <= 2 && want_fused && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
     if (fusedx) {
         // only when every layer takes the multi-row tensor-core path (a pending exchange is consumed
         // by the next layer's first projection)

@@ -97,20 +97,21 @@ def test_exchange_sums_in_rank_order_and_replays():
 
 
 @needs2
-@pytest.mark.parametrize("fused_exchange", [False, True])
-def test_sharded_decoder_matches_fp64_restatement(fused_exchange):
-    """fused_exchange: single-token steps push partial products from the matvec epilogue and sum
-    them while the next projection prepares x (SKN_OPT_FUSED_EXCHANGE) instead of launching the
-    exchange kernel."""
+@pytest.mark.parametrize("fused_exchange,B", [(False, 2), (True, 2), (False, 5), (True, 5)])
+def test_sharded_decoder_matches_fp64_restatement(fused_exchange, B):
+    """fused_exchange: single-token steps of one or two sequences push partial products from the matvec
+    epilogue and sum them while the next projection prepares x (SKN_OPT_FUSED_EXCHANGE) instead of launching
+    the exchange kernel.  Five sequences: the many-row path under tensor parallelism, where the option is
+    asked for but does not apply (the separate exchange runs)."""
     from test_gpu_llama import RefModel, rel
     cfg = LlamaConfig(n_layers=2, d_model=256, n_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=512)
     layers, head = random_model_blocks(cfg, seed=9)
-    B, T = 2, 5
+    T = 5
     ctxs = [skn.Context(device=d) for d in range(2)]
     for c in ctxs:
         c.set_fused_exchange(fused_exchange)
     exs = Exchange.connect_local(ctxs, B * 8 * cfg.d_model)
-    decs = [LlamaDecoder(ctxs[r], cfg, batch=B, max_tokens=8, max_ctx=32, exchange=exs[r]) for r in range(2)]
+    decs = [LlamaDecoder(ctxs[r], cfg, batch=B, max_tokens=8, max_ctx=32, exchange=exs[r]) for r in range(2)]      # noqa: E501
     ones = np.ones(cfg.d_model, dtype=np.float32)
     for dec in decs:
         for i, l in enumerate(layers):
