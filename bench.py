@@ -51,7 +51,7 @@ W_BYTES = N_ROWS * (N_COLS // 256) * 144
 ALG_BYTES = W_BYTES + 4 * N_COLS + 4 * N_ROWS      # 9 469 952 per matvec
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the matvec kernel on this workload (one ncu
 # capture of a 16-layer stack, 151 MB of weights)
-DRAM_TRAFFIC_PER_LAUNCH = 9489408
+DRAM_TRAFFIC_PER_LAUNCH = 9495040
 KERNEL_NAME = "skn_matvec_mma<0, 2, 1, true, 0>"
 METRIC = "q4k_matvec_gbs"
 UNIT = "GB/s"
