@@ -407,6 +407,73 @@ template <> struct VecLoad<2> {
     }
 };
 
+// Log-sum-exp merge of the ns splits of the G query heads of one (query, kv head) by the CTA that drew the last
+// ticket: called by the ATT_WARPS compute warps together (named barrier 1), out of line so that the streaming loops
+// of its callers keep their registers.  head0 = query * Hq + first head; scratch: ATT_WARPS * G * D floats of shared
+// memory that the caller no longer needs.
+template <int D, int G>
+static __device__ __noinline__ void attn_merge_tail(const float *__restrict__ part, float *__restrict__ out, float *scratch, size_t head0,
+                                                    int S, int ns) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // The tail is latency, not bandwidth: every load below is issued before the first one is consumed (a loop
+    // of load -> use over the splits would pay one trip to L2 per split).
+    // (max, sum) of every (head, split) in one round of loads, into the output staging buffer (free by now)
+    float *s_ms = scratch;                          // [G][ns] maxima, then [G][ns] sums, then [G][ns] weights
+    float *s_ls = s_ms + G * ns;
+    float *s_w = s_ls + G * ns;                     // 3 G ns <= ATT_WARPS G D floats (ns <= 64 <= 4 D / 3)
+    for (int i = threadIdx.x; i < G * ns; i += ATT_WARPS * 32) {
+        const int g = i / ns, sidx = i - g * ns;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(part + ((head0 + g) * S + sidx) * (D + 2)));
+        s_ms[i] = ml.x;
+        s_ls[i] = ml.y;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ATT_WARPS * 32) : "memory");
+    // weights w = exp(max_s - max) / sum: one warp per head, lanes over the splits
+    for (int g = warp; g < G; g += ATT_WARPS) {
+        float m = -INFINITY;
+        for (int sidx = lane; sidx < ns; sidx += 32) m = fmaxf(m, s_ms[g * ns + sidx]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int sidx = lane; sidx < ns; sidx += 32) {
+            const float w = expf(s_ms[g * ns + sidx] - m);
+            s_w[g * ns + sidx] = w;
+            l = fmaf(s_ls[g * ns + sidx], w, l);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        const float inv = 1.f / l;
+        for (int sidx = lane; sidx < ns; sidx += 32) s_w[g * ns + sidx] *= inv;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ATT_WARPS * 32) : "memory");
+    constexpr int MB = 16;                          // splits loaded per batch
+    constexpr int NO = (G * D + ATT_WARPS * 32 - 1) / (ATT_WARPS * 32);    // outputs per thread
+    float acc[NO];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) acc[j] = 0.f;
+    for (int sb = 0; sb < ns; sb += MB) {
+        float r[NO][MB];
+#pragma unroll
+        for (int j = 0; j < NO; ++j) {
+            const int i = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1), g = i / D, d = i % D;
+            const float *rec = part + (head0 + g) * S * (D + 2) + 2 + d;
+#pragma unroll
+            for (int u = 0; u < MB; ++u) r[j][u] = (sb + u < ns) ? __ldcg(rec + (size_t)(sb + u) * (D + 2)) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NO; ++j) {
+            const int g = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1) / D;
+#pragma unroll
+            for (int u = 0; u < MB; ++u) acc[j] = fmaf(r[j][u], (sb + u < ns) ? s_w[g * ns + sb + u] : 0.f, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NO; ++j) {
+        const int i = threadIdx.x + j * ATT_WARPS * 32;
+        if (i < G * D) out[head0 * D + i] = acc[j];
+    }
+}
+
 // D: head dim (64 or 128); G: query heads per kv head; TT: tokens per warp tile (TT*G <= 32)
 template <int D, int G, int TT, int CHUNK, class CT>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -600,63 +667,7 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // The tail is latency, not bandwidth: every load below is issued before the first one is consumed (a loop
-    // of load -> use over the splits would pay one trip to L2 per split).
-    // (max, sum) of every (head, split) in one round of loads, into the output staging buffer (free by now)
-    float *s_ms = &s_o[0][0][0];                    // [G][ns] maxima, then [G][ns] sums, then [G][ns] weights
-    float *s_ls = s_ms + G * ns;
-    float *s_w = s_ls + G * ns;                     // 3 G ns <= ATT_WARPS G D floats (ns <= 64 <= 4 D / 3)
-    for (int i = threadIdx.x; i < G * ns; i += ATT_WARPS * 32) {
-        const int g = i / ns, sidx = i - g * ns;
-        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(part + (((size_t)bq * Hq + kvh * G + g) * S + sidx) * (D + 2)));
-        s_ms[i] = ml.x;
-        s_ls[i] = ml.y;
-    }
-    __syncthreads();
-    // weights w = exp(max_s - max) / sum: one warp per head, lanes over the splits
-    for (int g = warp; g < G; g += ATT_WARPS) {
-        float m = -INFINITY;
-        for (int sidx = lane; sidx < ns; sidx += 32) m = fmaxf(m, s_ms[g * ns + sidx]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float l = 0.f;
-        for (int sidx = lane; sidx < ns; sidx += 32) {
-            const float w = expf(s_ms[g * ns + sidx] - m);
-            s_w[g * ns + sidx] = w;
-            l = fmaf(s_ls[g * ns + sidx], w, l);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        const float inv = 1.f / l;
-        for (int sidx = lane; sidx < ns; sidx += 32) s_w[g * ns + sidx] *= inv;
-    }
-    __syncthreads();
-    constexpr int MB = 16;                          // splits loaded per batch
-    constexpr int NO = (G * D + ATT_WARPS * 32 - 1) / (ATT_WARPS * 32);    // outputs per thread
-    float acc[NO];
-#pragma unroll
-    for (int j = 0; j < NO; ++j) acc[j] = 0.f;
-    for (int sb = 0; sb < ns; sb += MB) {
-        float r[NO][MB];
-#pragma unroll
-        for (int j = 0; j < NO; ++j) {
-            const int i = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1), g = i / D, d = i % D;
-            const float *rec = part + ((size_t)bq * Hq + kvh * G + g) * S * (D + 2) + 2 + d;
-#pragma unroll
-            for (int u = 0; u < MB; ++u) r[j][u] = (sb + u < ns) ? __ldcg(rec + (size_t)(sb + u) * (D + 2)) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < NO; ++j) {
-            const int g = min(threadIdx.x + j * ATT_WARPS * 32, G * D - 1) / D;
-#pragma unroll
-            for (int u = 0; u < MB; ++u) acc[j] = fmaf(r[j][u], (sb + u < ns) ? s_w[g * ns + sb + u] : 0.f, acc[j]);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < NO; ++j) {
-        const int i = threadIdx.x + j * ATT_WARPS * 32;
-        if (i < G * D) out[((size_t)bq * Hq + kvh * G) * D + i] = acc[j];
-    }
+    attn_merge_tail<D, G>(part, out, &s_o[0][0][0], (size_t)bq * Hq + kvh * G, S, ns);
     if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
 
@@ -669,11 +680,11 @@ skn_attn_split_kernel(const float *__restrict__ q, const CT *__restrict__ kc, co
 // chunk maximum and the probabilities are computed, so HBM stays busy across the two passes.
 // Writes the (max, sum, unnormalised output) record per (head, split); the merge kernel follows.
 template <int D, int G, int TT, class CT>
-__global__ void __launch_bounds__((ATT_WARPS + 1) * 32)
+__global__ void __launch_bounds__((ATT_WARPS + 1) * 32, 5)       // five CTAs per SM (44.5 KB each): at most 80 registers
 skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, const CT *__restrict__ vc,
                        const int32_t *__restrict__ len, const int32_t *__restrict__ start, int Hkv, int cap,
                        float scale, float *__restrict__ part, int S, int tq, int len_extra, int nst,
-                       int32_t *__restrict__ status) {
+                       int32_t *__restrict__ status, float *__restrict__ out, unsigned *__restrict__ tickets) {
     constexpr int CHUNK = ATT_CHUNK;
     constexpr int VEC = D / 32;
     constexpr int NV = TT * G;
@@ -692,7 +703,12 @@ skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, c
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int L = min(cap, max(0, len[b] + len_extra - (tq - 1 - bq % tq)));     // never past the ring: ns <= S
     const int t0 = sp * CHUNK;
-    if (t0 >= L) return;
+    if (t0 >= L) {
+        // an empty sequence has no split to merge: its output is zero
+        if (tickets && L == 0 && sp == 0)
+            for (int i = threadIdx.x; i < G * D; i += (ATT_WARPS + 1) * 32) out[((size_t)bq * Hkv * G + kvh * G) * D + i] = 0.f;
+        return;
+    }
     const int nt = min(CHUNK, L - t0);
     const int ntile = (nt + TILE - 1) / TILE;
     const int s0 = start[b];
@@ -869,6 +885,19 @@ skn_attn_stream_kernel(const float *__restrict__ q, const CT *__restrict__ kc, c
         rec[2 + d] = a;
         if (d == 0) { rec[0] = s_m[g]; rec[1] = s_l[g]; }
     }
+    if (!tickets) return;
+    // merge without a second launch (single-token decode): the CTA that draws the last ticket of its (sequence, kv
+    // head) combines the splits; the merge itself is a call, so the loops above keep their register count
+    __shared__ bool s_last;
+    __threadfence();
+    bar();
+    const int ns = (L + CHUNK - 1) / CHUNK;
+    if (threadIdx.x == 0) s_last = atomicAdd(&tickets[bq * Hkv + kvh], 1u) == (unsigned)(ns - 1);
+    bar();
+    if (!s_last) return;
+    __threadfence();
+    attn_merge_tail<D, G>(part, out, &s_o[0][0][0], (size_t)bq * Hq + kvh * G, S, ns);
+    if (threadIdx.x == 0) tickets[bq * Hkv + kvh] = 0;
 }
 
 // Log-sum-exp merge of the splits of one (query, head): D threads.  The splits' maxima and sums are
@@ -934,9 +963,11 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
     // sequences without any cached token are left to the merge kernel (it writes their zeros)
     // (small grids only: with many CTAs per SM a merge launch costs less than the serial tails)
     const bool small_grid = (int64_t)S * kv->n_kv_heads * kv->batch <= 2 * (int64_t)kv->ctx->sm_count;
-    unsigned *tickets = (tq == 1 && small_grid && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
+    static const int big_tickets = skn_tune_int("SKN_ATTN_BIG_TICKETS", 1);
+    const bool streamed_shape = !KvIsQ8<CT>::value && chunk == ATT_CHUNK && !small_grid;
+    unsigned *tickets = (tq == 1 && (small_grid || (streamed_shape && big_tickets)) && S <= ATT_MERGE_MAX_SPLITS && S <= chunk) ? kv->d_tickets : nullptr;
     // long contexts: tiles by bulk async copy through a shared-memory ring (quantised caches: per-lane loads at every length)
-    const bool streamed = !KvIsQ8<CT>::value && chunk == ATT_CHUNK && !tickets;
+    const bool streamed = streamed_shape || (!KvIsQ8<CT>::value && chunk == ATT_CHUNK && !tickets);
     if constexpr (!KvIsQ8<CT>::value) if (streamed) {
         constexpr int TILE_BYTES = ATT_WARPS * TT * D * (int)sizeof(CT);
         // two stages: measured, more resident CTAs per SM (five at 44 KB each for D = 128, G = 4) beat a deeper ring
@@ -951,7 +982,7 @@ static cudaError_t launch_attn(const skn_kvcache *kv, const float *q, float scal
             kv->ctx->attn_stream_cfg |= cfg_bit;
         }
         kern<<<grid, (ATT_WARPS + 1) * 32, smem, stream>>>(q, kc, vc, kv->d_len, kv->d_start, kv->n_kv_heads, kv->capacity,
-                                                          scale, part, S, tq, len_extra, nst, kv->ctx->d_status);
+                                                          scale, part, S, tq, len_extra, nst, kv->ctx->d_status, out, tickets);
     }
     if (streamed) {
         // (launched above)
