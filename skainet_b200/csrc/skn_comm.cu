@@ -21,6 +21,12 @@
 // q + 1, which needs this rank's push of q + 1, which this rank issues after its own reduce q
 // has completed.
 //
+// Decode-size vectors (up to COMM_LL_MAX floats) take a second, lower-latency form of the same exchange
+// (skn_allreduce_ll_kernel): every float travels as an 8-byte word {value, q + 1} written with one store, and the
+// receiver polls the words themselves.  No fence, no flag store behind the data: the exchange costs one trip
+// over NVLink instead of three (data, the acknowledgement the system fence waits for, the flag).  Its inbox
+// follows the first one in the same allocation: uint2 ll[NBUF][world][COMM_LL_MAX].
+//
 // No multicast, no bulk-async loads from peer memory: only ordinary stores to peers and loads
 // from local memory.
 #include "skn_internal.cuh"
@@ -34,6 +40,7 @@
 constexpr int COMM_NBUF = SKN_COMM_NBUF;
 constexpr int COMM_MAX_WORLD = SKN_COMM_MAX_WORLD;
 constexpr size_t COMM_FLAG_BYTES = SKN_COMM_FLAG_BYTES;
+constexpr int64_t COMM_LL_MAX = 65536;            // floats per (buffer, source rank) of the low-latency inbox
 
 struct skn_comm {
     uint32_t magic;
@@ -77,6 +84,77 @@ __device__ __forceinline__ float *comm_inbox(uint8_t *base, int buf, int world, 
 }
 __device__ __forceinline__ uint32_t *comm_flag(uint8_t *base, int buf, int src) {
     return reinterpret_cast<uint32_t *>(base) + buf * COMM_MAX_WORLD + src;
+}
+
+// The low-latency form for n <= COMM_LL_MAX: out[i] = resid[i] + sum over ranks of partial_r[i], ranks in order.
+// ll_off: byte offset of the low-latency inbox inside every rank's allocation.
+__global__ void __launch_bounds__(1024)
+skn_allreduce_ll_kernel(comm_peers peers, size_t ll_off, int rank, int world, uint32_t *__restrict__ state,
+                        int32_t *__restrict__ status, const float *__restrict__ partial, const float *__restrict__ resid,
+                        float *__restrict__ out, int64_t n) {
+    const uint32_t q = *reinterpret_cast<volatile uint32_t *>(state);
+    const uint32_t tag = q + 1u;
+    const int buf = (int)(q % COMM_NBUF);
+    const int64_t n4 = n / 4;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (int64_t)gridDim.x * blockDim.x;
+    auto inbox = [&](int owner, int src) {
+        return reinterpret_cast<uint2 *>(peers.base[owner] + ll_off) + ((int64_t)buf * world + src) * COMM_LL_MAX;
+    };
+    // 1. push: four tagged words per thread and peer
+    for (int64_t i = tid; i < n4; i += nthr) {
+        const float4 v = reinterpret_cast<const float4 *>(partial)[i];
+        const uint32_t w[4] = {__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w)};
+        for (int p = 1; p < world; ++p) {
+            uint2 *to = inbox((rank + p) % world, rank) + 4 * i;      // start with a different peer on every rank
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(to + j), "r"(w[j]), "r"(tag) : "memory");
+        }
+    }
+    // 2. + 3. poll the words of every peer (bounded) and sum in rank order
+    const bool waiting = *reinterpret_cast<volatile int32_t *>(status) == 0;
+    const uint64_t t0 = skn_globaltimer_ns(), limit = skn_wait_limit_ns(status);
+    bool gave_up = !waiting;
+    for (int64_t i = tid; i < n4; i += nthr) {
+        float4 acc = resid ? reinterpret_cast<const float4 *>(resid)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int src = 0; src < world; ++src) {
+            float4 v;
+            if (src == rank) {
+                v = reinterpret_cast<const float4 *>(partial)[i];
+            } else {
+                const uint2 *from = inbox(rank, src) + 4 * i;
+                uint2 a, b, c, d;
+                uint32_t spins = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a.x), "=r"(a.y) : "l"(from) : "memory");
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(b.x), "=r"(b.y) : "l"(from + 1) : "memory");
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(c.x), "=r"(c.y) : "l"(from + 2) : "memory");
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d.x), "=r"(d.y) : "l"(from + 3) : "memory");
+                    if ((a.y == tag && b.y == tag && c.y == tag && d.y == tag) || gave_up) break;
+                    if ((++spins & 255u) == 0 && skn_globaltimer_ns() - t0 > limit) {
+                        atomicExch(status, SKN_ERR_TIMEOUT);
+                        gave_up = true;
+                    }
+                }
+                v = make_float4(__uint_as_float(a.x), __uint_as_float(b.x), __uint_as_float(c.x), __uint_as_float(d.x));
+            }
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4 *>(out)[i] = acc;
+    }
+    __syncthreads();
+    // the CTA that finishes last moves the counter on
+    if (threadIdx.x == 0) {
+        if (gridDim.x == 1) {
+            *reinterpret_cast<volatile uint32_t *>(state) = q + 1;
+        } else {
+            __threadfence();
+            if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {
+                state[2] = 0;
+                *reinterpret_cast<volatile uint32_t *>(state) = q + 1;
+            }
+        }
+    }
 }
 
 // out[i] = resid[i] + sum over ranks of partial_r[i]   (resid may be NULL, out may alias resid
@@ -179,10 +257,14 @@ int32_t skn_comm_create(skn_ctx *ctx, int32_t rank, int32_t world, int64_t capac
     c->d_state = nullptr;
     c->connected = (world == 1);
     for (int i = 0; i < COMM_MAX_WORLD; ++i) { c->peer[i] = nullptr; c->ipc_mapped[i] = false; }
-    const size_t bytes = COMM_FLAG_BYTES + (size_t)COMM_NBUF * world * c->capacity * sizeof(float);
+    // flags | inbox | low-latency inbox (zero-filled: tag 0 never matches q + 1)
+    const size_t ll_off = COMM_FLAG_BYTES + (size_t)COMM_NBUF * world * c->capacity * sizeof(float);
+    const size_t ll_bytes = (size_t)COMM_NBUF * world * COMM_LL_MAX * sizeof(uint2);
+    const size_t bytes = ll_off + ll_bytes;
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e == cudaSuccess) e = cudaMalloc((void **)&c->local, bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, COMM_FLAG_BYTES);
+    if (e == cudaSuccess) e = cudaMemset(c->local + ll_off, 0, ll_bytes);
     if (e == cudaSuccess) e = cudaMalloc((void **)&c->d_state, 64);
     if (e == cudaSuccess) e = cudaMemset(c->d_state, 0, 64);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -303,6 +385,17 @@ int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *re
     SKN_CUDA(ctx, cudaSetDevice(ctx->device));
     comm_peers peers;
     for (int i = 0; i < COMM_MAX_WORLD; ++i) peers.base[i] = c->peer[i];
+    if (n <= COMM_LL_MAX) {
+        // decode sizes: the low-latency form (tagged 8-byte words); a CTA per 1024 quads, all resident
+        const size_t ll_off = COMM_FLAG_BYTES + (size_t)COMM_NBUF * c->world * c->capacity * sizeof(float);
+        const int64_t quads = n / 4;
+        const int threads_ll = quads >= 1024 ? 1024 : (int)((quads + 31) / 32 * 32);
+        const unsigned blocks_ll = (unsigned)((quads + 1023) / 1024);
+        skn_allreduce_ll_kernel<<<blocks_ll, threads_ll, 0, ctx->stream>>>(peers, ll_off, c->rank, c->world, c->d_state, ctx->d_status,
+                                                                       partial_dev, resid_dev, out_dev, n);
+        SKN_CUDA(ctx, cudaGetLastError());
+        return SKN_OK;
+    }
     // a decode-size vector: one CTA (no tickets, one fence); otherwise at most one CTA per SM, so
     // that every CTA is resident while any of them waits
     int threads = 256;
