@@ -225,7 +225,7 @@ def decode_parallelism(world: int, fused_exchange: str, batch: int) -> str:
     """How the decoder is spread over the ranks, as the bench line words it."""
     if world <= 1:
         return "none"
-    fused = (fused_exchange == "on" or (fused_exchange == "auto" and world >= 4)) and batch <= 2
+    fused = fused_exchange == "on" and batch <= 2          # (automatic = off in the library)
     return f"tp{world}" + (", exchange fused into the matvecs" if fused else "")
 
 

@@ -103,8 +103,9 @@ int32_t skn_ctx_set_stream(skn_ctx *ctx, void *cuda_stream);
  * K-sharded projections push their partial products into every rank's inbox from the matvec
  * epilogue and the next projection adds them to the residual stream while it prepares x,
  * instead of a separate exchange launch (skn_allreduce_dev) after each of them.  Same results
- * bit for bit.  Automatic means on from four ranks: measured slightly slower than the exchange
- * launches on 2 GPUs (every CTA of the consuming launch repeats the sum), faster on 4. */
+ * bit for bit.  Automatic means off: the separate exchange of decode-size vectors is a single
+ * trip over NVLink (tagged words, no fence) started early by programmatic dependent launch, and
+ * measures faster than the fused form, in which every CTA of the consuming launch repeats the sum. */
 #define SKN_OPT_FUSED_EXCHANGE 3
 /* SKN_OPT_KV_F16 (default 0): with value 1, decoders created afterwards (skn_llama_create, skn_llama_create_tp)
  * keep their KV caches in fp16 (see skn_kv_create_typed).  SKN_OPT_KV_DTYPE is the general form: its value is

@@ -91,7 +91,12 @@ __device__ __forceinline__ uint32_t *comm_flag(uint8_t *base, int buf, int src) 
 __global__ void __launch_bounds__(1024)
 skn_allreduce_ll_kernel(comm_peers peers, size_t ll_off, int rank, int world, uint32_t *__restrict__ state,
                         int32_t *__restrict__ status, const float *__restrict__ partial, const float *__restrict__ resid,
-                        float *__restrict__ out, int64_t n) {
+                        float *__restrict__ out, int64_t n, int early) {
+    // programmatic dependent launch on both sides (steps of a few rows): this kernel is resident when the producer of
+    // `partial` finishes, and the projection behind it starts at once and fetches its weights while the exchange
+    // is under way.  Measured on two GPUs: batch 1 +6 %, batch 16 -3 % (hence not for the larger vectors).
+    if (early) skn_pdl_launch_dependents();
+    skn_pdl_wait();
     const uint32_t q = *reinterpret_cast<volatile uint32_t *>(state);
     const uint32_t tag = q + 1u;
     const int buf = (int)(q % COMM_NBUF);
@@ -391,9 +396,18 @@ int32_t skn_allreduce_dev(skn_comm *c, const float *partial_dev, const float *re
         const int64_t quads = n / 4;
         const int threads_ll = quads >= 1024 ? 1024 : (int)((quads + 31) / 32 * 32);
         const unsigned blocks_ll = (unsigned)((quads + 1023) / 1024);
-        skn_allreduce_ll_kernel<<<blocks_ll, threads_ll, 0, ctx->stream>>>(peers, ll_off, c->rank, c->world, c->d_state, ctx->d_status,
-                                                                       partial_dev, resid_dev, out_dev, n);
-        SKN_CUDA(ctx, cudaGetLastError());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks_ll);
+        cfg.blockDim = dim3((unsigned)threads_ll);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        const int early = n <= 16384 ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = early;
+        SKN_CUDA(ctx, cudaLaunchKernelEx(&cfg, skn_allreduce_ll_kernel, peers, ll_off, (int)c->rank, (int)c->world, c->d_state,
+                                         ctx->d_status, partial_dev, resid_dev, out_dev, n, early));
         return SKN_OK;
     }
     // a decode-size vector: one CTA (no tickets, one fence); otherwise at most one CTA per SM, so

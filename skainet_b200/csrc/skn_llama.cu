@@ -301,8 +301,9 @@ int32_t skn_llama_forward_dev(skn_llama *m, const int32_t *tokens_dev, int32_t T
     float *xcur = m->x, *xalt = m->h;
     bool pending = false;
     skn_comm_view xview = {};
-    // (automatic: from four ranks on, where it measured faster than the exchange launches)
-    const bool want_fused = ctx->fused_exchange > 0 || (ctx->fused_exchange < 0 && m->world >= 4);
+    // (automatic = off: since the exchange launch became a single trip over NVLink, started early by programmatic
+    // dependent launch, it measures faster than the fused form at every rank count)
+    const bool want_fused = ctx->fused_exchange > 0;
     // (the fused exchange rides on the single-launch tensor-core matvec: one or two rows)
     bool fusedx = tp && fold && M <= 2 && want_fused && skn_comm_get_view(m->comm, &xview) && xview.capacity >= (int64_t)M * d;
     if (fusedx) {

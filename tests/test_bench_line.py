@@ -61,5 +61,5 @@ def test_decode_parallelism_wording(world, fused, batch):
         assert s == "none"
         return
     assert s.startswith(f"tp{world}")
-    want_fused = batch <= 2 and (fused == "on" or (fused == "auto" and world >= 4))
+    want_fused = batch <= 2 and fused == "on"
     assert ("fused" in s) == want_fused
