@@ -221,6 +221,61 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+DECODE_WORKLOAD = ("cfg5: Llama-style decoder, 32 layers, Q4_K projections, Q6_K embedding / LM head, "
+                   "512-token prefill then greedy decode, batch 1 and batch 16")
+
+
+def _decode_object(legs: dict) -> dict:
+    out = dict(legs)
+    out["tok_s"] = out.get("batch1", {}).get("tok_s")
+    out["unit"] = "tok/s"
+    out["scaling"] = "strong"
+    out["workload"] = DECODE_WORKLOAD
+    return out
+
+
+def guarded_decode_legs(run_leg, batches, deadline_s: float, on_give_up, on_leg_failed=None) -> dict:
+    """The `decode` object of the line: run_leg(B) for every batch size, a failed leg replaced by its error.
+    Ranks that fall out of step inside a leg (one raises, the others sit in a collective) would wait for one
+    another for ever, so every rank carries the same deadline: when it passes, on_give_up(decode object with
+    the legs finished so far, the others marked unfinished) is called from a timer thread; the bench prints
+    the headline line from there and leaves the process."""
+    legs: dict = {}
+    lock = threading.Lock()
+    state = {"done": False}
+
+    def expire():
+        with lock:
+            if state["done"]:
+                return
+            state["done"] = True
+            partial = dict(legs)
+        for B in batches:
+            partial.setdefault(f"batch{B}", {"error": f"not finished within {deadline_s:.0f} s"})
+        on_give_up(_decode_object(partial))
+
+    timer = threading.Timer(deadline_s, expire)
+    timer.daemon = True
+    timer.start()
+    try:
+        for B in batches:
+            try:
+                r = run_leg(B)
+            except Exception as exc:      # the headline line must survive a failure of the secondary leg
+                r = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                if on_leg_failed is not None:
+                    on_leg_failed()
+            with lock:
+                if state["done"]:
+                    break
+                legs[f"batch{B}"] = r
+    finally:
+        timer.cancel()
+        with lock:
+            state["done"] = True
+    return _decode_object(legs)
+
+
 def decode_parallelism(world: int, fused_exchange: str, batch: int) -> str:
     """How the decoder is spread over the ranks, as the bench line words it."""
     if world <= 1:
@@ -454,33 +509,39 @@ def run_ours(args):
     del x_dev, y_dev, y_all
     torch.cuda.empty_cache()
 
-    # ---- the decoder of configuration 5 on the same ranks (tok/s, strong scaling) ------------
-    decode = None
-    if not args.no_decode:
-        decode = {}
-        for B in (1, 16):
-            try:
-                decode[f"batch{B}"] = decode_measure(args, ctx, stream, world, rank, local, B, min(args.decode_steps, 128))
-            except Exception as exc:      # the headline line must survive a failure of the secondary leg
-                decode[f"batch{B}"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
-                torch.cuda.synchronize()
-        b1 = decode.get("batch1", {})
-        decode["tok_s"] = b1.get("tok_s")
-        decode["unit"] = "tok/s"
-        decode["scaling"] = "strong"
-        decode["workload"] = ("cfg5: Llama-style decoder, 32 layers, Q4_K projections, Q6_K embedding / LM head, "
-                              "512-token prefill then greedy decode, batch 1 and batch 16")
-
-    if rank == 0:
+    # ---- the line without its decode object: what a stuck decode leg must not cost -----------------
+    def build_line(decode):
         peak, peak_kind = measured_peak()
         cpu = None
         if world == 1 and not args.no_cpu:
             cpu, _ = cpu_baseline(args.cpu_seconds, layers=layers)
-        line = make_line(world=world, steps=args.steps, warmup=max(3, args.warmup), layers=layers, passes=passes,
+        return make_line(world=world, steps=args.steps, warmup=max(3, args.warmup), layers=layers, passes=passes,
                          order=args.order, ms=ms, ms_other=ms_other, graphed=graphed, e2e_s=e2e_s,
                          e2e_blocking_s=e2e_blocking_s, e2e_steps=e2e_steps, e2e_passes=e2e_passes, clocks=clocks,
                          peak=peak, peak_kind=peak_kind, decode=decode, cpu=cpu)
-        print(json.dumps(line), flush=True)
+
+    # ---- the decoder of configuration 5 on the same ranks (tok/s, strong scaling) ------------
+    decode = None
+    if not args.no_decode:
+        def leg(B):
+            return decode_measure(args, ctx, stream, world, rank, local, B, min(args.decode_steps, 128))
+
+        def leg_failed():
+            torch.cuda.synchronize()
+
+        def give_up(partial):
+            # (timer thread: the main thread may sit in a collective for good)
+            if rank == 0:
+                saved = args.no_cpu
+                args.no_cpu = True               # no CPU leg from here
+                print(json.dumps(build_line(partial)), flush=True)
+                args.no_cpu = saved
+            os._exit(0)
+
+        decode = guarded_decode_legs(leg, (1, 16), args.decode_deadline, give_up, leg_failed)
+
+    if rank == 0:
+        print(json.dumps(build_line(decode)), flush=True)
 
     ctx.close()
     if world > 1:
@@ -688,6 +749,13 @@ def decode_measure(args, ctx, stream, world, rank, local, B, steps, n_layers=Non
             dec.set_layer(i, layer, ones, ones)
         dec.set_head(emb, ones, np.roll(emb, 1, axis=0))
         prompt = torch.from_numpy(g.integers(0, cfg.vocab, size=(B, T)).astype(np.int32)).to(dev)
+        if world > 1:
+            # the ranks finish their uploads seconds apart: they enter the first exchange together, and the bound of
+            # the exchange waits is far above any skew that remains (a wait that runs out on one rank only would
+            # put the ranks out of step)
+            ctx.set_wait_limit_ms(30000)
+            torch.cuda.synchronize()
+            dist.barrier()
 
         def prefill():
             dec.reset()
@@ -750,6 +818,8 @@ def decode_measure(args, ctx, stream, world, rank, local, B, steps, n_layers=Non
         dec.close()
         if exchange is not None:
             exchange.close()
+        if world > 1:
+            ctx.set_wait_limit_ms(0)
     wbytes = cfg.n_layers * sum(n * (k // 256) * 144 for n, k in shapes.values()) + cfg.vocab * (cfg.d_model // 256) * 210
     peak, kind = measured_peak()
     gbs = wbytes / (ms * 1e-3) / 1e9
@@ -808,6 +878,8 @@ def main():
     ap.add_argument("--e2e-passes", type=int, default=20, help="passes per step of the host-pointer (e2e) leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the configuration-5 decoder leg of the headline line")
     ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--decode-deadline", type=float, default=300.0,
+                    help="seconds after which unfinished decode legs are given up and the line is printed without them")
     ap.add_argument("--decode-layers", type=int, default=32)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
@@ -820,7 +892,7 @@ def main():
                     help="attn / decode workloads: element type of the KV cache (f32 is what the configurations specify)")
     ap.add_argument("--fused-exchange", default="auto", choices=["auto", "on", "off"],
                     help="tensor-parallel decode: push partial sums from the matvec epilogue (SKN_OPT_FUSED_EXCHANGE); "
-                         "auto = on from four ranks")
+                         "auto = the library's choice (off)")
     ap.add_argument("--workload", default="matvec", choices=["matvec", "ffn", "attn", "sweep", "decode"],
                     help="matvec is the headline line; the others print one secondary JSON line (1 GPU)")
     args = ap.parse_args()

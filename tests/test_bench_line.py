@@ -63,3 +63,42 @@ def test_decode_parallelism_wording(world, fused, batch):
     assert s.startswith(f"tp{world}")
     want_fused = batch <= 2 and fused == "on"
     assert ("fused" in s) == want_fused
+
+
+def test_decode_legs_survive_a_failed_leg_and_a_stuck_one():
+    """guarded_decode_legs: a leg that raises is replaced by its error and the next one still runs; a leg that
+    never returns (ranks out of step in a collective) is given up after the deadline with the finished legs kept,
+    and the give-up hook is not called when every leg returns in time."""
+    import threading
+    import time
+    gave_up = []
+
+    def leg_ok(B):
+        if B == 16:
+            raise RuntimeError("boom")
+        return {"tok_s": 500.0, "batch": B}
+
+    d = bench.guarded_decode_legs(leg_ok, (1, 16), 5.0, gave_up.append, None)
+    assert d["batch1"]["tok_s"] == 500.0 and "RuntimeError: boom" in d["batch16"]["error"]
+    assert d["tok_s"] == 500.0 and d["unit"] == "tok/s" and d["scaling"] == "strong" and gave_up == []
+
+    release = threading.Event()
+
+    def leg_stuck(B):
+        if B == 16:
+            release.wait(10.0)          # stands for a collective that never completes
+        return {"tok_s": 100.0 * B, "batch": B}
+
+    t0 = time.perf_counter()
+    seen = []
+
+    def hook(partial):
+        seen.append(partial)
+        release.set()                   # (the bench leaves the process here)
+
+    d = bench.guarded_decode_legs(leg_stuck, (1, 16), 0.3, hook, None)
+    assert time.perf_counter() - t0 < 5.0
+    assert len(seen) == 1 and seen[0]["batch1"]["tok_s"] == 100.0 and "not finished" in seen[0]["batch16"]["error"]
+    assert seen[0]["tok_s"] == 100.0
+    assert "batch16" not in d          # the late leg's result is dropped: the line has been printed without it
+    json.dumps(seen[0])
