@@ -313,7 +313,10 @@ int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_hea
  * Every rank owns an inbox that its peers write with ordinary peer stores; one kernel per rank
  * pushes, waits (bounded: about two seconds, then SKN_ERR_TIMEOUT is reported by the next
  * skn_sync and later exchanges stop waiting) and sums in rank order, so every rank obtains the
- * same bits.  No library collective is involved and the sequence is CUDA-graph capturable.
+ * same bits.  Vectors of up to 65536 floats travel as tagged 8-byte words {value, exchange number}
+ * that the receiver polls, so that an exchange of decode size is a single trip over NVLink (no
+ * fence, no flag behind the data); the bound on the wait is SKN_OPT_WAIT_LIMIT_MS either way.
+ * No library collective is involved and the sequence is CUDA-graph capturable.
  *   one process per GPU : skn_comm_create on every rank, exchange skn_comm_handle() blobs
  *                         (skn_comm_handle_bytes() each) by any host channel, skn_comm_connect;
  *   one process, n GPUs : skn_comm_create per device, then skn_comm_connect_local(all of them).
