@@ -164,6 +164,11 @@ skn_matvec_rows(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
     const int gb = (int)((int64_t)blockIdx.x * G / gridDim.x) & even;
     const int ge = (blockIdx.x + 1 == gridDim.x) ? G : ((int)((int64_t)(blockIdx.x + 1) * G / gridDim.x) & even);
     const int ng = ge - gb;
+    // A CTA without groups leaves at once (every thread: no barrier has been touched yet).  The SwiGLU form rounds its
+    // boundaries to whole gate / up pairs, so with fewer than two groups per CTA some CTAs get none; such a CTA used to
+    // stay, and its plane producer waited for compute warps that never take a plane until the bounded wait ran out
+    // (two seconds per launch: 224 groups on 148 CTAs, the gate / up shard of an 8-way tensor-parallel decoder).
+    if (ng <= 0) return;
     const int rows = 16 * ng;
     const int nrt = (ng + R - 1) / R;
     const int ntiles = nrt * nks;               // tile i: K chunk i / nrt, row tile i % nrt
@@ -714,7 +719,10 @@ bool skn_rows_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const f
         ctx->rows_cfg |= cfg_bit;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)pl.grid);
+    // (SwiGLU: whole pairs per CTA, so at most one CTA per pair; the plan's partial-sum space covers the two or three
+    // groups a CTA then owns)
+    const int grid = (swiglu && pl.grid > G / 2) ? (int)(G / 2 > 0 ? G / 2 : 1) : pl.grid;
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((RW_W + 2) * 32);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
