@@ -306,6 +306,16 @@ int32_t skn_kv_append_many_dev(skn_kvcache *kv, const float *k_new_dev, const fl
 int32_t skn_attn_causal_dev(skn_kvcache *kv, const float *q_dev, int32_t n_q_heads, int32_t T, float scale,
                             float *out_dev, void *scratch_dev);
 
+/* Host arithmetic only (no device is touched, no context needed): the launch geometry the many-row
+ * matvec (3 to 16 activation rows, weights streamed once) would get for n_groups sixteen-row groups of
+ * n_cols columns on a GPU of sm_count SMs; swiglu: the interleaved gate / up form.  No reference
+ * counterpart (introspection for hosts that size shards, and for this library's CPU tests).
+ * out[8]: [0] 1 if the shape is covered, [1] CTAs, [2] most groups one CTA owns, [3] groups a CTA's
+ * partial-sum space holds, [4] CTAs without a group, [5] K chunks, [6] ring stages, [7] bytes of
+ * dynamic shared memory. */
+int32_t skn_rows_plan_query(int32_t sm_count, int32_t type, int64_t n_groups, int64_t n_cols, int32_t n_act,
+                            int32_t swiglu, int64_t *out);
+
 /* ---- Exchange between the GPUs of one box ------------------------------------------------------
  * Sum of per-rank partial products of a K-sharded (row-parallel) layer, and, with zero-filled
  * slots, the concatenation of the slices of an N-sharded (column-parallel) one.  The reference

@@ -37,6 +37,7 @@ SIGNATURES = {
     "skn_matmul": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
     "skn_matmul_async": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
     "skn_matmul_dev": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
+    "skn_rows_plan_query": (c_i32, [c_i32, c_i32, c_i64, c_i64, c_i32, c_i32, P(c_i64)]),
     "skn_matvec_group_dev": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_vp, c_vp]),
     "skn_matvec_fused_dev": (c_i32, [c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_float, c_vp]),
     "skn_ffn_swiglu": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),

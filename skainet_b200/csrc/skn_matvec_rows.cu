@@ -133,6 +133,14 @@ __device__ __forceinline__ int rw_group(const skn_rows_args &ar, int j, int &loc
     return tt;
 }
 
+// CTA b's run [gb, ge) of the launch's G sixteen-row groups; the SwiGLU form keeps whole gate / up pairs together
+// (even boundaries).  One definition for the kernel and for the host-side query of the layout.
+__host__ __device__ __forceinline__ void rw_cta_groups(int b, int grid, int G, bool swiglu, int &gb, int &ge) {
+    const int even = swiglu ? ~1 : ~0;
+    gb = (int)((int64_t)b * G / grid) & even;
+    ge = (b + 1 == grid) ? G : ((int)((int64_t)(b + 1) * G / grid) & even);
+}
+
 // 2-D tiled TMA load (no multicast) of a box at element coordinates (x: 8-byte units along the row, y: row)
 __device__ __forceinline__ void rw_tma_load_2d(uint32_t dst_smem, const CUtensorMap *tmap, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
@@ -160,9 +168,8 @@ skn_matvec_rows(const __grid_constant__ CUtensorMap tm0, const __grid_constant__
 
     // this CTA's run of 16-row groups (whole gate / up pairs in the SwiGLU form)
     const int G = ar.gcum[3];
-    const int even = f_swiglu ? ~1 : ~0;
-    const int gb = (int)((int64_t)blockIdx.x * G / gridDim.x) & even;
-    const int ge = (blockIdx.x + 1 == gridDim.x) ? G : ((int)((int64_t)(blockIdx.x + 1) * G / gridDim.x) & even);
+    int gb, ge;
+    rw_cta_groups((int)blockIdx.x, (int)gridDim.x, G, f_swiglu, gb, ge);
     const int ng = ge - gb;
     // A CTA without groups leaves at once (every thread: no barrier has been touched yet).  The SwiGLU form rounds its
     // boundaries to whole gate / up pairs, so with fewer than two groups per CTA some CTAs get none; such a CTA used to
@@ -595,6 +602,12 @@ static rw_plan rw_make_plan(const skn_ctx *ctx, int fmt, int64_t n_groups, int64
     return pl;
 }
 
+// CTAs of the launch: the plan's, or one per gate / up pair when the SwiGLU form would otherwise leave CTAs without
+// a pair (the plan's partial-sum space covers the two or three groups a CTA then owns)
+static int rw_launch_grid(const rw_plan &pl, int64_t G, bool swiglu) {
+    return (swiglu && pl.grid > G / 2) ? (int)(G / 2 > 0 ? G / 2 : 1) : pl.grid;
+}
+
 typedef CUresult (*rw_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                        const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -719,10 +732,7 @@ bool skn_rows_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const f
         ctx->rows_cfg |= cfg_bit;
     }
     cudaLaunchConfig_t cfg = {};
-    // (SwiGLU: whole pairs per CTA, so at most one CTA per pair; the plan's partial-sum space covers the two or three
-    // groups a CTA then owns)
-    const int grid = (swiglu && pl.grid > G / 2) ? (int)(G / 2 > 0 ? G / 2 : 1) : pl.grid;
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)rw_launch_grid(pl, G, swiglu));
     cfg.blockDim = dim3((RW_W + 2) * 32);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
@@ -730,4 +740,33 @@ bool skn_rows_try_group(skn_ctx *ctx, int n, const skn_tensor *const *w, const f
     cfg.numAttrs = 1;
     err = cudaLaunchKernelEx(&cfg, kern, tm[0], tm[1], tm[2], ar, (int)K, pl.geo, (const uint8_t *)xq, ctx->d_status);
     return true;
+}
+
+// Host arithmetic only (no device is touched): the layout a many-row launch of n_groups sixteen-row groups would get
+// on a GPU of sm_count SMs.  out[0] = 1 if the shape is covered (else the rest is unset), out[1] = CTAs, out[2] = most
+// groups any CTA owns, out[3] = groups a CTA's partial-sum space is sized for, out[4] = CTAs without any group,
+// out[5] = K chunks, out[6] = ring stages, out[7] = dynamic shared memory in bytes.
+extern "C" int32_t skn_rows_plan_query(int32_t sm_count, int32_t type, int64_t n_groups, int64_t n_cols, int32_t n_act, int32_t swiglu,
+                                       int64_t *out) {
+    if (!out || sm_count < 1 || n_groups < 1 || n_act < 1 || n_act > 16) return SKN_ERR_ARG;
+    for (int i = 0; i < 8; ++i) out[i] = 0;
+    const int fmt = rw_fmt_of(type);
+    if (fmt < 0 || n_cols % 256 || n_cols < 512 || n_cols > (1 << 18)) return SKN_OK;
+    skn_ctx fake = {};
+    fake.sm_count = sm_count;
+    const rw_plan pl = rw_make_plan(&fake, fmt, n_groups, n_cols, n_act);
+    if (!pl.ok) return SKN_OK;
+    const int grid = rw_launch_grid(pl, n_groups, swiglu != 0);
+    int most = 0, none = 0;
+    for (int b = 0; b < grid; ++b) {
+        int gb, ge;
+        rw_cta_groups(b, grid, (int)n_groups, swiglu != 0, gb, ge);
+        most = ge - gb > most ? ge - gb : most;
+        none += ge - gb <= 0;
+    }
+    const int nb = (int)(n_cols / 256);
+    const int64_t gmax = (n_groups + pl.grid - 1) / pl.grid + 1;
+    out[0] = 1; out[1] = grid; out[2] = most; out[3] = gmax; out[4] = none;
+    out[5] = (nb + pl.geo.KSB - 1) / pl.geo.KSB; out[6] = pl.geo.nst; out[7] = (int64_t)pl.smem;
+    return SKN_OK;
 }
