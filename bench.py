@@ -17,7 +17,9 @@ and the sampled clocks describe a sustained run).
             it as e2e.blocking_call;
   roofline  the matvec kernel against the measured HBM copy bandwidth;
   decode    configuration 5 (Llama-style decoder, tok/s at batch 1 and 16) on the same ranks,
-            tensor-parallel through the library's own exchange when N > 1 (strong scaling);
+            tensor-parallel through the library's own exchange when N > 1 (strong scaling); the legs
+            run under a deadline (--decode-deadline): a leg that fails or does not finish is reported
+            in its place and never costs the line;
   cpu_baseline  the CPU oracle (a C restatement; the reference's Kotlin cannot run here)
             timed on this host's cores on a bounded sample of the same workload.
 
